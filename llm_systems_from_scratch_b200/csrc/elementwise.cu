@@ -1,0 +1,638 @@
+// Bandwidth-bound kernels of the training step, written for sm_100a: every kernel moves 16 bytes per
+// thread per access, keeps reductions in fp32, and never synchronises with the host.
+//
+//   rmsnorm_fwd / rmsnorm_bwd    (reference: llm-systems/llm_systems/kernels/triton_rms_norm.py:30-149)
+//   silu_mul_fwd / silu_mul_bwd  (reference: llm-systems/llm_systems/kernels/triton_swiglu.py:27-86)
+//   rope (interleaved pairs)     (reference: llm-core/llm_core/model.py:93-104)
+//   embedding gather / scatter   (reference: llm-core/llm_core/model.py:48-49)
+//   cross-entropy fwd + in-place grad (reference: llm-systems/llm_systems/kernels/triton_cross_entropy.py:22-85)
+//   flat AdamW with bf16 mirror  (reference: llm-systems/llm_systems/kernels/triton_adamw.py:40-101)
+//   sum of squares / clip coefficient / scale / casts
+#include "ptx.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum for blockDim.x <= 1024; every thread receives the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 v = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  *reinterpret_cast<uint4*>(p) =
+      make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+__device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
+  float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// ------------------------------------------------------------------------ RMSNorm fwd
+// One warp per row; the row is read twice (the second read hits L1/L2).
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ w,
+                                                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                                          int rows, int d, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + (size_t)row * d;
+  float ss = 0.f;
+  for (int c = lane * 8; c < d; c += 256) {
+    float f[8];
+    load8(xr + c, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)d + eps);
+  if (lane == 0 && rstd != nullptr) rstd[row] = r;
+  __nv_bfloat16* yr = y + (size_t)row * d;
+  for (int c = lane * 8; c < d; c += 256) {
+    float f[8], g[8];
+    load8(xr + c, f);
+    load8(w + c, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * r * g[i];
+    store8(yr + c, f);
+  }
+}
+
+// ------------------------------------------------------------------------ RMSNorm bwd
+// dx = rstd * (dy*w) - rstd^3/d * sum(dy*w*x) * x ;  dw += dy * x * rstd.
+// Each block walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a thread owns up to MAXC groups of
+// 8 columns and keeps the weight-gradient partial for them in registers.  Partials go to
+// `dw_partial` (gridDim.x, d) fp32 and are summed in a fixed order by rmsnorm_dw_reduce_kernel.
+constexpr int RMS_BWD_THREADS = 256;
+constexpr int RMS_BWD_MAXC = 4;  // d <= 256 * 8 * 4 = 8192
+
+__global__ void __launch_bounds__(RMS_BWD_THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int d) {
+  __shared__ float red[32];
+  float wreg[RMS_BWD_MAXC][8];
+  float dwacc[RMS_BWD_MAXC][8];
+#pragma unroll
+  for (int j = 0; j < RMS_BWD_MAXC; ++j) {
+    const int c = (j * RMS_BWD_THREADS + threadIdx.x) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+    if (c < d) load8(w + c, wreg[j]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* dyr = dy + (size_t)row * d;
+    const __nv_bfloat16* xr = x + (size_t)row * d;
+    const float r = rstd[row];
+    float g[RMS_BWD_MAXC][8], xv[RMS_BWD_MAXC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < RMS_BWD_MAXC; ++j) {
+      const int c = (j * RMS_BWD_THREADS + threadIdx.x) * 8;
+      if (c < d) {
+        float dyv[8];
+        load8(dyr + c, dyv);
+        load8(xr + c, xv[j]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          dwacc[j][i] += dyv[i] * xv[j][i] * r;
+          g[j][i] = dyv[i] * wreg[j][i];
+          dot += g[j][i] * xv[j][i];
+        }
+      }
+    }
+    dot = block_sum(dot, red);
+    const float coef = r * r * r * dot / (float)d;
+    __nv_bfloat16* dxr = dx + (size_t)row * d;
+#pragma unroll
+    for (int j = 0; j < RMS_BWD_MAXC; ++j) {
+      const int c = (j * RMS_BWD_THREADS + threadIdx.x) * 8;
+      if (c < d) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = r * g[j][i] - coef * xv[j][i];
+        store8(dxr + c, o);
+      }
+    }
+  }
+  float* part = dw_partial + (size_t)blockIdx.x * d;
+#pragma unroll
+  for (int j = 0; j < RMS_BWD_MAXC; ++j) {
+    const int c = (j * RMS_BWD_THREADS + threadIdx.x) * 8;
+    if (c < d) {
+      *reinterpret_cast<float4*>(part + c) = make_float4(dwacc[j][0], dwacc[j][1], dwacc[j][2], dwacc[j][3]);
+      *reinterpret_cast<float4*>(part + c + 4) = make_float4(dwacc[j][4], dwacc[j][5], dwacc[j][6], dwacc[j][7]);
+    }
+  }
+}
+
+// dw[c] (=|+=) sum_p partial[p][c], fixed summation order => bitwise reproducible.
+__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nparts, int d,
+                                         int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * d + c];
+  dw[c] = accumulate ? dw[c] + s : s;
+}
+
+// --------------------------------------------------------------------------- SwiGLU
+// gu is (rows, 2F): gate columns [0,F), up columns [F,2F).
+__global__ void silu_mul_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h,
+                                    long long rows, int F) {
+  const long long groups = rows * (F / 8);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < groups;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / (F / 8);
+    const int c = (int)(i - row * (F / 8)) * 8;
+    float g[8], u[8], o[8];
+    load8(gu + row * 2 * F + c, g);
+    load8(gu + row * 2 * F + F + c, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+    store8(h + row * F + c, o);
+  }
+}
+
+__global__ void silu_mul_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __restrict__ gu,
+                                    __nv_bfloat16* __restrict__ dgu, long long rows, int F) {
+  const long long groups = rows * (F / 8);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < groups;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / (F / 8);
+    const int c = (int)(i - row * (F / 8)) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + row * 2 * F + c, g);
+    load8(gu + row * 2 * F + F + c, u);
+    load8(dh + row * F + c, d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float s = 1.f / (1.f + __expf(-g[k]));
+      const float silu = g[k] * s;
+      dg[k] = d[k] * u[k] * (s + silu * (1.f - s));
+      du[k] = d[k] * silu;
+    }
+    store8(dgu + row * 2 * F + c, dg);
+    store8(dgu + row * 2 * F + F + c, du);
+  }
+}
+
+// ----------------------------------------------------------------------------- RoPE
+// In-place rotation of the Q and K thirds of qkv (rows, 3*d), d = H*dh.  cos_sin is (2, ctx, dh/2) fp32.
+// Position of a row: positions[row] when given, else row % seq.  sign = -1 applies the inverse rotation.
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cos_sin,
+                            const int* __restrict__ positions, long long rows, int seq, int d, int dh, int ctx,
+                            float sign) {
+  const int gpr = 2 * d / 8;  // groups of 8 elements per row over the Q and K parts
+  const long long groups = rows * gpr;
+  const float* cosb = cos_sin;
+  const float* sinb = cos_sin + (size_t)ctx * (dh / 2);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < groups;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / gpr;
+    const int c = (int)(i - row * gpr) * 8;  // column within [0, 2d)
+    const int pos = positions ? positions[row] : (int)(row % seq);
+    const int e = c % dh;                    // element offset inside the head (multiple of 8)
+    float v[8];
+    __nv_bfloat16* p = qkv + row * 3 * d + c;
+    load8(p, v);
+    const float4 cs = *reinterpret_cast<const float4*>(cosb + (size_t)pos * (dh / 2) + e / 2);
+    const float4 sn = *reinterpret_cast<const float4*>(sinb + (size_t)pos * (dh / 2) + e / 2);
+    const float cc[4] = {cs.x, cs.y, cs.z, cs.w};
+    const float ss[4] = {sn.x * sign, sn.y * sign, sn.z * sign, sn.w * sign};
+    float o[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      o[2 * k] = cc[k] * v[2 * k] - ss[k] * v[2 * k + 1];
+      o[2 * k + 1] = ss[k] * v[2 * k] + cc[k] * v[2 * k + 1];
+    }
+    store8(p, o);
+  }
+}
+
+// ------------------------------------------------------------------------ Embedding
+__global__ void embedding_fwd_kernel(const long long* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
+                                     __nv_bfloat16* __restrict__ out, long long rows, int d, int vocab) {
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  long long t = tokens[row];
+  if (t < 0 || t >= vocab) t = 0;  // out-of-range ids are clamped rather than read out of bounds
+  const __nv_bfloat16* src = table + (size_t)t * d;
+  __nv_bfloat16* dst = out + (size_t)row * d;
+  for (int c = lane * 8; c < d; c += 256) *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+}
+
+// grad_table (V, d) fp32 += dx rows; one warp per token row, 16-byte vector reductions.
+__global__ void embedding_bwd_kernel(const long long* __restrict__ tokens, const __nv_bfloat16* __restrict__ dx,
+                                     float* __restrict__ grad_table, long long rows, int d, int vocab) {
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const long long t = tokens[row];
+  if (t < 0 || t >= vocab) return;
+  const __nv_bfloat16* src = dx + (size_t)row * d;
+  float* dst = grad_table + (size_t)t * d;
+  for (int c = lane * 8; c < d; c += 256) {
+    float f[8];
+    load8(src + c, f);
+    atomicAdd(reinterpret_cast<float4*>(dst + c), make_float4(f[0], f[1], f[2], f[3]));
+    atomicAdd(reinterpret_cast<float4*>(dst + c + 4), make_float4(f[4], f[5], f[6], f[7]));
+  }
+}
+
+// -------------------------------------------------------------------- Cross entropy
+// One block per row of logits (rows, ld) bf16 with `vocab` valid columns.  Pass 1: online max / sum.
+// Pass 2: overwrite the row with (softmax - onehot) * grad_scale / n_valid.  Row losses go to
+// `row_loss` (fp32); `n_valid` is a device float computed by count_valid_kernel (no host sync).
+constexpr int XENT_THREADS = 512;
+
+__global__ void count_valid_kernel(const long long* __restrict__ targets, long long rows, int ignore_index,
+                                   float* __restrict__ n_valid) {
+  __shared__ float red[32];
+  float c = 0.f;
+  for (long long i = threadIdx.x; i < rows; i += blockDim.x) c += (targets[i] != ignore_index) ? 1.f : 0.f;
+  c = block_sum(c, red);
+  if (threadIdx.x == 0) *n_valid = fmaxf(c, 1.f);
+}
+
+__global__ void __launch_bounds__(XENT_THREADS)
+xent_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets, float* __restrict__ row_loss,
+            const float* __restrict__ n_valid, long long ld, int vocab, int ignore_index, float grad_scale,
+            int write_grad) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const long long tgt = targets[row];
+  const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= vocab;
+  const int nvec = vocab / 8;
+  float m = -INFINITY, s = 0.f;
+  for (int g = threadIdx.x; g < nvec; g += XENT_THREADS) {
+    float f[8];
+    load8(lr + g * 8, f);
+    float lm = f[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) lm = fmaxf(lm, f[i]);
+    const float nm = fmaxf(m, lm);
+    float add = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) add += __expf(f[i] - nm);
+    s = s * __expf(m - nm) + add;
+    m = nm;
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < vocab; c += XENT_THREADS) {
+    const float f = __bfloat162float(lr[c]);
+    const float nm = fmaxf(m, f);
+    s = s * __expf(m - nm) + __expf(f - nm);
+    m = nm;
+  }
+  const float gm = block_max(m, red);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  const float gs = block_sum(s, red);
+  const float lse = gm + logf(gs);
+  const float nv = *n_valid;
+  if (threadIdx.x == 0) row_loss[row] = ignored ? 0.f : (lse - __bfloat162float(lr[tgt])) / nv;
+  if (!write_grad) return;
+  __syncthreads();  // the target logit has been read before anyone overwrites it
+  const float k = ignored ? 0.f : grad_scale / nv;
+  for (int g = threadIdx.x; g < nvec; g += XENT_THREADS) {
+    float f[8];
+    load8(lr + g * 8, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = g * 8 + i;
+      f[i] = (__expf(f[i] - lse) - ((c == tgt) ? 1.f : 0.f)) * k;
+    }
+    store8(lr + g * 8, f);
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < ld; c += XENT_THREADS) {
+    float f = 0.f;
+    if (c < vocab) f = (__expf(__bfloat162float(lr[c]) - lse) - ((c == tgt) ? 1.f : 0.f)) * k;
+    lr[c] = __float2bfloat16(f);
+  }
+}
+
+// loss (=|+=) sum(row_loss) in a fixed order (single block).
+__global__ void sum_rows_kernel(const float* __restrict__ v, long long n, float* __restrict__ out, int accumulate) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) s += v[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) *out = accumulate ? *out + s : s;
+}
+
+// argmax over the first `vocab` columns of each row of bf16 logits; ties -> lowest index.
+__global__ void argmax_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int vocab,
+                              long long* __restrict__ out) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const __nv_bfloat16* lr = logits + (long long)blockIdx.x * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
+    const float f = __bfloat162float(lr[c]);
+    if (f > best || (f == best && c < bi)) { best = f; bi = c; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) out[blockIdx.x] = bi;
+  }
+}
+
+// ---------------------------------------------------------------------------- AdamW
+// One pass over flat fp32 state: 4 B grad (or 2 B bf16) + 12 B state in, 12 B state + 2 B mirror out.
+//   m = b1 m + (1-b1) g ; v = b2 v + (1-b2) g^2 ; p -= alpha_t m / (sqrt(v)+eps) ; p -= lr wd p
+// `gscale` (device float, may be null) is multiplied into g: the clip coefficient stays on the device.
+template <typename GradT>
+__global__ void adamw_kernel(float* __restrict__ p, const GradT* __restrict__ g, float* __restrict__ m,
+                             float* __restrict__ v, __nv_bfloat16* __restrict__ mirror, long long n,
+                             const float* __restrict__ gscale, float lr, float b1, float b2, float eps, float wd,
+                             float alpha_t) {
+  const float gs = gscale ? *gscale : 1.f;
+  const long long nvec = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 pv = reinterpret_cast<float4*>(p)[i];
+    float4 mv = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    float gg[4];
+    if constexpr (sizeof(GradT) == 4) {
+      float4 t = reinterpret_cast<const float4*>(g)[i];
+      gg[0] = t.x; gg[1] = t.y; gg[2] = t.z; gg[3] = t.w;
+    } else {
+      uint2 t = reinterpret_cast<const uint2*>(g)[i];
+      float2 a = unpack_bf16x2(t.x), b = unpack_bf16x2(t.y);
+      gg[0] = a.x; gg[1] = a.y; gg[2] = b.x; gg[3] = b.y;
+    }
+    float pp[4] = {pv.x, pv.y, pv.z, pv.w}, mm[4] = {mv.x, mv.y, mv.z, mv.w}, vq[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gk = gg[k] * gs;
+      mm[k] = b1 * mm[k] + (1.f - b1) * gk;
+      vq[k] = b2 * vq[k] + (1.f - b2) * gk * gk;
+      pp[k] -= alpha_t * mm[k] / (sqrtf(vq[k]) + eps);
+      pp[k] -= lr * wd * pp[k];
+    }
+    reinterpret_cast<float4*>(p)[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+    reinterpret_cast<float4*>(m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(v)[i] = make_float4(vq[0], vq[1], vq[2], vq[3]);
+    if (mirror) reinterpret_cast<uint2*>(mirror)[i] = make_uint2(pack_bf16x2(pp[0], pp[1]), pack_bf16x2(pp[2], pp[3]));
+  }
+  // tail (n % 4 elements)
+  const long long tail0 = nvec * 4;
+  const long long t = tail0 + blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < n) {
+    float gk;
+    if constexpr (sizeof(GradT) == 4) gk = g[t] * gs; else gk = __bfloat162float(g[t]) * gs;
+    float mk = b1 * m[t] + (1.f - b1) * gk;
+    float vk = b2 * v[t] + (1.f - b2) * gk * gk;
+    float pk = p[t] - alpha_t * mk / (sqrtf(vk) + eps);
+    pk -= lr * wd * pk;
+    p[t] = pk; m[t] = mk; v[t] = vk;
+    if (mirror) mirror[t] = __float2bfloat16(pk);
+  }
+}
+
+// out += sum(x^2).  fp32 or bf16 input.  Per-block partials are combined with one atomic per block.
+template <typename T>
+__global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float f;
+    if constexpr (sizeof(T) == 4) f = x[i]; else f = __bfloat162float(x[i]);
+    s += f * f;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+// coef = min(1, max_norm / (sqrt(sumsq) + 1e-6)); also stores the norm.
+__global__ void clip_coef_kernel(const float* __restrict__ sumsq, float max_norm, float* __restrict__ coef,
+                                 float* __restrict__ norm_out) {
+  const float nrm = sqrtf(*sumsq);
+  if (norm_out) *norm_out = nrm;
+  *coef = fminf(1.f, max_norm / (nrm + 1e-6f));
+}
+
+template <typename T>
+__global__ void scale_kernel(T* __restrict__ x, long long n, const float* __restrict__ coef) {
+  const float c = *coef;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    if constexpr (sizeof(T) == 4) x[i] = x[i] * c; else x[i] = __float2bfloat16(__bfloat162float(x[i]) * c);
+  }
+}
+
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  const long long nvec = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 v = reinterpret_cast<const float4*>(src)[i];
+    reinterpret_cast<uint2*>(dst)[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+  }
+  const long long t = nvec * 4 + blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < n) dst[t] = __float2bfloat16(src[t]);
+}
+
+__global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = __bfloat162float(src[i]);
+}
+
+static int grid_for(long long work_items, int threads, int max_blocks = 148 * 16) {
+  long long b = (work_items + threads - 1) / threads;
+  if (b < 1) b = 1;
+  if (b > max_blocks) b = max_blocks;
+  return (int)b;
+}
+
+}  // namespace b200
+
+using namespace b200;
+#define CHECK_LAUNCH() return (cudaGetLastError() == cudaSuccess) ? 0 : -4
+#define ALIGNED16(p) ((reinterpret_cast<uintptr_t>(p) & 15) == 0)
+
+extern "C" int b200_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d, float eps,
+                                cudaStream_t st) {
+  if (d % 8 || !ALIGNED16(x) || !ALIGNED16(w) || !ALIGNED16(y)) return -10;
+  if (rows == 0) return 0;
+  rmsnorm_fwd_kernel<<<(rows + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                                     (__nv_bfloat16*)y, rstd, rows, d, eps);
+  CHECK_LAUNCH();
+}
+
+// Number of partial rows rmsnorm_bwd needs in its scratch buffer for a given row count.
+extern "C" int b200_rmsnorm_bwd_parts(int rows) { return rows < 148 * 4 ? (rows > 0 ? rows : 1) : 148 * 4; }
+
+// dw_partial: scratch of b200_rmsnorm_bwd_parts(rows) * d floats.  dw (d floats) is overwritten or accumulated.
+extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
+                                float* dw_partial, int rows, int d, int accumulate_dw, cudaStream_t st) {
+  if (d % 8 || d > RMS_BWD_THREADS * 8 * RMS_BWD_MAXC) return -10;
+  if (!ALIGNED16(dy) || !ALIGNED16(x) || !ALIGNED16(w) || !ALIGNED16(dx) || !ALIGNED16(dw_partial)) return -10;
+  if (rows == 0) return 0;
+  const int parts = b200_rmsnorm_bwd_parts(rows);
+  rmsnorm_bwd_kernel<<<parts, RMS_BWD_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                        (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx,
+                                                        dw_partial, rows, d);
+  rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_partial, dw, parts, d, accumulate_dw);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_silu_mul_fwd(const void* gu, void* h, long long rows, int F, cudaStream_t st) {
+  if (F % 8 || !ALIGNED16(gu) || !ALIGNED16(h)) return -10;
+  if (rows == 0) return 0;
+  silu_mul_fwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)h, rows, F);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_silu_mul_bwd(const void* dh, const void* gu, void* dgu, long long rows, int F, cudaStream_t st) {
+  if (F % 8 || !ALIGNED16(gu) || !ALIGNED16(dh) || !ALIGNED16(dgu)) return -10;
+  if (rows == 0) return 0;
+  silu_mul_bwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)dh, (const __nv_bfloat16*)gu,
+                                                                     (__nv_bfloat16*)dgu, rows, F);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_rope(void* qkv, const float* cos_sin, const int* positions, long long rows, int seq, int d, int dh,
+                         int ctx, int inverse, cudaStream_t st) {
+  if (dh % 8 || d % dh || !ALIGNED16(qkv) || !ALIGNED16(cos_sin) || seq <= 0) return -10;
+  if (positions == nullptr && seq > ctx) return -11;
+  if (rows == 0) return 0;
+  rope_kernel<<<grid_for(rows * (2 * d / 8), 256), 256, 0, st>>>((__nv_bfloat16*)qkv, cos_sin, positions, rows, seq, d,
+                                                                 dh, ctx, inverse ? -1.f : 1.f);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_embedding_fwd(const long long* tokens, const void* table, void* out, long long rows, int d,
+                                  int vocab, cudaStream_t st) {
+  if (d % 8 || !ALIGNED16(table) || !ALIGNED16(out)) return -10;
+  if (rows == 0) return 0;
+  embedding_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(tokens, (const __nv_bfloat16*)table,
+                                                                   (__nv_bfloat16*)out, rows, d, vocab);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_embedding_bwd(const long long* tokens, const void* dx, float* grad_table, long long rows, int d,
+                                  int vocab, cudaStream_t st) {
+  if (d % 8 || !ALIGNED16(dx) || !ALIGNED16(grad_table)) return -10;
+  if (rows == 0) return 0;
+  embedding_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(tokens, (const __nv_bfloat16*)dx, grad_table, rows, d,
+                                                                   vocab);
+  CHECK_LAUNCH();
+}
+
+// scratch: rows + 1 floats (row losses, then n_valid).  loss (device float) is overwritten or accumulated.
+extern "C" int b200_xent(void* logits, const long long* targets, float* loss, float* scratch, long long rows,
+                         long long ld, int vocab, int ignore_index, float grad_scale, int write_grad,
+                         int accumulate_loss, cudaStream_t st) {
+  if (!ALIGNED16(logits) || ld % 8 || vocab > ld) return -10;
+  if (rows == 0) return 0;
+  float* n_valid = scratch + rows;
+  count_valid_kernel<<<1, 1024, 0, st>>>(targets, rows, ignore_index, n_valid);
+  xent_kernel<<<(unsigned)rows, XENT_THREADS, 0, st>>>((__nv_bfloat16*)logits, targets, scratch, n_valid, ld, vocab,
+                                                       ignore_index, grad_scale, write_grad);
+  sum_rows_kernel<<<1, 1024, 0, st>>>(scratch, rows, loss, accumulate_loss);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_argmax(const void* logits, long long rows, long long ld, int vocab, long long* out, cudaStream_t st) {
+  if (rows == 0) return 0;
+  argmax_kernel<<<(unsigned)rows, 256, 0, st>>>((const __nv_bfloat16*)logits, ld, vocab, out);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_adamw(float* p, const void* g, int grad_is_bf16, float* m, float* v, void* mirror, long long n,
+                          const float* gscale, float lr, float b1, float b2, float eps, float wd, float alpha_t,
+                          cudaStream_t st) {
+  if (!ALIGNED16(p) || !ALIGNED16(g) || !ALIGNED16(m) || !ALIGNED16(v) || (mirror && (reinterpret_cast<uintptr_t>(mirror) & 7)))
+    return -10;
+  if (n == 0) return 0;
+  const int grid = grid_for(n / 4 + 4, 256, 148 * 8);
+  if (grad_is_bf16)
+    adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, (const __nv_bfloat16*)g, m, v, (__nv_bfloat16*)mirror, n, gscale,
+                                                      lr, b1, b2, eps, wd, alpha_t);
+  else
+    adamw_kernel<float><<<grid, 256, 0, st>>>(p, (const float*)g, m, v, (__nv_bfloat16*)mirror, n, gscale, lr, b1, b2, eps,
+                                              wd, alpha_t);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t st) {
+  if (n == 0) return 0;
+  const int grid = grid_for(n, 512, 148 * 4);
+  if (is_bf16) sumsq_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>((const __nv_bfloat16*)x, n, out);
+  else sumsq_kernel<float><<<grid, 512, 0, st>>>((const float*)x, n, out);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_clip_coef(const float* sumsq, float max_norm, float* coef, float* norm_out, cudaStream_t st) {
+  clip_coef_kernel<<<1, 1, 0, st>>>(sumsq, max_norm, coef, norm_out);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_scale(void* x, int is_bf16, long long n, const float* coef, cudaStream_t st) {
+  if (n == 0) return 0;
+  const int grid = grid_for(n, 256, 148 * 8);
+  if (is_bf16) scale_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16*)x, n, coef);
+  else scale_kernel<float><<<grid, 256, 0, st>>>((float*)x, n, coef);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_cast_f32_bf16(const float* src, void* dst, long long n, cudaStream_t st) {
+  if (!ALIGNED16(src) || (reinterpret_cast<uintptr_t>(dst) & 7)) return -10;
+  if (n == 0) return 0;
+  cast_f32_to_bf16_kernel<<<grid_for(n / 4 + 4, 256, 148 * 8), 256, 0, st>>>(src, (__nv_bfloat16*)dst, n);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_cast_bf16_f32(const void* src, float* dst, long long n, cudaStream_t st) {
+  if (n == 0) return 0;
+  cast_bf16_to_f32_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, st>>>((const __nv_bfloat16*)src, dst, n);
+  CHECK_LAUNCH();
+}

@@ -1,0 +1,432 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a:  D[m,n] = sum_k A(m,k) * B(n,k)
+//
+//   warp 0      TMA producer   (cp.async.bulk.tensor -> 128B-swizzled smem ring, mbarrier tx-count)
+//   warp 1      MMA issuer     (one thread: tcgen05.mma kind::f16, 128 x BN x 16, accumulators in TMEM)
+//   warps 2-5   epilogue       (tcgen05.ld -> registers -> fused epilogue -> global)
+//
+// Two TMEM accumulators (2 x BN columns) let the epilogue of tile i overlap the main loop of
+// tile i+1.  Either operand may be K-major (rows of K contiguous) or MN-major (stored as
+// (K, MN) with MN contiguous), which covers forward (x W^T), dgrad (dy W) and wgrad (dy^T x)
+// without any transposed copies.  This replaces the library GEMM behind the reference's
+// `Linear.forward` (llm-core/llm_core/model.py:31-32) and its autograd-generated backward.
+//
+// Edge tiles: TMA zero-fills out-of-range rows / K tail; stores are predicated.
+#include "ptx.cuh"
+
+#include <stdio.h>
+
+namespace b200 {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+
+enum GemmEpilogue : int {
+  EPI_BF16 = 0,       // C = bf16(acc)
+  EPI_F32 = 1,        // C = acc (fp32)
+  EPI_BF16_RES = 2,   // C = bf16(acc + R)   (R bf16, may alias C)
+  EPI_F32_ACC = 3,    // C += acc (fp32 read-modify-write)
+};
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const void* R;
+  long long ldr;
+  int epi;
+  int num_m_tiles, num_n_tiles, group_m;
+  uint32_t* status;
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int DATA_BYTES = STAGES * (A_BYTES + B_BYTES);
+  // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then tmem holder + abort word
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int TOTAL = DATA_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& m_blk, int& n_blk) {
+  const int per_group = p.group_m * p.num_n_tiles;
+  const int g = tile / per_group;
+  const int first_m = g * p.group_m;
+  const int gm = min(p.group_m, p.num_m_tiles - first_m);
+  const int r = tile - g * per_group;
+  m_blk = first_m + r % gm;
+  n_blk = r / gm;
+}
+
+__device__ __forceinline__ void report(const GemmParams& p, volatile uint32_t* abort_word, uint32_t code) {
+  *abort_word = code;
+  if (p.status != nullptr) atomicCAS(p.status, 0u, code | (blockIdx.x << 8));
+}
+
+// One 32-column chunk of one output row.
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int col0, const uint32_t (&acc)[32]) {
+  if (row >= p.M) return;
+  const int ncols = min(32, p.N - col0);
+  if (ncols <= 0) return;
+  if (p.epi == EPI_BF16 || p.epi == EPI_BF16_RES) {
+    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+    const bool vec_ok = (ncols == 32) && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    if (p.epi == EPI_BF16_RES) {
+      const __nv_bfloat16* r = reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)row * p.ldr + col0;
+      const bool rvec = vec_ok && ((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+      if (rvec) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 rv = *reinterpret_cast<const uint4*>(r + j * 8);
+          const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            float2 f = unpack_bf16x2(rr[t]);
+            o[t] = pack_bf16x2(__uint_as_float(acc[j * 8 + 2 * t]) + f.x,
+                               __uint_as_float(acc[j * 8 + 2 * t + 1]) + f.y);
+          }
+          *reinterpret_cast<uint4*>(c + j * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      } else {
+        for (int j = 0; j < ncols; ++j)
+          c[j] = __float2bfloat16(__uint_as_float(acc[j]) + __bfloat162float(r[j]));
+      }
+    } else if (vec_ok) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t o[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          o[t] = pack_bf16x2(__uint_as_float(acc[j * 8 + 2 * t]), __uint_as_float(acc[j * 8 + 2 * t + 1]));
+        *reinterpret_cast<uint4*>(c + j * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    } else {
+      for (int j = 0; j < ncols; ++j) c[j] = __float2bfloat16(__uint_as_float(acc[j]));
+    }
+  } else {
+    float* c = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+    const bool vec_ok = (ncols == 32) && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    if (p.epi == EPI_F32) {
+      if (vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(c + j * 4) = make_uint4(acc[j * 4], acc[j * 4 + 1], acc[j * 4 + 2], acc[j * 4 + 3]);
+      } else {
+        for (int j = 0; j < ncols; ++j) c[j] = __uint_as_float(acc[j]);
+      }
+    } else {  // EPI_F32_ACC
+      if (vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 v = *reinterpret_cast<float4*>(c + j * 4);
+          v.x += __uint_as_float(acc[j * 4]);
+          v.y += __uint_as_float(acc[j * 4 + 1]);
+          v.z += __uint_as_float(acc[j * 4 + 2]);
+          v.w += __uint_as_float(acc[j * 4 + 3]);
+          *reinterpret_cast<float4*>(c + j * 4) = v;
+        }
+      } else {
+        for (int j = 0; j < ncols; ++j) c[j] += __uint_as_float(acc[j]);
+      }
+    }
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmParams p) {
+  using S = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * S::A_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::DATA_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile uint32_t* abort_word = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 128);
+    }
+    *abort_word = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(tile, p, m_blk, n_blk);
+        const int m0 = m_blk * BM, n0 = n_blk * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word)) {
+            report(p, abort_word, ERR_WAIT_EMPTY);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full_bar[stage], S::A_BYTES + S::B_BYTES);
+          uint8_t* a_dst = smem_a + stage * S::A_BYTES;
+          uint8_t* b_dst = smem_b + stage * S::B_BYTES;
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full_bar[stage], m0 + j * 64, k0);
+          } else {
+            tma_load_2d(a_dst, &tmA, &full_bar[stage], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[stage], n0 + j * 64, k0);
+          } else {
+            tma_load_2d(b_dst, &tmB, &full_bar[stage], k0, n0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1, abort_word)) {
+          report(p, abort_word, ERR_WAIT_TMEM_EMPTY);
+          ok = false;
+          break;
+        }
+        acc_phase[acc] ^= 1;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word)) {
+            report(p, abort_word, ERR_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem_a + stage * S::A_BYTES);
+          const uint32_t b_base = smem_u32(smem_b + stage * S::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = A_MN ? make_smem_desc(a_base + k * (UMMA_K * 128), 8192, 1024)
+                                         : make_smem_desc(a_base + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc = B_MN ? make_smem_desc(b_base + k * (UMMA_K * 128), 8192, 1024)
+                                         : make_smem_desc(b_base + k * (UMMA_K * 2), 16, 1024);
+            umma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // smem stage is free once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&tmem_full[acc]);  // accumulator complete
+      }
+    }
+  } else {
+    // --------------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
+    uint32_t acc_phase[2] = {0, 0};
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      int m_blk, n_blk;
+      tile_coords(tile, p, m_blk, n_blk);
+      const int acc = local & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase[acc], abort_word)) {
+        if (lane == 0) report(p, abort_word, ERR_WAIT_TMEM_FULL);
+        ok = false;
+        break;
+      }
+      acc_phase[acc] ^= 1;
+      tc_fence_after();
+      const int row = m_blk * BM + quarter * 32 + lane;
+      const int n0 = n_blk * BN;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        if (n0 + c * 32 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        epilogue_store(p, row, n0 + c * 32, r);
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    // Give copies that may still be in flight time to land before shared memory is released.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// bf16 matrix with `rows` rows of `cols` contiguous elements, row stride `ld` elements;
+// box = (box_cols, box_rows), 128-byte swizzle.
+int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+                      uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_num_sms;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t stream) {
+  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  using S = GemmSmem<BN, STAGES>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess) return -3;
+    configured = true;
+  }
+  p.num_m_tiles = (p.M + BM - 1) / BM;
+  p.num_n_tiles = (p.N + BN - 1) / BN;
+  p.group_m = 16;
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  int grid = num_sms();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = tiles;
+  kern<<<grid, 192, S::TOTAL, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// D (M x N) = A * B^T-style contraction over K.
+//   a_mn == 0: A is (M, K) row-major with row stride lda;  a_mn == 1: A is stored (K, M) with row stride lda.
+//   b_mn == 0: B is (N, K) row-major with row stride ldb;  b_mn == 1: B is stored (K, N) with row stride ldb.
+//   epi: 0 bf16 out, 1 fp32 out, 2 bf16 out + bf16 residual R, 3 fp32 accumulate into C.
+// Requirements (checked): base pointers 16-byte aligned; lda, ldb multiples of 8 elements.
+// Returns 0 on success, negative on argument / launch errors.  `status` (device uint32, may be null)
+// receives a non-zero code if a bounded wait inside the kernel gave up.
+extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                              long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int b_mn,
+                              int epi, int bn_hint, int max_ctas, uint32_t* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
+    return -10;
+  if (epi == EPI_BF16_RES && R == nullptr) return -11;
+  int bn = bn_hint;
+  if (bn != 128 && bn != 256) {
+    const long long mt = (M + BM - 1) / BM;
+    const long long sms = num_sms();
+    const long long w256 = (mt * ((N + 255) / 256) + sms - 1) / sms * 256 * 10;
+    const long long w128 = (mt * ((N + 127) / 128) + sms - 1) / sms * 128 * 11;
+    bn = (w128 < w256) ? 128 : 256;
+  }
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (a_mn)
+    rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 64);
+  else
+    rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BM);
+  if (rc) return -20 + rc;
+  if (b_mn)
+    rc = make_tmap_bf16_2d(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 64);
+  else
+    rc = make_tmap_bf16_2d(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, bn);
+  if (rc) return -30 + rc;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.R = R; p.ldr = ldr; p.epi = epi; p.status = status;
+  p.num_m_tiles = p.num_n_tiles = p.group_m = 0;
+
+#define DISPATCH(BN_)                                                                    \
+  if (a_mn && b_mn) return launch_gemm<BN_, true, true>(tmA, tmB, p, max_ctas, stream);   \
+  if (a_mn) return launch_gemm<BN_, true, false>(tmA, tmB, p, max_ctas, stream);          \
+  if (b_mn) return launch_gemm<BN_, false, true>(tmA, tmB, p, max_ctas, stream);          \
+  return launch_gemm<BN_, false, false>(tmA, tmB, p, max_ctas, stream);
+  if (bn == 256) { DISPATCH(256) }
+  DISPATCH(128)
+#undef DISPATCH
+}

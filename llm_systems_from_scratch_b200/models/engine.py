@@ -1,0 +1,404 @@
+"""Hand-written forward and backward of the decoder stack on fused ops.
+
+Instead of letting autograd record ~60 small kernels per block (the reference's eager path,
+llm-core/llm_core/model.py:289-292,353-390), each transformer block is ONE autograd node whose
+forward and backward are explicit sequences of fused kernels:
+
+    forward : rmsnorm -> QKV GEMM -> RoPE -> flash attention -> out-proj GEMM (+residual)
+              rmsnorm -> gate|up GEMM -> silu*mul -> down GEMM (+residual)
+    backward: the mirrored 7 dgrad / wgrad GEMMs, attention backward, fused norm backward.
+
+Weights reach a block through a *provider*, so the same code serves a locally held arena, a
+DDP replica (provider fires bucket all-reduces as ranges of the gradient arena complete) and
+FSDP (provider hands out gathered bf16 shards and reduce-scatters the gradient staging).
+Activations are row-major ``(batch*seq, features)``; attention reads Q, K and V straight out of
+the packed QKV activation, so no head transposes exist anywhere.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import NamedTuple
+
+import torch
+
+from .. import ops
+
+
+class BlockWeights(NamedTuple):
+    wqkv: torch.Tensor   # (3d, d)
+    wo: torch.Tensor     # (d, d)
+    wgu: torch.Tensor    # (2F, d)  gate rows, then up rows
+    wdown: torch.Tensor  # (d, F)
+    n1: torch.Tensor     # (d,)
+    n2: torch.Tensor     # (d,)
+
+
+class HeadWeights(NamedTuple):
+    emb: torch.Tensor    # (V, d)
+    norm: torch.Tensor   # (d,)
+    lm: torch.Tensor     # (V, d)
+
+
+@dataclass
+class EngineConfig:
+    d_model: int
+    n_heads: int
+    d_ff: int
+    vocab: int
+    n_layers: int
+    eps: float = 1e-5
+    recompute: bool = False   # per-block activation checkpointing
+
+    @property
+    def d_head(self) -> int:
+        return self.d_model // self.n_heads
+
+    @property
+    def vocab_padded(self) -> int:
+        return -(-self.vocab // 64) * 64
+
+
+class BlockSaved(NamedTuple):
+    x: torch.Tensor
+    rstd1: torch.Tensor
+    h1: torch.Tensor
+    qkv: torch.Tensor
+    o: torch.Tensor
+    lse: torch.Tensor
+    x2: torch.Tensor
+    rstd2: torch.Tensor
+    h2: torch.Tensor
+    gu: torch.Tensor
+    hh: torch.Tensor
+
+
+def block_forward(x, w: BlockWeights, cfg: EngineConfig, rope_cache, batch: int, seq: int, keep: bool):
+    """x (M, d) -> (y (M, d), saved activations or None)."""
+    h1, rstd1 = ops.rmsnorm_fwd(x, w.n1, cfg.eps)
+    qkv = ops.gemm(h1, w.wqkv, "nt")
+    ops.rope_(qkv, rope_cache, None, cfg.n_heads, False, seq)
+    o, lse = ops.attention_fwd(qkv, batch, seq, cfg.n_heads)
+    x2 = ops.gemm(o, w.wo, "nt", residual=x)
+    h2, rstd2 = ops.rmsnorm_fwd(x2, w.n2, cfg.eps)
+    gu = ops.gemm(h2, w.wgu, "nt")
+    hh = ops.silu_mul_fwd(gu)
+    y = ops.gemm(hh, w.wdown, "nt", residual=x2)
+    saved = BlockSaved(x, rstd1, h1, qkv, o, lse, x2, rstd2, h2, gu, hh) if keep else None
+    return y, saved
+
+
+def block_backward(dy, w: BlockWeights, s: BlockSaved, gw: BlockWeights, cfg: EngineConfig, rope_cache,
+                   batch: int, seq: int):
+    """Returns dx; writes every weight gradient of the block into the views in ``gw``."""
+    # ---- feed-forward half
+    dhh = ops.gemm(dy, w.wdown, "nn")
+    ops.gemm(dy, s.hh, "tn", out=gw.wdown)
+    dgu = ops.silu_mul_bwd(dhh, s.gu)
+    del dhh
+    dh2 = ops.gemm(dgu, w.wgu, "nn")
+    ops.gemm(dgu, s.h2, "tn", out=gw.wgu)
+    del dgu
+    dx2 = _norm_bwd(dh2, s.x2, w.n2, s.rstd2, gw.n2, dy)
+    del dh2
+    # ---- attention half
+    do = ops.gemm(dx2, w.wo, "nn")
+    ops.gemm(dx2, s.o, "tn", out=gw.wo)
+    dqkv = ops.attention_bwd(do, s.qkv, s.o, s.lse, batch, seq, cfg.n_heads)
+    del do
+    ops.rope_(dqkv, rope_cache, None, cfg.n_heads, True, seq)
+    dh1 = ops.gemm(dqkv, w.wqkv, "nn")
+    ops.gemm(dqkv, s.h1, "tn", out=gw.wqkv)
+    del dqkv
+    dx = _norm_bwd(dh1, s.x, w.n1, s.rstd1, gw.n1, dx2)
+    return dx
+
+
+def _norm_bwd(dyn, x, w, rstd, dw_out, dres):
+    """RMSNorm backward with the residual-branch gradient added in the same pass."""
+    if dyn.is_cuda:
+        from ..ops import native
+        if dw_out.dtype == torch.float32:
+            dx, _ = native.rmsnorm_bwd(dyn, x, w, rstd, dw_out=dw_out, dres=dres)
+        else:
+            dx, dw = native.rmsnorm_bwd(dyn, x, w, rstd, dres=dres)
+            dw_out.copy_(dw)
+        return dx
+    dx, dw = ops.torch_impl.rmsnorm_bwd(dyn, x, w, rstd)
+    dw_out.copy_(dw.to(dw_out.dtype))
+    return dx + dres
+
+
+class LocalProvider:
+    """Weights and gradients taken from a model-local ``ParamArena``."""
+
+    def __init__(self, arena, layer_names: list[dict], head_names: dict):
+        self.arena = arena
+        self.layer_names = layer_names
+        self.head_names = head_names
+        self.post_backward_hooks = []   # callables (kind, index) -> None; used by DDP
+        self._w_cache = None
+        self._g_cache = None
+        self._cache_key = None
+
+    def _views(self, flat):
+        a = self.arena
+        layers = []
+        for names in self.layer_names:
+            q = a.by_name[names["q"]]
+            d = q.shape[1]
+            wqkv = flat[q.start:q.start + 3 * q.numel].view(3 * q.shape[0], d)
+            g = a.by_name[names["gate"]]
+            if names.get("up") is None:           # merged (2F, d) parameter
+                wgu = flat[g.start:g.start + g.numel].view(g.shape)
+            else:
+                wgu = flat[g.start:g.start + 2 * g.numel].view(2 * g.shape[0], d)
+            layers.append(BlockWeights(wqkv, a.view(flat, names["o"]), wgu, a.view(flat, names["down"]),
+                                       a.view(flat, names["n1"]), a.view(flat, names["n2"])))
+        hn = self.head_names
+        head = HeadWeights(a.view(flat, hn["emb"]), a.view(flat, hn["norm"]), a.view(flat, hn["lm"]))
+        return layers, head
+
+    def begin_step(self):
+        """Refresh the compute mirror (if stale) and the cached views."""
+        flat = self.arena.mirror()
+        key = (flat.data_ptr(), self.arena.grad.data_ptr() if self.arena.grad is not None else 0)
+        if key != self._cache_key:
+            self._w_cache = self._views(flat)
+            self._g_cache = None
+            self._cache_key = key
+
+    def block_weights(self, i: int, backward: bool = False) -> BlockWeights:
+        return self._w_cache[0][i]
+
+    def head_weights(self, backward: bool = False) -> HeadWeights:
+        return self._w_cache[1]
+
+    def _grads(self):
+        if self._g_cache is None:
+            self.arena.bind_grads()
+            self._g_cache = self._views(self.arena.grad)
+            self._cache_key = (self._cache_key[0], self.arena.grad.data_ptr())
+        return self._g_cache
+
+    def block_grads(self, i: int) -> BlockWeights:
+        return self._grads()[0][i]
+
+    def head_grads(self) -> HeadWeights:
+        return self._grads()[1]
+
+    def pre_backward(self, kind: str, i: int):
+        pass
+
+    def post_backward(self, kind: str, i: int):
+        for h in self.post_backward_hooks:
+            h(kind, i)
+        if kind == "embed" and not self.arena.grads_bound:
+            self.arena.bind_grads()
+
+
+class _BlockFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, anchor, eng, i, batch, seq):
+        w = eng.provider.block_weights(i)
+        keep = torch.is_grad_enabled() or ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        cfg = eng.cfg
+        y, saved = block_forward(x, w, cfg, eng.rope_cache, batch, seq, keep and not cfg.recompute)
+        ctx.eng, ctx.i, ctx.batch, ctx.seq = eng, i, batch, seq
+        ctx.saved = saved
+        ctx.x_in = x if cfg.recompute else None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        eng, i = ctx.eng, ctx.i
+        prov = eng.provider
+        prov.pre_backward("block", i)
+        w = prov.block_weights(i, backward=True)
+        saved = ctx.saved
+        if saved is None:
+            _, saved = block_forward(ctx.x_in, w, eng.cfg, eng.rope_cache, ctx.batch, ctx.seq, True)
+        dx = block_backward(dy.contiguous(), w, saved, prov.block_grads(i), eng.cfg, eng.rope_cache, ctx.batch, ctx.seq)
+        ctx.saved = None
+        ctx.x_in = None
+        prov.post_backward("block", i)
+        return dx, None, None, None, None, None
+
+
+class _EmbedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, anchor, eng):
+        w = eng.provider.head_weights().emb
+        ctx.eng = eng
+        ctx.tokens = tokens
+        return ops.embedding_fwd(tokens, w)
+
+    @staticmethod
+    def backward(ctx, dx):
+        prov = ctx.eng.provider
+        prov.pre_backward("embed", 0)
+        g = prov.head_grads().emb
+        if g.dtype == torch.float32:
+            ops.embedding_bwd(dx.contiguous(), ctx.tokens, g)
+        else:
+            tmp = torch.zeros(g.shape, dtype=torch.float32, device=g.device)
+            ops.embedding_bwd(dx.contiguous(), ctx.tokens, tmp)
+            g.copy_(tmp)
+        prov.post_backward("embed", 0)
+        return None, None, None
+
+
+class _HeadFn(torch.autograd.Function):
+    """Final RMSNorm + lm_head producing materialised logits (API-compatible path)."""
+
+    @staticmethod
+    def forward(ctx, x, anchor, eng):
+        hw = eng.provider.head_weights()
+        cfg = eng.cfg
+        hn, rstd = ops.rmsnorm_fwd(x, hw.norm, cfg.eps)
+        buf = torch.empty((x.shape[0], cfg.vocab_padded), dtype=x.dtype, device=x.device)
+        logits = buf[:, :cfg.vocab]
+        ops.gemm(hn, hw.lm, "nt", out=logits)
+        ctx.eng = eng
+        ctx.saved = (x, rstd, hn)
+        return logits
+
+    @staticmethod
+    def backward(ctx, dlogits):
+        eng = ctx.eng
+        prov = eng.provider
+        prov.pre_backward("head", 0)
+        hw = prov.head_weights(backward=True)
+        gw = prov.head_grads()
+        x, rstd, hn = ctx.saved
+        ctx.saved = None
+        if dlogits.stride(1) != 1 or dlogits.stride(0) % 8 != 0 or dlogits.data_ptr() % 16 != 0:
+            buf = torch.zeros((dlogits.shape[0], eng.cfg.vocab_padded), dtype=x.dtype, device=x.device)
+            buf[:, :eng.cfg.vocab] = dlogits
+            dlogits = buf[:, :eng.cfg.vocab]
+        elif dlogits.dtype != x.dtype:
+            dlogits = dlogits.to(x.dtype)
+        dhn = ops.gemm(dlogits, hw.lm, "nn")
+        ops.gemm(dlogits, hn, "tn", out=gw.lm)
+        dx = _head_norm_bwd(dhn, x, hw.norm, rstd, gw.norm)
+        prov.post_backward("head", 0)
+        return dx, None, None
+
+
+def _head_norm_bwd(dyn, x, w, rstd, dw_out):
+    if dyn.is_cuda:
+        from ..ops import native
+        if dw_out.dtype == torch.float32:
+            dx, _ = native.rmsnorm_bwd(dyn, x, w, rstd, dw_out=dw_out)
+        else:
+            dx, dw = native.rmsnorm_bwd(dyn, x, w, rstd)
+            dw_out.copy_(dw)
+        return dx
+    dx, dw = ops.torch_impl.rmsnorm_bwd(dyn, x, w, rstd)
+    dw_out.copy_(dw.to(dw_out.dtype))
+    return dx
+
+
+class _HeadLossFn(torch.autograd.Function):
+    """Final RMSNorm + lm_head + mean cross-entropy without ever holding the full logits.
+
+    Rows are processed in chunks: logits chunk -> loss + d(logits) in place -> the chunk's
+    contribution to d(hidden) and d(lm_head).  The gradients are produced during forward and
+    scaled by the incoming gradient in backward, so one (chunk, V) buffer is all that is live.
+    """
+
+    @staticmethod
+    def forward(ctx, x, anchor, eng, targets, chunk_rows):
+        prov = eng.provider
+        hw = prov.head_weights()
+        cfg = eng.cfg
+        m = x.shape[0]
+        need_grad = torch.is_grad_enabled() or ctx.needs_input_grad[0]
+        hn, rstd = ops.rmsnorm_fwd(x, hw.norm, cfg.eps)
+        loss = torch.zeros((), dtype=torch.float32, device=x.device)
+        n_valid = (targets != -100).sum().clamp(min=1).float()   # stays on the device
+        buf = torch.empty((min(chunk_rows, m), cfg.vocab_padded), dtype=x.dtype, device=x.device)
+        dhn = torch.empty_like(hn) if need_grad else None
+        gw = prov.head_grads() if need_grad else None
+        lm_acc = None
+        for r0 in range(0, m, chunk_rows):
+            r1 = min(m, r0 + chunk_rows)
+            logits = buf[:r1 - r0, :cfg.vocab]
+            ops.gemm(hn[r0:r1], hw.lm, "nt", out=logits)
+            tg = targets[r0:r1]
+            if need_grad:
+                part = ops.xent_fwd_bwd(buf[:r1 - r0], tg, 1.0, -100, cfg.vocab)
+            else:
+                part = ops.xent_fwd(buf[:r1 - r0], tg, -100, cfg.vocab)
+            # each chunk normalised by its own valid count -> re-weight to the global mean
+            cnt = (tg != -100).sum().clamp(min=1).float()
+            wgt = cnt / n_valid
+            loss = loss + part * wgt
+            if need_grad:
+                if m > chunk_rows:
+                    ops.scale_(buf[:r1 - r0], wgt) if buf[:r1 - r0].is_contiguous() else buf[:r1 - r0].mul_(wgt)
+                ops.gemm(logits, hw.lm, "nn", out=dhn[r0:r1])
+                if gw.lm.dtype == torch.float32:
+                    ops.gemm(logits, hn[r0:r1], "tn", out=gw.lm, accumulate=(r0 > 0))
+                else:
+                    if lm_acc is None:
+                        lm_acc = torch.empty(gw.lm.shape, dtype=torch.float32, device=x.device)
+                    ops.gemm(logits, hn[r0:r1], "tn", out=lm_acc, accumulate=(r0 > 0))
+        if need_grad and lm_acc is not None:
+            gw.lm.copy_(lm_acc)
+        ctx.eng = eng
+        ctx.saved = (x, rstd, dhn)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        eng = ctx.eng
+        prov = eng.provider
+        prov.pre_backward("head", 0)
+        hw = prov.head_weights(backward=True)
+        gw = prov.head_grads()
+        x, rstd, dhn = ctx.saved
+        ctx.saved = None
+        # The gradients were produced in forward for d(loss) = 1; apply the incoming factor on the
+        # device (two bandwidth-bound launches, no host synchronisation).
+        scale = dloss.to(torch.float32).reshape(())
+        ops.scale_(dhn, scale)
+        if gw.lm.is_contiguous() and gw.lm.dtype in (torch.float32, torch.bfloat16):
+            ops.scale_(gw.lm, scale)
+        else:
+            gw.lm.mul_(scale.to(gw.lm.dtype))
+        dx = _head_norm_bwd(dhn, x, hw.norm, rstd, gw.norm)
+        prov.post_backward("head", 0)
+        return dx, None, None, None, None
+
+
+class NativeEngine:
+    """Runs a ``TransformerLM``-shaped stack through the fused forward/backward."""
+
+    def __init__(self, cfg: EngineConfig, provider, rope_cache: torch.Tensor):
+        self.cfg = cfg
+        self.provider = provider
+        self.rope_cache = rope_cache
+        self.loss_chunk_rows = 4096
+
+    def _anchor(self):
+        return self.provider.arena.anchor
+
+    def hidden(self, tokens: torch.Tensor) -> tuple[torch.Tensor, int, int]:
+        seq = tokens.shape[-1]
+        batch = tokens.numel() // seq
+        self.provider.begin_step()
+        anchor = self._anchor()
+        flat = tokens.reshape(-1).contiguous()
+        x = _EmbedFn.apply(flat, anchor, self)
+        for i in range(self.cfg.n_layers):
+            x = _BlockFn.apply(x, anchor, self, i, batch, seq)
+        return x, batch, seq
+
+    def logits(self, tokens: torch.Tensor) -> torch.Tensor:
+        x, batch, seq = self.hidden(tokens)
+        out = _HeadFn.apply(x, self._anchor(), self)
+        return out.view(*tokens.shape, self.cfg.vocab) if out.is_contiguous() else out.unflatten(0, tuple(tokens.shape))
+
+    def loss(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        x, batch, seq = self.hidden(tokens)
+        return _HeadLossFn.apply(x, self._anchor(), self, targets.reshape(-1).contiguous(), self.loss_chunk_rows)

@@ -1,0 +1,386 @@
+"""ctypes bindings to the sm_100a kernel library (``_b200_kernels.so``).
+
+Every wrapper validates shapes, dtypes, contiguity and alignment on the host *before*
+launching (the launchers re-check alignment and return a negative code rather than
+faulting), allocates outputs with PyTorch's caching allocator, and launches on the
+current CUDA stream.  On a machine with a GPU a missing library is an error, never a
+silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_b200_kernels.so"
+_STATUS: dict[int, torch.Tensor] = {}
+
+c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def load(required: bool = True):
+    """Load the kernel library once.  ``required`` raises if it is missing."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not _LIB_PATH.exists():
+        if os.environ.get("B200_AUTO_BUILD", "1") == "1":
+            try:
+                from ..build_ext import build
+                build()
+            except Exception as e:  # pragma: no cover - build machine specific
+                if required:
+                    raise KernelError(f"kernel library missing and build failed: {e}") from e
+                return None
+        if not _LIB_PATH.exists():
+            if required:
+                raise KernelError(f"kernel library not found at {_LIB_PATH}; run build_ext.build()")
+            return None
+    lib = ctypes.CDLL(str(_LIB_PATH))
+    _declare(lib)
+    _LIB = lib
+    return lib
+
+
+def available() -> bool:
+    """True when CUDA is usable and the kernel library loads."""
+    if not torch.cuda.is_available():
+        return False
+    return load(required=True) is not None
+
+
+def _declare(lib):
+    P, I, L, F = c_void_p, c_int, c_ll, c_float
+    sigs = {
+        "b200_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, P, P],
+        "b200_rmsnorm_fwd": [P, P, P, P, I, I, F, P],
+        "b200_rmsnorm_bwd_parts": [I],
+        "b200_rmsnorm_bwd": [P, P, P, P, P, P, P, I, I, I, P],
+        "b200_silu_mul_fwd": [P, P, L, I, P],
+        "b200_silu_mul_bwd": [P, P, P, L, I, P],
+        "b200_rope": [P, P, P, L, I, I, I, I, I, P],
+        "b200_embedding_fwd": [P, P, P, L, I, I, P],
+        "b200_embedding_bwd": [P, P, P, L, I, I, P],
+        "b200_xent": [P, P, P, P, L, L, I, I, F, I, I, P],
+        "b200_argmax": [P, L, L, I, P, P],
+        "b200_adamw": [P, P, I, P, P, P, L, P, F, F, F, F, F, F, P],
+        "b200_sumsq": [P, I, L, P, P],
+        "b200_clip_coef": [P, F, P, P, P],
+        "b200_scale": [P, I, L, P, P],
+        "b200_cast_f32_bf16": [P, P, L, P],
+        "b200_cast_bf16_f32": [P, P, L, P],
+    }
+    optional = {
+        "b200_flash_fwd": [P, P, P, I, I, I, I, F, P, P],
+        "b200_flash_bwd": [P, P, P, P, P, P, I, I, I, I, F, P, P],
+        "b200_flash_varlen_fwd": [P, P, P, I, I, I, I, F, P, P],
+        "b200_paged_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P],
+        "b200_kv_append": [P, P, P, P, L, I, P],
+        "b200_sample": [P, L, L, I, F, I, P, P, P, P],
+    }
+    for name, args in {**sigs, **optional}.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            if name in sigs:
+                raise KernelError(f"symbol {name} missing from {_LIB_PATH}")
+            continue
+        fn.argtypes = args
+        fn.restype = I
+
+
+def has(symbol: str) -> bool:
+    lib = load(required=False)
+    return lib is not None and hasattr(lib, symbol)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device uint32 status word written by kernels whose bounded waits gave up."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    if dev not in _STATUS:
+        _STATUS[dev] = torch.zeros(4, dtype=torch.int32, device=f"cuda:{dev}")
+    return _STATUS[dev]
+
+
+def check_status(device=None):
+    """Synchronise and raise if any kernel recorded a wait that ran out."""
+    w = status_word(device)
+    v = int(w[0].item())
+    if v != 0:
+        w.zero_()
+        raise KernelError(f"kernel reported error code {v & 0xff} from CTA {v >> 8}")
+
+
+def _check(rc: int, name: str):
+    if rc != 0:
+        raise KernelError(f"{name} failed with code {rc}")
+
+
+def _req(cond: bool, msg: str):
+    if not cond:
+        raise ValueError(msg)
+
+
+def _rowmajor(t: torch.Tensor, name: str):
+    _req(t.dim() == 2 and t.stride(1) == 1, f"{name} must be 2-D with unit inner stride")
+
+
+# ----------------------------------------------------------------------------- GEMM
+EPI_BF16, EPI_F32, EPI_BF16_RES, EPI_F32_ACC = 0, 1, 2, 3
+
+
+def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, bn_hint=0, max_ctas=0):
+    """bf16 tensor-core GEMM (tcgen05).  layout 'nt' | 'nn' | 'tn' as in ``torch_impl.gemm``."""
+    lib = load()
+    _req(a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "gemm inputs must be bf16")
+    _rowmajor(a, "a")
+    _rowmajor(b, "b")
+    if layout == "nt":
+        m, k = a.shape
+        n, kb = b.shape
+        a_mn, b_mn = 0, 0
+    elif layout == "nn":
+        m, k = a.shape
+        kb, n = b.shape
+        a_mn, b_mn = 0, 1
+    elif layout == "tn":
+        k, m = a.shape
+        kb, n = b.shape
+        a_mn, b_mn = 1, 1
+    else:
+        raise ValueError(layout)
+    _req(k == kb, f"contraction mismatch {k} vs {kb}")
+    lda, ldb = a.stride(0), b.stride(0)
+    _req(lda % 8 == 0 and ldb % 8 == 0, "leading dimensions must be multiples of 8 elements")
+    _req(a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0, "operands must be 16-byte aligned")
+    if out is None:
+        dt = out_dtype or torch.bfloat16
+        out = torch.empty((m, n), dtype=dt, device=a.device)
+    else:
+        _rowmajor(out, "out")
+        _req(tuple(out.shape) == (m, n), f"out shape {tuple(out.shape)} != {(m, n)}")
+    if out.dtype == torch.bfloat16:
+        _req(not accumulate, "accumulate needs an fp32 output")
+        epi = EPI_BF16_RES if residual is not None else EPI_BF16
+    elif out.dtype == torch.float32:
+        _req(residual is None, "residual needs a bf16 output")
+        epi = EPI_F32_ACC if accumulate else EPI_F32
+    else:
+        raise ValueError("out must be bf16 or fp32")
+    ldr = 0
+    if residual is not None:
+        _rowmajor(residual, "residual")
+        _req(residual.dtype == torch.bfloat16 and tuple(residual.shape) == (m, n), "residual must be bf16 (M,N)")
+        ldr = residual.stride(0)
+    rc = lib.b200_gemm_bf16(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb, out.stride(0), ldr,
+                            a_mn, b_mn, epi, bn_hint, max_ctas, _ptr(status_word(a.device)), _stream())
+    _check(rc, "b200_gemm_bf16")
+    return out
+
+
+# -------------------------------------------------------------------------- RMSNorm
+def rmsnorm_fwd(x, w, eps: float):
+    lib = load()
+    _req(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "rmsnorm inputs must be bf16")
+    _req(x.is_contiguous() and w.is_contiguous(), "rmsnorm inputs must be contiguous")
+    d = x.shape[-1]
+    rows = x.numel() // d
+    _req(w.numel() == d and d % 8 == 0, "bad rmsnorm width")
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _check(lib.b200_rmsnorm_fwd(_ptr(x), _ptr(w), _ptr(y), _ptr(rstd), rows, d, float(eps), _stream()), "rmsnorm_fwd")
+    return y, rstd
+
+
+def rmsnorm_bwd(dy, x, w, rstd, dw_out=None, accumulate=False):
+    lib = load()
+    _req(dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "bf16 expected")
+    _req(dy.is_contiguous() and x.is_contiguous(), "contiguous expected")
+    d = x.shape[-1]
+    rows = x.numel() // d
+    _req(d % 8 == 0 and d <= 8192, "rmsnorm_bwd supports widths that are multiples of 8 up to 8192")
+    _req(rstd.numel() == rows and rstd.dtype == torch.float32, "bad rstd")
+    dx = torch.empty_like(x)
+    dw = dw_out if dw_out is not None else torch.empty(d, dtype=torch.float32, device=x.device)
+    _req(dw.dtype == torch.float32 and dw.numel() == d and dw.is_contiguous(), "dw must be fp32 (d,)")
+    parts = lib.b200_rmsnorm_bwd_parts(rows)
+    scratch = torch.empty(parts * d, dtype=torch.float32, device=x.device)
+    _check(lib.b200_rmsnorm_bwd(_ptr(dy), _ptr(x), _ptr(w), _ptr(rstd), _ptr(dx), _ptr(dw), _ptr(scratch), rows, d,
+                                1 if accumulate else 0, _stream()), "rmsnorm_bwd")
+    return dx, dw
+
+
+# --------------------------------------------------------------------------- SwiGLU
+def silu_mul_fwd(gu):
+    lib = load()
+    _req(gu.dtype == torch.bfloat16 and gu.dim() == 2 and gu.is_contiguous(), "gu must be contiguous bf16 (M, 2F)")
+    rows, two_f = gu.shape
+    f = two_f // 2
+    _req(two_f % 2 == 0 and f % 8 == 0, "F must be a multiple of 8")
+    h = torch.empty((rows, f), dtype=gu.dtype, device=gu.device)
+    _check(lib.b200_silu_mul_fwd(_ptr(gu), _ptr(h), rows, f, _stream()), "silu_mul_fwd")
+    return h
+
+
+def silu_mul_bwd(dh, gu):
+    lib = load()
+    rows, two_f = gu.shape
+    f = two_f // 2
+    _req(dh.dtype == torch.bfloat16 and dh.is_contiguous() and tuple(dh.shape) == (rows, f), "bad dh")
+    _req(gu.dtype == torch.bfloat16 and gu.is_contiguous() and f % 8 == 0, "bad gu")
+    dgu = torch.empty_like(gu)
+    _check(lib.b200_silu_mul_bwd(_ptr(dh), _ptr(gu), _ptr(dgu), rows, f, _stream()), "silu_mul_bwd")
+    return dgu
+
+
+# ----------------------------------------------------------------------------- RoPE
+def rope_(qkv, cos_sin, positions, n_heads: int, inverse: bool = False, seq: int | None = None):
+    """positions: (M,) int32 tensor, or None with ``seq`` given (position = row % seq)."""
+    lib = load()
+    _req(qkv.dtype == torch.bfloat16 and qkv.dim() == 2 and qkv.is_contiguous(), "qkv must be contiguous bf16")
+    rows, three_d = qkv.shape
+    d = three_d // 3
+    dh = d // n_heads
+    _req(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[0] == 2, "bad rope cache")
+    ctx = cos_sin.shape[1]
+    _req(cos_sin.shape[2] == dh // 2 and dh % 8 == 0, "head dim must be a multiple of 8 and match the cache")
+    if positions is not None:
+        _req(positions.dtype == torch.int32 and positions.numel() == rows and positions.is_contiguous(),
+             "positions must be int32 (M,)")
+        seq_arg = 1
+    else:
+        _req(seq is not None and seq <= ctx and rows % seq == 0, "seq must divide rows and fit the rope cache")
+        seq_arg = seq
+    _check(lib.b200_rope(_ptr(qkv), _ptr(cos_sin), _ptr(positions), rows, seq_arg, d, dh, ctx, 1 if inverse else 0,
+                         _stream()), "rope")
+    return qkv
+
+
+# ------------------------------------------------------------------------ Embedding
+def embedding_fwd(tokens, weight, out_dtype=None):
+    lib = load()
+    _req(tokens.dtype == torch.int64 and tokens.is_contiguous(), "tokens must be contiguous int64")
+    _req(weight.dtype == torch.bfloat16 and weight.is_contiguous() and weight.dim() == 2, "table must be bf16 (V,d)")
+    v, d = weight.shape
+    rows = tokens.numel()
+    out = torch.empty((rows, d), dtype=torch.bfloat16, device=weight.device)
+    _check(lib.b200_embedding_fwd(_ptr(tokens), _ptr(weight), _ptr(out), rows, d, v, _stream()), "embedding_fwd")
+    return out
+
+
+def embedding_bwd(dx, tokens, grad_weight, accumulate=False):
+    lib = load()
+    _req(dx.dtype == torch.bfloat16 and dx.is_contiguous(), "dx must be contiguous bf16")
+    _req(grad_weight.dtype == torch.float32 and grad_weight.is_contiguous(), "grad table must be fp32")
+    _req(tokens.dtype == torch.int64 and tokens.is_contiguous(), "tokens must be contiguous int64")
+    v, d = grad_weight.shape
+    rows = tokens.numel()
+    _req(dx.numel() == rows * d, "dx shape mismatch")
+    if not accumulate:
+        grad_weight.zero_()
+    _check(lib.b200_embedding_bwd(_ptr(tokens), _ptr(dx), _ptr(grad_weight), rows, d, v, _stream()), "embedding_bwd")
+    return grad_weight
+
+
+# -------------------------------------------------------------------- Cross entropy
+def xent_fwd_bwd(logits, targets, grad_scale: float = 1.0, ignore_index: int = -100, valid_cols=None,
+                 write_grad: bool = True, loss_out=None, accumulate_loss=False):
+    lib = load()
+    _req(logits.dtype == torch.bfloat16 and logits.dim() == 2 and logits.stride(1) == 1, "logits must be bf16 2-D")
+    rows, cols = logits.shape
+    ld = logits.stride(0)
+    v = valid_cols or cols
+    _req(ld % 8 == 0 and v <= ld, "logits row stride must be a multiple of 8 elements")
+    _req(targets.dtype == torch.int64 and targets.numel() == rows and targets.is_contiguous(), "bad targets")
+    loss = loss_out if loss_out is not None else torch.empty((), dtype=torch.float32, device=logits.device)
+    scratch = torch.empty(rows + 1, dtype=torch.float32, device=logits.device)
+    _check(lib.b200_xent(_ptr(logits), _ptr(targets), _ptr(loss), _ptr(scratch), rows, ld, v, ignore_index,
+                         float(grad_scale), 1 if write_grad else 0, 1 if accumulate_loss else 0, _stream()), "xent")
+    return loss
+
+
+def xent_fwd(logits, targets, ignore_index: int = -100, valid_cols=None):
+    return xent_fwd_bwd(logits, targets, 1.0, ignore_index, valid_cols, write_grad=False)
+
+
+def argmax_rows(logits, valid_cols=None):
+    lib = load()
+    _req(logits.dtype == torch.bfloat16 and logits.dim() == 2 and logits.stride(1) == 1, "logits must be bf16 2-D")
+    rows, cols = logits.shape
+    out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    _check(lib.b200_argmax(_ptr(logits), rows, logits.stride(0), valid_cols or cols, _ptr(out), _stream()), "argmax")
+    return out
+
+
+# ---------------------------------------------------------------------------- AdamW
+def adamw_step(master, grad, m, v, mirror, lr, beta1, beta2, eps, weight_decay, step: int, grad_scale=None):
+    lib = load()
+    n = master.numel()
+    _req(master.dtype == torch.float32 and m.dtype == torch.float32 and v.dtype == torch.float32, "state must be fp32")
+    _req(master.is_contiguous() and grad.is_contiguous() and m.is_contiguous() and v.is_contiguous(), "contiguous")
+    _req(grad.numel() == n and m.numel() == n and v.numel() == n, "size mismatch")
+    _req(grad.dtype in (torch.float32, torch.bfloat16), "grad must be fp32 or bf16")
+    if mirror is not None:
+        _req(mirror.dtype == torch.bfloat16 and mirror.numel() == n and mirror.is_contiguous(), "bad mirror")
+    if grad_scale is not None:
+        _req(grad_scale.dtype == torch.float32 and grad_scale.numel() == 1, "grad_scale must be a device float")
+    alpha_t = lr * math.sqrt(1 - beta2 ** step) / (1 - beta1 ** step)
+    _check(lib.b200_adamw(_ptr(master), _ptr(grad), 1 if grad.dtype == torch.bfloat16 else 0, _ptr(m), _ptr(v),
+                          _ptr(mirror), n, _ptr(grad_scale), float(lr), float(beta1), float(beta2), float(eps),
+                          float(weight_decay), float(alpha_t), _stream()), "adamw")
+
+
+def sumsq(x, out=None):
+    lib = load()
+    _req(x.is_contiguous() and x.dtype in (torch.float32, torch.bfloat16), "sumsq needs contiguous fp32/bf16")
+    if out is None:
+        out = torch.zeros((), dtype=torch.float32, device=x.device)
+    _check(lib.b200_sumsq(_ptr(x), 1 if x.dtype == torch.bfloat16 else 0, x.numel(), _ptr(out), _stream()), "sumsq")
+    return out
+
+
+def clip_coef(sumsq_t, max_norm: float, coef_out=None, norm_out=None):
+    lib = load()
+    if coef_out is None:
+        coef_out = torch.empty((), dtype=torch.float32, device=sumsq_t.device)
+    _check(lib.b200_clip_coef(_ptr(sumsq_t), float(max_norm), _ptr(coef_out), _ptr(norm_out), _stream()), "clip_coef")
+    return coef_out
+
+
+def scale_(x, coef):
+    lib = load()
+    _req(x.is_contiguous() and x.dtype in (torch.float32, torch.bfloat16), "scale needs contiguous fp32/bf16")
+    _req(torch.is_tensor(coef) and coef.dtype == torch.float32 and coef.numel() == 1, "coef must be a device float")
+    _check(lib.b200_scale(_ptr(x), 1 if x.dtype == torch.bfloat16 else 0, x.numel(), _ptr(coef), _stream()), "scale")
+    return x
+
+
+def cast_copy(dst, src):
+    lib = load()
+    _req(dst.is_contiguous() and src.is_contiguous() and dst.numel() == src.numel(), "cast needs equal contiguous")
+    if src.dtype == torch.float32 and dst.dtype == torch.bfloat16:
+        _check(lib.b200_cast_f32_bf16(_ptr(src), _ptr(dst), src.numel(), _stream()), "cast")
+    elif src.dtype == torch.bfloat16 and dst.dtype == torch.float32:
+        _check(lib.b200_cast_bf16_f32(_ptr(src), _ptr(dst), src.numel(), _stream()), "cast")
+    else:
+        dst.copy_(src)
+    return dst

@@ -1,0 +1,98 @@
+"""tcgen05 GEMM against an fp32 PyTorch matmul of the same bf16 inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, layout):
+    af, bf = a.float(), b.float()
+    if layout == "nt":
+        return af @ bf.t()
+    if layout == "nn":
+        return af @ bf
+    return af.t() @ bf
+
+
+def _make(layout, m, n, k, dev):
+    g = torch.Generator(device=dev).manual_seed(m * 7 + n * 3 + k)
+    if layout == "nt":
+        a = torch.randn(m, k, device=dev, generator=g)
+        b = torch.randn(n, k, device=dev, generator=g)
+    elif layout == "nn":
+        a = torch.randn(m, k, device=dev, generator=g)
+        b = torch.randn(k, n, device=dev, generator=g)
+    else:
+        a = torch.randn(k, m, device=dev, generator=g)
+        b = torch.randn(k, n, device=dev, generator=g)
+    return a.bfloat16(), b.bfloat16()
+
+
+def _check(out, ref, k):
+    err = (out.float() - ref).abs().max().item()
+    tol = 2e-2 * (k ** 0.5) if out.dtype == torch.bfloat16 else 1e-3 * (k ** 0.5)
+    assert err <= tol, f"max abs err {err} > {tol}"
+
+
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (1000, 1336, 520),
+                                   (136, 72, 72), (2048, 5504, 2048)])
+def test_gemm_layouts(layout, bn, shape):
+    from llm_systems_from_scratch_b200.ops import native
+    m, n, k = shape
+    a, b = _make(layout, m, n, k, "cuda")
+    out = native.gemm(a, b, layout, out_dtype=torch.float32, bn_hint=bn)
+    native.check_status()
+    _check(out, _ref(a, b, layout), k)
+    out16 = native.gemm(a, b, layout, bn_hint=bn)
+    native.check_status()
+    _check(out16, _ref(a, b, layout), k)
+
+
+def test_gemm_residual_and_accumulate():
+    from llm_systems_from_scratch_b200.ops import native
+    m, n, k = 512, 1024, 768
+    a, b = _make("nt", m, n, k, "cuda")
+    res = torch.randn(m, n, device="cuda").bfloat16()
+    out = native.gemm(a, b, "nt", residual=res)
+    native.check_status()
+    _check(out, _ref(a, b, "nt") + res.float(), k)
+    # in-place residual: out aliases the residual
+    buf = res.clone()
+    native.gemm(a, b, "nt", out=buf, residual=buf)
+    native.check_status()
+    _check(buf, _ref(a, b, "nt") + res.float(), k)
+    acc = torch.ones(m, n, device="cuda", dtype=torch.float32)
+    native.gemm(a, b, "nt", out=acc, accumulate=True)
+    native.check_status()
+    _check(acc, _ref(a, b, "nt") + 1.0, k)
+
+
+def test_gemm_strided_views_and_auto_tile():
+    from llm_systems_from_scratch_b200.ops import native
+    m, k = 640, 512
+    big = torch.randn(m, 3 * k, device="cuda").bfloat16()
+    a = big[:, k:2 * k]                      # row stride 3k, offset k
+    w = torch.randn(1344, k, device="cuda").bfloat16()
+    out = native.gemm(a, w, "nt")
+    native.check_status()
+    _check(out, a.float() @ w.float().t(), k)
+    outbuf = torch.zeros(m, 2 * 1344, device="cuda", dtype=torch.bfloat16)
+    native.gemm(a, w, "nt", out=outbuf[:, 1344:])
+    native.check_status()
+    _check(outbuf[:, 1344:], a.float() @ w.float().t(), k)
+    assert outbuf[:, :1344].abs().max().item() == 0
+
+
+def test_gemm_many_tiles_persistent():
+    from llm_systems_from_scratch_b200.ops import native
+    m, n, k = 4096, 4096, 512
+    a, b = _make("nt", m, n, k, "cuda")
+    out = native.gemm(a, b, "nt")
+    native.check_status()
+    _check(out, _ref(a, b, "nt"), k)
+    # fewer CTAs than tiles forces several tiles per CTA and accumulator double-buffering
+    out2 = native.gemm(a, b, "nt", max_ctas=5)
+    native.check_status()
+    assert torch.equal(out, out2)
