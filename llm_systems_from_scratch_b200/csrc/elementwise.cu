@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
 }
 
 // ------------------------------------------------------------------------ RMSNorm bwd
-// dx = rstd * (dy*w) - rstd^3/d * sum(dy*w*x) * x ;  dw += dy * x * rstd.
+// dx = [dres +] rstd * (dy*w) - rstd^3/d * sum(dy*w*x) * x ;  dw += dy * x * rstd.
 // Each block walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a thread owns up to MAXC groups of
 // 8 columns and keeps the weight-gradient partial for them in registers.  Partials go to
 // `dw_partial` (gridDim.x, d) fp32 and are summed in a fixed order by rmsnorm_dw_reduce_kernel.
@@ -99,7 +99,8 @@ constexpr int RMS_BWD_MAXC = 4;  // d <= 256 * 8 * 4 = 8192
 __global__ void __launch_bounds__(RMS_BWD_THREADS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int d) {
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int rows, int d) {
   __shared__ float red[32];
   float wreg[RMS_BWD_MAXC][8];
   float dwacc[RMS_BWD_MAXC][8];
@@ -141,6 +142,12 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         float o[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = r * g[j][i] - coef * xv[j][i];
+        if (dres != nullptr) {  // gradient arriving through the residual branch
+          float e[8];
+          load8(dres + (size_t)row * d + c, e);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += e[i];
+        }
         store8(dxr + c, o);
       }
     }
@@ -511,15 +518,19 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* w, void* y, float* rs
 extern "C" int b200_rmsnorm_bwd_parts(int rows) { return rows < 148 * 4 ? (rows > 0 ? rows : 1) : 148 * 4; }
 
 // dw_partial: scratch of b200_rmsnorm_bwd_parts(rows) * d floats.  dw (d floats) is overwritten or accumulated.
-extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
-                                float* dw_partial, int rows, int d, int accumulate_dw, cudaStream_t st) {
+// dres (bf16, same shape as dx, may be null) is added to dx.
+extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                                void* dx, float* dw, float* dw_partial, int rows, int d, int accumulate_dw,
+                                cudaStream_t st) {
   if (d % 8 || d > RMS_BWD_THREADS * 8 * RMS_BWD_MAXC) return -10;
-  if (!ALIGNED16(dy) || !ALIGNED16(x) || !ALIGNED16(w) || !ALIGNED16(dx) || !ALIGNED16(dw_partial)) return -10;
+  if (!ALIGNED16(dy) || !ALIGNED16(x) || !ALIGNED16(w) || !ALIGNED16(dx) || !ALIGNED16(dw_partial) ||
+      !ALIGNED16(dres))
+    return -10;
   if (rows == 0) return 0;
   const int parts = b200_rmsnorm_bwd_parts(rows);
   rmsnorm_bwd_kernel<<<parts, RMS_BWD_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                        (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx,
-                                                        dw_partial, rows, d);
+                                                        (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
+                                                        (__nv_bfloat16*)dx, dw_partial, rows, d);
   rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_partial, dw, parts, d, accumulate_dw);
   CHECK_LAUNCH();
 }

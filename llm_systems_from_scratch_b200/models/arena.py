@@ -64,6 +64,7 @@ class ParamArena:
         self.compute_dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
         self._mirror: torch.Tensor | None = None
         self._mirror_fresh = False
+        self._mirror_versions = -1
         self.grad: torch.Tensor | None = None
         self.grads_bound = False
         self._sumsq = None
@@ -73,6 +74,11 @@ class ParamArena:
         self.anchor = torch.zeros(1, dtype=torch.float32, device=device, requires_grad=True)
 
     # ---------------------------------------------------------------- compute mirror
+    def _versions(self) -> int:
+        # In-place PyTorch updates of a parameter (optimizers, load_state_dict) bump its version
+        # counter; kernels launched through raw pointers do not and report freshness explicitly.
+        return sum(p._version for p in self.params)
+
     def mirror(self) -> torch.Tensor:
         """bf16 copy of the master weights (the master itself on CPU), refreshed when stale."""
         if self.compute_dtype == torch.float32:
@@ -80,9 +86,11 @@ class ParamArena:
         if self._mirror is None:
             self._mirror = torch.empty(self.numel, dtype=torch.bfloat16, device=self.device)
             self._mirror_fresh = False
-        if not self._mirror_fresh:
+        ver = self._versions()
+        if not self._mirror_fresh or ver != self._mirror_versions:
             ops.cast_copy(self._mirror, self.master)
             self._mirror_fresh = True
+            self._mirror_versions = ver
         return self._mirror
 
     def mirror_buffer(self) -> torch.Tensor | None:
@@ -94,7 +102,9 @@ class ParamArena:
         return self._mirror
 
     def mark_mirror(self, fresh: bool):
+        """Called by an optimizer that updated master and mirror together in one kernel."""
         self._mirror_fresh = fresh
+        self._mirror_versions = self._versions()
 
     # --------------------------------------------------------------------- gradients
     def ensure_grads(self) -> torch.Tensor:

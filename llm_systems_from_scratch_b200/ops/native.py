@@ -67,7 +67,7 @@ def _declare(lib):
         "b200_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, P, P],
         "b200_rmsnorm_fwd": [P, P, P, P, I, I, F, P],
         "b200_rmsnorm_bwd_parts": [I],
-        "b200_rmsnorm_bwd": [P, P, P, P, P, P, P, I, I, I, P],
+        "b200_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
         "b200_silu_mul_fwd": [P, P, L, I, P],
         "b200_silu_mul_bwd": [P, P, P, L, I, P],
         "b200_rope": [P, P, P, L, I, I, I, I, I, P],
@@ -85,7 +85,7 @@ def _declare(lib):
     optional = {
         "b200_flash_fwd": [P, P, P, I, I, I, I, F, P, P],
         "b200_flash_bwd": [P, P, P, P, P, P, I, I, I, I, F, P, P],
-        "b200_flash_varlen_fwd": [P, P, P, I, I, I, I, F, P, P],
+        "b200_flash_varlen_fwd": [P, P, P, I, I, I, I, I, F, P, P],
         "b200_paged_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P],
         "b200_kv_append": [P, P, P, P, L, I, P],
         "b200_sample": [P, L, L, I, F, I, P, P, P, P],
@@ -211,7 +211,7 @@ def rmsnorm_fwd(x, w, eps: float):
     return y, rstd
 
 
-def rmsnorm_bwd(dy, x, w, rstd, dw_out=None, accumulate=False):
+def rmsnorm_bwd(dy, x, w, rstd, dw_out=None, accumulate=False, dres=None):
     lib = load()
     _req(dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "bf16 expected")
     _req(dy.is_contiguous() and x.is_contiguous(), "contiguous expected")
@@ -222,9 +222,11 @@ def rmsnorm_bwd(dy, x, w, rstd, dw_out=None, accumulate=False):
     dx = torch.empty_like(x)
     dw = dw_out if dw_out is not None else torch.empty(d, dtype=torch.float32, device=x.device)
     _req(dw.dtype == torch.float32 and dw.numel() == d and dw.is_contiguous(), "dw must be fp32 (d,)")
+    if dres is not None:
+        _req(dres.dtype == torch.bfloat16 and dres.is_contiguous() and dres.numel() == x.numel(), "bad dres")
     parts = lib.b200_rmsnorm_bwd_parts(rows)
     scratch = torch.empty(parts * d, dtype=torch.float32, device=x.device)
-    _check(lib.b200_rmsnorm_bwd(_ptr(dy), _ptr(x), _ptr(w), _ptr(rstd), _ptr(dx), _ptr(dw), _ptr(scratch), rows, d,
+    _check(lib.b200_rmsnorm_bwd(_ptr(dy), _ptr(x), _ptr(w), _ptr(rstd), _ptr(dres), _ptr(dx), _ptr(dw), _ptr(scratch), rows, d,
                                 1 if accumulate else 0, _stream()), "rmsnorm_bwd")
     return dx, dw
 
