@@ -1,0 +1,613 @@
+// Causal FlashAttention backward for sm_100a on the packed (batch*seq, 3*H*dh) QKV layout.
+// Gradient of the reference's attention call (llm-core/llm_core/model.py:381-385) without ever
+// materialising the (S, S) probabilities: they are recomputed tile by tile from Q, K and the saved
+// log-sum-exp.  Three kernels, each value of dQ, dK and dV is written exactly once (no atomics, so
+// results are bitwise reproducible):
+//
+//   flash_delta_kernel   delta[b,h,s] = sum_d dO * O
+//   flash_dkdv_kernel    CTA = 128 keys of one (b,h); walks 64-query steps i >= diagonal:
+//                          S^T = K Q_i^T, dP^T = V dO_i^T        (TMEM, double buffered)
+//                          P^T = exp2(S^T*c - lse), dS^T = P^T*(dP^T - delta)*scale -> swizzled smem
+//                          dV += P^T dO_i,  dK += dS^T Q_i        (TMEM accumulators)
+//   flash_dq_kernel      CTA = 128 queries; walks 64-key steps j <= diagonal:
+//                          S = Q K_j^T, dP = dO V_j^T ; dS -> smem ; dQ += dS K_j
+//
+// Roles per CTA: warp 0 TMA producer, warp 1 tcgen05.mma issuer, warps 2-5 one tile row per thread.
+#include "ptx.cuh"
+
+namespace b200 {
+
+int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+                      uint32_t box_rows);
+
+struct FlashBwdParams {
+  const float* lse;     // (batch, heads, seq)
+  const float* delta;   // (batch, heads, seq)
+  __nv_bfloat16* dqkv;  // (rows, 3d)
+  int batch, seq, heads, d;
+  float scale, scale_log2;
+  uint32_t* status;
+};
+
+// delta = rowsum(dO * O) per (row, head); one warp per (row, head).
+__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                   float* __restrict__ delta, int batch, int seq, int heads, int dh) {
+  const int lane = threadIdx.x & 31;
+  const long long w = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = (long long)batch * seq * heads;
+  if (w >= total) return;
+  const long long row = w / heads;
+  const int h = (int)(w % heads);
+  const size_t base = (size_t)row * heads * dh + (size_t)h * dh;
+  float s = 0.f;
+  for (int c = lane * 8; c < dh; c += 256) {
+    uint4 a = *reinterpret_cast<const uint4*>(o + base + c);
+    uint4 b = *reinterpret_cast<const uint4*>(dout + base + c);
+    const uint32_t aa[4] = {a.x, a.y, a.z, a.w}, bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 x = unpack_bf16x2(aa[i]), y = unpack_bf16x2(bb[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) {
+    const int b = (int)(row / seq), sidx = (int)(row % seq);
+    delta[((size_t)b * heads + h) * seq + sidx] = s;
+  }
+}
+
+__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Write 64 bf16 values (one 128-byte row of a 128B-swizzled panel) from fp32 registers.
+__device__ __forceinline__ void store_row64_swizzled(uint8_t* panel, int r, const float (&v)[64]) {
+  uint8_t* row = panel + r * 128;
+#pragma unroll
+  for (int c16 = 0; c16 < 8; ++c16) {
+    uint4 u = make_uint4(pack_bf16x2(v[c16 * 8 + 0], v[c16 * 8 + 1]), pack_bf16x2(v[c16 * 8 + 2], v[c16 * 8 + 3]),
+                         pack_bf16x2(v[c16 * 8 + 4], v[c16 * 8 + 5]), pack_bf16x2(v[c16 * 8 + 6], v[c16 * 8 + 7]));
+    *reinterpret_cast<uint4*>(row + ((c16 ^ (r & 7)) << 4)) = u;
+  }
+}
+
+// ------------------------------------------------------------------------------ dK / dV
+template <int DH>
+struct DkDvSmem {
+  static constexpr int PANELS = DH / 64;
+  static constexpr int KV_TILE = 128 * DH * 2;   // K_j or V_j (128 keys)
+  static constexpr int Q_TILE = 64 * DH * 2;     // Q_i or dO_i (64 queries)
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + KV_TILE;
+  static constexpr int OFF_Q = OFF_V + KV_TILE;          // 2 stages
+  static constexpr int OFF_DO = OFF_Q + 2 * Q_TILE;      // 2 stages
+  static constexpr int OFF_PT = OFF_DO + 2 * Q_TILE;     // 128 x 64 bf16
+  static constexpr int OFF_DST = OFF_PT + 16384;
+  static constexpr int OFF_VEC = OFF_DST + 16384;        // lse[2][64], delta[2][64] floats
+  static constexpr int OFF_BAR = OFF_VEC + 4 * 64 * 4;
+  static constexpr int NUM_BARS = 1 + 2 + 2 + 2 + 2 + 1 + 1;
+  static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(192, 1)
+flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 over qkv
+                  const __grid_constant__ CUtensorMap tm_q,    // box 64 x 64 over qkv
+                  const __grid_constant__ CUtensorMap tm_do,   // box 64 x 64 over dO
+                  const FlashBwdParams p) {
+  using L = DkDvSmem<DH>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* kv_full = bars;
+  uint64_t* qd_full = bars + 1;   // [2]
+  uint64_t* qd_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;    // [2]
+  uint64_t* s_empty = bars + 7;   // [2]
+  uint64_t* p_full = bars + 9;
+  uint64_t* p_empty = bars + 10;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
+  volatile uint32_t* abort_word = tmem_holder + 1;
+  float* lse_s = reinterpret_cast<float*>(smem + L::OFF_VEC);   // [2][64]
+  float* delta_s = lse_s + 128;                                  // [2][64]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x % (p.batch * p.heads);
+  const int jblk = blockIdx.x / (p.batch * p.heads);   // 128-key block; small j = most work, scheduled first
+  const int b = bh / p.heads, h = bh % p.heads;
+  const int row_base = b * p.seq;
+  const int k0 = jblk * 128;
+  const int n_q64 = (p.seq + 63) / 64;
+  const int i0 = 2 * jblk;
+  const int n_steps = n_q64 - i0;   // >= 1 because k0 < seq
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qd_full[i], 1);
+      mbar_init(&qd_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(p_empty, 1);
+    *abort_word = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tm_kv);
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tm_st = tmem_base;         // S^T: 2 x 64 columns
+  const uint32_t tm_dpt = tmem_base + 128;  // dP^T: 2 x 64 columns
+  const uint32_t tm_dv = tmem_base + 256;   // DH columns
+  const uint32_t tm_dk = tmem_base + 384;   // DH columns
+
+  const int col_q = h * DH, col_k = p.d + h * DH, col_v = 2 * p.d + h * DH;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * L::KV_TILE);
+#pragma unroll
+      for (int pn = 0; pn < L::PANELS; ++pn) {
+        tma_load_2d(smem + L::OFF_K + pn * 16384, &tm_kv, kv_full, col_k + pn * 64, row_base + k0);
+        tma_load_2d(smem + L::OFF_V + pn * 16384, &tm_kv, kv_full, col_v + pn * 64, row_base + k0);
+      }
+      for (int t = 0; t < n_steps; ++t) {
+        const int st = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        const int qrow = row_base + (i0 + t) * 64;
+        if (!mbar_wait(&qd_empty[st], ph ^ 1, abort_word)) { *abort_word = ERR_WAIT_EMPTY; break; }
+        mbar_expect_tx(&qd_full[st], 2 * L::Q_TILE);
+#pragma unroll
+        for (int pn = 0; pn < L::PANELS; ++pn) {
+          tma_load_2d(smem + L::OFF_Q + st * L::Q_TILE + pn * 8192, &tm_q, &qd_full[st], col_q + pn * 64, qrow);
+          tma_load_2d(smem + L::OFF_DO + st * L::Q_TILE + pn * 8192, &tm_do, &qd_full[st], h * DH + pn * 64, qrow);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_12 = make_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_34 = make_idesc_bf16(128, DH, false, true);
+      const uint32_t k_addr = smem_u32(smem + L::OFF_K), v_addr = smem_u32(smem + L::OFF_V);
+      const uint32_t pt_addr = smem_u32(smem + L::OFF_PT), dst_addr = smem_u32(smem + L::OFF_DST);
+      auto issue12 = [&](int t) {
+        const int st = t & 1;
+        const uint32_t q_addr = smem_u32(smem + L::OFF_Q + st * L::Q_TILE);
+        const uint32_t do_addr = smem_u32(smem + L::OFF_DO + st * L::Q_TILE);
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k) {
+          const uint32_t offa = (k / 4) * 16384 + (k % 4) * 32;   // 128-row panels
+          const uint32_t offb = (k / 4) * 8192 + (k % 4) * 32;    // 64-row panels
+          umma_f16_ss(tm_st + st * 64, make_smem_desc(k_addr + offa, 16, 1024), make_smem_desc(q_addr + offb, 16, 1024),
+                      idesc_12, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k) {
+          const uint32_t offa = (k / 4) * 16384 + (k % 4) * 32;
+          const uint32_t offb = (k / 4) * 8192 + (k % 4) * 32;
+          umma_f16_ss(tm_dpt + st * 64, make_smem_desc(v_addr + offa, 16, 1024),
+                      make_smem_desc(do_addr + offb, 16, 1024), idesc_12, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[st]);
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_word) && mbar_wait(&qd_full[0], 0, abort_word);
+      if (ok) { tc_fence_after(); issue12(0); }
+      for (int t = 0; t < n_steps && ok; ++t) {
+        const int st = t & 1;
+        if (t + 1 < n_steps) {
+          const int st1 = (t + 1) & 1;
+          const uint32_t ph1 = ((t + 1) >> 1) & 1;
+          ok = mbar_wait(&qd_full[st1], ph1, abort_word) && mbar_wait(&s_empty[st1], ph1 ^ 1, abort_word);
+          if (!ok) break;
+          tc_fence_after();
+          issue12(t + 1);
+        }
+        ok = mbar_wait(p_full, t & 1, abort_word);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(smem + L::OFF_Q + st * L::Q_TILE);
+        const uint32_t do_addr = smem_u32(smem + L::OFF_DO + st * L::Q_TILE);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {   // K = 64 queries
+          // B operands are MN-major: dh contiguous, 16 queries = 2048 B per step, dh panels 8192 B apart
+          umma_f16_ss(tm_dv, make_smem_desc(pt_addr + k * 32, 16, 1024), make_smem_desc(do_addr + k * 2048, 8192, 1024),
+                      idesc_34, (t > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          umma_f16_ss(tm_dk, make_smem_desc(dst_addr + k * 32, 16, 1024), make_smem_desc(q_addr + k * 2048, 8192, 1024),
+                      idesc_34, (t > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(p_empty);
+        umma_commit(&qd_empty[st]);
+      }
+      if (!ok) *abort_word = ERR_WAIT_FULL;
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;      // key row inside the tile
+    const int tid = (warp - 2) * 32 + lane; // 0..127 among the compute threads
+    const int key_idx = k0 + r;
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    const float* lse_g = p.lse + ((size_t)b * p.heads + h) * p.seq;
+    const float* delta_g = p.delta + ((size_t)b * p.heads + h) * p.seq;
+    bool ok = true;
+    for (int t = 0; t < n_steps; ++t) {
+      const int st = t & 1;
+      const uint32_t ph = (t >> 1) & 1;
+      const int qb = (i0 + t) * 64;
+      {  // stage lse (as log2 units) and delta of the 64 queries; +inf lse zeroes padded queries
+        const int qi = qb + (tid & 63);
+        if (tid < 64) lse_s[st * 64 + tid] = (qi < p.seq) ? lse_g[qi] * 1.4426950408889634f : INFINITY;
+        else delta_s[st * 64 + (tid - 64)] = (qi < p.seq) ? delta_g[qi] : 0.f;
+      }
+      named_barrier_sync(1, 128);   // every compute thread reaches this each step, also after a failed wait
+      if (!ok) continue;
+      if (!mbar_wait(&s_full[st], ph, abort_word)) { ok = false; continue; }
+      tc_fence_after();
+      uint32_t sreg[2][32], dreg[2][32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld_32x32(tm_st + lane_addr + st * 64 + c * 32, sreg[c]);
+        tmem_ld_32x32(tm_dpt + lane_addr + st * 64 + c * 32, dreg[c]);
+      }
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_empty[st]);
+      const bool need_mask = (qb < k0 + 128);   // tile touches the diagonal
+      float pv[64], dsv[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float sv = __uint_as_float(sreg[c >> 5][c & 31]);
+        const float dp = __uint_as_float(dreg[c >> 5][c & 31]);
+        const float lse2 = lse_s[st * 64 + c];
+        float pe = exp2f(sv * p.scale_log2 - lse2);
+        const bool dead = (lse2 == INFINITY) || (need_mask && (qb + c < key_idx));
+        pe = dead ? 0.f : pe;
+        pv[c] = pe;
+        dsv[c] = dead ? 0.f : pe * (dp - delta_s[st * 64 + c]) * p.scale;
+      }
+      if (t > 0) {
+        if (!mbar_wait(p_empty, (t - 1) & 1, abort_word)) { ok = false; continue; }
+      }
+      store_row64_swizzled(smem + L::OFF_PT, r, pv);
+      store_row64_swizzled(smem + L::OFF_DST, r, dsv);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok) ok = mbar_wait(p_empty, (n_steps - 1) & 1, abort_word);
+    if (ok) {
+      tc_fence_after();
+      const bool valid = key_idx < p.seq;
+      __nv_bfloat16* dk_row = p.dqkv + (size_t)(row_base + key_idx) * 3 * p.d + col_k;
+      __nv_bfloat16* dv_row = p.dqkv + (size_t)(row_base + key_idx) * 3 * p.d + col_v;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t a[32], g[32];
+        tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
+        tmem_ld_32x32(tm_dv + lane_addr + c * 32, g);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            *reinterpret_cast<uint4*>(dk_row + c * 32 + q * 8) =
+                make_uint4(pack_bf16x2(__uint_as_float(a[q * 8 + 0]), __uint_as_float(a[q * 8 + 1])),
+                           pack_bf16x2(__uint_as_float(a[q * 8 + 2]), __uint_as_float(a[q * 8 + 3])),
+                           pack_bf16x2(__uint_as_float(a[q * 8 + 4]), __uint_as_float(a[q * 8 + 5])),
+                           pack_bf16x2(__uint_as_float(a[q * 8 + 6]), __uint_as_float(a[q * 8 + 7])));
+            *reinterpret_cast<uint4*>(dv_row + c * 32 + q * 8) =
+                make_uint4(pack_bf16x2(__uint_as_float(g[q * 8 + 0]), __uint_as_float(g[q * 8 + 1])),
+                           pack_bf16x2(__uint_as_float(g[q * 8 + 2]), __uint_as_float(g[q * 8 + 3])),
+                           pack_bf16x2(__uint_as_float(g[q * 8 + 4]), __uint_as_float(g[q * 8 + 5])),
+                           pack_bf16x2(__uint_as_float(g[q * 8 + 6]), __uint_as_float(g[q * 8 + 7])));
+          }
+        }
+      }
+    } else if (lane == 0) {
+      *abort_word = ERR_WAIT_TMEM_FULL;
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0u, (*abort_word) | (blockIdx.x << 8));
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ----------------------------------------------------------------------------------- dQ
+template <int DH>
+struct DqSmem {
+  static constexpr int PANELS = DH / 64;
+  static constexpr int Q_TILE = 128 * DH * 2;   // Q_i or dO_i (128 queries)
+  static constexpr int KV_TILE = 64 * DH * 2;   // K_j or V_j (64 keys)
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_DO = OFF_Q + Q_TILE;
+  static constexpr int OFF_K = OFF_DO + Q_TILE;        // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * KV_TILE;    // 2 stages
+  static constexpr int OFF_DS = OFF_V + 2 * KV_TILE;   // 128 x 64 bf16
+  static constexpr int OFF_BAR = OFF_DS + 16384;
+  static constexpr int NUM_BARS = 1 + 2 + 2 + 2 + 2 + 1 + 1;
+  static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(192, 1)
+flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 over qkv
+                const __grid_constant__ CUtensorMap tm_do,   // box 64 x 128 over dO
+                const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 64 over qkv
+                const FlashBwdParams p) {
+  using L = DqSmem<DH>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* qd_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;    // [2]
+  uint64_t* s_empty = bars + 7;   // [2]
+  uint64_t* p_full = bars + 9;
+  uint64_t* p_empty = bars + 10;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
+  volatile uint32_t* abort_word = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qblk = (p.seq + 127) / 128;
+  const int bh = blockIdx.x % (p.batch * p.heads);
+  const int iblk = n_qblk - 1 - blockIdx.x / (p.batch * p.heads);   // latest (heaviest) query tiles first
+  const int b = bh / p.heads, h = bh % p.heads;
+  const int row_base = b * p.seq;
+  const int q0 = iblk * 128;
+  const int n_steps = min((p.seq + 63) / 64, 2 * iblk + 2);   // 64-key steps up to the diagonal
+
+  if (threadIdx.x == 0) {
+    mbar_init(qd_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(p_empty, 1);
+    *abort_word = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_do);
+    prefetch_tensormap(&tm_kv);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tm_s = tmem_base;          // 2 x 64
+  const uint32_t tm_dp = tmem_base + 128;   // 2 x 64
+  const uint32_t tm_dq = tmem_base + 256;   // DH
+
+  const int col_q = h * DH, col_k = p.d + h * DH, col_v = 2 * p.d + h * DH;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(qd_full, 2 * L::Q_TILE);
+#pragma unroll
+      for (int pn = 0; pn < L::PANELS; ++pn) {
+        tma_load_2d(smem + L::OFF_Q + pn * 16384, &tm_q, qd_full, col_q + pn * 64, row_base + q0);
+        tma_load_2d(smem + L::OFF_DO + pn * 16384, &tm_do, qd_full, h * DH + pn * 64, row_base + q0);
+      }
+      for (int t = 0; t < n_steps; ++t) {
+        const int st = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        const int krow = row_base + t * 64;
+        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_word)) { *abort_word = ERR_WAIT_EMPTY; break; }
+        mbar_expect_tx(&kv_full[st], 2 * L::KV_TILE);
+#pragma unroll
+        for (int pn = 0; pn < L::PANELS; ++pn) {
+          tma_load_2d(smem + L::OFF_K + st * L::KV_TILE + pn * 8192, &tm_kv, &kv_full[st], col_k + pn * 64, krow);
+          tma_load_2d(smem + L::OFF_V + st * L::KV_TILE + pn * 8192, &tm_kv, &kv_full[st], col_v + pn * 64, krow);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_12 = make_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_3 = make_idesc_bf16(128, DH, false, true);
+      const uint32_t q_addr = smem_u32(smem + L::OFF_Q), do_addr = smem_u32(smem + L::OFF_DO);
+      const uint32_t ds_addr = smem_u32(smem + L::OFF_DS);
+      auto issue12 = [&](int t) {
+        const int st = t & 1;
+        const uint32_t k_addr = smem_u32(smem + L::OFF_K + st * L::KV_TILE);
+        const uint32_t v_addr = smem_u32(smem + L::OFF_V + st * L::KV_TILE);
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k) {
+          const uint32_t offa = (k / 4) * 16384 + (k % 4) * 32;
+          const uint32_t offb = (k / 4) * 8192 + (k % 4) * 32;
+          umma_f16_ss(tm_s + st * 64, make_smem_desc(q_addr + offa, 16, 1024), make_smem_desc(k_addr + offb, 16, 1024),
+                      idesc_12, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k) {
+          const uint32_t offa = (k / 4) * 16384 + (k % 4) * 32;
+          const uint32_t offb = (k / 4) * 8192 + (k % 4) * 32;
+          umma_f16_ss(tm_dp + st * 64, make_smem_desc(do_addr + offa, 16, 1024),
+                      make_smem_desc(v_addr + offb, 16, 1024), idesc_12, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[st]);
+      };
+      bool ok = mbar_wait(qd_full, 0, abort_word) && mbar_wait(&kv_full[0], 0, abort_word);
+      if (ok) { tc_fence_after(); issue12(0); }
+      for (int t = 0; t < n_steps && ok; ++t) {
+        const int st = t & 1;
+        if (t + 1 < n_steps) {
+          const int st1 = (t + 1) & 1;
+          const uint32_t ph1 = ((t + 1) >> 1) & 1;
+          ok = mbar_wait(&kv_full[st1], ph1, abort_word) && mbar_wait(&s_empty[st1], ph1 ^ 1, abort_word);
+          if (!ok) break;
+          tc_fence_after();
+          issue12(t + 1);
+        }
+        ok = mbar_wait(p_full, t & 1, abort_word);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(smem + L::OFF_K + st * L::KV_TILE);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {   // K = 64 keys; B = K_j MN-major (dh contiguous)
+          umma_f16_ss(tm_dq, make_smem_desc(ds_addr + k * 32, 16, 1024), make_smem_desc(k_addr + k * 2048, 8192, 1024),
+                      idesc_3, (t > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(p_empty);
+        umma_commit(&kv_empty[st]);
+      }
+      if (!ok) *abort_word = ERR_WAIT_FULL;
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int q_idx = q0 + r;
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    const bool valid = q_idx < p.seq;
+    const size_t vec = ((size_t)b * p.heads + h) * p.seq + q_idx;
+    const float lse2 = valid ? p.lse[vec] * 1.4426950408889634f : INFINITY;
+    const float dlt = valid ? p.delta[vec] : 0.f;
+    bool ok = true;
+    for (int t = 0; t < n_steps; ++t) {
+      const int st = t & 1;
+      const uint32_t ph = (t >> 1) & 1;
+      const int kb = t * 64;
+      if (!mbar_wait(&s_full[st], ph, abort_word)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sreg[2][32], dreg[2][32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld_32x32(tm_s + lane_addr + st * 64 + c * 32, sreg[c]);
+        tmem_ld_32x32(tm_dp + lane_addr + st * 64 + c * 32, dreg[c]);
+      }
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_empty[st]);
+      const bool need_mask = (kb + 64 > q0);
+      float dsv[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float sv = __uint_as_float(sreg[c >> 5][c & 31]);
+        const float dp = __uint_as_float(dreg[c >> 5][c & 31]);
+        const float pe = exp2f(sv * p.scale_log2 - lse2);
+        const bool dead = !valid || (need_mask && (kb + c > q_idx));
+        dsv[c] = dead ? 0.f : pe * (dp - dlt) * p.scale;
+      }
+      if (t > 0) {
+        if (!mbar_wait(p_empty, (t - 1) & 1, abort_word)) { ok = false; break; }
+      }
+      store_row64_swizzled(smem + L::OFF_DS, r, dsv);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok) ok = mbar_wait(p_empty, (n_steps - 1) & 1, abort_word);
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* dq_row = p.dqkv + (size_t)(row_base + q_idx) * 3 * p.d + col_q;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t a[32];
+        tmem_ld_32x32(tm_dq + lane_addr + c * 32, a);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(dq_row + c * 32 + q * 8) =
+                make_uint4(pack_bf16x2(__uint_as_float(a[q * 8 + 0]), __uint_as_float(a[q * 8 + 1])),
+                           pack_bf16x2(__uint_as_float(a[q * 8 + 2]), __uint_as_float(a[q * 8 + 3])),
+                           pack_bf16x2(__uint_as_float(a[q * 8 + 4]), __uint_as_float(a[q * 8 + 5])),
+                           pack_bf16x2(__uint_as_float(a[q * 8 + 6]), __uint_as_float(a[q * 8 + 7])));
+        }
+      }
+    } else if (lane == 0) {
+      *abort_word = ERR_WAIT_TMEM_FULL;
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0u, (*abort_word) | (blockIdx.x << 8));
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int DH>
+static int launch_flash_bwd(const void* qkv, const void* dout, const FlashBwdParams& p, cudaStream_t stream) {
+  const uint64_t rows = (uint64_t)p.batch * p.seq;
+  CUtensorMap tm_qkv128, tm_qkv64, tm_do128, tm_do64;
+  if (make_tmap_bf16_2d(&tm_qkv128, qkv, rows, 3ull * p.d, 3ull * p.d, 64, 128)) return -20;
+  if (make_tmap_bf16_2d(&tm_qkv64, qkv, rows, 3ull * p.d, 3ull * p.d, 64, 64)) return -20;
+  if (make_tmap_bf16_2d(&tm_do128, dout, rows, (uint64_t)p.d, (uint64_t)p.d, 64, 128)) return -20;
+  if (make_tmap_bf16_2d(&tm_do64, dout, rows, (uint64_t)p.d, (uint64_t)p.d, 64, 64)) return -20;
+  auto k1 = flash_dkdv_kernel<DH>;
+  auto k2 = flash_dq_kernel<DH>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, DkDvSmem<DH>::TOTAL) != cudaSuccess) return -3;
+    if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<DH>::TOTAL) != cudaSuccess) return -3;
+    configured = true;
+  }
+  const int n_kblk = (p.seq + 127) / 128;
+  k1<<<p.batch * p.heads * n_kblk, 192, DkDvSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_qkv64, tm_do64, p);
+  k2<<<p.batch * p.heads * n_kblk, 192, DqSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_do128, tm_qkv64, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// qkv (rows, 3d), o / dout (rows, d) bf16; lse (batch, heads, seq) from the forward; delta: scratch of the
+// same shape (fp32); dqkv (rows, 3d) bf16 receives dQ | dK | dV.  dh must be 64 or 128.
+extern "C" int b200_flash_bwd(const void* qkv, const void* o, const void* dout, const float* lse, float* delta,
+                              void* dqkv, int batch, int seq, int heads, int dh, float scale, uint32_t* status,
+                              cudaStream_t stream) {
+  if (dh != 64 && dh != 128) return -10;
+  if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(dout) |
+       reinterpret_cast<uintptr_t>(dqkv)) & 15)
+    return -10;
+  if (batch <= 0 || seq <= 0) return 0;
+  const long long warps = (long long)batch * seq * heads;
+  flash_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
+                                                                      delta, batch, seq, heads, dh);
+  FlashBwdParams p;
+  p.lse = lse; p.delta = delta; p.dqkv = (__nv_bfloat16*)dqkv;
+  p.batch = batch; p.seq = seq; p.heads = heads; p.d = heads * dh;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  return dh == 64 ? launch_flash_bwd<64>(qkv, dout, p, stream) : launch_flash_bwd<128>(qkv, dout, p, stream);
+}
