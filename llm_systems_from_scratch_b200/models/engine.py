@@ -128,6 +128,31 @@ def _norm_bwd(dyn, x, w, rstd, dw_out, dres):
     return dx + dres
 
 
+def _seg_view(by_name, flat, name, base):
+    seg = by_name[name]
+    return flat[seg.start - base:seg.start - base + seg.numel].view(seg.shape)
+
+
+def block_views(by_name, names: dict, flat: torch.Tensor, base: int) -> BlockWeights:
+    """Views of one block's tensors inside ``flat``, whose element 0 is arena offset ``base``."""
+    q = by_name[names["q"]]
+    d = q.shape[1]
+    wqkv = flat[q.start - base:q.start - base + 3 * q.numel].view(3 * q.shape[0], d)
+    g = by_name[names["gate"]]
+    if names.get("up") is None:           # merged (2F, d) parameter
+        wgu = flat[g.start - base:g.start - base + g.numel].view(g.shape)
+    else:
+        wgu = flat[g.start - base:g.start - base + 2 * g.numel].view(2 * g.shape[0], d)
+    return BlockWeights(wqkv, _seg_view(by_name, flat, names["o"], base), wgu,
+                        _seg_view(by_name, flat, names["down"], base), _seg_view(by_name, flat, names["n1"], base),
+                        _seg_view(by_name, flat, names["n2"], base))
+
+
+def head_views(by_name, names: dict, flat: torch.Tensor, base: int) -> HeadWeights:
+    return HeadWeights(_seg_view(by_name, flat, names["emb"], base), _seg_view(by_name, flat, names["norm"], base),
+                       _seg_view(by_name, flat, names["lm"], base))
+
+
 class LocalProvider:
     """Weights and gradients taken from a model-local ``ParamArena``."""
 
@@ -141,22 +166,8 @@ class LocalProvider:
         self._cache_key = None
 
     def _views(self, flat):
-        a = self.arena
-        layers = []
-        for names in self.layer_names:
-            q = a.by_name[names["q"]]
-            d = q.shape[1]
-            wqkv = flat[q.start:q.start + 3 * q.numel].view(3 * q.shape[0], d)
-            g = a.by_name[names["gate"]]
-            if names.get("up") is None:           # merged (2F, d) parameter
-                wgu = flat[g.start:g.start + g.numel].view(g.shape)
-            else:
-                wgu = flat[g.start:g.start + 2 * g.numel].view(2 * g.shape[0], d)
-            layers.append(BlockWeights(wqkv, a.view(flat, names["o"]), wgu, a.view(flat, names["down"]),
-                                       a.view(flat, names["n1"]), a.view(flat, names["n2"])))
-        hn = self.head_names
-        head = HeadWeights(a.view(flat, hn["emb"]), a.view(flat, hn["norm"]), a.view(flat, hn["lm"]))
-        return layers, head
+        layers = [block_views(self.arena.by_name, names, flat, 0) for names in self.layer_names]
+        return layers, head_views(self.arena.by_name, self.head_names, flat, 0)
 
     def begin_step(self):
         """Refresh the compute mirror (if stale) and the cached views."""
@@ -189,6 +200,9 @@ class LocalProvider:
     def pre_backward(self, kind: str, i: int):
         pass
 
+    def post_forward(self, kind: str, i: int):
+        pass
+
     def post_backward(self, kind: str, i: int):
         for h in self.post_backward_hooks:
             h(kind, i)
@@ -206,6 +220,7 @@ class _BlockFn(torch.autograd.Function):
         ctx.eng, ctx.i, ctx.batch, ctx.seq = eng, i, batch, seq
         ctx.saved = saved
         ctx.x_in = x if cfg.recompute else None
+        eng.provider.post_forward("block", i)
         return y
 
     @staticmethod

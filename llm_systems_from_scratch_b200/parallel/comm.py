@@ -1,0 +1,127 @@
+"""Collective back ends behind one small interface.
+
+The wrappers in this package (``DDP``, ``FSDP``) talk to a ``Communicator``:
+
+* ``TorchDistComm`` issues ``torch.distributed`` collectives (NCCL on GPUs, gloo on CPU ranks).
+  It is the bring-up path, the baseline the fused kernels are measured against, and what the
+  CPU multi-process tests run on.  gloo has no reduce-scatter, so it is emulated with an
+  all-reduce and a slice.
+* ``PeerComm`` (``parallel.peer``) runs hand-written kernels on NVLink peer memory: a pull
+  all-gather into local staging, a reduce-scatter fused with scale / fp32 accumulation /
+  AdamW, and a two-shot bucket all-reduce with the 1/world scale folded in.
+
+The reference calls ``dist.all_gather`` / ``dist.reduce_scatter`` / ``dist.all_reduce`` /
+``dist.broadcast`` directly at six call sites (llm-systems/llm_systems/parallelism/ddp.py:21-23,58;
+fsdp_zero3.py:94,131-134,213-220).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+class Communicator:
+    rank: int = 0
+    world_size: int = 1
+
+    def all_gather(self, full: torch.Tensor, shard: torch.Tensor):
+        raise NotImplementedError
+
+    def reduce_scatter_mean(self, out_shard: torch.Tensor, full: torch.Tensor):
+        raise NotImplementedError
+
+    def all_reduce_mean(self, flat: torch.Tensor):
+        raise NotImplementedError
+
+    def all_reduce_sum(self, flat: torch.Tensor):
+        raise NotImplementedError
+
+    def broadcast(self, t: torch.Tensor, src: int = 0):
+        raise NotImplementedError
+
+    def barrier(self):
+        pass
+
+
+class SingleProcessComm(Communicator):
+    """World of one: every collective is the identity (copies only where buffers differ)."""
+
+    def all_gather(self, full, shard):
+        if full.data_ptr() != shard.data_ptr():
+            full[:shard.numel()].copy_(shard)
+
+    def reduce_scatter_mean(self, out_shard, full):
+        if out_shard.data_ptr() != full.data_ptr():
+            out_shard.copy_(full[:out_shard.numel()])
+
+    def all_reduce_mean(self, flat):
+        pass
+
+    def all_reduce_sum(self, flat):
+        pass
+
+    def broadcast(self, t, src=0):
+        pass
+
+
+class TorchDistComm(Communicator):
+    def __init__(self, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        self.backend = dist.get_backend(group)
+
+    def all_gather(self, full, shard):
+        n = shard.numel()
+        if self.backend == "gloo":
+            chunks = [full[i * n:(i + 1) * n] for i in range(self.world_size)]
+            dist.all_gather(chunks, shard.contiguous(), group=self.group)
+        else:
+            dist.all_gather_into_tensor(full[:n * self.world_size], shard, group=self.group)
+
+    def reduce_scatter_mean(self, out_shard, full):
+        n = out_shard.numel()
+        ws = self.world_size
+        if self.backend == "gloo":
+            tmp = full[:n * ws].to(torch.float32)
+            dist.all_reduce(tmp, group=self.group)
+            out_shard.copy_(tmp[self.rank * n:(self.rank + 1) * n] / ws)
+        elif out_shard.dtype == full.dtype:
+            dist.reduce_scatter_tensor(out_shard, full[:n * ws], op=dist.ReduceOp.AVG, group=self.group)
+        else:
+            tmp = torch.empty(n, dtype=full.dtype, device=full.device)
+            dist.reduce_scatter_tensor(tmp, full[:n * ws], op=dist.ReduceOp.AVG, group=self.group)
+            out_shard.copy_(tmp)
+
+    def all_reduce_mean(self, flat):
+        if self.backend == "gloo":
+            dist.all_reduce(flat, group=self.group)
+            flat.div_(self.world_size)
+        else:
+            dist.all_reduce(flat, op=dist.ReduceOp.AVG, group=self.group)
+
+    def all_reduce_sum(self, flat):
+        dist.all_reduce(flat, group=self.group)
+
+    def broadcast(self, t, src=0):
+        dist.broadcast(t, src=src, group=self.group)
+
+    def barrier(self):
+        dist.barrier(group=self.group)
+
+
+def make_communicator(group=None, kind: str = "auto") -> Communicator:
+    """``kind``: 'auto' | 'torch' | 'peer'.  'auto' picks peer-memory kernels when every rank of an
+    initialised NCCL group sits on one node with peer access, else torch.distributed."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return SingleProcessComm()
+    if dist.get_world_size(group) == 1 and kind != "peer":
+        return SingleProcessComm()
+    if kind in ("auto", "peer") and dist.get_backend(group) == "nccl":
+        try:
+            from .peer import PeerComm
+            return PeerComm(group)
+        except Exception:
+            if kind == "peer":
+                raise
+    return TorchDistComm(group)

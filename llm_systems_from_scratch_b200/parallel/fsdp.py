@@ -1,0 +1,464 @@
+"""ZeRO-3 fully-sharded data parallelism over the fused engine.
+
+Same contract as the reference wrapper (llm-systems/llm_systems/parallelism/fsdp_zero3.py:239-419):
+``FSDP(module, process_group=None)`` with ``.module``, ``.fsdp_units``, ``parameters()`` yielding
+only the flat shards (so the optimizer state is sharded), ``train/eval/zero_grad``, ``forward`` and
+``finish_gradient_synchronization()``; one unit per transformer block plus one "remaining" unit
+(embedding, final norm, lm_head); shards are padded with zeros to a multiple of the world size and
+rank r owns the r-th slice of its unit.
+
+What is different by design:
+
+* Units are index ranges of the model's flat parameter arena, so sharding, gathering and gradient
+  reduction never concatenate or copy per-parameter tensors.
+* Parameters are communicated in bf16 (fp32 master, m and v stay sharded); gathered weights land
+  in a small pool of persistent buffers that are really reused, instead of a fresh allocation per
+  gather whose storage stays referenced.
+* The block forward/backward is the fused engine; gathers are prefetched one unit ahead on a side
+  stream in both directions; each block's gradient is reduce-scattered as soon as its backward
+  finishes, overlapping the next block's backward.
+* Gradient clipping through ``clip_gradient(model.parameters(), max_norm)`` uses the *global* norm
+  (one all-reduce of a scalar); the reference clips every rank by its local shard norm.
+* With a world size of one, gathered weights alias the shard and gradients are written straight
+  into the shard gradient: no copies, no staging.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from .. import ops
+from ..models.arena import ParamArena, Segment
+from ..models.engine import block_views, head_views
+from .comm import Communicator, make_communicator
+
+
+class _ShardArena(ParamArena):
+    """Arena over the per-unit shards of one rank: lets AdamW / clipping run as single launches."""
+
+    def __init__(self, units, device, compute_dtype, comm: Communicator):  # noqa: super().__init__ not called
+        self.device = device
+        self.comm = comm
+        self.segments, self.by_name, self.params = [], {}, []
+        off = 0
+        for u in units:
+            seg = Segment(u.name, off, u.shard_numel, (u.shard_numel,))
+            self.segments.append(seg)
+            self.by_name[u.name] = seg
+            off += u.shard_numel
+        self.numel = off
+        self.num_tensors = len(units)
+        self.master = torch.zeros(off, dtype=torch.float32, device=device)
+        self.grad = torch.zeros(off, dtype=torch.float32, device=device)
+        self.grads_bound = True
+        self.compute_dtype = compute_dtype
+        self._mirror = None if compute_dtype == torch.float32 else torch.zeros(off, dtype=compute_dtype, device=device)
+        self._mirror_fresh = False
+        self._mirror_versions = -1
+        self._group_ranges = {}
+        self._sumsq = self._coef = self._norm = None
+        self.anchor = torch.zeros(1, dtype=torch.float32, device=device, requires_grad=True)
+
+    def grad_sumsq(self) -> torch.Tensor:
+        s = super().grad_sumsq()
+        self.comm.all_reduce_sum(s)   # global norm: one scalar all-reduce
+        return s
+
+
+class FSDPUnit:
+    """One shard group (a transformer block, or the remaining embedding / norm / head tensors)."""
+
+    def __init__(self, owner: "FSDP", index: int, name: str, start: int, end: int, module: nn.Module):
+        self.owner, self.index, self.name, self.module = owner, index, name, module
+        self.rank, self.world_size = owner.rank, owner.world_size
+        self.process_group = owner.process_group
+        self.training = True
+        self.arena_start, self.arena_end = start, end
+        self.original_numel = end - start
+        ws = self.world_size
+        quantum = ws * 64
+        self.padded_numel = -(-self.original_numel // quantum) * quantum
+        self.shard_numel = self.padded_numel // ws
+        self.flat_shard: nn.Parameter | None = None     # fp32 master shard (bound by the owner)
+        self.mirror_shard: torch.Tensor | None = None   # compute-dtype copy that is gathered
+        self.flat_full: torch.Tensor | None = None      # gathered weights while resident
+        self.gather_event = None
+        self.scatter_event = None
+        self.gather_handle = None
+        self.scatter_handle = None
+        self.flat_grad = None
+        self.slot = None
+
+    # ---- reference-compatible surface --------------------------------------------------
+    def all_gather_params(self, async_op: bool = True):
+        self.owner._gather(self)
+        if not async_op:
+            self.wait_gather()
+
+    def wait_gather(self):
+        self.owner._wait_gather(self)
+
+    def discard_full_params(self):
+        self.owner._release(self)
+
+    def reduce_scatter_grads(self, comm_stream=None, async_op: bool = True):
+        self.owner._reduce_scatter(self)
+        if not async_op:
+            self.wait_scatter()
+
+    def wait_scatter(self):
+        self.owner._wait_scatter(self)
+
+
+class _FSDPProvider:
+    """Feeds the fused engine with gathered weights and gradient staging, driving the collectives."""
+
+    def __init__(self, owner: "FSDP"):
+        self.o = owner
+        self.arena = owner.shard_arena
+
+    def begin_step(self):
+        self.o._begin_step()
+
+    def block_weights(self, i: int, backward: bool = False):
+        o = self.o
+        u = o.layer_units[i]
+        if not backward:
+            o._wait_gather(u)
+            if i + 1 < len(o.layer_units):
+                o._gather(o.layer_units[i + 1])
+        return o._weight_views(u)
+
+    def head_weights(self, backward: bool = False):
+        o = self.o
+        o._wait_gather(o.head_unit)
+        return o._weight_views(o.head_unit)
+
+    def block_grads(self, i: int):
+        return self.o._grad_views(self.o.layer_units[i])
+
+    def head_grads(self):
+        return self.o._grad_views(self.o.head_unit)
+
+    def post_forward(self, kind: str, i: int):
+        o = self.o
+        keep_last = o.training and torch.is_grad_enabled() and i == len(o.layer_units) - 1
+        if not keep_last:   # the last block's weights are needed again first thing in backward
+            o._release(o.layer_units[i])
+
+    def pre_backward(self, kind: str, i: int):
+        o = self.o
+        n = len(o.layer_units)
+        if kind == "head":
+            if n:
+                o._gather(o.layer_units[n - 1])
+        elif kind == "block":
+            o._gather(o.layer_units[i])
+            o._wait_gather(o.layer_units[i])
+            if i > 0:
+                o._gather(o.layer_units[i - 1])
+
+    def post_backward(self, kind: str, i: int):
+        o = self.o
+        if kind == "block":
+            u = o.layer_units[i]
+            o._release(u)
+            o._reduce_scatter(u)
+        elif kind == "embed":
+            o._reduce_scatter(o.head_unit)
+
+
+class FSDP(nn.Module):
+    def __init__(self, module: nn.Module, process_group=None, comm: str | Communicator = "auto"):
+        super().__init__()
+        if not hasattr(module, "engine"):
+            raise TypeError("FSDP wraps a TransformerLM from this package (it drives the fused engine)")
+        self.process_group = process_group
+        self.comm = comm if isinstance(comm, Communicator) else make_communicator(process_group, comm)
+        self.rank, self.world_size = self.comm.rank, self.comm.world_size
+        module.use_custom_triton = True   # always run the fused engine under FSDP
+        eng = module.engine()
+        self.engine_ref = eng
+        full = eng.provider.arena
+        self.device = full.device
+        self.cuda = self.device.type == "cuda"
+        self.compute_dtype = full.compute_dtype
+        self._by_name = full.by_name
+        self._layer_names = eng.provider.layer_names
+        self._head_names = eng.provider.head_names
+        self._full_segments = full.segments
+        self._full_numel = full.numel
+        self.comm.broadcast(full.master, src=0)   # every rank shards the same initial weights
+
+        self.fsdp_units: list[FSDPUnit] = []
+        self.layer_units: list[FSDPUnit] = []
+        for i, layer in enumerate(module.layers):
+            s, e = full.group_range(f"layer{i}")
+            u = FSDPUnit(self, len(self.fsdp_units), f"layer{i}", s, e, layer)
+            self.fsdp_units.append(u)
+            self.layer_units.append(u)
+        s, e = full.group_range("head")
+        self.head_unit = FSDPUnit(self, len(self.fsdp_units), "head", s, e, module)
+        self.fsdp_units.append(self.head_unit)
+        self.unit_modules = [u.module for u in self.fsdp_units]
+
+        self.shard_arena = _ShardArena(self.fsdp_units, self.device, self.compute_dtype, self.comm)
+        sa = self.shard_arena
+        for u, seg in zip(self.fsdp_units, sa.segments):
+            lo = u.arena_start + self.rank * u.shard_numel
+            hi = min(lo + u.shard_numel, u.arena_end)
+            dst = sa.master[seg.start:seg.start + seg.numel]
+            if hi > lo:
+                dst[:hi - lo].copy_(full.master[lo:hi])
+            u.flat_shard = nn.Parameter(dst, requires_grad=True)
+            u.flat_shard.grad = sa.grad[seg.start:seg.start + seg.numel]
+            u.flat_shard._arena = sa
+            u.mirror_shard = (sa._mirror if sa._mirror is not None else sa.master)[seg.start:seg.start + seg.numel]
+            sa.params.append(u.flat_shard)
+        # release the unsharded weights: module parameters become empty placeholders
+        for p in module.parameters():
+            p.requires_grad_(False)
+            p.data = torch.empty(0, device=p.device, dtype=p.dtype)
+            if hasattr(p, "_arena"):
+                del p._arena
+        full.master = None
+        full.grad = None
+        full._mirror = None
+        eng.provider = _FSDPProvider(self)
+        self.module = module
+
+        # ---- persistent communication buffers
+        ws = self.world_size
+        self.n_slots = 2
+        max_p = max((u.padded_numel for u in self.layer_units), default=0)
+        if ws > 1:
+            mk = lambda n: self._comm_buffer(n)
+            self._full_slots = [mk(max_p) for _ in range(self.n_slots)] if max_p else []
+            self._stage_slots = [mk(max_p) for _ in range(self.n_slots)] if max_p else []
+            self._head_full = mk(self.head_unit.padded_numel)
+            self._head_stage = mk(self.head_unit.padded_numel)
+        self._slot_owner = [None] * self.n_slots
+        self._slot_free_ev = [None] * self.n_slots      # compute stream done with the gathered slot
+        self._stage_free_ev = [None] * self.n_slots     # comm stream done reading the staging slot
+        self._views_cache: dict = {}
+        self.comm_stream = torch.cuda.Stream(device=self.device) if self.cuda else None
+        self._step_started = False
+
+    # --------------------------------------------------------------------------- helpers
+    def _comm_buffer(self, numel: int) -> torch.Tensor:
+        alloc = getattr(self.comm, "alloc", None)
+        if alloc is not None:
+            return alloc(numel, self.compute_dtype)
+        return torch.empty(numel, dtype=self.compute_dtype, device=self.device)
+
+    def _on_comm(self):
+        return torch.cuda.stream(self.comm_stream) if self.cuda else _NullCtx()
+
+    def parameters(self, recurse: bool = True):
+        for u in self.fsdp_units:
+            if u.flat_shard is not None:
+                yield u.flat_shard
+
+    def train(self, mode: bool = True):
+        self.training = mode
+        self.module.train(mode)
+        for u in self.fsdp_units:
+            u.training = mode
+        return self
+
+    def eval(self):
+        return self.train(False)
+
+    def zero_grad(self, set_to_none: bool = False):
+        pass   # every shard-gradient slice is overwritten by the next backward's reduce-scatter
+
+    # ------------------------------------------------------------------ gather machinery
+    def _begin_step(self):
+        sa = self.shard_arena
+        if sa._mirror is not None:
+            ver = sa._versions()
+            if not sa._mirror_fresh or ver != sa._mirror_versions:
+                ops.cast_copy(sa._mirror, sa.master)
+                sa._mirror_fresh, sa._mirror_versions = True, ver
+        if self.cuda:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+        # weights changed since the last gather: drop whatever is still resident
+        for u in self.fsdp_units:
+            u.flat_full = None
+            u.gather_event = None
+            u.slot = None
+        self._slot_owner = [None] * self.n_slots
+        self._gather(self.head_unit)
+        if self.layer_units:
+            self._gather(self.layer_units[0])
+
+    def _gather(self, u: FSDPUnit):
+        if u.flat_full is not None:
+            return
+        if self.world_size == 1:
+            u.flat_full = u.mirror_shard
+            return
+        if u is self.head_unit:
+            buf = self._head_full
+            slot = None
+        else:
+            slot = u.index % self.n_slots
+            buf = self._full_slots[slot][:u.padded_numel]
+        with self._on_comm():
+            if slot is not None and self._slot_free_ev[slot] is not None:
+                self.comm_stream.wait_event(self._slot_free_ev[slot])
+            self.comm.all_gather(buf[:u.padded_numel], u.mirror_shard)
+            if self.cuda:
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+                u.gather_event = ev
+        u.flat_full = buf[:u.padded_numel]
+        u.slot = slot
+        if slot is not None:
+            self._slot_owner[slot] = u
+
+    def _wait_gather(self, u: FSDPUnit):
+        if u.flat_full is None:
+            self._gather(u)
+        if u.gather_event is not None:
+            torch.cuda.current_stream().wait_event(u.gather_event)
+            u.gather_event = None
+
+    def _release(self, u: FSDPUnit):
+        if u.flat_full is None or self.world_size == 1:
+            if self.world_size == 1:
+                u.flat_full = None
+            return
+        if u.slot is not None and self.cuda:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self._slot_free_ev[u.slot] = ev
+        u.flat_full = None
+        u.slot = None
+
+    def _weight_views(self, u: FSDPUnit):
+        buf = u.flat_full
+        key = ("w", u.index, buf.data_ptr())
+        v = self._views_cache.get(key)
+        if v is None:
+            if u is self.head_unit:
+                v = head_views(self._by_name, self._head_names, buf, u.arena_start)
+            else:
+                v = block_views(self._by_name, self._layer_names[u.index], buf, u.arena_start)
+            self._views_cache[key] = v
+        return v
+
+    # ---------------------------------------------------------------- gradient machinery
+    def _grad_buffer(self, u: FSDPUnit) -> torch.Tensor:
+        if self.world_size == 1:
+            return u.flat_shard.grad
+        if u is self.head_unit:
+            return self._head_stage
+        slot = u.index % self.n_slots
+        if self._stage_free_ev[slot] is not None:
+            torch.cuda.current_stream().wait_event(self._stage_free_ev[slot])
+            self._stage_free_ev[slot] = None
+        return self._stage_slots[slot][:u.padded_numel]
+
+    def _grad_views(self, u: FSDPUnit):
+        buf = self._grad_buffer(u)
+        key = ("g", u.index, buf.data_ptr())
+        v = self._views_cache.get(key)
+        if v is None:
+            if u is self.head_unit:
+                v = head_views(self._by_name, self._head_names, buf, u.arena_start)
+            else:
+                v = block_views(self._by_name, self._layer_names[u.index], buf, u.arena_start)
+            self._views_cache[key] = v
+        return v
+
+    def _reduce_scatter(self, u: FSDPUnit):
+        if self.world_size == 1:
+            return
+        stage = self._head_stage if u is self.head_unit else self._stage_slots[u.index % self.n_slots]
+        stage = stage[:u.padded_numel]
+        if self.cuda:
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream())
+        with self._on_comm():
+            if self.cuda:
+                self.comm_stream.wait_event(ready)
+            self.comm.reduce_scatter_mean(u.flat_shard.grad, stage)
+            if self.cuda:
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+                u.scatter_event = ev
+                if u is not self.head_unit:
+                    self._stage_free_ev[u.index % self.n_slots] = ev
+
+    def _wait_scatter(self, u: FSDPUnit):
+        if u.scatter_event is not None:
+            torch.cuda.current_stream().wait_event(u.scatter_event)
+            u.scatter_event = None
+
+    # ---------------------------------------------------------------------- entry points
+    def forward(self, token_ids, targets=None):
+        """``forward(token_ids)`` returns logits; ``forward(token_ids, targets)`` returns the fused loss."""
+        eng = self.engine_ref
+        out = eng.logits(token_ids) if targets is None else eng.loss(token_ids, targets)
+        if not (self.training and torch.is_grad_enabled()):
+            for u in self.fsdp_units:
+                self._release(u)
+        return out
+
+    def loss(self, token_ids, targets):
+        return self.forward(token_ids, targets)
+
+    def finish_gradient_synchronization(self):
+        """After ``loss.backward()``: all shard gradients are complete once this returns (stream-ordered)."""
+        if self.cuda and self.world_size > 1:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        for u in self.fsdp_units:
+            u.scatter_event = None
+            self._release(u)
+
+    # ------------------------------------------------------------------------ checkpoint
+    @torch.no_grad()
+    def full_state_dict(self, dtype=torch.float32) -> dict:
+        """Gather the fp32 master weights of every unit and return a complete (unsharded) state dict
+        with the module's own key names.  Collective: call on every rank."""
+        flat = torch.zeros(self._full_numel, dtype=torch.float32, device=self.device)
+        for u in self.fsdp_units:
+            if self.world_size == 1:
+                flat[u.arena_start:u.arena_end].copy_(u.flat_shard.data[:u.original_numel])
+                continue
+            tmp = torch.empty(u.padded_numel, dtype=torch.float32, device=self.device)
+            self.comm.all_gather(tmp, u.flat_shard.data)
+            flat[u.arena_start:u.arena_end].copy_(tmp[:u.original_numel])
+        out = {}
+        order = {s.name: s for s in self._full_segments}
+        for name, _ in self.module.named_parameters():
+            seg = order[name]
+            out[name] = flat[seg.start:seg.start + seg.numel].view(seg.shape).to(dtype).cpu()
+        return out
+
+    @torch.no_grad()
+    def load_full_state_dict(self, state: dict):
+        """Inverse of ``full_state_dict``: every rank copies its own slices out of a full state dict."""
+        flat = torch.zeros(self._full_numel, dtype=torch.float32, device=self.device)
+        order = {s.name: s for s in self._full_segments}
+        sd = dict(state)
+        self.module._convert_ffn_keys(sd, "")
+        for name, seg in order.items():
+            flat[seg.start:seg.start + seg.numel].copy_(sd[name].reshape(-1).to(self.device, torch.float32))
+        for u in self.fsdp_units:
+            lo = u.arena_start + self.rank * u.shard_numel
+            hi = min(lo + u.shard_numel, u.arena_end)
+            u.flat_shard.data.zero_()
+            if hi > lo:
+                u.flat_shard.data[:hi - lo].copy_(flat[lo:hi])
+        self.shard_arena._mirror_fresh = False
+
+
+class _NullCtx:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

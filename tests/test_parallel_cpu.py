@@ -1,0 +1,132 @@
+"""DDP and FSDP wrappers on 2-3 CPU ranks (gloo) against single-process training on the full batch."""
+import os
+import socket
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+CFG = dict(vocab_size=157, context_length=16, d_model=64, num_layers=3, num_heads=4, d_ff=136, rope_theta=10000.0)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _batch(world, per_rank=2, seq=16, seed=5):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randint(0, CFG["vocab_size"], (world * per_rank, seq), generator=g)
+    y = torch.randint(0, CFG["vocab_size"], (world * per_rank, seq), generator=g)
+    return x, y
+
+
+def _single_process_reference(world, steps, native, clip):
+    from llm_systems_from_scratch_b200.models.transformer import TransformerLM
+    from llm_systems_from_scratch_b200.ops import functional as Fn
+    from llm_systems_from_scratch_b200.optim import FusedAdamW
+    torch.manual_seed(0)
+    model = TransformerLM(**CFG, use_custom_triton=native)
+    opt = FusedAdamW(model.parameters(), lr=1e-2, weight_decay=0.1)
+    for s in range(steps):
+        x, y = _batch(world, seed=5 + s)
+        model.zero_grad()
+        model.loss(x, y).backward()
+        if clip:
+            Fn.clip_gradient(model.parameters(), clip)
+        opt.step()
+    return {k: v.clone() for k, v in model.state_dict().items()}
+
+
+def _worker(rank, world, port, mode, native, steps, clip, out_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from llm_systems_from_scratch_b200.models.transformer import TransformerLM
+        from llm_systems_from_scratch_b200.ops import functional as Fn
+        from llm_systems_from_scratch_b200.optim import FusedAdamW
+        from llm_systems_from_scratch_b200.parallel import DDP, FSDP
+        torch.manual_seed(rank)            # different init per rank: the wrapper must broadcast rank 0's
+        model = TransformerLM(**CFG, use_custom_triton=native)
+        if rank == 0:
+            torch.manual_seed(0)
+            model = TransformerLM(**CFG, use_custom_triton=native)
+        wrapped = DDP(model, bucket_size_mb=0.05) if mode == "ddp" else FSDP(model)
+        opt = FusedAdamW(wrapped.parameters(), lr=1e-2, weight_decay=0.1)
+        per = 2
+        for s in range(steps):
+            x, y = _batch(world, seed=5 + s)
+            xs, ys = x[rank * per:(rank + 1) * per], y[rank * per:(rank + 1) * per]
+            wrapped.zero_grad()
+            wrapped.loss(xs, ys).backward()
+            wrapped.finish_gradient_synchronization()
+            if clip:
+                Fn.clip_gradient(wrapped.parameters(), clip)
+            opt.step()
+        sd = wrapped.full_state_dict() if mode == "fsdp" else model.state_dict()
+        if rank == 0:
+            torch.save({k: v.clone() for k, v in sd.items()}, out_path)
+        if mode == "ddp":
+            n_buckets = len(wrapped._buckets)
+            assert n_buckets >= 2, n_buckets
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(mode, native, world, steps=3, clip=0.0):
+    port = _free_port()
+    with tempfile.TemporaryDirectory() as d:
+        out = os.path.join(d, "sd.pt")
+        mp.spawn(_worker, args=(world, port, mode, native, steps, clip, out), nprocs=world, join=True)
+        got = torch.load(out)
+    ref = _single_process_reference(world, steps, native, clip)
+    assert set(got) == set(ref)
+    for k in ref:
+        assert torch.allclose(got[k], ref[k], atol=3e-4, rtol=1e-4), (k, (got[k] - ref[k]).abs().max().item())
+
+
+def test_ddp_arena_mode_matches_single_process():
+    _run("ddp", native=True, world=2)
+
+
+def test_ddp_generic_mode_matches_single_process():
+    _run("ddp", native=False, world=2)
+
+
+def test_fsdp_matches_single_process():
+    _run("fsdp", native=True, world=2)
+
+
+def test_fsdp_three_ranks_with_global_clipping():
+    _run("fsdp", native=True, world=3, steps=2, clip=0.25)
+
+
+def test_fsdp_world_size_one_aliases_shards():
+    from llm_systems_from_scratch_b200.models.transformer import TransformerLM
+    from llm_systems_from_scratch_b200.optim import FusedAdamW
+    from llm_systems_from_scratch_b200.parallel import FSDP
+    torch.manual_seed(0)
+    model = TransformerLM(**CFG, use_custom_triton=True)
+    ref = _single_process_reference(1, 2, True, 0.0)
+    f = FSDP(model)
+    assert len(f.fsdp_units) == CFG["num_layers"] + 1
+    assert len(list(f.parameters())) == CFG["num_layers"] + 1
+    assert all(p.numel() == 0 for p in model.parameters())       # unsharded weights are really released
+    opt = FusedAdamW(f.parameters(), lr=1e-2, weight_decay=0.1)
+    for s in range(2):
+        x, y = _batch(1, seed=5 + s)
+        f.zero_grad()
+        f.loss(x, y).backward()
+        f.finish_gradient_synchronization()
+        opt.step()
+    got = f.full_state_dict()
+    for k in ref:
+        assert torch.allclose(got[k], ref[k], atol=3e-4, rtol=1e-4), k
+    logits = f(x)
+    assert logits.shape == (2, 16, CFG["vocab_size"])
