@@ -130,9 +130,26 @@ def check_status(device=None):
         raise KernelError(f"kernel reported error code {v & 0xff} from CTA {v >> 8}")
 
 
+# Kernels launched per launcher call (a launcher may issue several).  Used to count this package's
+# own launches inside a timed region.
+_KERNELS_PER_CALL = {"rmsnorm_bwd": 2, "xent": 3, "flash_bwd": 3}
+_LAUNCHES = 0
+
+
+def reset_launch_count():
+    global _LAUNCHES
+    _LAUNCHES = 0
+
+
+def launch_count() -> int:
+    return _LAUNCHES
+
+
 def _check(rc: int, name: str):
+    global _LAUNCHES
     if rc != 0:
         raise KernelError(f"{name} failed with code {rc}")
+    _LAUNCHES += _KERNELS_PER_CALL.get(name, 1)
 
 
 def _req(cond: bool, msg: str):
