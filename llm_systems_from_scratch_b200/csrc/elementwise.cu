@@ -342,11 +342,8 @@ xent_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ ta
     }
     store8(lr + g * 8, f);
   }
-  for (int c = nvec * 8 + threadIdx.x; c < ld; c += XENT_THREADS) {
-    float f = 0.f;
-    if (c < vocab) f = (__expf(__bfloat162float(lr[c]) - lse) - ((c == tgt) ? 1.f : 0.f)) * k;
-    lr[c] = __float2bfloat16(f);
-  }
+  for (int c = nvec * 8 + threadIdx.x; c < vocab; c += XENT_THREADS)   // columns past `vocab` are never touched
+    lr[c] = __float2bfloat16((__expf(__bfloat162float(lr[c]) - lse) - ((c == tgt) ? 1.f : 0.f)) * k);
 }
 
 // loss (=|+=) sum(row_loss) in a fixed order (single block).

@@ -1,0 +1,69 @@
+"""train.py / generate.py end to end on CPU with a tiny model (single process, resume, generation)."""
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import yaml
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DATA = os.path.join(os.path.dirname(__file__), "data")
+
+
+def _config(tmp_path, max_steps=6):
+    rng = np.random.default_rng(0)
+    for name in ("train", "val"):
+        rng.integers(0, 300, size=4096, dtype=np.uint32).tofile(tmp_path / f"{name}.bin")
+    cfg = {
+        "model": dict(vocab_size=300, context_length=32, d_model=64, num_layers=2, num_heads=4, d_ff=136, rope_theta=10000.0),
+        "training": dict(device="cpu", batch_size=4, max_steps=max_steps, val_interval=3, gpu_log_interval=100,
+                         checkpoint_dir=str(tmp_path / "ckpt"), wandb=False, wandb_project="x", seed=0,
+                         metrics_file=str(tmp_path / "metrics.jsonl")),
+        "optimizer": dict(learning_rate_max="1.0e-2", learning_rate_min="1.0e-3", weight_decay=0.1, max_grad_norm=1.0,
+                          warmup_steps=2, decay_steps=6),
+        "dataset": dict(train_path=str(tmp_path / "train.bin"), val_path=str(tmp_path / "val.bin")),
+    }
+    path = tmp_path / "cfg.yaml"
+    path.write_text(yaml.safe_dump(cfg))
+    return str(path)
+
+
+@pytest.mark.parametrize("native", [False, True])
+def test_train_resume_generate(tmp_path, native, capsys):
+    sys.path.insert(0, ROOT)
+    import generate
+    import train
+    cfg = _config(tmp_path)
+    train.train_worker(0, 1, [], cfg, False, False, False, native)
+    out = capsys.readouterr().out
+    assert "[Rank 0] Step 5: loss = " in out and "tok/s = " in out and "[Validation] Step 3" in out
+    ck = tmp_path / "ckpt"
+    assert (ck / "ckpt_3.pt").exists() and (ck / "ckpt_final.pt").exists() and (ck / "model_config.json").exists()
+    final = torch.load(ck / "ckpt_final.pt")
+    assert final["iteration"] == 6 and "optimizer" in final
+    assert json.load(open(ck / "model_config.json"))["use_custom_triton"] is native
+    lines = [json.loads(l) for l in open(tmp_path / "metrics.jsonl")]
+    assert sum("train/loss" in r for r in lines) == 6
+    # resume from the step-3 checkpoint: continues at step 3 and ends with the same iteration count
+    train.train_worker(0, 1, [], cfg, False, False, False, native, resume=str(ck / "ckpt_3.pt"))
+    out = capsys.readouterr().out
+    assert "resumed from" in out and "Step 3:" in out and "Step 2:" not in out
+    # generation from the final checkpoint with the golden tokenizer files
+    generate.main(["--config", str(ck / "model_config.json"), "--checkpoint", str(ck / "ckpt_final.pt"),
+                   "--vocab", os.path.join(DATA, "vocab.json"), "--merges", os.path.join(DATA, "merges.json"),
+                   "--max-tokens", "5", "--temperature", "0", "--device", "cpu", "--prompt", "the "])
+    assert isinstance(capsys.readouterr().out, str)
+
+
+def test_config_validation_rejects_indivisible_batch(tmp_path):
+    from llm_systems_from_scratch_b200.utils.config import load_config, validate
+    cfg = load_config(_config(tmp_path))
+    with pytest.raises(ValueError):
+        validate(cfg, world_size=3)
+    del cfg["optimizer"]["warmup_steps"]
+    with pytest.raises(KeyError):
+        validate(cfg)
+    for name in ("sample", "cpu_tiny", "ddp_124m", "fsdp_1p3b", "fsdp_7b", "serve_1p3b"):
+        validate(load_config(os.path.join(ROOT, "configures", f"{name}.yaml")), world_size=8)
