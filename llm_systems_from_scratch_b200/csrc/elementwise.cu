@@ -644,3 +644,48 @@ extern "C" int b200_cast_bf16_f32(const void* src, float* dst, long long n, cuda
   cast_bf16_to_f32_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, st>>>((const __nv_bfloat16*)src, dst, n);
   CHECK_LAUNCH();
 }
+
+// ------------------------------------------------------------------ allocation-free RMSNorm backward
+#include "no_alloc.h"
+
+namespace b200 {
+// Weight-gradient partials for b200_rmsnorm_bwd_noalloc.  In host code this name is only a stand-in:
+// the device address is obtained with cudaGetSymbolAddress below and passed to the kernels.
+static __device__ __align__(256) float g_noalloc_dw_partials[B200_NOALLOC_MAX_PARTS * B200_NOALLOC_MAX_D];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+// Resolve (once per device, with that device current) where the scratch array lives on this GPU.
+static float* noalloc_scratch_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return nullptr;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress((void**)&ptr, g_noalloc_dw_partials) != cudaSuccess) return nullptr;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  return g_noalloc_ptr[dev];
+}
+}  // namespace b200
+
+extern "C" int b200_rmsnorm_bwd_noalloc_max_d(void) { return B200_NOALLOC_MAX_D; }
+
+extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                        const void* dres, void* dx, float* dw, int rows, int d, int accumulate_dw,
+                                        cudaStream_t st) {
+  if (d > B200_NOALLOC_MAX_D) return B200_ERR_NOALLOC_TOO_LARGE;
+  if (d <= 0 || d % 8 || rows < 0) return -10;
+  if (!ALIGNED16(dy) || !ALIGNED16(x) || !ALIGNED16(w) || !ALIGNED16(dx) || !ALIGNED16(dres)) return -10;
+  if (rows == 0) return 0;
+  float* scratch = noalloc_scratch_for_current_device();
+  if (scratch == nullptr) return B200_ERR_NOALLOC_SETUP;
+  const int parts = rows < B200_NOALLOC_MAX_PARTS ? rows : B200_NOALLOC_MAX_PARTS;
+  // Every partial row [0, parts) x [0, d) is written by the first kernel before the second reads it,
+  // so nothing in the shared array has to be cleared between calls.
+  rmsnorm_bwd_kernel<<<parts, RMS_BWD_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                        (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
+                                                        (__nv_bfloat16*)dx, scratch, rows, d);
+  rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, st>>>(scratch, dw, parts, d, accumulate_dw);
+  CHECK_LAUNCH();
+}
