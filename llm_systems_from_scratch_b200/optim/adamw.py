@@ -116,6 +116,11 @@ class FusedAdamW(torch.optim.Optimizer):
             lr, (b1, b2), eps, wd = group["lr"], group["betas"], group["eps"], group["weight_decay"]
             arena = self._arena_of(group)
             if arena is not None and arena.grad is not None:
+                if getattr(self, "external_update", False):
+                    # the update already ran inside the fused reduce-scatter kernels of this step
+                    self.flat_state(gi, group, arena)["t"] += 1
+                    arena.mark_mirror(True)
+                    continue
                 st = self._flat.get(gi)
                 if st is None or st["m"].numel() != arena.numel or st["m"].device != arena.master.device:
                     prev_t = st["t"] if st else 1
@@ -145,6 +150,15 @@ class FusedAdamW(torch.optim.Optimizer):
                     p.data.copy_(tmp)
                 st["t"] += 1
         return loss
+
+    def flat_state(self, gi, group, arena):
+        """Flat {"t","m","v"} state of group ``gi`` over ``arena`` (created on first use)."""
+        st = self._flat.get(gi)
+        if st is None or st["m"].numel() != arena.numel:
+            st = {"t": 1, "m": torch.zeros_like(arena.master), "v": torch.zeros_like(arena.master)}
+            self._adopt_param_state(group, arena, st)
+            self._flat[gi] = st
+        return st
 
     # ------------------------------------------------------------- state-dict interchange
     def _adopt_param_state(self, group, arena, flat):

@@ -27,8 +27,14 @@ class Communicator:
     def all_gather(self, full: torch.Tensor, shard: torch.Tensor):
         raise NotImplementedError
 
-    def reduce_scatter_mean(self, out_shard: torch.Tensor, full: torch.Tensor):
+    def reduce_scatter_mean(self, out_shard: torch.Tensor, full: torch.Tensor, key=None, sumsq=None):
         raise NotImplementedError
+
+    def pre_gather_sync(self):
+        """Stream-ordered point after which every rank's weight shards are safe to read."""
+
+    def wait_readers(self, staging: torch.Tensor, key=None):
+        """Stream-ordered point after which ``staging`` may be overwritten."""
 
     def all_reduce_mean(self, flat: torch.Tensor):
         raise NotImplementedError
@@ -50,7 +56,7 @@ class SingleProcessComm(Communicator):
         if full.data_ptr() != shard.data_ptr():
             full[:shard.numel()].copy_(shard)
 
-    def reduce_scatter_mean(self, out_shard, full):
+    def reduce_scatter_mean(self, out_shard, full, key=None, sumsq=None):
         if out_shard.data_ptr() != full.data_ptr():
             out_shard.copy_(full[:out_shard.numel()])
 
@@ -79,7 +85,7 @@ class TorchDistComm(Communicator):
         else:
             dist.all_gather_into_tensor(full[:n * self.world_size], shard, group=self.group)
 
-    def reduce_scatter_mean(self, out_shard, full):
+    def reduce_scatter_mean(self, out_shard, full, key=None, sumsq=None):
         n = out_shard.numel()
         ws = self.world_size
         if self.backend == "gloo":

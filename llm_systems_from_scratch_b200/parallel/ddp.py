@@ -79,6 +79,8 @@ class DDP(nn.Module):
         arena = eng.provider.arena
         self.comm.broadcast(arena.master, src=0)
         arena.mark_mirror(False)
+        if hasattr(self.comm, "alloc") and arena.grad is None:
+            arena.grad = self.comm.alloc(arena.numel, torch.float32)   # peers reduce it in place over NVLink
         arena.bind_grads()
         n_layers = len(self.module.layers)
         by = arena.by_name

@@ -53,7 +53,12 @@ class _ShardArena(ParamArena):
         self.grad = torch.zeros(off, dtype=torch.float32, device=device)
         self.grads_bound = True
         self.compute_dtype = compute_dtype
-        self._mirror = None if compute_dtype == torch.float32 else torch.zeros(off, dtype=compute_dtype, device=device)
+        if compute_dtype == torch.float32:
+            self._mirror = None
+        elif hasattr(comm, "alloc"):
+            self._mirror = comm.alloc(off, compute_dtype)   # peers pull weight shards straight out of this buffer
+        else:
+            self._mirror = torch.zeros(off, dtype=compute_dtype, device=device)
         self._mirror_fresh = False
         self._mirror_versions = -1
         self._group_ranges = {}
@@ -233,15 +238,18 @@ class FSDP(nn.Module):
         self.n_slots = 2
         max_p = max((u.padded_numel for u in self.layer_units), default=0)
         if ws > 1:
-            mk = lambda n: self._comm_buffer(n)
-            self._full_slots = [mk(max_p) for _ in range(self.n_slots)] if max_p else []
+            mk = lambda n: self._comm_buffer(n)                  # readable by peers
+            loc = lambda n: torch.empty(n, dtype=self.compute_dtype, device=self.device)
+            self._full_slots = [loc(max_p) for _ in range(self.n_slots)] if max_p else []
             self._stage_slots = [mk(max_p) for _ in range(self.n_slots)] if max_p else []
-            self._head_full = mk(self.head_unit.padded_numel)
+            self._head_full = loc(self.head_unit.padded_numel)
             self._head_stage = mk(self.head_unit.padded_numel)
         self._slot_owner = [None] * self.n_slots
         self._slot_free_ev = [None] * self.n_slots      # compute stream done with the gathered slot
         self._stage_free_ev = [None] * self.n_slots     # comm stream done reading the staging slot
         self._views_cache: dict = {}
+        self._head_stage_checked = False
+        self._fused_opt = None
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.cuda else None
         self._step_started = False
 
@@ -283,6 +291,9 @@ class FSDP(nn.Module):
                 sa._mirror_fresh, sa._mirror_versions = True, ver
         if self.cuda:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
+        if self.world_size > 1:
+            with self._on_comm():
+                self.comm.pre_gather_sync()   # every rank's optimizer has finished rewriting its weight shard
         # weights changed since the last gather: drop whatever is still resident
         for u in self.fsdp_units:
             u.flat_full = None
@@ -354,11 +365,15 @@ class FSDP(nn.Module):
         if self.world_size == 1:
             return u.flat_shard.grad
         if u is self.head_unit:
+            if not self._head_stage_checked:
+                self.comm.wait_readers(self._head_stage, "stage_head")
+                self._head_stage_checked = True
             return self._head_stage
         slot = u.index % self.n_slots
         if self._stage_free_ev[slot] is not None:
             torch.cuda.current_stream().wait_event(self._stage_free_ev[slot])
             self._stage_free_ev[slot] = None
+            self.comm.wait_readers(self._stage_slots[slot], f"stage{slot}")   # peers are done reading it too
         return self._stage_slots[slot][:u.padded_numel]
 
     def _grad_views(self, u: FSDPUnit):
@@ -384,13 +399,60 @@ class FSDP(nn.Module):
         with self._on_comm():
             if self.cuda:
                 self.comm_stream.wait_event(ready)
-            self.comm.reduce_scatter_mean(u.flat_shard.grad, stage)
+            key = "stage_head" if u is self.head_unit else f"stage{u.index % self.n_slots}"
+            if self._fused_opt is not None and hasattr(self.comm, "reduce_scatter_adamw"):
+                self._fused_reduce_scatter(u, stage, key)
+            else:
+                self.comm.reduce_scatter_mean(u.flat_shard.grad, stage, key=key)
+            if u is self.head_unit:
+                self._head_stage_checked = False
             if self.cuda:
                 ev = torch.cuda.Event()
                 ev.record(self.comm_stream)
                 u.scatter_event = ev
                 if u is not self.head_unit:
                     self._stage_free_ev[u.index % self.n_slots] = ev
+
+    # ------------------------------------------------------- fused reduce-scatter + AdamW
+    def attach_optimizer(self, optimizer, max_grad_norm: float | None = None):
+        """Run AdamW inside each unit's reduce-scatter kernel (needs the peer-memory communicator).
+
+        The update of a unit then overlaps the backward of the next one and the reduced gradient never
+        goes through HBM.  Because a unit is updated before the step's global gradient norm is known,
+        clipping uses the coefficient computed from the *previous* step's norm (the first step is
+        unclipped); ``optimizer.step()`` afterwards only advances the step counter.
+        """
+        if self.world_size == 1 or not hasattr(self.comm, "reduce_scatter_adamw"):
+            return False
+        sa = self.shard_arena
+        self._fused_opt = optimizer
+        optimizer.external_update = True
+        self._max_grad_norm = max_grad_norm
+        self._norm_sq = torch.zeros((), dtype=torch.float32, device=self.device)
+        self._prev_coef = torch.ones((), dtype=torch.float32, device=self.device)
+        optimizer.flat_state(0, optimizer.param_groups[0], sa)
+        return True
+
+    def _fused_reduce_scatter(self, u: FSDPUnit, stage, key):
+        opt, sa = self._fused_opt, self.shard_arena
+        g = opt.param_groups[0]
+        st = opt.flat_state(0, g, sa)
+        seg = sa.by_name[u.name]
+        sl = slice(seg.start, seg.start + seg.numel)
+        self.comm.reduce_scatter_adamw(
+            stage, key, sa.master[sl], st["m"][sl], st["v"][sl], None if sa._mirror is None else sa._mirror[sl],
+            g["lr"], g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"], st["t"],
+            grad_scale=self._prev_coef if self._max_grad_norm else None, sumsq=self._norm_sq)
+
+    def finish_fused_step(self):
+        """After ``finish_gradient_synchronization`` in fused mode: turn this step's gradient norm into
+        the clip coefficient used by the next step.  Returns the (device) gradient norm."""
+        self.comm.all_reduce_sum(self._norm_sq)
+        norm = self._norm_sq.sqrt()
+        if self._max_grad_norm:
+            ops.clip_coef(self._norm_sq, self._max_grad_norm, self._prev_coef)
+        self._norm_sq = torch.zeros_like(self._norm_sq)
+        return norm
 
     def _wait_scatter(self, u: FSDPUnit):
         if u.scatter_event is not None:

@@ -1,0 +1,232 @@
+"""Peer-memory communicator: hand-written collectives over NVLink / NVSwitch.
+
+Every rank allocates its communication buffers with plain ``cudaMalloc`` (outside PyTorch's caching
+allocator), exports them through CUDA IPC, and maps every peer's copy.  torch.distributed is used
+only as plumbing (exchanging the 64-byte handles, a few scalar reductions).  The collectives
+themselves are kernels of this package (``csrc/comm_kernels.cu``) that load from / store to peer
+addresses and synchronise through epoch-numbered flags with bounded waits.
+
+Buffers handed to the collectives must come from ``alloc``; calls on other tensors fall back to
+``TorchDistComm`` so the communicator is always usable as a drop-in.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+from .comm import Communicator, TorchDistComm
+
+_ULL = ctypes.c_ulonglong
+
+
+class _CudaArray:
+    """Minimal ``__cuda_array_interface__`` holder so torch can alias raw device memory."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+def _declare(lib):
+    P, I, L, F = ctypes.c_void_p, ctypes.c_int, _ULL, ctypes.c_float
+    U = ctypes.c_uint
+    lib.b200_ipc_alloc.argtypes = [L, ctypes.POINTER(_ULL)]
+    lib.b200_ipc_free.argtypes = [L]
+    lib.b200_ipc_get_handle.argtypes = [L, ctypes.c_char_p]
+    lib.b200_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(_ULL)]
+    lib.b200_ipc_close.argtypes = [L]
+    lib.b200_peer_barrier.argtypes = [P, L, I, I, U, L, P, P]
+    lib.b200_peer_allgather.argtypes = [P, P, L, I, I, I, P]
+    lib.b200_peer_reduce_scatter.argtypes = [P, P, L, L, P, P, L, I, I, U, I, P, P, P, P, P, F, F, F, F, F, F, L, P, P,
+                                             I, P]
+    lib.b200_peer_wait.argtypes = [P, I, U, L, P, P]
+    lib.b200_peer_allreduce.argtypes = [P, P, L, L, L, I, I, U, L, P, P, I, P]
+    for n in ("b200_ipc_alloc", "b200_ipc_free", "b200_ipc_get_handle", "b200_ipc_open", "b200_ipc_close",
+              "b200_peer_barrier", "b200_peer_allgather", "b200_peer_reduce_scatter", "b200_peer_wait",
+              "b200_peer_allreduce"):
+        getattr(lib, n).restype = I
+
+
+class PeerComm(Communicator):
+    FLAG_ROWS = 64          # rows of `world` uint32 flags
+    ROW_BARRIER = 0
+    WAIT_LIMIT_NS = 5_000_000_000   # a peer that is 5 s late is reported, never waited for indefinitely
+
+    def __init__(self, group=None, wait_limit_s: float | None = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("PeerComm needs CUDA")
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        if self.world_size > 16:
+            raise RuntimeError("PeerComm supports up to 16 ranks on one node")
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.lib = native.load()
+        _declare(self.lib)
+        self.fallback = TorchDistComm(group)
+        self.limit_ns = int((wait_limit_s * 1e9) if wait_limit_s else self.WAIT_LIMIT_NS)
+        self._allocs: list[dict] = []      # {"base", "nbytes", "peers": [ptr per rank]}
+        self._epochs: dict[int, int] = {}
+        self._next_row = 1
+        self._rows: dict[str, tuple[int, int]] = {}
+        flags = self.alloc(self.FLAG_ROWS * self.world_size, torch.int32)
+        self.flags = flags
+        self._flag_bases = self._table(self._find(flags)["peers"])
+        self._counter = torch.zeros(64, dtype=torch.int32, device=self.device)
+        self._counter_used = 0
+        self.barrier()
+
+    # ------------------------------------------------------------------ memory
+    def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """Collective: a zero-initialised buffer that every peer can address.  All ranks must call
+        ``alloc`` in the same order with the same sizes."""
+        nbytes = -(-numel * torch.empty((), dtype=dtype).element_size() // 256) * 256
+        out = _ULL(0)
+        rc = self.lib.b200_ipc_alloc(nbytes, ctypes.byref(out))
+        if rc != 0:
+            raise RuntimeError(f"peer buffer allocation of {nbytes} bytes failed ({rc})")
+        base = out.value
+        handle = ctypes.create_string_buffer(64)
+        if self.lib.b200_ipc_get_handle(base, handle) != 0:
+            raise RuntimeError("cudaIpcGetMemHandle failed")
+        gathered = [None] * self.world_size
+        dist.all_gather_object(gathered, bytes(handle.raw), group=self.group)
+        peers = []
+        for r, h in enumerate(gathered):
+            if r == self.rank:
+                peers.append(base)
+                continue
+            p = _ULL(0)
+            rc = self.lib.b200_ipc_open(h, ctypes.byref(p))
+            if rc != 0:
+                raise RuntimeError(f"cudaIpcOpenMemHandle for rank {r} failed ({rc})")
+            peers.append(p.value)
+        self._allocs.append({"base": base, "nbytes": nbytes, "peers": peers})
+        raw = torch.as_tensor(_CudaArray(base, nbytes), device=self.device)
+        return raw.view(dtype)[:numel]
+
+    def _find(self, t: torch.Tensor):
+        p = t.data_ptr()
+        for a in self._allocs:
+            if a["base"] <= p < a["base"] + a["nbytes"]:
+                return a
+        return None
+
+    def _table(self, ptrs: list[int]):
+        return (_ULL * self.world_size)(*ptrs)
+
+    def _peer_table(self, t: torch.Tensor):
+        a = self._find(t)
+        if a is None:
+            return None
+        off = t.data_ptr() - a["base"]
+        return self._table([p + off for p in a["peers"]])
+
+    def _rows_for(self, key: str) -> tuple[int, int]:
+        """Two flag rows (ready, done) reserved for one logical buffer."""
+        if key not in self._rows:
+            if self._next_row + 2 > self.FLAG_ROWS:
+                raise RuntimeError("out of flag rows")
+            self._rows[key] = (self._next_row, self._next_row + 1)
+            self._next_row += 2
+        return self._rows[key]
+
+    def _bump(self, row: int) -> int:
+        e = self._epochs.get(row, 0) + 1
+        self._epochs[row] = e
+        return e
+
+    def _counter_slot(self):
+        i = self._counter_used % 64
+        self._counter_used += 1
+        return self._counter[i:i + 1]
+
+    def _status(self):
+        return native.status_word(self.device).data_ptr()
+
+    @staticmethod
+    def _stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    # ------------------------------------------------------------- collectives
+    def barrier(self):
+        """Device-side barrier on the current stream (flag exchange between all ranks)."""
+        e = self._bump(self.ROW_BARRIER)
+        native._check(self.lib.b200_peer_barrier(self._flag_bases, self.ROW_BARRIER * self.world_size, self.world_size,
+                                                 self.rank, e, self.limit_ns, self._status(), self._stream()),
+                      "peer_barrier")
+
+    def pre_gather_sync(self):
+        self.barrier()
+
+    def all_gather(self, full, shard):
+        table = self._peer_table(shard)
+        nbytes = shard.numel() * shard.element_size()
+        if table is None or nbytes % 16 or full.data_ptr() % 16:
+            return self.fallback.all_gather(full, shard)
+        native._check(self.lib.b200_peer_allgather(table, full.data_ptr(), nbytes, self.world_size, self.rank, 64,
+                                                   self._stream()), "peer_allgather")
+
+    def _reduce_scatter(self, staging, key, mode, grad_out, sumsq, adam):
+        table = self._peer_table(staging)
+        ready, done = self._rows_for(key)
+        e = self._bump(ready)
+        self._epochs[done] = e
+        n = staging.numel() // self.world_size
+        a = adam or {}
+        ptr = lambda t: 0 if t is None else t.data_ptr()
+        native._check(self.lib.b200_peer_reduce_scatter(
+            table, self._flag_bases, ready * self.world_size, done * self.world_size, ptr(grad_out), ptr(sumsq), n,
+            self.world_size, self.rank, e, mode, ptr(a.get("master")), ptr(a.get("m")), ptr(a.get("v")),
+            ptr(a.get("mirror")), ptr(a.get("gscale")), a.get("lr", 0.0), a.get("b1", 0.0), a.get("b2", 0.0),
+            a.get("eps", 0.0), a.get("wd", 0.0), a.get("alpha_t", 0.0), self.limit_ns, self._counter_slot().data_ptr(),
+            self._status(), 96, self._stream()), "peer_reduce_scatter")
+
+    def reduce_scatter_mean(self, out_shard, full, key: str | None = None, sumsq=None):
+        ok = (self._find(full) is not None and full.dtype == torch.bfloat16 and out_shard.dtype == torch.float32
+              and (full.numel() // self.world_size) % 8 == 0)
+        if not ok:
+            return self.fallback.reduce_scatter_mean(out_shard, full)
+        self._reduce_scatter(full, key or f"rs{full.data_ptr()}", 0, out_shard, sumsq, None)
+
+    def reduce_scatter_adamw(self, full, key, master, m, v, mirror, lr, beta1, beta2, eps, weight_decay, step,
+                             grad_scale=None, grad_out=None, sumsq=None):
+        """Reduce-scatter fused with the AdamW update of this rank's shard (one kernel)."""
+        alpha_t = lr * math.sqrt(1 - beta2 ** step) / (1 - beta1 ** step)
+        self._reduce_scatter(full, key, 1, grad_out, sumsq,
+                             dict(master=master, m=m, v=v, mirror=mirror, gscale=grad_scale, lr=lr, b1=beta1, b2=beta2,
+                                  eps=eps, wd=weight_decay, alpha_t=alpha_t))
+
+    def wait_readers(self, staging, key: str | None = None):
+        """Before overwriting ``staging``: wait until every peer has finished reading its last contents."""
+        key = key or f"rs{staging.data_ptr()}"
+        if key not in self._rows:
+            return
+        _, done = self._rows[key]
+        e = self._epochs.get(done, 0)
+        if e == 0:
+            return
+        flags = self.flags.data_ptr() + done * self.world_size * 4
+        native._check(self.lib.b200_peer_wait(flags, self.world_size, e, self.limit_ns, self._status(), self._stream()),
+                      "peer_wait")
+
+    def all_reduce_mean(self, flat):
+        table = self._peer_table(flat)
+        if table is None or flat.dtype != torch.float32 or flat.numel() % 4 or flat.data_ptr() % 16:
+            return self.fallback.all_reduce_mean(flat)
+        ready, done = self._rows_for(f"ar{flat.data_ptr()}:{flat.numel()}")
+        e = self._bump(ready)
+        self._epochs[done] = e
+        native._check(self.lib.b200_peer_allreduce(table, self._flag_bases, ready * self.world_size,
+                                                   done * self.world_size, flat.numel(), self.world_size, self.rank, e,
+                                                   self.limit_ns, self._counter_slot().data_ptr(), self._status(), 96,
+                                                   self._stream()), "peer_allreduce")
+
+    def all_reduce_sum(self, flat):
+        self.fallback.all_reduce_sum(flat)      # scalars (norms, counters): plumbing
+
+    def broadcast(self, t, src=0):
+        self.fallback.broadcast(t, src)

@@ -1,0 +1,172 @@
+"""Peer-memory collectives and the FSDP / DDP wrappers on 2+ GPUs (child processes, NCCL for plumbing)."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _spawn(fn, world, *args):
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    mp.spawn(fn, args=(world, _free_port()) + args, nprocs=world, join=True)
+
+
+def _init(rank, world, port):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+
+
+def test_bounded_flag_wait_reports_instead_of_hanging():
+    """One GPU: wait on a flag nobody sets, with a 1 ms limit; the kernel returns an error status."""
+    import ctypes
+    from llm_systems_from_scratch_b200.ops import native
+    lib = native.load()
+    P, I, U, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_ulonglong
+    lib.b200_peer_wait.argtypes = [P, I, U, L, P, P]
+    lib.b200_peer_wait.restype = I
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    status = native.status_word()
+    status.zero_()
+    rc = lib.b200_peer_wait(flags.data_ptr(), 4, 1, 1_000_000, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    with pytest.raises(native.KernelError):
+        native.check_status()
+    assert int(status[0]) == 0                       # cleared by check_status
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0   # the context is still usable
+
+
+def _collectives(rank, world, port):
+    import torch.distributed as dist
+    _init(rank, world, port)
+    try:
+        from llm_systems_from_scratch_b200.ops import native, torch_impl
+        from llm_systems_from_scratch_b200.parallel.peer import PeerComm
+        comm = PeerComm()
+        n = 64 * 1024 + 64
+        g = torch.Generator(device="cuda").manual_seed(100 + rank)
+        # all-gather of bf16 shards
+        shard = comm.alloc(n, torch.bfloat16)
+        shard.copy_(torch.randn(n, device="cuda", generator=g))
+        comm.barrier()
+        full = torch.empty(world * n, dtype=torch.bfloat16, device="cuda")
+        comm.all_gather(full, shard)
+        ref = torch.empty_like(full)
+        dist.all_gather_into_tensor(ref, shard)
+        assert torch.equal(full, ref)
+        # reduce-scatter (mean) of bf16 staging into fp32 with sum of squares
+        stage = comm.alloc(world * n, torch.bfloat16)
+        for it in range(3):                          # repeated use exercises the epoch / reuse protocol
+            comm.wait_readers(stage, "t")
+            stage.copy_(torch.randn(world * n, device="cuda", generator=g))
+            out = torch.empty(n, dtype=torch.float32, device="cuda")
+            ss = torch.zeros((), device="cuda")
+            comm.reduce_scatter_mean(out, stage, key="t", sumsq=ss)
+            tmp = stage.float()
+            dist.all_reduce(tmp)
+            want = tmp[rank * n:(rank + 1) * n] / world
+            assert torch.allclose(out, want, atol=1e-6), (out - want).abs().max()
+            assert abs(ss.item() - want.pow(2).sum().item()) < 1e-2 * want.pow(2).sum().item()
+        # fused reduce-scatter + AdamW against reduce-scatter followed by the AdamW kernel
+        comm.wait_readers(stage, "t")
+        stage.copy_(torch.randn(world * n, device="cuda", generator=g))
+        p0 = torch.randn(n, device="cuda", generator=g)
+        m0 = 0.1 * torch.randn(n, device="cuda", generator=g)
+        v0 = 0.1 * torch.rand(n, device="cuda", generator=g)
+        coef = torch.tensor(0.5, device="cuda")
+        tmp = stage.float()
+        dist.all_reduce(tmp)
+        gref = tmp[rank * n:(rank + 1) * n] / world
+        pr, mr, vr = p0.clone(), m0.clone(), v0.clone()
+        torch_impl.adamw_step(pr, gref, mr, vr, None, 1e-3, 0.9, 0.95, 1e-8, 0.1, 3, grad_scale=coef)
+        p, m, v = p0.clone(), m0.clone(), v0.clone()
+        mirror = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        comm.reduce_scatter_adamw(stage, "t", p, m, v, mirror, 1e-3, 0.9, 0.95, 1e-8, 0.1, 3, grad_scale=coef)
+        assert torch.allclose(p, pr, atol=1e-6, rtol=1e-5) and torch.allclose(m, mr, atol=1e-6) and torch.allclose(v, vr, atol=1e-6)
+        assert torch.equal(mirror, p.bfloat16())
+        # in-place mean all-reduce of fp32
+        buf = comm.alloc(n, torch.float32)
+        for it in range(3):
+            buf.copy_(torch.randn(n, device="cuda", generator=g))
+            want = buf.clone()
+            dist.all_reduce(want)
+            want /= world
+            comm.all_reduce_mean(buf)
+            assert torch.allclose(buf, want, atol=1e-6)
+        torch.cuda.synchronize()
+        native.check_status()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_peer_collectives_match_nccl(world):
+    _spawn(_collectives, world)
+
+
+CFG = dict(vocab_size=1003, context_length=128, d_model=256, num_layers=3, num_heads=4, d_ff=688, rope_theta=10000.0)
+
+
+def _train(rank, world, port, mode, comm_kind, fused, out):
+    import torch.distributed as dist
+    _init(rank, world, port)
+    try:
+        from llm_systems_from_scratch_b200.models.transformer import TransformerLM
+        from llm_systems_from_scratch_b200.ops import native
+        from llm_systems_from_scratch_b200.optim import FusedAdamW
+        from llm_systems_from_scratch_b200.parallel import DDP, FSDP
+        torch.manual_seed(0)
+        model = TransformerLM(**CFG, use_custom_triton=True).cuda()
+        wrapped = FSDP(model, comm=comm_kind) if mode == "fsdp" else DDP(model, bucket_size_mb=1.0, comm=comm_kind)
+        opt = FusedAdamW(wrapped.parameters(), lr=1e-3, weight_decay=0.1)
+        if fused:
+            assert wrapped.attach_optimizer(opt, max_grad_norm=None)
+        arena = wrapped.shard_arena if mode == "fsdp" else model.engine().provider.arena
+        losses = []
+        for step in range(4):
+            g = torch.Generator().manual_seed(7)      # the same batch every step: the loss must go down
+            x = torch.randint(0, CFG["vocab_size"], (2 * world, 128), generator=g)[rank * 2:(rank + 1) * 2].cuda()
+            y = torch.randint(0, CFG["vocab_size"], (2 * world, 128), generator=g)[rank * 2:(rank + 1) * 2].cuda()
+            loss = wrapped.loss(x, y)
+            loss.backward()
+            wrapped.finish_gradient_synchronization()
+            if fused:
+                wrapped.finish_fused_step()
+            else:
+                opt.set_grad_scale(arena.clip_coef(1e9))
+            opt.step()
+            t = loss.detach().clone()
+            dist.all_reduce(t)
+            losses.append(t.item() / world)
+        torch.cuda.synchronize()
+        native.check_status()
+        if rank == 0:
+            torch.save(losses, out)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode,fused", [("fsdp", False), ("fsdp", True), ("ddp", False)])
+def test_peer_training_matches_nccl_training(tmp_path, mode, fused):
+    a, b = str(tmp_path / "nccl.pt"), str(tmp_path / "peer.pt")
+    _spawn(_train, 2, mode, "torch", False, a)
+    _spawn(_train, 2, mode, "peer", fused, b)
+    la, lb = torch.load(a), torch.load(b)
+    assert la[-1] < la[0]
+    assert max(abs(p - q) for p, q in zip(la, lb)) < 2e-2, (la, lb)
