@@ -358,7 +358,7 @@ static int num_sms() {
 
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t stream) {
-  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   using S = GemmSmem<BN, STAGES>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN, STAGES>;
   static bool configured = false;
@@ -396,7 +396,14 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
     return -10;
   if (epi == EPI_BF16_RES && R == nullptr) return -11;
   int bn = bn_hint;
-  if (bn != 128 && bn != 256) {
+  const bool small_ok = !a_mn && !b_mn;   // narrow tiles exist for the K-major (decode) layout only
+  if (small_ok && (bn == 32 || bn == 64)) {
+    // explicit request
+  } else if (small_ok && bn != 128 && bn != 256 && M <= BM) {
+    // one row of tiles: weight streaming is the bound, so use enough CTAs to pull from all of HBM
+    const int sms = num_sms();
+    bn = (N / 128 >= sms) ? 128 : ((N / 64 >= sms * 2 / 3) ? 64 : 32);
+  } else if (bn != 128 && bn != 256) {
     const long long mt = (M + BM - 1) / BM;
     const long long sms = num_sms();
     const long long w256 = (mt * ((N + 255) / 256) + sms - 1) / sms * 256 * 10;
@@ -427,6 +434,8 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   if (b_mn) return launch_gemm<BN_, false, true>(tmA, tmB, p, max_ctas, stream);          \
   return launch_gemm<BN_, false, false>(tmA, tmB, p, max_ctas, stream);
   if (bn == 256) { DISPATCH(256) }
+  if (bn == 64) return launch_gemm<64, false, false>(tmA, tmB, p, max_ctas, stream);
+  if (bn == 32) return launch_gemm<32, false, false>(tmA, tmB, p, max_ctas, stream);
   DISPATCH(128)
 #undef DISPATCH
 }

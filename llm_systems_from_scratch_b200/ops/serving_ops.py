@@ -1,0 +1,75 @@
+"""Decode-time ops: paged-KV attention and KV-cache append (CUDA kernels, PyTorch statement on CPU)."""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import native, torch_impl
+
+_declared = False
+
+
+def _lib():
+    global _declared
+    lib = native.load()
+    if not _declared:
+        P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        lib.b200_paged_decode.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P]
+        lib.b200_paged_decode.restype = I
+        lib.b200_kv_append.argtypes = [P, P, P, P, L, I, P]
+        lib.b200_kv_append.restype = I
+        _declared = True
+    return lib
+
+
+def kv_append(k_cache, v_cache, qkv, slot_mapping):
+    """Write the K and V thirds of qkv (R, 3d) into cache slots ``page * page_size + offset`` (int64, -1 skips)."""
+    if not qkv.is_cuda:
+        keep = slot_mapping >= 0
+        return torch_impl.kv_append(k_cache, v_cache, qkv[keep], slot_mapping[keep])
+    lib = _lib()
+    d = qkv.shape[1] // 3
+    native._req(qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and k_cache.is_contiguous(), "bad kv_append inputs")
+    native._req(slot_mapping.dtype == torch.int64 and slot_mapping.numel() == qkv.shape[0], "bad slot mapping")
+    native._check(lib.b200_kv_append(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(),
+                                     qkv.shape[0], d, native._stream()), "kv_append")
+
+
+def choose_splits(rows: int, heads: int, max_context: int, sms: int = 148) -> int:
+    """Enough CTAs to fill the GPU, at least ~256 tokens per split."""
+    want = max(1, (2 * sms + rows * heads - 1) // max(1, rows * heads))
+    return max(1, min(want, max(1, max_context // 256), 32))
+
+
+def paged_decode_attention(qkv, k_cache, v_cache, block_tables, context_lens, n_heads: int, splits: int = 0,
+                           scratch=None):
+    """One query token per request against its paged KV history.
+
+    qkv: (R, 3d) packed (only the query third is read) or (R, d); caches: (num_pages, page_size, d);
+    block_tables: (R, max_pages) int32; context_lens: (R,) int32, number of cached tokens to attend to.
+    Returns (R, d).
+    """
+    r, width = qkv.shape
+    d = k_cache.shape[-1]
+    dh = d // n_heads
+    if not qkv.is_cuda:
+        return torch_impl.paged_decode_attention(qkv[:, :d], k_cache, v_cache, block_tables, context_lens, n_heads)
+    lib = _lib()
+    native._req(qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1, "qkv must be bf16 with unit inner stride")
+    native._req(block_tables.dtype == torch.int32 and context_lens.dtype == torch.int32, "tables must be int32")
+    page = k_cache.shape[1]
+    max_pages = block_tables.shape[1]
+    if splits <= 0:
+        splits = choose_splits(r, n_heads, max_pages * page)
+    out = torch.empty((r, d), dtype=torch.bfloat16, device=qkv.device)
+    if scratch is None:
+        scratch = torch.empty(r * n_heads * splits * (dh + 2), dtype=torch.float32, device=qkv.device)
+    part_o = scratch[:r * n_heads * splits * dh]
+    part_ml = scratch[r * n_heads * splits * dh:]
+    native._check(lib.b200_paged_decode(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                                        context_lens.data_ptr(), out.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(),
+                                        r, qkv.stride(0), n_heads, dh, page, max_pages, splits, 1.0 / math.sqrt(dh),
+                                        native._stream()), "paged_decode")
+    return out
