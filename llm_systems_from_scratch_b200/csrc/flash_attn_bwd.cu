@@ -58,8 +58,35 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
   }
 }
 
+// The element-wise stage of both kernels is spread over BWD_CG warpgroups: warpgroup g handles
+// columns [g*BWD_COLS, (g+1)*BWD_COLS) of every 64-column step, so 16 warps (4 per scheduler) hide each
+// other's TMEM-load, exp2 and shared-memory latencies instead of one warp per scheduler.
+constexpr int BWD_RING = 3;   // TMA ring depth for the per-step tiles: the load of step t+2 is in flight during step t
+constexpr int BWD_CG = 4;
+constexpr int BWD_COLS = 64 / BWD_CG;                 // 16 columns per thread and step
+constexpr int BWD_COMPUTE_THREADS = 128 * BWD_CG;     // 512
+constexpr int BWD_THREADS = 64 + BWD_COMPUTE_THREADS; // + TMA warp + MMA warp
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Write 16 bf16 values (chunks 2*cg and 2*cg+1 of one 128-byte row of a 128B-swizzled panel).
+__device__ __forceinline__ void store_row16_swizzled(uint8_t* panel, int r, int cg, const float (&v)[16]) {
+  uint8_t* row = panel + r * 128;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int c16 = cg * 2 + j;
+    uint4 u = make_uint4(pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]), pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]),
+                         pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]), pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]));
+    *reinterpret_cast<uint4*>(row + ((c16 ^ (r & 7)) << 4)) = u;
+  }
 }
 
 // Write 64 bf16 values (one 128-byte row of a 128B-swizzled panel) from fp32 registers.
@@ -81,18 +108,18 @@ struct DkDvSmem {
   static constexpr int Q_TILE = 64 * DH * 2;     // Q_i or dO_i (64 queries)
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + KV_TILE;
-  static constexpr int OFF_Q = OFF_V + KV_TILE;          // 2 stages
-  static constexpr int OFF_DO = OFF_Q + 2 * Q_TILE;      // 2 stages
-  static constexpr int OFF_PT = OFF_DO + 2 * Q_TILE;     // 128 x 64 bf16
-  static constexpr int OFF_DST = OFF_PT + 16384;
-  static constexpr int OFF_VEC = OFF_DST + 16384;        // lse[2][64], delta[2][64] floats
+  static constexpr int OFF_Q = OFF_V + KV_TILE;                // BWD_RING stages
+  static constexpr int OFF_DO = OFF_Q + BWD_RING * Q_TILE;     // BWD_RING stages
+  static constexpr int OFF_PT = OFF_DO + BWD_RING * Q_TILE;    // 128 x 64 bf16
+  static constexpr int OFF_DST = OFF_PT + 2 * 16384;     // P^T and dS^T are double buffered
+  static constexpr int OFF_VEC = OFF_DST + 2 * 16384;    // lse[2][64], delta[2][64] floats
   static constexpr int OFF_BAR = OFF_VEC + 4 * 64 * 4;
-  static constexpr int NUM_BARS = 1 + 2 + 2 + 2 + 2 + 1 + 1;
+  static constexpr int NUM_BARS = 1 + 2 * BWD_RING + 8;
   static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
 };
 
 template <int DH>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 over qkv
                   const __grid_constant__ CUtensorMap tm_q,    // box 64 x 64 over qkv
                   const __grid_constant__ CUtensorMap tm_do,   // box 64 x 64 over dO
@@ -102,12 +129,12 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* kv_full = bars;
-  uint64_t* qd_full = bars + 1;   // [2]
-  uint64_t* qd_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;    // [2]
-  uint64_t* s_empty = bars + 7;   // [2]
-  uint64_t* p_full = bars + 9;
-  uint64_t* p_empty = bars + 10;
+  uint64_t* qd_full = bars + 1;                    // [BWD_RING]
+  uint64_t* qd_empty = qd_full + BWD_RING;         // [BWD_RING]
+  uint64_t* s_full = qd_empty + BWD_RING;          // [2]
+  uint64_t* s_empty = s_full + 2;                  // [2]
+  uint64_t* p_full = s_empty + 2;                  // [2]
+  uint64_t* p_empty = p_full + 2;                  // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
   volatile uint32_t* abort_word = tmem_holder + 1;
   float* lse_s = reinterpret_cast<float*>(smem + L::OFF_VEC);   // [2][64]
@@ -125,14 +152,16 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < BWD_RING; ++i) {
       mbar_init(&qd_full[i], 1);
       mbar_init(&qd_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
     }
-    mbar_init(p_full, 128);
-    mbar_init(p_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], BWD_COMPUTE_THREADS);
+      mbar_init(&p_full[i], BWD_COMPUTE_THREADS);
+      mbar_init(&p_empty[i], 1);
+    }
     *abort_word = 0;
     fence_barrier_init();
     prefetch_tensormap(&tm_kv);
@@ -163,8 +192,8 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
         tma_load_2d(smem + L::OFF_V + pn * 16384, &tm_kv, kv_full, col_v + pn * 64, row_base + k0);
       }
       for (int t = 0; t < n_steps; ++t) {
-        const int st = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+        const int st = t % BWD_RING;
+        const uint32_t ph = (t / BWD_RING) & 1;
         const int qrow = row_base + (i0 + t) * 64;
         if (!mbar_wait(&qd_empty[st], ph ^ 1, abort_word)) { *abort_word = ERR_WAIT_EMPTY; break; }
         mbar_expect_tx(&qd_full[st], 2 * L::Q_TILE);
@@ -180,11 +209,11 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
       constexpr uint32_t idesc_12 = make_idesc_bf16(128, 64, false, false);
       constexpr uint32_t idesc_34 = make_idesc_bf16(128, DH, false, true);
       const uint32_t k_addr = smem_u32(smem + L::OFF_K), v_addr = smem_u32(smem + L::OFF_V);
-      const uint32_t pt_addr = smem_u32(smem + L::OFF_PT), dst_addr = smem_u32(smem + L::OFF_DST);
+      const uint32_t pt_base = smem_u32(smem + L::OFF_PT), dst_base = smem_u32(smem + L::OFF_DST);
       auto issue12 = [&](int t) {
-        const int st = t & 1;
-        const uint32_t q_addr = smem_u32(smem + L::OFF_Q + st * L::Q_TILE);
-        const uint32_t do_addr = smem_u32(smem + L::OFF_DO + st * L::Q_TILE);
+        const int st = t & 1, rs = t % BWD_RING;
+        const uint32_t q_addr = smem_u32(smem + L::OFF_Q + rs * L::Q_TILE);
+        const uint32_t do_addr = smem_u32(smem + L::OFF_DO + rs * L::Q_TILE);
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k) {
           const uint32_t offa = (k / 4) * 16384 + (k % 4) * 32;   // 128-row panels
@@ -208,16 +237,19 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
         if (t + 1 < n_steps) {
           const int st1 = (t + 1) & 1;
           const uint32_t ph1 = ((t + 1) >> 1) & 1;
-          ok = mbar_wait(&qd_full[st1], ph1, abort_word) && mbar_wait(&s_empty[st1], ph1 ^ 1, abort_word);
+          ok = mbar_wait(&qd_full[(t + 1) % BWD_RING], ((t + 1) / BWD_RING) & 1, abort_word) &&
+               mbar_wait(&s_empty[st1], ph1 ^ 1, abort_word);
           if (!ok) break;
           tc_fence_after();
           issue12(t + 1);
         }
-        ok = mbar_wait(p_full, t & 1, abort_word);
+        ok = mbar_wait(&p_full[st], (t >> 1) & 1, abort_word);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(smem + L::OFF_Q + st * L::Q_TILE);
-        const uint32_t do_addr = smem_u32(smem + L::OFF_DO + st * L::Q_TILE);
+        const int rs = t % BWD_RING;
+        const uint32_t q_addr = smem_u32(smem + L::OFF_Q + rs * L::Q_TILE);
+        const uint32_t do_addr = smem_u32(smem + L::OFF_DO + rs * L::Q_TILE);
+        const uint32_t pt_addr = pt_base + st * 16384, dst_addr = dst_base + st * 16384;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {   // K = 64 queries
           // B operands are MN-major: dh contiguous, 16 queries = 2048 B per step, dh panels 8192 B apart
@@ -229,72 +261,77 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
           umma_f16_ss(tm_dk, make_smem_desc(dst_addr + k * 32, 16, 1024), make_smem_desc(q_addr + k * 2048, 8192, 1024),
                       idesc_34, (t > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(p_empty);
-        umma_commit(&qd_empty[st]);
+        umma_commit(&p_empty[st]);
+        umma_commit(&qd_empty[rs]);
       }
       if (!ok) *abort_word = ERR_WAIT_FULL;
     }
   } else {
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;      // key row inside the tile
-    const int tid = (warp - 2) * 32 + lane; // 0..127 among the compute threads
+    const int tid = (warp - 2) * 32 + lane; // 0..511 among the compute threads
+    const int cg = (warp - 2) >> 2;         // column group of this warpgroup
     const int key_idx = k0 + r;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const float* lse_g = p.lse + ((size_t)b * p.heads + h) * p.seq;
     const float* delta_g = p.delta + ((size_t)b * p.heads + h) * p.seq;
     bool ok = true;
+    // threads 0-63 carry lse, 64-127 carry delta; +inf lse zeroes the probabilities of padded queries
+    auto fetch_vec = [&](int t) -> float {
+      const int qi = (i0 + t) * 64 + (tid & 63);
+      if (tid < 64) return (qi < p.seq) ? lse_g[qi] * 1.4426950408889634f : INFINITY;
+      if (tid < 128) return (qi < p.seq) ? delta_g[qi] : 0.f;
+      return 0.f;
+    };
+    float staged = fetch_vec(0);
     for (int t = 0; t < n_steps; ++t) {
       const int st = t & 1;
       const uint32_t ph = (t >> 1) & 1;
       const int qb = (i0 + t) * 64;
-      {  // stage lse (as log2 units) and delta of the 64 queries; +inf lse zeroes padded queries
-        const int qi = qb + (tid & 63);
-        if (tid < 64) lse_s[st * 64 + tid] = (qi < p.seq) ? lse_g[qi] * 1.4426950408889634f : INFINITY;
-        else delta_s[st * 64 + (tid - 64)] = (qi < p.seq) ? delta_g[qi] : 0.f;
-      }
-      named_barrier_sync(1, 128);   // every compute thread reaches this each step, also after a failed wait
+      // lse (in log2 units) and delta of this step's 64 queries were fetched one step ahead
+      if (tid < 64) lse_s[st * 64 + tid] = staged;
+      else if (tid < 128) delta_s[st * 64 + (tid - 64)] = staged;
+      named_barrier_sync(1, BWD_COMPUTE_THREADS);   // reached by every compute thread each step, also after a failed wait
+      if (t + 1 < n_steps) staged = fetch_vec(t + 1);   // in flight while this step computes
       if (!ok) continue;
       if (!mbar_wait(&s_full[st], ph, abort_word)) { ok = false; continue; }
       tc_fence_after();
-      uint32_t sreg[2][32], dreg[2][32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld_32x32(tm_st + lane_addr + st * 64 + c * 32, sreg[c]);
-        tmem_ld_32x32(tm_dpt + lane_addr + st * 64 + c * 32, dreg[c]);
-      }
+      uint32_t sreg[BWD_COLS], dreg[BWD_COLS];
+      tmem_ld_32x16(tm_st + lane_addr + st * 64 + cg * BWD_COLS, sreg);
+      tmem_ld_32x16(tm_dpt + lane_addr + st * 64 + cg * BWD_COLS, dreg);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&s_empty[st]);
       const bool need_mask = (qb < k0 + 128);   // tile touches the diagonal
-      float pv[64], dsv[64];
+      float pv[BWD_COLS], dsv[BWD_COLS];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float sv = __uint_as_float(sreg[c >> 5][c & 31]);
-        const float dp = __uint_as_float(dreg[c >> 5][c & 31]);
-        const float lse2 = lse_s[st * 64 + c];
-        float pe = exp2f(sv * p.scale_log2 - lse2);
-        const bool dead = (lse2 == INFINITY) || (need_mask && (qb + c < key_idx));
+      for (int c = 0; c < BWD_COLS; ++c) {
+        const int col = cg * BWD_COLS + c;
+        const float sv = __uint_as_float(sreg[c]);
+        const float dp = __uint_as_float(dreg[c]);
+        const float lse2 = lse_s[st * 64 + col];
+        float pe = fast_exp2(sv * p.scale_log2 - lse2);
+        const bool dead = (lse2 == INFINITY) || (need_mask && (qb + col < key_idx));
         pe = dead ? 0.f : pe;
         pv[c] = pe;
-        dsv[c] = dead ? 0.f : pe * (dp - delta_s[st * 64 + c]) * p.scale;
+        dsv[c] = dead ? 0.f : pe * (dp - delta_s[st * 64 + col]) * p.scale;
       }
-      if (t > 0) {
-        if (!mbar_wait(p_empty, (t - 1) & 1, abort_word)) { ok = false; continue; }
-      }
-      store_row64_swizzled(smem + L::OFF_PT, r, pv);
-      store_row64_swizzled(smem + L::OFF_DST, r, dsv);
+      // buffer st was last read by the MMAs of step t-2
+      if (!mbar_wait(&p_empty[st], ph ^ 1, abort_word)) { ok = false; continue; }
+      store_row16_swizzled(smem + L::OFF_PT + st * 16384, r, cg, pv);
+      store_row16_swizzled(smem + L::OFF_DST + st * 16384, r, cg, dsv);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[st]);
     }
-    if (ok) ok = mbar_wait(p_empty, (n_steps - 1) & 1, abort_word);
+    if (ok) ok = mbar_wait(&p_empty[(n_steps - 1) & 1], ((n_steps - 1) >> 1) & 1, abort_word);
     if (ok) {
       tc_fence_after();
       const bool valid = key_idx < p.seq;
       __nv_bfloat16* dk_row = p.dqkv + (size_t)(row_base + key_idx) * 3 * p.d + col_k;
       __nv_bfloat16* dv_row = p.dqkv + (size_t)(row_base + key_idx) * 3 * p.d + col_v;
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = cg; c < DH / 32; c += BWD_CG) {   // each warpgroup stores its own 32-column slices
         uint32_t a[32], g[32];
         tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
         tmem_ld_32x32(tm_dv + lane_addr + c * 32, g);
@@ -343,16 +380,16 @@ struct DqSmem {
   static constexpr int KV_TILE = 64 * DH * 2;   // K_j or V_j (64 keys)
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_DO = OFF_Q + Q_TILE;
-  static constexpr int OFF_K = OFF_DO + Q_TILE;        // 2 stages
-  static constexpr int OFF_V = OFF_K + 2 * KV_TILE;    // 2 stages
-  static constexpr int OFF_DS = OFF_V + 2 * KV_TILE;   // 128 x 64 bf16
-  static constexpr int OFF_BAR = OFF_DS + 16384;
-  static constexpr int NUM_BARS = 1 + 2 + 2 + 2 + 2 + 1 + 1;
+  static constexpr int OFF_K = OFF_DO + Q_TILE;               // BWD_RING stages
+  static constexpr int OFF_V = OFF_K + BWD_RING * KV_TILE;    // BWD_RING stages
+  static constexpr int OFF_DS = OFF_V + BWD_RING * KV_TILE;   // 128 x 64 bf16
+  static constexpr int OFF_BAR = OFF_DS + 2 * 16384;   // dS is double buffered
+  static constexpr int NUM_BARS = 1 + 2 * BWD_RING + 8;
   static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
 };
 
 template <int DH>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 over qkv
                 const __grid_constant__ CUtensorMap tm_do,   // box 64 x 128 over dO
                 const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 64 over qkv
@@ -362,12 +399,12 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* qd_full = bars;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;    // [2]
-  uint64_t* s_empty = bars + 7;   // [2]
-  uint64_t* p_full = bars + 9;
-  uint64_t* p_empty = bars + 10;
+  uint64_t* kv_full = bars + 1;                    // [BWD_RING]
+  uint64_t* kv_empty = kv_full + BWD_RING;         // [BWD_RING]
+  uint64_t* s_full = kv_empty + BWD_RING;          // [2]
+  uint64_t* s_empty = s_full + 2;                  // [2]
+  uint64_t* p_full = s_empty + 2;                  // [2]
+  uint64_t* p_empty = p_full + 2;                  // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
   volatile uint32_t* abort_word = tmem_holder + 1;
 
@@ -382,14 +419,16 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
 
   if (threadIdx.x == 0) {
     mbar_init(qd_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < BWD_RING; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
     }
-    mbar_init(p_full, 128);
-    mbar_init(p_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], BWD_COMPUTE_THREADS);
+      mbar_init(&p_full[i], BWD_COMPUTE_THREADS);
+      mbar_init(&p_empty[i], 1);
+    }
     *abort_word = 0;
     fence_barrier_init();
     prefetch_tensormap(&tm_q);
@@ -419,8 +458,8 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
         tma_load_2d(smem + L::OFF_DO + pn * 16384, &tm_do, qd_full, h * DH + pn * 64, row_base + q0);
       }
       for (int t = 0; t < n_steps; ++t) {
-        const int st = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+        const int st = t % BWD_RING;
+        const uint32_t ph = (t / BWD_RING) & 1;
         const int krow = row_base + t * 64;
         if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_word)) { *abort_word = ERR_WAIT_EMPTY; break; }
         mbar_expect_tx(&kv_full[st], 2 * L::KV_TILE);
@@ -436,11 +475,11 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
       constexpr uint32_t idesc_12 = make_idesc_bf16(128, 64, false, false);
       constexpr uint32_t idesc_3 = make_idesc_bf16(128, DH, false, true);
       const uint32_t q_addr = smem_u32(smem + L::OFF_Q), do_addr = smem_u32(smem + L::OFF_DO);
-      const uint32_t ds_addr = smem_u32(smem + L::OFF_DS);
+      const uint32_t ds_base = smem_u32(smem + L::OFF_DS);
       auto issue12 = [&](int t) {
-        const int st = t & 1;
-        const uint32_t k_addr = smem_u32(smem + L::OFF_K + st * L::KV_TILE);
-        const uint32_t v_addr = smem_u32(smem + L::OFF_V + st * L::KV_TILE);
+        const int st = t & 1, rs = t % BWD_RING;
+        const uint32_t k_addr = smem_u32(smem + L::OFF_K + rs * L::KV_TILE);
+        const uint32_t v_addr = smem_u32(smem + L::OFF_V + rs * L::KV_TILE);
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k) {
           const uint32_t offa = (k / 4) * 16384 + (k % 4) * 32;
@@ -464,22 +503,25 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
         if (t + 1 < n_steps) {
           const int st1 = (t + 1) & 1;
           const uint32_t ph1 = ((t + 1) >> 1) & 1;
-          ok = mbar_wait(&kv_full[st1], ph1, abort_word) && mbar_wait(&s_empty[st1], ph1 ^ 1, abort_word);
+          ok = mbar_wait(&kv_full[(t + 1) % BWD_RING], ((t + 1) / BWD_RING) & 1, abort_word) &&
+               mbar_wait(&s_empty[st1], ph1 ^ 1, abort_word);
           if (!ok) break;
           tc_fence_after();
           issue12(t + 1);
         }
-        ok = mbar_wait(p_full, t & 1, abort_word);
+        ok = mbar_wait(&p_full[st], (t >> 1) & 1, abort_word);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(smem + L::OFF_K + st * L::KV_TILE);
+        const int rs = t % BWD_RING;
+        const uint32_t k_addr = smem_u32(smem + L::OFF_K + rs * L::KV_TILE);
+        const uint32_t ds_addr = ds_base + st * 16384;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {   // K = 64 keys; B = K_j MN-major (dh contiguous)
           umma_f16_ss(tm_dq, make_smem_desc(ds_addr + k * 32, 16, 1024), make_smem_desc(k_addr + k * 2048, 8192, 1024),
                       idesc_3, (t > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(p_empty);
-        umma_commit(&kv_empty[st]);
+        umma_commit(&p_empty[st]);
+        umma_commit(&kv_empty[rs]);
       }
       if (!ok) *abort_word = ERR_WAIT_FULL;
     }
@@ -487,6 +529,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int q_idx = q0 + r;
+    const int cg = (warp - 2) >> 2;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const bool valid = q_idx < p.seq;
     const size_t vec = ((size_t)b * p.heads + h) * p.seq + q_idx;
@@ -499,39 +542,35 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
       const int kb = t * 64;
       if (!mbar_wait(&s_full[st], ph, abort_word)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sreg[2][32], dreg[2][32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld_32x32(tm_s + lane_addr + st * 64 + c * 32, sreg[c]);
-        tmem_ld_32x32(tm_dp + lane_addr + st * 64 + c * 32, dreg[c]);
-      }
+      uint32_t sreg[BWD_COLS], dreg[BWD_COLS];
+      tmem_ld_32x16(tm_s + lane_addr + st * 64 + cg * BWD_COLS, sreg);
+      tmem_ld_32x16(tm_dp + lane_addr + st * 64 + cg * BWD_COLS, dreg);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&s_empty[st]);
       const bool need_mask = (kb + 64 > q0);
-      float dsv[64];
+      float dsv[BWD_COLS];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float sv = __uint_as_float(sreg[c >> 5][c & 31]);
-        const float dp = __uint_as_float(dreg[c >> 5][c & 31]);
-        const float pe = exp2f(sv * p.scale_log2 - lse2);
-        const bool dead = !valid || (need_mask && (kb + c > q_idx));
+      for (int c = 0; c < BWD_COLS; ++c) {
+        const int col = cg * BWD_COLS + c;
+        const float sv = __uint_as_float(sreg[c]);
+        const float dp = __uint_as_float(dreg[c]);
+        const float pe = fast_exp2(sv * p.scale_log2 - lse2);
+        const bool dead = !valid || (need_mask && (kb + col > q_idx));
         dsv[c] = dead ? 0.f : pe * (dp - dlt) * p.scale;
       }
-      if (t > 0) {
-        if (!mbar_wait(p_empty, (t - 1) & 1, abort_word)) { ok = false; break; }
-      }
-      store_row64_swizzled(smem + L::OFF_DS, r, dsv);
+      if (!mbar_wait(&p_empty[st], ph ^ 1, abort_word)) { ok = false; break; }
+      store_row16_swizzled(smem + L::OFF_DS + st * 16384, r, cg, dsv);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[st]);
     }
-    if (ok) ok = mbar_wait(p_empty, (n_steps - 1) & 1, abort_word);
+    if (ok) ok = mbar_wait(&p_empty[(n_steps - 1) & 1], ((n_steps - 1) >> 1) & 1, abort_word);
     if (ok) {
       tc_fence_after();
       __nv_bfloat16* dq_row = p.dqkv + (size_t)(row_base + q_idx) * 3 * p.d + col_q;
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = cg; c < DH / 32; c += BWD_CG) {
         uint32_t a[32];
         tmem_ld_32x32(tm_dq + lane_addr + c * 32, a);
         tmem_ld_wait();
@@ -582,8 +621,8 @@ static int launch_flash_bwd(const void* qkv, const void* dout, const FlashBwdPar
     configured = true;
   }
   const int n_kblk = (p.seq + 127) / 128;
-  k1<<<p.batch * p.heads * n_kblk, 192, DkDvSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_qkv64, tm_do64, p);
-  k2<<<p.batch * p.heads * n_kblk, 192, DqSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_do128, tm_qkv64, p);
+  k1<<<p.batch * p.heads * n_kblk, BWD_THREADS, DkDvSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_qkv64, tm_do64, p);
+  k2<<<p.batch * p.heads * n_kblk, BWD_THREADS, DqSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_do128, tm_qkv64, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
