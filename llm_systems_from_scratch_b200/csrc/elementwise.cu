@@ -94,8 +94,11 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
 // 8 columns and keeps the weight-gradient partial for them in registers.  Partials go to
 // `dw_partial` (gridDim.x, d) fp32 and are summed in a fixed order by rmsnorm_dw_reduce_kernel.
 constexpr int RMS_BWD_THREADS = 256;
-constexpr int RMS_BWD_MAXC = 4;  // d <= 256 * 8 * 4 = 8192
+constexpr int RMS_BWD_MAXC_LIMIT = 4;  // d <= 256 * 8 * 4 = 8192
 
+// RMS_BWD_MAXC is a template parameter so that narrow rows (d <= 2048 needs one group per thread) use
+// few registers and several blocks fit on an SM; with the widest instance only one block fits.
+template <int RMS_BWD_MAXC>
 __global__ void __launch_bounds__(RMS_BWD_THREADS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -519,15 +522,21 @@ extern "C" int b200_rmsnorm_bwd_parts(int rows) { return rows < 148 * 4 ? (rows 
 extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                                 void* dx, float* dw, float* dw_partial, int rows, int d, int accumulate_dw,
                                 cudaStream_t st) {
-  if (d % 8 || d > RMS_BWD_THREADS * 8 * RMS_BWD_MAXC) return -10;
+  if (d % 8 || d > RMS_BWD_THREADS * 8 * RMS_BWD_MAXC_LIMIT) return -10;
   if (!ALIGNED16(dy) || !ALIGNED16(x) || !ALIGNED16(w) || !ALIGNED16(dx) || !ALIGNED16(dw_partial) ||
       !ALIGNED16(dres))
     return -10;
   if (rows == 0) return 0;
   const int parts = b200_rmsnorm_bwd_parts(rows);
-  rmsnorm_bwd_kernel<<<parts, RMS_BWD_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                        (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
-                                                        (__nv_bfloat16*)dx, dw_partial, rows, d);
+#define RMS_BWD_LAUNCH(C)                                                                                   \
+  rmsnorm_bwd_kernel<C><<<parts, RMS_BWD_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, \
+                                                           (const __nv_bfloat16*)w, rstd,                     \
+                                                           (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx,    \
+                                                           dw_partial, rows, d)
+  if (d <= 2048) RMS_BWD_LAUNCH(1);
+  else if (d <= 4096) RMS_BWD_LAUNCH(2);
+  else RMS_BWD_LAUNCH(4);
+#undef RMS_BWD_LAUNCH
   rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_partial, dw, parts, d, accumulate_dw);
   CHECK_LAUNCH();
 }
@@ -683,9 +692,9 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   const int parts = rows < B200_NOALLOC_MAX_PARTS ? rows : B200_NOALLOC_MAX_PARTS;
   // Every partial row [0, parts) x [0, d) is written by the first kernel before the second reads it,
   // so nothing in the shared array has to be cleared between calls.
-  rmsnorm_bwd_kernel<<<parts, RMS_BWD_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                        (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
-                                                        (__nv_bfloat16*)dx, scratch, rows, d);
+  rmsnorm_bwd_kernel<RMS_BWD_MAXC_LIMIT><<<parts, RMS_BWD_THREADS, 0, st>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
+      (__nv_bfloat16*)dx, scratch, rows, d);
   rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, st>>>(scratch, dw, parts, d, accumulate_dw);
   CHECK_LAUNCH();
 }

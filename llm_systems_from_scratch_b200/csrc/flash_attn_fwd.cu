@@ -7,7 +7,7 @@
 // diagonal:
 //   warp 0     TMA producer: Q once, then K_j / V_j into two-stage rings (128B swizzle)
 //   warp 1     MMA issuer:   S_j = Q K_j^T (TMEM, double buffered)  and  O += P_j V_j (TMEM)
-//   warps 2-5  softmax:      tcgen05.ld S_j -> online softmax in registers (one row per thread)
+//   warps 2-9  softmax:      tcgen05.ld S_j -> online softmax in registers (two threads per row, 64 columns each)
 //                            -> P_j as bf16 into swizzled smem; rescale O in TMEM only when the
 //                            running max moved by more than 2^8 (vote per warp)
 // S_{j+1} is issued before P_j V_j, so the tensor core computes the next scores while the softmax
@@ -19,8 +19,19 @@ namespace b200 {
 int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
                       uint32_t box_rows);
 
+__device__ __forceinline__ float fa_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 constexpr int FA_BQ = 128;   // queries per CTA
 constexpr int FA_BK = 128;   // keys per step
+constexpr int FA_THREADS = 64 + 256;   // TMA warp, MMA warp, 8 softmax warps
+
+__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
 struct FlashFwdParams {
   __nv_bfloat16* o;      // (rows, d)
@@ -41,13 +52,14 @@ struct FlashFwdSmem {
   static constexpr int OFF_K = OFF_Q + TILE_BYTES;
   static constexpr int OFF_V = OFF_K + 2 * TILE_BYTES;
   static constexpr int OFF_P = OFF_V + 2 * TILE_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_XCH = OFF_P + P_BYTES;        // row-max / row-sum exchange: 3 x 2 x 128 floats
+  static constexpr int OFF_BAR = OFF_XCH + 3 * 2 * 128 * 4;   // two step buffers + one for the final sums
   static constexpr int NUM_BARS = 1 + 4 + 4 + 2 + 2 + 2;  // q, k full/empty, v full/empty, s full/empty, p full/empty
   static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
 };
 
 template <int DH>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(FA_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParams p) {
   using L = FlashFwdSmem<DH>;
   extern __shared__ uint8_t smem_raw[];
@@ -91,9 +103,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&s_empty[i], 256);
     }
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_init(p_empty, 1);
     *abort_word = 0;
     fence_barrier_init();
@@ -187,48 +199,59 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
     }
   } else if (active) {
     // ----------------------------------------------------------------- softmax warps
+    // Two warpgroups share every row: warpgroup g owns score columns [64g, 64g+64) and output
+    // columns [g*DH/2, (g+1)*DH/2).  They exchange the row maximum once per step through shared
+    // memory; the row sum is kept as two partial sums and combined at the end.
     const int quarter = warp & 3;
+    const int wg = (warp - 2) >> 2;             // 0 or 1
     const int r = quarter * 32 + lane;          // row inside the query tile
     const int q_idx = q0 + r;                   // position inside the sequence
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-    float m_run = -INFINITY;                    // running max in scaled log2 units
-    float l_run = 0.f;
-    uint8_t* p_row = smem + L::OFF_P + r * 128;
+    float m_run = -INFINITY;                    // running max in scaled log2 units (identical in both halves)
+    float l_run = 0.f;                          // this half's part of the row sum
+    uint8_t* p_row = smem + L::OFF_P + wg * 16384 + r * 128;
+    float* xch = reinterpret_cast<float*>(smem + L::OFF_XCH);   // [2 steps][2 halves][128 rows]
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int st = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&s_full[st], ph, abort_word)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t s[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + lane_addr + st * 128 + c * 32, s[c]);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&s_empty[st]);
-      const bool diag = (j == n_kv - 1);
-      const int k0 = j * FA_BK;
       float mx = -INFINITY;
+      uint32_t s[2][32];
+      if (ok && !mbar_wait(&s_full[st], ph, abort_word)) ok = false;
+      if (ok) {
+        tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c) tmem_ld_32x32(tmem_s + lane_addr + st * 128 + wg * 64 + c * 32, s[c]);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&s_empty[st]);
+        const bool diag = (j == n_kv - 1);
+        const int k0 = j * FA_BK + wg * 64;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(s[c][i]) * p.scale_log2;
-          if (diag && (k0 + c * 32 + i > q_idx)) v = -INFINITY;
-          s[c][i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float v = __uint_as_float(s[c][i]) * p.scale_log2;
+            if (diag && (k0 + c * 32 + i > q_idx)) v = -INFINITY;
+            s[c][i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+        xch[(st * 2 + wg) * 128 + r] = mx;
+      }
+      named_barrier_sync(1, 256);               // reached by all 256 softmax threads every step
+      if (!ok) continue;
+      mx = fmaxf(mx, xch[(st * 2 + (wg ^ 1)) * 128 + r]);
       // Lazy rescale: keep the old reference max unless it moved by more than 8 (a factor 256).
       float m_new = m_run;
       if (mx > m_run + 8.f) m_new = mx;
       const bool need = m_new != m_run;
-      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+      const float alpha = (m_run == -INFINITY) ? 0.f : fa_exp2(m_run - m_new);
       float sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float e = exp2f(__uint_as_float(s[c][i]) - m_new);
+          const float e = fa_exp2(__uint_as_float(s[c][i]) - m_new);
           sum += e;
           s[c][i] = __float_as_uint(e);
         }
@@ -236,50 +259,53 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
       m_run = m_new;
       // P_{j-1} V_{j-1} must have finished before P is overwritten or O is rescaled.
       if (j > 0) {
-        if (!mbar_wait(p_empty, (j - 1) & 1, abort_word)) { ok = false; break; }
+        if (!mbar_wait(p_empty, (j - 1) & 1, abort_word)) { ok = false; continue; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, need)) {
           const float f = need ? alpha : 1.f;
 #pragma unroll 1
-          for (int c = 0; c < DH / 16; ++c) {
+          for (int c = 0; c < DH / 32; ++c) {   // this warpgroup's half of the output columns
             uint32_t o[16];
-            tmem_ld_32x16(tmem_o + lane_addr + c * 16, o);
+            const uint32_t col = wg * (DH / 2) + c * 16;
+            tmem_ld_32x16(tmem_o + lane_addr + col, o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st_32x16(tmem_o + lane_addr + c * 16, o);
+            tmem_st_32x16(tmem_o + lane_addr + col, o);
           }
           tmem_st_wait();
         }
       }
-      // P row -> swizzled smem: 16-byte chunk c16 of panel pn lands at chunk (c16 ^ (r & 7)).
+      // P row -> swizzled smem (panel = warpgroup): 16-byte chunk c16 lands at chunk (c16 ^ (r & 7)).
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const int key = c * 32 + q * 8;
-          const int pn = key >> 6, c16 = (key & 63) >> 3;
+          const int c16 = c * 4 + q;
           uint4 v = make_uint4(pack_bf16x2(__uint_as_float(s[c][q * 8 + 0]), __uint_as_float(s[c][q * 8 + 1])),
                                pack_bf16x2(__uint_as_float(s[c][q * 8 + 2]), __uint_as_float(s[c][q * 8 + 3])),
                                pack_bf16x2(__uint_as_float(s[c][q * 8 + 4]), __uint_as_float(s[c][q * 8 + 5])),
                                pack_bf16x2(__uint_as_float(s[c][q * 8 + 6]), __uint_as_float(s[c][q * 8 + 7])));
-          *reinterpret_cast<uint4*>(p_row + pn * 16384 + ((c16 ^ (r & 7)) << 4)) = v;
+          *reinterpret_cast<uint4*>(p_row + ((c16 ^ (r & 7)) << 4)) = v;
         }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
     }
     // ------------------------------------------------------------------- epilogue
+    xch[512 + wg * 128 + r] = l_run;            // combine the two partial row sums (own buffer: no reuse hazard)
+    named_barrier_sync(1, 256);
+    const float l_tot = l_run + xch[512 + (wg ^ 1) * 128 + r];
     if (ok && n_kv > 0) ok = mbar_wait(p_empty, (n_kv - 1) & 1, abort_word);
     if (ok) {
       tc_fence_after();
-      const float inv_l = 1.f / l_run;
+      const float inv_l = 1.f / l_tot;
       const bool valid = q_idx < seq_len;
-      __nv_bfloat16* orow = p.o + (size_t)(row_base + q_idx) * p.d + h * DH;
+      __nv_bfloat16* orow = p.o + (size_t)(row_base + q_idx) * p.d + h * DH + wg * (DH / 2);
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = 0; c < DH / 64; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32(tmem_o + lane_addr + c * 32, o);
+        tmem_ld_32x32(tmem_o + lane_addr + wg * (DH / 2) + c * 32, o);
         tmem_ld_wait();
         if (valid) {
 #pragma unroll
@@ -292,8 +318,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
           }
         }
       }
-      if (valid && p.lse != nullptr)
-        p.lse[((size_t)b * p.heads + h) * p.seq + q_idx] = (m_run + log2f(l_run)) * 0.6931471805599453f;
+      if (wg == 0 && valid && p.lse != nullptr)
+        p.lse[((size_t)b * p.heads + h) * p.seq + q_idx] = (m_run + log2f(l_tot)) * 0.6931471805599453f;
     } else if (lane == 0) {
       *abort_word = ERR_WAIT_TMEM_FULL;
     }
@@ -324,7 +350,7 @@ static int launch_flash_fwd(const CUtensorMap& tm, const FlashFwdParams& p, cuda
     configured = true;
   }
   const int grid = p.batch * p.heads * p.n_qblk;
-  kern<<<grid, 192, L::TOTAL, stream>>>(tm, p);
+  kern<<<grid, FA_THREADS, L::TOTAL, stream>>>(tm, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
