@@ -59,12 +59,12 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
 }
 
 // The element-wise stage of both kernels is spread over BWD_CG warpgroups: warpgroup g handles
-// columns [g*BWD_COLS, (g+1)*BWD_COLS) of every 64-column step, so 16 warps (4 per scheduler) hide each
+// columns [g*BWD_COLS, (g+1)*BWD_COLS) of every 64-column step, so 8 warps (2 per scheduler) hide each
 // other's TMEM-load, exp2 and shared-memory latencies instead of one warp per scheduler.
 constexpr int BWD_RING = 3;   // TMA ring depth for the per-step tiles: the load of step t+2 is in flight during step t
-constexpr int BWD_CG = 4;
-constexpr int BWD_COLS = 64 / BWD_CG;                 // 16 columns per thread and step
-constexpr int BWD_COMPUTE_THREADS = 128 * BWD_CG;     // 512
+constexpr int BWD_CG = 2;
+constexpr int BWD_COLS = 64 / BWD_CG;                 // 32 columns per thread and step
+constexpr int BWD_COMPUTE_THREADS = 128 * BWD_CG;     // 256
 constexpr int BWD_THREADS = 64 + BWD_COMPUTE_THREADS; // + TMA warp + MMA warp
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -77,12 +77,12 @@ __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-// Write 16 bf16 values (chunks 2*cg and 2*cg+1 of one 128-byte row of a 128B-swizzled panel).
-__device__ __forceinline__ void store_row16_swizzled(uint8_t* panel, int r, int cg, const float (&v)[16]) {
+// Write BWD_COLS bf16 values (this column group's 16-byte chunks of one 128-byte row of a 128B-swizzled panel).
+__device__ __forceinline__ void store_row16_swizzled(uint8_t* panel, int r, int cg, const float (&v)[BWD_COLS]) {
   uint8_t* row = panel + r * 128;
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int c16 = cg * 2 + j;
+  for (int j = 0; j < BWD_COLS / 8; ++j) {
+    const int c16 = cg * (BWD_COLS / 8) + j;
     uint4 u = make_uint4(pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]), pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]),
                          pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]), pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]));
     *reinterpret_cast<uint4*>(row + ((c16 ^ (r & 7)) << 4)) = u;
@@ -297,24 +297,31 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
       if (!mbar_wait(&s_full[st], ph, abort_word)) { ok = false; continue; }
       tc_fence_after();
       uint32_t sreg[BWD_COLS], dreg[BWD_COLS];
-      tmem_ld_32x16(tm_st + lane_addr + st * 64 + cg * BWD_COLS, sreg);
-      tmem_ld_32x16(tm_dpt + lane_addr + st * 64 + cg * BWD_COLS, dreg);
+      tmem_ld_32x32(tm_st + lane_addr + st * 64 + cg * BWD_COLS, sreg);
+      tmem_ld_32x32(tm_dpt + lane_addr + st * 64 + cg * BWD_COLS, dreg);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&s_empty[st]);
       const bool need_mask = (qb < k0 + 128);   // tile touches the diagonal
       float pv[BWD_COLS], dsv[BWD_COLS];
+      const float* lse_v = lse_s + st * 64 + cg * BWD_COLS;       // lse * log2(e); +inf marks a padded query
+      const float* dlt_v = delta_s + st * 64 + cg * BWD_COLS;
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < BWD_COLS; ++c) {
-        const int col = cg * BWD_COLS + c;
-        const float sv = __uint_as_float(sreg[c]);
-        const float dp = __uint_as_float(dreg[c]);
-        const float lse2 = lse_s[st * 64 + col];
-        float pe = fast_exp2(sv * p.scale_log2 - lse2);
-        const bool dead = (lse2 == INFINITY) || (need_mask && (qb + col < key_idx));
-        pe = dead ? 0.f : pe;
-        pv[c] = pe;
-        dsv[c] = dead ? 0.f : pe * (dp - delta_s[st * 64 + col]) * p.scale;
+        for (int c = 0; c < BWD_COLS; ++c) {
+          const int col = cg * BWD_COLS + c;
+          float pe = fast_exp2(__uint_as_float(sreg[c]) * p.scale_log2 - lse_v[c]);   // exp2(-inf) = 0 for padded queries
+          pe = (qb + col < key_idx) ? 0.f : pe;
+          pv[c] = pe;
+          dsv[c] = pe * (__uint_as_float(dreg[c]) - dlt_v[c]) * p.scale;
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < BWD_COLS; ++c) {
+          const float pe = fast_exp2(__uint_as_float(sreg[c]) * p.scale_log2 - lse_v[c]);
+          pv[c] = pe;
+          dsv[c] = pe * (__uint_as_float(dreg[c]) - dlt_v[c]) * p.scale;
+        }
       }
       // buffer st was last read by the MMAs of step t-2
       if (!mbar_wait(&p_empty[st], ph ^ 1, abort_word)) { ok = false; continue; }
@@ -534,7 +541,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
     const bool valid = q_idx < p.seq;
     const size_t vec = ((size_t)b * p.heads + h) * p.seq + q_idx;
     const float lse2 = valid ? p.lse[vec] * 1.4426950408889634f : INFINITY;
-    const float dlt = valid ? p.delta[vec] : 0.f;
+    const float dlt_scaled = valid ? p.delta[vec] * p.scale : 0.f;
     bool ok = true;
     for (int t = 0; t < n_steps; ++t) {
       const int st = t & 1;
@@ -543,21 +550,28 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
       if (!mbar_wait(&s_full[st], ph, abort_word)) { ok = false; break; }
       tc_fence_after();
       uint32_t sreg[BWD_COLS], dreg[BWD_COLS];
-      tmem_ld_32x16(tm_s + lane_addr + st * 64 + cg * BWD_COLS, sreg);
-      tmem_ld_32x16(tm_dp + lane_addr + st * 64 + cg * BWD_COLS, dreg);
+      tmem_ld_32x32(tm_s + lane_addr + st * 64 + cg * BWD_COLS, sreg);
+      tmem_ld_32x32(tm_dp + lane_addr + st * 64 + cg * BWD_COLS, dreg);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&s_empty[st]);
       const bool need_mask = (kb + 64 > q0);
       float dsv[BWD_COLS];
+      // lse2 is +inf for padded query rows, so their probabilities are exactly zero
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < BWD_COLS; ++c) {
-        const int col = cg * BWD_COLS + c;
-        const float sv = __uint_as_float(sreg[c]);
-        const float dp = __uint_as_float(dreg[c]);
-        const float pe = fast_exp2(sv * p.scale_log2 - lse2);
-        const bool dead = !valid || (need_mask && (kb + col > q_idx));
-        dsv[c] = dead ? 0.f : pe * (dp - dlt) * p.scale;
+        for (int c = 0; c < BWD_COLS; ++c) {
+          const int col = cg * BWD_COLS + c;
+          float pe = fast_exp2(__uint_as_float(sreg[c]) * p.scale_log2 - lse2);
+          pe = (kb + col > q_idx) ? 0.f : pe;
+          dsv[c] = pe * (__uint_as_float(dreg[c]) * p.scale - dlt_scaled);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < BWD_COLS; ++c) {
+          const float pe = fast_exp2(__uint_as_float(sreg[c]) * p.scale_log2 - lse2);
+          dsv[c] = pe * (__uint_as_float(dreg[c]) * p.scale - dlt_scaled);
+        }
       }
       if (!mbar_wait(&p_empty[st], ph ^ 1, abort_word)) { ok = false; break; }
       store_row16_swizzled(smem + L::OFF_DS + st * 16384, r, cg, dsv);
