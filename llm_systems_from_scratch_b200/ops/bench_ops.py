@@ -1,0 +1,146 @@
+"""Micro-benchmarks of the hand-written kernels (CUDA-event timing, L2 flushed between iterations).
+
+    python -m llm_systems_from_scratch_b200.ops.bench_ops gemm            # training GEMM shapes vs cuBLAS
+    python -m llm_systems_from_scratch_b200.ops.bench_ops attention       # FlashAttention fwd/bwd vs SDPA
+    python -m llm_systems_from_scratch_b200.ops.bench_ops elementwise     # bandwidth-bound kernels vs the copy roofline
+    python -m llm_systems_from_scratch_b200.ops.bench_ops gemm-small      # one small GEMM, three launches (for ncu)
+    python -m llm_systems_from_scratch_b200.ops.bench_ops attention-small # one small attention fwd+bwd (for ncu)
+
+Each line of output is one JSON record.  The "-small" modes exist so that a profiler capture ends by
+itself in seconds: inputs are larger than L2 but only a few hundred MB.
+"""
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+from . import attention, native
+
+
+def timeit(fn, iters: int = 10, warm: int = 3, flush: bool = True) -> float:
+    """Median milliseconds of ``fn`` over ``iters`` runs; L2 is overwritten between runs."""
+    scrub = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if scrub is not None:
+            scrub.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def _operands(layout, m, n, k):
+    if layout == "nt":
+        return torch.randn(m, k, device="cuda").bfloat16(), torch.randn(n, k, device="cuda").bfloat16()
+    if layout == "nn":
+        return torch.randn(m, k, device="cuda").bfloat16(), torch.randn(k, n, device="cuda").bfloat16()
+    return torch.randn(k, m, device="cuda").bfloat16(), torch.randn(k, n, device="cuda").bfloat16()
+
+
+GEMM_SHAPES = [("nt", 16384, 6144, 2048), ("nt", 16384, 2048, 2048), ("nt", 16384, 11008, 2048),
+               ("nt", 16384, 2048, 5504), ("nn", 16384, 2048, 6144), ("nn", 16384, 2048, 11008),
+               ("nn", 16384, 5504, 2048), ("tn", 6144, 2048, 16384), ("tn", 11008, 2048, 16384),
+               ("tn", 2048, 5504, 16384), ("nt", 16384, 50264, 2048), ("nt", 8192, 8192, 8192),
+               ("nt", 64, 6144, 2048), ("nt", 64, 2048, 5504), ("nt", 64, 50264, 2048)]
+
+
+def bench_gemm():
+    for layout, m, n, k in GEMM_SHAPES:
+        a, b = _operands(layout, m, n, k)
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        t = timeit(lambda: native.gemm(a, b, layout, out=out))
+        ref = {"nt": lambda: torch.matmul(a, b.t(), out=out), "nn": lambda: torch.matmul(a, b, out=out),
+               "tn": lambda: torch.matmul(a.t(), b, out=out)}[layout]
+        t2 = timeit(ref)
+        native.check_status()
+        flops = 2.0 * m * n * k
+        print(json.dumps({"op": "gemm", "layout": layout, "m": m, "n": n, "k": k, "ms": round(t, 4),
+                          "tflops": round(flops / t / 1e9, 1), "cublas_ms": round(t2, 4),
+                          "cublas_tflops": round(flops / t2 / 1e9, 1)}), flush=True)
+
+
+def bench_attention():
+    for b, s, h, dh in [(8, 2048, 16, 128), (16, 1024, 12, 64), (2, 4096, 32, 128)]:
+        qkv = torch.randn(b * s, 3 * h * dh, device="cuda").bfloat16()
+        flops = 4.0 * b * h * s * s * dh / 2
+        o, lse = attention.attention_fwd(qkv, b, s, h)
+        do = torch.randn_like(o)
+        t_f = timeit(lambda: attention.attention_fwd(qkv, b, s, h))
+        t_b = timeit(lambda: attention.attention_bwd(do, qkv, o, lse, b, s, h))
+        q, k, v = (x.reshape(b, s, h, dh).transpose(1, 2).detach().requires_grad_() for x in
+                   qkv.view(b * s, 3, h * dh).unbind(1))
+        oo = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+        g = torch.randn_like(oo)
+        t_sf = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True))
+        t_sb = timeit(lambda: torch.autograd.grad(oo, (q, k, v), g, retain_graph=True))
+        native.check_status()
+        print(json.dumps({"op": "attention", "shape": [b, s, h, dh], "fwd_ms": round(t_f, 4),
+                          "fwd_tflops": round(flops / t_f / 1e9, 1), "bwd_ms": round(t_b, 4),
+                          "bwd_tflops": round(2.5 * flops / t_b / 1e9, 1), "sdpa_fwd_ms": round(t_sf, 4),
+                          "sdpa_bwd_ms": round(t_sb, 4)}), flush=True)
+
+
+def bench_elementwise():
+    rows, d, f = 16384, 2048, 5504
+    x = torch.randn(rows, d, device="cuda").bfloat16()
+    w = torch.ones(d, device="cuda").bfloat16()
+    dy = torch.randn_like(x)
+    gu = torch.randn(rows, 2 * f, device="cuda").bfloat16()
+    dh = torch.randn(rows, f, device="cuda").bfloat16()
+    _, rstd = native.rmsnorm_fwd(x, w, 1e-5)
+    n = 64 << 20
+    p, g, m, v = (torch.randn(n, device="cuda") for _ in range(4))
+    v.abs_()
+    mirror = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    cases = [("rmsnorm_fwd", lambda: native.rmsnorm_fwd(x, w, 1e-5), 2 * x.numel() * 2),
+             ("rmsnorm_bwd", lambda: native.rmsnorm_bwd(dy, x, w, rstd, dres=dy), 4 * x.numel() * 2),
+             ("silu_mul_fwd", lambda: native.silu_mul_fwd(gu), 3 * rows * f * 2),
+             ("silu_mul_bwd", lambda: native.silu_mul_bwd(dh, gu), 5 * rows * f * 2),
+             ("adamw", lambda: native.adamw_step(p, g, m, v, mirror, 1e-3, 0.9, 0.95, 1e-8, 0.1, 3), n * 30)]
+    for name, fn, nbytes in cases:
+        t = timeit(fn)
+        print(json.dumps({"op": name, "ms": round(t, 4), "gb_per_s": round(nbytes / t / 1e6, 1)}), flush=True)
+
+
+def gemm_small():
+    a, b = _operands("nt", 8192, 6144, 2048)
+    out = torch.empty(8192, 6144, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        native.gemm(a, b, "nt", out=out, bn_hint=256)
+    torch.cuda.synchronize()
+    native.check_status()
+    print(json.dumps({"op": "gemm-small", "ok": True}))
+
+
+def attention_small():
+    b, s, h, dh = 4, 2048, 16, 128
+    qkv = torch.randn(b * s, 3 * h * dh, device="cuda").bfloat16()
+    o, lse = attention.attention_fwd(qkv, b, s, h)
+    do = torch.randn_like(o)
+    for _ in range(2):
+        attention.attention_fwd(qkv, b, s, h)
+        attention.attention_bwd(do, qkv, o, lse, b, s, h)
+    torch.cuda.synchronize()
+    native.check_status()
+    print(json.dumps({"op": "attention-small", "ok": True}))
+
+
+def main(argv=None):
+    argv = argv if argv is not None else sys.argv[1:]
+    mode = argv[0] if argv else "gemm"
+    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "gemm-small": gemm_small,
+     "attention-small": attention_small}[mode]()
+
+
+if __name__ == "__main__":
+    main()
