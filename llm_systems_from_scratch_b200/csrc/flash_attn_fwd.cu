@@ -227,15 +227,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
         mbar_arrive(&s_empty[st]);
         const bool diag = (j == n_kv - 1);
         const int k0 = j * FA_BK + wg * 64;
+        // row maximum over the raw scores (the softmax scale is positive, so it is applied afterwards)
+        if (diag) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float v = __uint_as_float(s[c][i]) * p.scale_log2;
-            if (diag && (k0 + c * 32 + i > q_idx)) v = -INFINITY;
-            s[c][i] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
-          }
+            for (int i = 0; i < 32; ++i) {
+              if (k0 + c * 32 + i > q_idx) s[c][i] = 0xff800000u;   // -inf
+              mx = fmaxf(mx, __uint_as_float(s[c][i]));
+            }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+        }
+        mx *= p.scale_log2;
         xch[(st * 2 + wg) * 128 + r] = mx;
       }
       named_barrier_sync(1, 256);               // reached by all 256 softmax threads every step
@@ -251,7 +258,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
       for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float e = fa_exp2(__uint_as_float(s[c][i]) - m_new);
+          const float e = fa_exp2(fmaf(__uint_as_float(s[c][i]), p.scale_log2, -m_new));   // exp2(-inf) = 0 for masked keys
           sum += e;
           s[c][i] = __float_as_uint(e);
         }

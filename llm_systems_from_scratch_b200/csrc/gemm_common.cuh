@@ -1,0 +1,114 @@
+// Shared pieces of the tcgen05 GEMM kernels: problem description, tile order and the fused epilogue.
+#pragma once
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+
+enum GemmEpilogue : int {
+  EPI_BF16 = 0,       // C = bf16(acc)
+  EPI_F32 = 1,        // C = acc (fp32)
+  EPI_BF16_RES = 2,   // C = bf16(acc + R)   (R bf16, may alias C)
+  EPI_F32_ACC = 3,    // C += acc (fp32 read-modify-write)
+};
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const void* R;
+  long long ldr;
+  int epi;
+  int num_m_tiles, num_n_tiles, group_m;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& m_blk, int& n_blk) {
+  const int per_group = p.group_m * p.num_n_tiles;
+  const int g = tile / per_group;
+  const int first_m = g * p.group_m;
+  const int gm = min(p.group_m, p.num_m_tiles - first_m);
+  const int r = tile - g * per_group;
+  m_blk = first_m + r % gm;
+  n_blk = r / gm;
+}
+
+__device__ __forceinline__ void report(const GemmParams& p, volatile uint32_t* abort_word, uint32_t code) {
+  *abort_word = code;
+  if (p.status != nullptr) atomicCAS(p.status, 0u, code | (blockIdx.x << 8));
+}
+
+// One 32-column chunk of one output row.
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int col0, const uint32_t (&acc)[32]) {
+  if (row >= p.M) return;
+  const int ncols = min(32, p.N - col0);
+  if (ncols <= 0) return;
+  if (p.epi == EPI_BF16 || p.epi == EPI_BF16_RES) {
+    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+    const bool vec_ok = (ncols == 32) && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    if (p.epi == EPI_BF16_RES) {
+      const __nv_bfloat16* r = reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)row * p.ldr + col0;
+      const bool rvec = vec_ok && ((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+      if (rvec) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 rv = *reinterpret_cast<const uint4*>(r + j * 8);
+          const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            float2 f = unpack_bf16x2(rr[t]);
+            o[t] = pack_bf16x2(__uint_as_float(acc[j * 8 + 2 * t]) + f.x,
+                               __uint_as_float(acc[j * 8 + 2 * t + 1]) + f.y);
+          }
+          *reinterpret_cast<uint4*>(c + j * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      } else {
+        for (int j = 0; j < ncols; ++j)
+          c[j] = __float2bfloat16(__uint_as_float(acc[j]) + __bfloat162float(r[j]));
+      }
+    } else if (vec_ok) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t o[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          o[t] = pack_bf16x2(__uint_as_float(acc[j * 8 + 2 * t]), __uint_as_float(acc[j * 8 + 2 * t + 1]));
+        *reinterpret_cast<uint4*>(c + j * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    } else {
+      for (int j = 0; j < ncols; ++j) c[j] = __float2bfloat16(__uint_as_float(acc[j]));
+    }
+  } else {
+    float* c = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+    const bool vec_ok = (ncols == 32) && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    if (p.epi == EPI_F32) {
+      if (vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(c + j * 4) = make_uint4(acc[j * 4], acc[j * 4 + 1], acc[j * 4 + 2], acc[j * 4 + 3]);
+      } else {
+        for (int j = 0; j < ncols; ++j) c[j] = __uint_as_float(acc[j]);
+      }
+    } else {  // EPI_F32_ACC
+      if (vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 v = *reinterpret_cast<float4*>(c + j * 4);
+          v.x += __uint_as_float(acc[j * 4]);
+          v.y += __uint_as_float(acc[j * 4 + 1]);
+          v.z += __uint_as_float(acc[j * 4 + 2]);
+          v.w += __uint_as_float(acc[j * 4 + 3]);
+          *reinterpret_cast<float4*>(c + j * 4) = v;
+        }
+      } else {
+        for (int j = 0; j < ncols; ++j) c[j] += __uint_as_float(acc[j]);
+      }
+    }
+  }
+}
+
+}  // namespace b200

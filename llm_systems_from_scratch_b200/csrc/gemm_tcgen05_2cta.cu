@@ -1,0 +1,313 @@
+// bf16 GEMM on CTA pairs (tcgen05 cta_group::2): two SMs of a cluster cooperate on one 256 x 256 output
+// tile.  Each CTA loads its own 128 rows of A and one half (128 rows) of the B tile; the tensor cores of
+// both SMs consume both halves of B, so per FLOP a CTA writes and reads a third less shared memory than
+// the single-CTA kernel in gemm_tcgen05.cu, whose tensor pipe is capped by shared-memory bandwidth
+// (TMA writes + MMA operand reads need 192 B/clk/SM there, 128 here).
+//
+// Roles (per CTA): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only; both allocate TMEM),
+// warps 2-5 epilogue.  Synchronisation inside the pair:
+//   full[s]        lives in the leader; both CTAs' TMA loads complete their bytes on it
+//   empty[s]       one per CTA; the leader's tcgen05.commit arrives on both (commit multicast)
+//   tmem_full[a]   one per CTA; commit multicast
+//   tmem_empty[a]  lives in the leader; the 2 x 128 epilogue threads of the pair arrive on it
+// TMA loads are ordinary (non-multicast) loads.  Every wait is bounded (see ptx.cuh).
+#include "gemm_common.cuh"
+
+namespace b200 {
+
+int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+                      uint32_t box_rows);
+
+constexpr int P_BN = 256;        // tile columns of the pair
+constexpr int P_HALF = 128;      // B rows held by one CTA
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = BM * BK * 2;       // 16 KB
+constexpr int P_B_BYTES = P_HALF * BK * 2;   // 16 KB
+constexpr int P_DATA = P_STAGES * (P_A_BYTES + P_B_BYTES);
+constexpr int P_BARS = 2 * P_STAGES + 4;
+constexpr int P_SMEM = P_DATA + P_BARS * 8 + 16 + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local_smem_addr` inside CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tiled load whose byte count is signalled on a barrier given by its shared::cluster address
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tm, uint32_t bar_cluster_addr,
+                                                 int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* holder, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_pair_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on the barrier at the same shared-memory offset in both CTAs of the pair once the MMAs issued so
+// far have completed
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + P_STAGES * P_A_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_DATA);
+  uint64_t* empty_bar = full_bar + P_STAGES;
+  uint64_t* tmem_full = empty_bar + P_STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile uint32_t* abort_word = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  constexpr uint32_t TMEM_COLS = 512;   // two accumulators of 256 columns
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 256);
+    }
+    *abort_word = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_holder, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // the peer's barriers are initialised before anything can arrive on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;   // tiles of 256 x 256
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int m_blk, n_blk;
+        tile_coords(tile, p, m_blk, n_blk);
+        const int m0 = m_blk * 256 + (int)rank * BM;
+        const int n0 = n_blk * P_BN + (int)rank * P_HALF;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word)) {
+            report(p, abort_word, ERR_WAIT_EMPTY);
+            ok = false;
+            break;
+          }
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * (P_A_BYTES + P_B_BYTES));
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);   // the leader's barrier
+          uint8_t* a_dst = smem_a + stage * P_A_BYTES;
+          uint8_t* b_dst = smem_b + stage * P_B_BYTES;
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(a_dst + j * 8192, &tmA, bar, m0 + j * 64, k0);
+          } else {
+            tma_load_2d_pair(a_dst, &tmA, bar, k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < P_HALF / 64; ++j) tma_load_2d_pair(b_dst + j * 8192, &tmB, bar, n0 + j * 64, k0);
+          } else {
+            tma_load_2d_pair(b_dst, &tmB, bar, k0, n0);
+          }
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, P_BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0, acc_phase[2] = {0, 0};
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1, abort_word)) {
+          report(p, abort_word, ERR_WAIT_TMEM_EMPTY);
+          ok = false;
+          break;
+        }
+        acc_phase[acc] ^= 1;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * P_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word)) {
+            report(p, abort_word, ERR_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem_a + stage * P_A_BYTES);
+          const uint32_t b_base = smem_u32(smem_b + stage * P_B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = A_MN ? make_smem_desc(a_base + k * (UMMA_K * 128), 8192, 1024)
+                                         : make_smem_desc(a_base + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc = B_MN ? make_smem_desc(b_base + k * (UMMA_K * 128), 8192, 1024)
+                                         : make_smem_desc(b_base + k * (UMMA_K * 2), 16, 1024);
+            umma_pair_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage]);   // frees this stage in both CTAs
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit_pair(&tmem_full[acc]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    uint32_t acc_phase[2] = {0, 0};
+    int local = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+      int m_blk, n_blk;
+      tile_coords(tile, p, m_blk, n_blk);
+      const int acc = local & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase[acc], abort_word)) {
+        if (lane == 0) report(p, abort_word, ERR_WAIT_TMEM_FULL);
+        ok = false;
+        break;
+      }
+      acc_phase[acc] ^= 1;
+      tc_fence_after();
+      const int row = m_blk * 256 + (int)rank * BM + quarter * 32 + lane;
+      const int n0 = n_blk * P_BN;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * P_BN;
+#pragma unroll 1
+      for (int c = 0; c < P_BN / 32; ++c) {
+        if (n0 + c * 32 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        epilogue_store(p, row, n0 + c * 32, r);
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));   // the leader owns this barrier
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();      // neither CTA releases TMEM or exits while the other may still signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int sms, cudaStream_t stream) {
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM) != cudaSuccess) return -3;
+    configured = true;
+  }
+  p.num_m_tiles = (p.M + 255) / 256;
+  p.num_n_tiles = (p.N + P_BN - 1) / P_BN;
+  p.group_m = 8;
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  int pairs = sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<pairs * 2, 192, P_SMEM, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Same contract as b200_gemm_bf16 (gemm_tcgen05.cu); tiles are 256 x 256 on CTA pairs.
+extern "C" int b200_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                                   long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int b_mn,
+                                   int epi, uint32_t* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
+    return -10;
+  if (epi == EPI_BF16_RES && R == nullptr) return -11;
+  CUtensorMap tmA, tmB;
+  int rc = a_mn ? make_tmap_bf16_2d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 64)
+                : make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BM);
+  if (rc) return -20 + rc;
+  rc = b_mn ? make_tmap_bf16_2d(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 64)
+            : make_tmap_bf16_2d(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, P_HALF);
+  if (rc) return -30 + rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.R = R; p.ldr = ldr; p.epi = epi; p.status = status;
+  p.num_m_tiles = p.num_n_tiles = p.group_m = 0;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (a_mn && b_mn) return launch_pair<true, true>(tmA, tmB, p, sms, stream);
+  if (a_mn) return launch_pair<true, false>(tmA, tmB, p, sms, stream);
+  if (b_mn) return launch_pair<false, true>(tmA, tmB, p, sms, stream);
+  return launch_pair<false, false>(tmA, tmB, p, sms, stream);
+}

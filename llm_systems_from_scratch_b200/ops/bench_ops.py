@@ -58,14 +58,16 @@ def bench_gemm():
     for layout, m, n, k in GEMM_SHAPES:
         a, b = _operands(layout, m, n, k)
         out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
-        t = timeit(lambda: native.gemm(a, b, layout, out=out))
+        t = timeit(lambda: native.gemm(a, b, layout, out=out, pair=False))
+        t_pair = timeit(lambda: native.gemm(a, b, layout, out=out, pair=True)) if m >= 256 else float("nan")
         ref = {"nt": lambda: torch.matmul(a, b.t(), out=out), "nn": lambda: torch.matmul(a, b, out=out),
                "tn": lambda: torch.matmul(a.t(), b, out=out)}[layout]
         t2 = timeit(ref)
         native.check_status()
         flops = 2.0 * m * n * k
         print(json.dumps({"op": "gemm", "layout": layout, "m": m, "n": n, "k": k, "ms": round(t, 4),
-                          "tflops": round(flops / t / 1e9, 1), "cublas_ms": round(t2, 4),
+                          "tflops": round(flops / t / 1e9, 1), "pair_ms": round(t_pair, 4),
+                          "pair_tflops": round(flops / t_pair / 1e9, 1), "cublas_ms": round(t2, 4),
                           "cublas_tflops": round(flops / t2 / 1e9, 1)}), flush=True)
 
 

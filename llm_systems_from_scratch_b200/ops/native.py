@@ -65,6 +65,7 @@ def _declare(lib):
     P, I, L, F = c_void_p, c_int, c_ll, c_float
     sigs = {
         "b200_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, P, P],
+        "b200_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P],
         "b200_rmsnorm_fwd": [P, P, P, P, I, I, F, P],
         "b200_rmsnorm_bwd_parts": [I],
         "b200_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
@@ -165,8 +166,16 @@ def _rowmajor(t: torch.Tensor, name: str):
 EPI_BF16, EPI_F32, EPI_BF16_RES, EPI_F32_ACC = 0, 1, 2, 3
 
 
-def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, bn_hint=0, max_ctas=0):
-    """bf16 tensor-core GEMM (tcgen05).  layout 'nt' | 'nn' | 'tn' as in ``torch_impl.gemm``."""
+# Problems at least this large (rows of the output) run on CTA pairs (cta_group::2, 256 x 256 tiles).
+PAIR_MIN_M = int(os.environ.get("B200_GEMM_PAIR_MIN_M", "1024"))
+USE_PAIR = os.environ.get("B200_GEMM_PAIR", "1") == "1"
+
+
+def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, bn_hint=0, max_ctas=0,
+         pair=None):
+    """bf16 tensor-core GEMM (tcgen05).  layout 'nt' | 'nn' | 'tn' as in ``torch_impl.gemm``.
+
+    ``pair`` forces (True) or forbids (False) the CTA-pair kernel; by default large problems use it."""
     lib = load()
     _req(a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "gemm inputs must be bf16")
     _rowmajor(a, "a")
@@ -208,6 +217,13 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
         _rowmajor(residual, "residual")
         _req(residual.dtype == torch.bfloat16 and tuple(residual.shape) == (m, n), "residual must be bf16 (M,N)")
         ldr = residual.stride(0)
+    if pair is None:
+        pair = USE_PAIR and bn_hint == 0 and max_ctas == 0 and m >= PAIR_MIN_M and n >= 256
+    if pair:
+        rc = lib.b200_gemm_bf16_pair(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb, out.stride(0),
+                                     ldr, a_mn, b_mn, epi, _ptr(status_word(a.device)), _stream())
+        _check(rc, "b200_gemm_bf16_pair")
+        return out
     rc = lib.b200_gemm_bf16(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb, out.stride(0), ldr,
                             a_mn, b_mn, epi, bn_hint, max_ctas, _ptr(status_word(a.device)), _stream())
     _check(rc, "b200_gemm_bf16")

@@ -96,3 +96,22 @@ def test_gemm_many_tiles_persistent():
     out2 = native.gemm(a, b, "nt", max_ctas=5)
     native.check_status()
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 512), (1000, 1336, 520), (136, 264, 72), (2048, 5504, 2048),
+                                   (4096, 4096, 1024)])
+def test_gemm_cta_pair_kernel(layout, shape):
+    """cta_group::2 kernel (256 x 256 tiles on CTA pairs) against fp32 matmul and the single-CTA kernel."""
+    from llm_systems_from_scratch_b200.ops import native
+    m, n, k = shape
+    a, b = _make(layout, m, n, k, "cuda")
+    out = native.gemm(a, b, layout, out_dtype=torch.float32, pair=True)
+    native.check_status()
+    _check(out, _ref(a, b, layout), k)
+    single = native.gemm(a, b, layout, out_dtype=torch.float32, pair=False)
+    assert torch.allclose(out, single, atol=1e-3 * k ** 0.5, rtol=1e-3)
+    res = torch.randn(m, n, device="cuda").bfloat16()
+    out16 = native.gemm(a, b, layout, residual=res, pair=True)
+    native.check_status()
+    _check(out16, _ref(a, b, layout) + res.float(), k)
