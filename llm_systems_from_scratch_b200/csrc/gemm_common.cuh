@@ -15,7 +15,22 @@ enum GemmEpilogue : int {
   EPI_F32_ACC = 3,    // C += acc (fp32 read-modify-write)
 };
 
+// Optional all-gather carried by a GEMM launch: while the MMA warps work, two copy warps per CTA pull
+// the weight shards of the *next* FSDP unit from every peer GPU into a local buffer (plain 16-byte peer
+// loads, no TMA, no multicast).  `done` is bumped once per CTA when its slice has landed, so a consumer
+// on another stream can wait for `done >= expected` instead of a kernel boundary.
+struct GatherTask {
+  const uint4* src[16];          // shard base address of every rank as mapped on this GPU
+  uint4* dst;                    // local buffer of world * shard_vec vectors; null = no gather
+  unsigned long long shard_vec;  // 16-byte vectors per shard
+  int world, rank;
+  uint32_t* done;
+};
+
 struct GemmParams {
+  GatherTask gather;
+  const uint32_t* wait_counter;  // optional: do not touch operand B before *wait_counter >= wait_value
+  uint32_t wait_value;
   int M, N, K;
   void* C;
   long long ldc;

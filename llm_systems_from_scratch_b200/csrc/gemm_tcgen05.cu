@@ -320,6 +320,8 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.R = R; p.ldr = ldr; p.epi = epi; p.status = status;
   p.num_m_tiles = p.num_n_tiles = p.group_m = 0;
+  p.gather.dst = nullptr; p.gather.done = nullptr; p.gather.shard_vec = 0; p.gather.world = 0; p.gather.rank = 0;
+  p.wait_counter = nullptr; p.wait_value = 0;
 
 #define DISPATCH(BN_)                                                                    \
   if (a_mn && b_mn) return launch_gemm<BN_, true, true>(tmA, tmB, p, max_ctas, stream);   \

@@ -21,6 +21,7 @@ int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t 
 constexpr int P_BN = 256;        // tile columns of the pair
 constexpr int P_HALF = 128;      // B rows held by one CTA
 constexpr int P_STAGES = 6;
+constexpr int P_THREADS = 256;    // TMA warp, MMA warp, 4 epilogue warps, 2 gather-copy warps
 constexpr int P_A_BYTES = BM * BK * 2;       // 16 KB
 constexpr int P_B_BYTES = P_HALF * BK * 2;   // 16 KB
 constexpr int P_DATA = P_STAGES * (P_A_BYTES + P_B_BYTES);
@@ -31,6 +32,11 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -85,7 +91,7 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 }
 
 template <bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -137,6 +143,19 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      if (p.wait_counter != nullptr) {
+        // operand B is being gathered by another kernel: wait (bounded) until every slice has landed
+        const uint64_t t0 = globaltimer_ns();
+        while ((int32_t)(ld_acquire_gpu(p.wait_counter) - p.wait_value) < 0) {
+          if (globaltimer_ns() - t0 > B200_WAIT_LIMIT_NS) {
+            report(p, abort_word, ERR_WAIT_FLAG);
+            ok = false;
+            break;
+          }
+          __nanosleep(128);
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");   // generic-proxy writes -> TMA reads
+      }
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int m_blk, n_blk;
         tile_coords(tile, p, m_blk, n_blk);
@@ -215,6 +234,30 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (ok) umma_commit_pair(&tmem_full[acc]);
       }
     }
+  } else if (warp >= 6) {
+    // ---------------------------------------------------------------- gather-copy warps
+    if (p.gather.dst != nullptr) {
+      const GatherTask& g = p.gather;
+      const int t = (warp - 6) * 32 + lane;                  // 0..63
+      const size_t stride = (size_t)gridDim.x * 64;
+      for (int k = 0; k < g.world; ++k) {
+        const int src_rank = (g.rank + k) % g.world;         // every GPU starts at a different peer
+        const uint4* src = g.src[src_rank];
+        uint4* dst = g.dst + (size_t)src_rank * g.shard_vec;
+        size_t i = (size_t)blockIdx.x * 64 + t;
+        // four independent 16-byte loads in flight per thread hide the NVLink latency
+        for (; i + 3 * stride < g.shard_vec; i += 4 * stride) {
+          const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+          dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+        }
+        for (; i < g.shard_vec; i += stride) dst[i] = src[i];
+      }
+      asm volatile("bar.sync 2, 64;" ::: "memory");         // both copy warps are done
+      if (t == 0 && g.done != nullptr) {
+        __threadfence();
+        atomicAdd(g.done, 1u);
+      }
+    }
   } else {
     const int quarter = warp & 3;
     uint32_t acc_phase[2] = {0, 0};
@@ -276,7 +319,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   int pairs = sms / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<pairs * 2, 192, P_SMEM, stream>>>(tmA, tmB, p);
+  kern<<<pairs * 2, P_THREADS, P_SMEM, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -285,9 +328,10 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
 using namespace b200;
 
 // Same contract as b200_gemm_bf16 (gemm_tcgen05.cu); tiles are 256 x 256 on CTA pairs.
-extern "C" int b200_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
-                                   long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int b_mn,
-                                   int epi, uint32_t* status, cudaStream_t stream) {
+static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
+                          long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int epi,
+                          const GatherTask* gather, const uint32_t* wait_counter, uint32_t wait_value,
+                          uint32_t* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -10;
@@ -303,6 +347,9 @@ extern "C" int b200_gemm_bf16_pair(const void* A, const void* B, void* C, const 
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.R = R; p.ldr = ldr; p.epi = epi; p.status = status;
   p.num_m_tiles = p.num_n_tiles = p.group_m = 0;
+  if (gather != nullptr) p.gather = *gather;
+  else { p.gather.dst = nullptr; p.gather.done = nullptr; p.gather.shard_vec = 0; p.gather.world = 0; p.gather.rank = 0; }
+  p.wait_counter = wait_counter; p.wait_value = wait_value;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -310,4 +357,41 @@ extern "C" int b200_gemm_bf16_pair(const void* A, const void* B, void* C, const 
   if (a_mn) return launch_pair<true, false>(tmA, tmB, p, sms, stream);
   if (b_mn) return launch_pair<false, true>(tmA, tmB, p, sms, stream);
   return launch_pair<false, false>(tmA, tmB, p, sms, stream);
+}
+
+extern "C" int b200_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                                   long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int b_mn,
+                                   int epi, uint32_t* status, cudaStream_t stream) {
+  return gemm_pair_impl(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, epi, nullptr, nullptr, 0, status, stream);
+}
+
+// The same GEMM carrying an all-gather: while the tensor cores work, copy warps pull `shard_bytes` from each
+// of `world` peer shard addresses (`src_ptrs`, host array) into `gather_dst` (rank-major).  `done_counter`
+// (device uint32, may be null) is incremented once per CTA when its slice is complete; the number of CTAs
+// launched is returned through `ctas_out` so that a consumer knows the value to wait for.
+// `wait_counter` / `wait_value` (may be null / 0) make this GEMM wait until its own B operand has been
+// gathered by an earlier carrier that may still be running.
+extern "C" int b200_gemm_bf16_pair_gather(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                                          long long lda, long long ldb, long long ldc, long long ldr, int a_mn,
+                                          int b_mn, int epi, const unsigned long long* src_ptrs, void* gather_dst,
+                                          unsigned long long shard_bytes, int world, int rank,
+                                          uint32_t* done_counter, int* ctas_out, const uint32_t* wait_counter,
+                                          unsigned int wait_value, uint32_t* status, cudaStream_t stream) {
+  if (world > 16 || shard_bytes % 16 || (reinterpret_cast<uintptr_t>(gather_dst) & 15)) return -10;
+  GatherTask g;
+  for (int i = 0; i < 16; ++i) g.src[i] = i < world ? reinterpret_cast<const uint4*>(src_ptrs[i]) : nullptr;
+  g.dst = reinterpret_cast<uint4*>(gather_dst);
+  g.shard_vec = shard_bytes / 16;
+  g.world = world; g.rank = rank; g.done = done_counter;
+  if (ctas_out != nullptr) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = ((M + 255) / 256) * ((N + P_BN - 1) / P_BN);
+    int pairs = sms / 2;
+    if (tiles < pairs) pairs = tiles;
+    *ctas_out = pairs * 2;
+  }
+  return gemm_pair_impl(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, epi, gather_dst ? &g : nullptr,
+                        wait_counter, wait_value, status, stream);
 }

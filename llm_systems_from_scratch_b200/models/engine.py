@@ -72,15 +72,16 @@ class BlockSaved(NamedTuple):
     hh: torch.Tensor
 
 
-def block_forward(x, w: BlockWeights, cfg: EngineConfig, rope_cache, batch: int, seq: int, keep: bool):
-    """x (M, d) -> (y (M, d), saved activations or None)."""
+def block_forward(x, w: BlockWeights, cfg: EngineConfig, rope_cache, batch: int, seq: int, keep: bool, gather=None):
+    """x (M, d) -> (y (M, d), saved activations or None).  ``gather`` is an optional pending all-gather
+    (the next FSDP unit's weights) that the largest GEMM of the block carries."""
     h1, rstd1 = ops.rmsnorm_fwd(x, w.n1, cfg.eps)
     qkv = ops.gemm(h1, w.wqkv, "nt")
     ops.rope_(qkv, rope_cache, None, cfg.n_heads, False, seq)
     o, lse = ops.attention_fwd(qkv, batch, seq, cfg.n_heads)
     x2 = ops.gemm(o, w.wo, "nt", residual=x)
     h2, rstd2 = ops.rmsnorm_fwd(x2, w.n2, cfg.eps)
-    gu = ops.gemm(h2, w.wgu, "nt")
+    gu = ops.gemm(h2, w.wgu, "nt", gather=gather)
     hh = ops.silu_mul_fwd(gu)
     y = ops.gemm(hh, w.wdown, "nt", residual=x2)
     saved = BlockSaved(x, rstd1, h1, qkv, o, lse, x2, rstd2, h2, gu, hh) if keep else None
@@ -88,10 +89,11 @@ def block_forward(x, w: BlockWeights, cfg: EngineConfig, rope_cache, batch: int,
 
 
 def block_backward(dy, w: BlockWeights, s: BlockSaved, gw: BlockWeights, cfg: EngineConfig, rope_cache,
-                   batch: int, seq: int):
-    """Returns dx; writes every weight gradient of the block into the views in ``gw``."""
+                   batch: int, seq: int, gather=None):
+    """Returns dx; writes every weight gradient of the block into the views in ``gw``.  ``gather`` (the
+    previous unit's weights, needed next) rides on the first GEMM."""
     # ---- feed-forward half
-    dhh = ops.gemm(dy, w.wdown, "nn")
+    dhh = ops.gemm(dy, w.wdown, "nn", gather=gather)
     ops.gemm(dy, s.hh, "tn", out=gw.wdown)
     dgu = ops.silu_mul_bwd(dhh, s.gu)
     del dhh
@@ -203,6 +205,9 @@ class LocalProvider:
     def post_forward(self, kind: str, i: int):
         pass
 
+    def take_gather(self, kind: str, i: int):
+        return None
+
     def post_backward(self, kind: str, i: int):
         for h in self.post_backward_hooks:
             h(kind, i)
@@ -216,7 +221,8 @@ class _BlockFn(torch.autograd.Function):
         w = eng.provider.block_weights(i)
         keep = torch.is_grad_enabled() or ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
         cfg = eng.cfg
-        y, saved = block_forward(x, w, cfg, eng.rope_cache, batch, seq, keep and not cfg.recompute)
+        y, saved = block_forward(x, w, cfg, eng.rope_cache, batch, seq, keep and not cfg.recompute,
+                                 gather=eng.provider.take_gather("fwd", i))
         ctx.eng, ctx.i, ctx.batch, ctx.seq = eng, i, batch, seq
         ctx.saved = saved
         ctx.x_in = x if cfg.recompute else None
@@ -232,7 +238,8 @@ class _BlockFn(torch.autograd.Function):
         saved = ctx.saved
         if saved is None:
             _, saved = block_forward(ctx.x_in, w, eng.cfg, eng.rope_cache, ctx.batch, ctx.seq, True)
-        dx = block_backward(dy.contiguous(), w, saved, prov.block_grads(i), eng.cfg, eng.rope_cache, ctx.batch, ctx.seq)
+        dx = block_backward(dy.contiguous(), w, saved, prov.block_grads(i), eng.cfg, eng.rope_cache, ctx.batch, ctx.seq,
+                            gather=prov.take_gather("bwd", i))
         ctx.saved = None
         ctx.x_in = None
         prov.post_backward("block", i)

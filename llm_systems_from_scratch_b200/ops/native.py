@@ -66,6 +66,8 @@ def _declare(lib):
     sigs = {
         "b200_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, P, P],
         "b200_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P],
+        "b200_gemm_bf16_pair_gather": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P, ctypes.c_ulonglong, I, I, P, P,
+                                       P, ctypes.c_uint, P, P],
         "b200_rmsnorm_fwd": [P, P, P, P, I, I, F, P],
         "b200_rmsnorm_bwd_parts": [I],
         "b200_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
@@ -172,7 +174,7 @@ USE_PAIR = os.environ.get("B200_GEMM_PAIR", "1") == "1"
 
 
 def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, bn_hint=0, max_ctas=0,
-         pair=None):
+         pair=None, gather=None):
     """bf16 tensor-core GEMM (tcgen05).  layout 'nt' | 'nn' | 'tn' as in ``torch_impl.gemm``.
 
     ``pair`` forces (True) or forbids (False) the CTA-pair kernel; by default large problems use it."""
@@ -219,6 +221,18 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
         ldr = residual.stride(0)
     if pair is None:
         pair = USE_PAIR and bn_hint == 0 and max_ctas == 0 and m >= PAIR_MIN_M and n >= 256
+    gargs = gather.native_args() if (gather is not None and not gather.done) else None
+    if gather is not None and not gather.done and (gargs is None or not pair):
+        gather.run()           # this launch cannot carry it: stand-alone collective
+        gargs = None
+    if pair and gargs is not None:
+        table, dst, nbytes, world, rank = gargs
+        rc = lib.b200_gemm_bf16_pair_gather(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb,
+                                            out.stride(0), ldr, a_mn, b_mn, epi, table, dst, nbytes, world, rank,
+                                            None, None, None, 0, _ptr(status_word(a.device)), _stream())
+        _check(rc, "b200_gemm_bf16_pair_gather")
+        gather.mark_done()
+        return out
     if pair:
         rc = lib.b200_gemm_bf16_pair(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb, out.stride(0),
                                      ldr, a_mn, b_mn, epi, _ptr(status_word(a.device)), _stream())

@@ -19,8 +19,11 @@ def _f(x: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- GEMM
-def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False):
-    """layout 'nt': a(M,K) b(N,K) -> a@b.T ; 'nn': a(M,K) b(K,N) ; 'tn': a(K,M) b(K,N) -> a.T@b."""
+def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, gather=None):
+    """layout 'nt': a(M,K) b(N,K) -> a@b.T ; 'nn': a(M,K) b(K,N) ; 'tn': a(K,M) b(K,N) -> a.T@b.
+    ``gather`` (a pending all-gather that the CUDA kernel would carry) is simply performed first."""
+    if gather is not None:
+        gather.run()
     af, bf = _f(a), _f(b)
     if layout == "nt":
         r = af @ bf.t()

@@ -20,6 +20,36 @@ import torch
 import torch.distributed as dist
 
 
+class GatherTask:
+    """An all-gather that has been decided but not launched yet.
+
+    A GEMM launch can carry it (``ops.gemm(..., gather=task)``): on the CTA-pair tensor-core kernel two
+    extra warps per CTA pull the shards from peer memory while the MMA warps compute, so the gather costs
+    no launch of its own and overlaps the math tile by tile.  Anywhere else ``run()`` performs it as a
+    stand-alone collective.  Either way ``done`` becomes true.
+    """
+
+    def __init__(self, comm: "Communicator", full: torch.Tensor, shard: torch.Tensor, on_done=None):
+        self.comm, self.full, self.shard, self.on_done = comm, full, shard, on_done
+        self.done = False
+
+    def native_args(self):
+        """(peer pointer table, destination pointer, shard bytes, world, rank) or None when the
+        communicator cannot expose peer addresses for ``shard``."""
+        fn = getattr(self.comm, "gather_args", None)
+        return fn(self.full, self.shard) if fn is not None else None
+
+    def mark_done(self):
+        self.done = True
+        if self.on_done is not None:
+            self.on_done()
+
+    def run(self):
+        if not self.done:
+            self.comm.all_gather(self.full, self.shard)
+            self.mark_done()
+
+
 class Communicator:
     rank: int = 0
     world_size: int = 1

@@ -31,7 +31,7 @@ from torch import nn
 from .. import ops
 from ..models.arena import ParamArena, Segment
 from ..models.engine import block_views, head_views
-from .comm import Communicator, make_communicator
+from .comm import Communicator, GatherTask, make_communicator
 
 
 class _ShardArena(ParamArena):
@@ -132,7 +132,7 @@ class _FSDPProvider:
         if not backward:
             o._wait_gather(u)
             if i + 1 < len(o.layer_units):
-                o._gather(o.layer_units[i + 1])
+                o._gather(o.layer_units[i + 1], defer=True)
         return o._weight_views(u)
 
     def head_weights(self, backward: bool = False):
@@ -162,7 +162,11 @@ class _FSDPProvider:
             o._gather(o.layer_units[i])
             o._wait_gather(o.layer_units[i])
             if i > 0:
-                o._gather(o.layer_units[i - 1])
+                o._gather(o.layer_units[i - 1], defer=True)
+
+    def take_gather(self, kind: str, i: int):
+        task, self.o._deferred = self.o._deferred, None
+        return task
 
     def post_backward(self, kind: str, i: int):
         o = self.o
@@ -175,8 +179,10 @@ class _FSDPProvider:
 
 
 class FSDP(nn.Module):
-    def __init__(self, module: nn.Module, process_group=None, comm: str | Communicator = "auto"):
+    def __init__(self, module: nn.Module, process_group=None, comm: str | Communicator = "auto",
+                 fuse_gather: bool | None = None):
         super().__init__()
+        self._fuse_gather_arg = fuse_gather
         if not hasattr(module, "engine"):
             raise TypeError("FSDP wraps a TransformerLM from this package (it drives the fused engine)")
         self.process_group = process_group
@@ -250,6 +256,9 @@ class FSDP(nn.Module):
         self._views_cache: dict = {}
         self._head_stage_checked = False
         self._fused_opt = None
+        # A gather that a GEMM of the engine will carry (copy warps inside the tensor-core kernel)
+        self.fuse_gather = hasattr(self.comm, "gather_args") if self._fuse_gather_arg is None else self._fuse_gather_arg
+        self._deferred: GatherTask | None = None
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.cuda else None
         self._step_started = False
 
@@ -289,11 +298,12 @@ class FSDP(nn.Module):
             if not sa._mirror_fresh or ver != sa._mirror_versions:
                 ops.cast_copy(sa._mirror, sa.master)
                 sa._mirror_fresh, sa._mirror_versions = True, ver
+        if self.world_size > 1:
+            self.comm.pre_gather_sync()       # every rank's optimizer has finished rewriting its weight shard
         if self.cuda:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
-        if self.world_size > 1:
-            with self._on_comm():
-                self.comm.pre_gather_sync()   # every rank's optimizer has finished rewriting its weight shard
+        if self._deferred is not None:
+            self._deferred = None
         # weights changed since the last gather: drop whatever is still resident
         for u in self.fsdp_units:
             u.flat_full = None
@@ -304,7 +314,7 @@ class FSDP(nn.Module):
         if self.layer_units:
             self._gather(self.layer_units[0])
 
-    def _gather(self, u: FSDPUnit):
+    def _gather(self, u: FSDPUnit, defer: bool = False):
         if u.flat_full is not None:
             return
         if self.world_size == 1:
@@ -316,6 +326,19 @@ class FSDP(nn.Module):
         else:
             slot = u.index % self.n_slots
             buf = self._full_slots[slot][:u.padded_numel]
+        if defer and self.fuse_gather and slot is not None:
+            # Hand the gather to the engine: its next large GEMM carries it on the compute stream, which is
+            # also where the slot's previous occupant was released, so stream order protects the buffer.
+            if self._deferred is not None:
+                self._deferred.run()
+            task = GatherTask(self.comm, buf[:u.padded_numel], u.mirror_shard)
+            self._deferred = task
+            u.pending = task
+            u.gather_event = None
+            u.flat_full = buf[:u.padded_numel]
+            u.slot = slot
+            self._slot_owner[slot] = u
+            return
         with self._on_comm():
             if slot is not None and self._slot_free_ev[slot] is not None:
                 self.comm_stream.wait_event(self._slot_free_ev[slot])
@@ -332,6 +355,13 @@ class FSDP(nn.Module):
     def _wait_gather(self, u: FSDPUnit):
         if u.flat_full is None:
             self._gather(u)
+        pending = getattr(u, "pending", None)
+        if pending is not None:
+            if not pending.done:          # nobody carried it: run it now as a stand-alone collective
+                if self._deferred is pending:
+                    self._deferred = None
+                pending.run()
+            u.pending = None
         if u.gather_event is not None:
             torch.cuda.current_stream().wait_event(u.gather_event)
             u.gather_event = None

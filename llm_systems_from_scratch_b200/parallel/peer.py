@@ -170,6 +170,14 @@ class PeerComm(Communicator):
         native._check(self.lib.b200_peer_allgather(table, full.data_ptr(), nbytes, self.world_size, self.rank, 64,
                                                    self._stream()), "peer_allgather")
 
+    def gather_args(self, full, shard):
+        """Arguments for a GEMM-carried all-gather of ``shard`` into ``full`` (see ``comm.GatherTask``)."""
+        table = self._peer_table(shard)
+        nbytes = shard.numel() * shard.element_size()
+        if table is None or nbytes % 16 or full.data_ptr() % 16:
+            return None
+        return table, full.data_ptr(), nbytes, self.world_size, self.rank
+
     def _reduce_scatter(self, staging, key, mode, grad_out, sumsq, adam):
         table = self._peer_table(staging)
         ready, done = self._rows_for(key)

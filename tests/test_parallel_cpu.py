@@ -57,7 +57,8 @@ def _worker(rank, world, port, mode, native, steps, clip, out_path):
         if rank == 0:
             torch.manual_seed(0)
             model = TransformerLM(**CFG, use_custom_triton=native)
-        wrapped = DDP(model, bucket_size_mb=0.05) if mode == "ddp" else FSDP(model)
+        # fuse_gather=True exercises the deferred-gather bookkeeping (on CPU the GEMM simply runs the gather first)
+        wrapped = DDP(model, bucket_size_mb=0.05) if mode == "ddp" else FSDP(model, fuse_gather=(world == 3))
         opt = FusedAdamW(wrapped.parameters(), lr=1e-2, weight_decay=0.1)
         per = 2
         for s in range(steps):
