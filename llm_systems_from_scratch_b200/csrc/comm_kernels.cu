@@ -73,14 +73,52 @@ __global__ void peer_barrier_kernel(PeerPtrs flag_bases, size_t row_offset, int 
 }
 
 // dst[p * n_vec + i] = src_p[i] for every peer p (16-byte vectors); the local shard is copied too.
-__global__ void peer_allgather_kernel(PeerPtrs src, uint4* __restrict__ dst, size_t n_vec, int world, int rank) {
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (int k = 0; k < world; ++k) {
-    const int p = (rank + k) % world;   // start at a different peer on every rank
-    const uint4* s = reinterpret_cast<const uint4*>(src.p[p]);
-    uint4* d = dst + (size_t)p * n_vec;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_vec; i += stride) d[i] = s[i];
+// A thread keeps WORLD x U loads in flight, one from every peer for U consecutive strides, so that all
+// NVLink ports are busy at once and the round-trip latency is covered.
+template <int WORLD, int U>
+__device__ __forceinline__ void gather_body(const PeerPtrs& src, uint4* __restrict__ dst, size_t n_vec, int rank,
+                                            size_t first, size_t stride) {
+  size_t i = first;
+  for (; i + (U - 1) * stride < n_vec; i += U * stride) {
+    uint4 v[WORLD][U];
+#pragma unroll
+    for (int k = 0; k < WORLD; ++k) {
+      const uint4* s = reinterpret_cast<const uint4*>(src.p[(rank + k) % WORLD]);
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[k][u] = s[i + u * stride];
+    }
+#pragma unroll
+    for (int k = 0; k < WORLD; ++k) {
+      uint4* d = dst + (size_t)((rank + k) % WORLD) * n_vec;
+#pragma unroll
+      for (int u = 0; u < U; ++u) d[i + u * stride] = v[k][u];
+    }
   }
+  for (; i < n_vec; i += stride)
+#pragma unroll
+    for (int k = 0; k < WORLD; ++k) {
+      const int p = (rank + k) % WORLD;
+      dst[(size_t)p * n_vec + i] = reinterpret_cast<const uint4*>(src.p[p])[i];
+    }
+}
+
+__device__ __forceinline__ void gather_any(const PeerPtrs& src, uint4* __restrict__ dst, size_t n_vec, int world,
+                                           int rank, size_t first, size_t stride) {
+  switch (world) {
+    case 2: gather_body<2, 4>(src, dst, n_vec, rank, first, stride); break;
+    case 4: gather_body<4, 2>(src, dst, n_vec, rank, first, stride); break;
+    case 8: gather_body<8, 1>(src, dst, n_vec, rank, first, stride); break;
+    default:
+      for (int k = 0; k < world; ++k) {
+        const int p = (rank + k) % world;
+        for (size_t i = first; i < n_vec; i += stride) dst[(size_t)p * n_vec + i] = reinterpret_cast<const uint4*>(src.p[p])[i];
+      }
+  }
+}
+
+__global__ void peer_allgather_kernel(PeerPtrs src, uint4* __restrict__ dst, size_t n_vec, int world, int rank) {
+  gather_any(src, dst, n_vec, world, rank, blockIdx.x * (size_t)blockDim.x + threadIdx.x,
+             (size_t)gridDim.x * blockDim.x);
 }
 
 struct AdamArgs {
@@ -94,7 +132,7 @@ struct AdamArgs {
 
 // mode 0: grad_out[i] = mean_p staging_p[rank*n + i]  (fp32), sumsq += sum(grad^2) when sumsq != null
 // mode 1: the same mean feeds AdamW directly (grad_out may be null)
-template <int MODE>
+template <int MODE, int WORLD>
 __global__ void __launch_bounds__(512)
 peer_reduce_scatter_kernel(PeerPtrs staging, PeerPtrs flag_bases, size_t ready_row, size_t done_row, float* grad_out,
                            float* sumsq, AdamArgs adam, size_t n, int world, int rank, uint32_t epoch,
@@ -114,9 +152,14 @@ peer_reduce_scatter_kernel(PeerPtrs staging, PeerPtrs flag_bases, size_t ready_r
   float ss = 0.f;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_vec; i += stride) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int p = 0; p < world; ++p) {   // fixed order: bitwise reproducible
-      const uint4 u = reinterpret_cast<const uint4*>(staging.p[p])[(size_t)rank * n_vec + i];
+    uint4 in[WORLD > 0 ? WORLD : 1];
+    if (WORLD > 0) {                    // all peer loads are issued before the first one is consumed
+#pragma unroll
+      for (int p = 0; p < WORLD; ++p) in[p] = reinterpret_cast<const uint4*>(staging.p[p])[(size_t)rank * n_vec + i];
+    }
+#pragma unroll
+    for (int p = 0; p < (WORLD > 0 ? WORLD : world); ++p) {   // fixed order: bitwise reproducible
+      const uint4 u = WORLD > 0 ? in[p] : reinterpret_cast<const uint4*>(staging.p[p])[(size_t)rank * n_vec + i];
       const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
       acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
       acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
@@ -210,8 +253,14 @@ peer_allreduce_kernel(PeerPtrs bufs, PeerPtrs flag_bases, size_t ready_row, size
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = lo + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < hi; i += stride) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < world; ++p) {
-      const float4 u = reinterpret_cast<const float4*>(bufs.p[p])[i];
+    float4 in[MAX_WORLD];
+#pragma unroll
+    for (int p = 0; p < MAX_WORLD; ++p)
+      if (p < world) in[p] = reinterpret_cast<const float4*>(bufs.p[p])[i];   // all loads in flight together
+#pragma unroll
+    for (int p = 0; p < MAX_WORLD; ++p) {
+      if (p >= world) break;
+      const float4 u = in[p];
       acc.x += u.x; acc.y += u.y; acc.z += u.z; acc.w += u.w;
     }
     acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
@@ -288,7 +337,7 @@ extern "C" int b200_peer_allgather(const unsigned long long* src_ptrs, void* dst
                                    int world, int rank, int ctas, cudaStream_t st) {
   if (world > MAX_WORLD || shard_bytes % 16 || (reinterpret_cast<uintptr_t>(dst) & 15)) return -10;
   if (shard_bytes == 0) return 0;
-  peer_allgather_kernel<<<ctas > 0 ? ctas : 64, 512, 0, st>>>(make_ptrs(src_ptrs, world), (uint4*)dst, shard_bytes / 16,
+  peer_allgather_kernel<<<ctas > 0 ? ctas : 128, 512, 0, st>>>(make_ptrs(src_ptrs, world), (uint4*)dst, shard_bytes / 16,
                                                                world, rank);
   COMM_CHECK();
 }
@@ -306,14 +355,21 @@ extern "C" int b200_peer_reduce_scatter(const unsigned long long* staging_ptrs, 
   if (mode == 1 && (master == nullptr || m == nullptr || v == nullptr)) return -11;
   AdamArgs a{master, m, v, (__nv_bfloat16*)mirror, gscale, lr, b1, b2, eps, wd, alpha_t};
   const int grid = ctas > 0 ? ctas : 96;
-  if (mode == 0)
-    peer_reduce_scatter_kernel<0><<<grid, 512, 0, st>>>(make_ptrs(staging_ptrs, world), make_ptrs(flag_bases, world),
-                                                        ready_row, done_row, grad_out, sumsq, a, n, world, rank, epoch,
-                                                        limit_ns, counter, status);
-  else
-    peer_reduce_scatter_kernel<1><<<grid, 512, 0, st>>>(make_ptrs(staging_ptrs, world), make_ptrs(flag_bases, world),
-                                                        ready_row, done_row, grad_out, sumsq, a, n, world, rank, epoch,
-                                                        limit_ns, counter, status);
+#define RS_LAUNCH(MODE_, WORLD_)                                                                                  \
+  peer_reduce_scatter_kernel<MODE_, WORLD_><<<grid, 512, 0, st>>>(make_ptrs(staging_ptrs, world),                 \
+                                                                  make_ptrs(flag_bases, world), ready_row, done_row, \
+                                                                  grad_out, sumsq, a, n, world, rank, epoch, limit_ns, \
+                                                                  counter, status)
+#define RS_WORLD(MODE_)                        \
+  switch (world) {                             \
+    case 2: RS_LAUNCH(MODE_, 2); break;        \
+    case 4: RS_LAUNCH(MODE_, 4); break;        \
+    case 8: RS_LAUNCH(MODE_, 8); break;        \
+    default: RS_LAUNCH(MODE_, 0); break;       \
+  }
+  if (mode == 0) { RS_WORLD(0) } else { RS_WORLD(1) }
+#undef RS_WORLD
+#undef RS_LAUNCH
   COMM_CHECK();
 }
 

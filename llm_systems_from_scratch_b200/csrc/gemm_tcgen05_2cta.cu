@@ -20,6 +20,11 @@ int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t 
 
 constexpr int P_BN = 256;        // tile columns of the pair
 constexpr int P_HALF = 128;      // B rows held by one CTA
+template <int V>
+struct IntC {
+  static constexpr int value = V;
+};
+
 constexpr int P_STAGES = 6;
 constexpr int P_THREADS = 256;    // TMA warp, MMA warp, 4 epilogue warps, 2 gather-copy warps
 constexpr int P_A_BYTES = BM * BK * 2;       // 16 KB
@@ -240,18 +245,37 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const GatherTask& g = p.gather;
       const int t = (warp - 6) * 32 + lane;                  // 0..63
       const size_t stride = (size_t)gridDim.x * 64;
-      for (int k = 0; k < g.world; ++k) {
-        const int src_rank = (g.rank + k) % g.world;         // every GPU starts at a different peer
-        const uint4* src = g.src[src_rank];
-        uint4* dst = g.dst + (size_t)src_rank * g.shard_vec;
-        size_t i = (size_t)blockIdx.x * 64 + t;
-        // four independent 16-byte loads in flight per thread hide the NVLink latency
-        for (; i + 3 * stride < g.shard_vec; i += 4 * stride) {
-          const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
-          dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+      // one load from every peer in flight per thread (times 4 / 2 strides for 2 / 4 ranks)
+      const size_t first = (size_t)blockIdx.x * 64 + t;
+      auto body = [&](auto world_c, auto unroll_c) {
+        constexpr int W = decltype(world_c)::value, U = decltype(unroll_c)::value;
+        size_t i = first;
+        for (; i + (U - 1) * stride < g.shard_vec; i += U * stride) {
+          uint4 v[W][U];
+#pragma unroll
+          for (int k = 0; k < W; ++k)
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[k][u] = g.src[(g.rank + k) % W][i + u * stride];
+#pragma unroll
+          for (int k = 0; k < W; ++k)
+#pragma unroll
+            for (int u = 0; u < U; ++u) g.dst[(size_t)((g.rank + k) % W) * g.shard_vec + i + u * stride] = v[k][u];
         }
-        for (; i < g.shard_vec; i += stride) dst[i] = src[i];
-      }
+        for (; i < g.shard_vec; i += stride)
+#pragma unroll
+          for (int k = 0; k < W; ++k) {
+            const int pr = (g.rank + k) % W;
+            g.dst[(size_t)pr * g.shard_vec + i] = g.src[pr][i];
+          }
+      };
+      if (g.world == 8) body(IntC<8>{}, IntC<2>{});
+      else if (g.world == 4) body(IntC<4>{}, IntC<4>{});
+      else if (g.world == 2) body(IntC<2>{}, IntC<8>{});
+      else
+        for (int k = 0; k < g.world; ++k) {
+          const int pr = (g.rank + k) % g.world;
+          for (size_t i = first; i < g.shard_vec; i += stride) g.dst[(size_t)pr * g.shard_vec + i] = g.src[pr][i];
+        }
       asm volatile("bar.sync 2, 64;" ::: "memory");         // both copy warps are done
       if (t == 0 && g.done != nullptr) {
         __threadfence();
