@@ -167,13 +167,24 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 }
 
 // dw[c] (=|+=) sum_p partial[p][c], fixed summation order => bitwise reproducible.
+// A block of 256 threads owns 32 columns: thread (g, x) sums partial rows g, g+8, ... of column x, then the
+// 8 row groups are combined in a fixed order through shared memory.
 __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nparts, int d,
                                          int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
+  __shared__ float sm[8][32];
+  const int x = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + x;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * d + c];
-  dw[c] = accumulate ? dw[c] + s : s;
+  if (c < d)
+    for (int p = g; p < nparts; p += 8) s += partial[(size_t)p * d + c];
+  sm[g][x] = s;
+  __syncthreads();
+  if (g == 0 && c < d) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sm[k][x];
+    dw[c] = accumulate ? dw[c] + t : t;
+  }
 }
 
 // --------------------------------------------------------------------------- SwiGLU
@@ -537,7 +548,7 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
   else if (d <= 4096) RMS_BWD_LAUNCH(2);
   else RMS_BWD_LAUNCH(4);
 #undef RMS_BWD_LAUNCH
-  rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_partial, dw, parts, d, accumulate_dw);
+  rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 256, 0, st>>>(dw_partial, dw, parts, d, accumulate_dw);
   CHECK_LAUNCH();
 }
 
@@ -585,13 +596,18 @@ extern "C" int b200_embedding_bwd(const long long* tokens, const void* dx, float
 }
 
 // scratch: rows + 1 floats (row losses, then n_valid).  loss (device float) is overwritten or accumulated.
+// n_valid_in (device float, may be null): normalise by this count instead of the number of non-ignored
+// targets among these rows, so that a caller processing the rows in chunks gets the global mean directly.
 extern "C" int b200_xent(void* logits, const long long* targets, float* loss, float* scratch, long long rows,
                          long long ld, int vocab, int ignore_index, float grad_scale, int write_grad,
-                         int accumulate_loss, cudaStream_t st) {
+                         int accumulate_loss, const float* n_valid_in, cudaStream_t st) {
   if (!ALIGNED16(logits) || ld % 8 || vocab > ld) return -10;
   if (rows == 0) return 0;
-  float* n_valid = scratch + rows;
-  count_valid_kernel<<<1, 1024, 0, st>>>(targets, rows, ignore_index, n_valid);
+  const float* n_valid = n_valid_in;
+  if (n_valid == nullptr) {
+    count_valid_kernel<<<1, 1024, 0, st>>>(targets, rows, ignore_index, scratch + rows);
+    n_valid = scratch + rows;
+  }
   xent_kernel<<<(unsigned)rows, XENT_THREADS, 0, st>>>((__nv_bfloat16*)logits, targets, scratch, n_valid, ld, vocab,
                                                        ignore_index, grad_scale, write_grad);
   sum_rows_kernel<<<1, 1024, 0, st>>>(scratch, rows, loss, accumulate_loss);
@@ -695,6 +711,6 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   rmsnorm_bwd_kernel<RMS_BWD_MAXC_LIMIT><<<parts, RMS_BWD_THREADS, 0, st>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
       (__nv_bfloat16*)dx, scratch, rows, d);
-  rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, st>>>(scratch, dw, parts, d, accumulate_dw);
+  rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 256, 0, st>>>(scratch, dw, parts, d, accumulate_dw);
   CHECK_LAUNCH();
 }

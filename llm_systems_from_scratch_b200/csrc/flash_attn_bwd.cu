@@ -27,34 +27,78 @@ struct FlashBwdParams {
   int batch, seq, heads, d;
   float scale, scale_log2;
   uint32_t* status;
+  // Optional: dQ and dK are rotated back (transpose of the forward rotary embedding) before they are
+  // stored, so the caller receives gradients with respect to the un-rotated projections.
+  // (2, rope_ctx, dh/2) fp32 table; null = off.
+  const float* rope_cs;
+  int rope_ctx;
 };
 
-// delta = rowsum(dO * O) per (row, head); one warp per (row, head).
-__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                                   float* __restrict__ delta, int batch, int seq, int heads, int dh) {
-  const int lane = threadIdx.x & 31;
-  const long long w = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
-  const long long total = (long long)batch * seq * heads;
-  if (w >= total) return;
-  const long long row = w / heads;
-  const int h = (int)(w % heads);
-  const size_t base = (size_t)row * heads * dh + (size_t)h * dh;
-  float s = 0.f;
-  for (int c = lane * 8; c < dh; c += 256) {
-    uint4 a = *reinterpret_cast<const uint4*>(o + base + c);
-    uint4 b = *reinterpret_cast<const uint4*>(dout + base + c);
-    const uint32_t aa[4] = {a.x, a.y, a.z, a.w}, bb[4] = {b.x, b.y, b.z, b.w};
+// Inverse interleaved-pair rotation of 32 consecutive head columns starting at column e of the head.
+template <int DH>
+__device__ __forceinline__ void unrotate32(const FlashBwdParams& p, int pos, int e, uint32_t (&a)[32]) {
+  const float* cs = p.rope_cs + (size_t)pos * (DH / 2) + e / 2;
+  const float* sn = cs + (size_t)p.rope_ctx * (DH / 2);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 x = unpack_bf16x2(aa[i]), y = unpack_bf16x2(bb[i]);
-      s += x.x * y.x + x.y * y.y;
+  for (int q = 0; q < 4; ++q) {
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + q * 4);
+    const float4 s4 = *reinterpret_cast<const float4*>(sn + q * 4);
+    const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float x0 = __uint_as_float(a[q * 8 + 2 * t]), x1 = __uint_as_float(a[q * 8 + 2 * t + 1]);
+      a[q * 8 + 2 * t] = __float_as_uint(cc[t] * x0 + ss[t] * x1);
+      a[q * 8 + 2 * t + 1] = __float_as_uint(cc[t] * x1 - ss[t] * x0);
     }
   }
+}
+
+// delta = rowsum(dO * O) per (row, head).  dh/8 lanes cover one (row, head) with 16-byte loads, so a warp
+// handles 32/(dh/8) of them at once, and every thread keeps two items in flight.
+template <int DH>
+__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                   float* __restrict__ delta, long long items, int seq, int heads) {
+  constexpr int LPI = DH / 8;                       // lanes per item
+  const int lane = threadIdx.x & 31;
+  const int li = lane % LPI;
+  const long long group = (blockIdx.x * (long long)blockDim.x + threadIdx.x) / LPI;   // item index, first pass
+  const long long n_groups = (long long)gridDim.x * blockDim.x / LPI;
+  for (long long w0 = group; w0 < items; w0 += 2 * n_groups) {
+    const long long w1 = w0 + n_groups;
+    const bool has1 = w1 < items;                   // uniform across the LPI lanes of an item
+    const uint4 a0 = *reinterpret_cast<const uint4*>(o + w0 * DH + li * 8);
+    const uint4 b0 = *reinterpret_cast<const uint4*>(dout + w0 * DH + li * 8);
+    uint4 a1 = make_uint4(0, 0, 0, 0), b1 = a1;
+    if (has1) {
+      a1 = *reinterpret_cast<const uint4*>(o + w1 * DH + li * 8);
+      b1 = *reinterpret_cast<const uint4*>(dout + w1 * DH + li * 8);
+    }
+    float s0 = 0.f, s1 = 0.f;
+    const uint32_t aa0[4] = {a0.x, a0.y, a0.z, a0.w}, bb0[4] = {b0.x, b0.y, b0.z, b0.w};
+    const uint32_t aa1[4] = {a1.x, a1.y, a1.z, a1.w}, bb1[4] = {b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) {
-    const int b = (int)(row / seq), sidx = (int)(row % seq);
-    delta[((size_t)b * heads + h) * seq + sidx] = s;
+    for (int i = 0; i < 4; ++i) {
+      float2 x = unpack_bf16x2(aa0[i]), y = unpack_bf16x2(bb0[i]);
+      s0 += x.x * y.x + x.y * y.y;
+      x = unpack_bf16x2(aa1[i]); y = unpack_bf16x2(bb1[i]);
+      s1 += x.x * y.x + x.y * y.y;
+    }
+    // the loop bound depends on the item index, which differs between the item groups of a warp, so the
+    // reduction uses a mask of the lanes that belong to this item only
+    const unsigned mask = (LPI == 32) ? 0xffffffffu : (((1u << LPI) - 1u) << (lane - li));
+#pragma unroll
+    for (int off = LPI / 2; off > 0; off >>= 1) {
+      s0 += __shfl_xor_sync(mask, s0, off);
+      s1 += __shfl_xor_sync(mask, s1, off);
+    }
+    if (li == 0) {
+      const long long row0 = w0 / heads;
+      delta[((row0 / seq) * heads + (w0 % heads)) * seq + row0 % seq] = s0;
+      if (has1) {
+        const long long row1 = w1 / heads;
+        delta[((row1 / seq) * heads + (w1 % heads)) * seq + row1 % seq] = s1;
+      }
+    }
   }
 }
 
@@ -343,6 +387,7 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
         tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
         tmem_ld_32x32(tm_dv + lane_addr + c * 32, g);
         tmem_ld_wait();
+        if (valid && p.rope_cs != nullptr) unrotate32<DH>(p, key_idx, c * 32, a);
         if (valid) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -588,6 +633,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
         uint32_t a[32];
         tmem_ld_32x32(tm_dq + lane_addr + c * 32, a);
         tmem_ld_wait();
+        if (valid && p.rope_cs != nullptr) unrotate32<DH>(p, q_idx, c * 32, a);
         if (valid) {
 #pragma unroll
           for (int q = 0; q < 4; ++q)
@@ -646,21 +692,47 @@ using namespace b200;
 
 // qkv (rows, 3d), o / dout (rows, d) bf16; lse (batch, heads, seq) from the forward; delta: scratch of the
 // same shape (fp32); dqkv (rows, 3d) bf16 receives dQ | dK | dV.  dh must be 64 or 128.
-extern "C" int b200_flash_bwd(const void* qkv, const void* o, const void* dout, const float* lse, float* delta,
-                              void* dqkv, int batch, int seq, int heads, int dh, float scale, uint32_t* status,
-                              cudaStream_t stream) {
+static int flash_bwd_impl(const void* qkv, const void* o, const void* dout, const float* lse, float* delta, void* dqkv,
+                          int batch, int seq, int heads, int dh, float scale, const float* rope_cs, int rope_ctx,
+                          uint32_t* status, cudaStream_t stream) {
   if (dh != 64 && dh != 128) return -10;
   if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(dout) |
        reinterpret_cast<uintptr_t>(dqkv)) & 15)
     return -10;
   if (batch <= 0 || seq <= 0) return 0;
-  const long long warps = (long long)batch * seq * heads;
-  flash_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
-                                                                      delta, batch, seq, heads, dh);
+  const long long items = (long long)batch * seq * heads;   // (row, head) pairs; o and dout are (rows, heads*dh)
+  {
+    const int lpi = dh / 8;
+    long long blocks = (items * lpi + 2 * 256 - 1) / (2 * 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    if (dh == 128)
+      flash_delta_kernel<128><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
+                                                                    delta, items, seq, heads);
+    else
+      flash_delta_kernel<64><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
+                                                                   delta, items, seq, heads);
+  }
   FlashBwdParams p;
   p.lse = lse; p.delta = delta; p.dqkv = (__nv_bfloat16*)dqkv;
   p.batch = batch; p.seq = seq; p.heads = heads; p.d = heads * dh;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.rope_cs = rope_cs; p.rope_ctx = rope_ctx;
   return dh == 64 ? launch_flash_bwd<64>(qkv, dout, p, stream) : launch_flash_bwd<128>(qkv, dout, p, stream);
+}
+
+extern "C" int b200_flash_bwd(const void* qkv, const void* o, const void* dout, const float* lse, float* delta,
+                              void* dqkv, int batch, int seq, int heads, int dh, float scale, uint32_t* status,
+                              cudaStream_t stream) {
+  return flash_bwd_impl(qkv, o, dout, lse, delta, dqkv, batch, seq, heads, dh, scale, nullptr, 0, status, stream);
+}
+
+// As b200_flash_bwd, but `qkv` holds rotated Q and K (rotary embedding already applied) and the returned dQ / dK
+// are gradients with respect to the projections before the rotation.  cos_sin: (2, ctx, dh/2) fp32, seq <= ctx.
+extern "C" int b200_flash_bwd_rope(const void* qkv, const void* o, const void* dout, const float* lse, float* delta,
+                                   void* dqkv, int batch, int seq, int heads, int dh, float scale,
+                                   const float* cos_sin, int ctx, uint32_t* status, cudaStream_t stream) {
+  if (cos_sin == nullptr || seq > ctx || (reinterpret_cast<uintptr_t>(cos_sin) & 15)) return -12;
+  return flash_bwd_impl(qkv, o, dout, lse, delta, dqkv, batch, seq, heads, dh, scale, cos_sin, ctx, status, stream);
 }

@@ -31,6 +31,11 @@ struct GemmParams {
   GatherTask gather;
   const uint32_t* wait_counter;  // optional: do not touch operand B before *wait_counter >= wait_value
   uint32_t wait_value;
+  // Optional rotary embedding fused into the epilogue of the QKV projection: output columns [0, 2*rope_d)
+  // (the Q and K thirds) are rotated pair-wise by the angle of position (row % rope_seq); the table is
+  // (2, rope_ctx, rope_dh/2) fp32 (cos, then sin).  Null = off.
+  const float* rope_cs;
+  int rope_seq, rope_d, rope_dh, rope_ctx;
   int M, N, K;
   void* C;
   long long ldc;
@@ -56,11 +61,32 @@ __device__ __forceinline__ void report(const GemmParams& p, volatile uint32_t* a
   if (p.status != nullptr) atomicCAS(p.status, 0u, code | (blockIdx.x << 8));
 }
 
+// Interleaved-pair rotation of a 32-column accumulator chunk (16 pairs, all inside one head).
+__device__ __forceinline__ void epilogue_rope(const GemmParams& p, int row, int col0, uint32_t (&acc)[32]) {
+  const int pos = row % p.rope_seq;
+  const int e = col0 % p.rope_dh;                       // multiple of 32
+  const float* cs = p.rope_cs + (size_t)pos * (p.rope_dh / 2) + e / 2;
+  const float* sn = cs + (size_t)p.rope_ctx * (p.rope_dh / 2);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + q * 4);
+    const float4 s4 = *reinterpret_cast<const float4*>(sn + q * 4);
+    const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float x0 = __uint_as_float(acc[q * 8 + 2 * t]), x1 = __uint_as_float(acc[q * 8 + 2 * t + 1]);
+      acc[q * 8 + 2 * t] = __float_as_uint(cc[t] * x0 - ss[t] * x1);
+      acc[q * 8 + 2 * t + 1] = __float_as_uint(ss[t] * x0 + cc[t] * x1);
+    }
+  }
+}
+
 // One 32-column chunk of one output row.
-__device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int col0, const uint32_t (&acc)[32]) {
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int col0, uint32_t (&acc)[32]) {
   if (row >= p.M) return;
   const int ncols = min(32, p.N - col0);
   if (ncols <= 0) return;
+  if (p.rope_cs != nullptr && col0 < 2 * p.rope_d && ncols == 32) epilogue_rope(p, row, col0, acc);
   if (p.epi == EPI_BF16 || p.epi == EPI_BF16_RES) {
     __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
     const bool vec_ok = (ncols == 32) && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);

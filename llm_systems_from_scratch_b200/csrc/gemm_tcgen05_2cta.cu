@@ -355,7 +355,8 @@ using namespace b200;
 static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
                           long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int epi,
                           const GatherTask* gather, const uint32_t* wait_counter, uint32_t wait_value,
-                          uint32_t* status, cudaStream_t stream) {
+                          uint32_t* status, cudaStream_t stream, const float* rope_cs = nullptr, int rope_seq = 0,
+                          int rope_d = 0, int rope_dh = 0, int rope_ctx = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -10;
@@ -374,6 +375,7 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
   if (gather != nullptr) p.gather = *gather;
   else { p.gather.dst = nullptr; p.gather.done = nullptr; p.gather.shard_vec = 0; p.gather.world = 0; p.gather.rank = 0; }
   p.wait_counter = wait_counter; p.wait_value = wait_value;
+  p.rope_cs = rope_cs; p.rope_seq = rope_seq; p.rope_d = rope_d; p.rope_dh = rope_dh; p.rope_ctx = rope_ctx;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -418,4 +420,15 @@ extern "C" int b200_gemm_bf16_pair_gather(const void* A, const void* B, void* C,
   }
   return gemm_pair_impl(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, epi, gather_dst ? &g : nullptr,
                         wait_counter, wait_value, status, stream);
+}
+
+// QKV projection with the rotary embedding applied in the epilogue: C (M x 3*d) = A * B^T, then the Q and K
+// thirds are rotated by the angle of position (row % seq).  cos_sin: (2, ctx, dh/2) fp32.  bf16 output only.
+extern "C" int b200_gemm_bf16_pair_rope(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                        long long ldb, long long ldc, const float* cos_sin, int seq, int d, int dh,
+                                        int ctx, uint32_t* status, cudaStream_t stream) {
+  if (cos_sin == nullptr || seq <= 0 || seq > ctx || dh % 32 || d % dh || N != 3 * d) return -12;
+  if (reinterpret_cast<uintptr_t>(cos_sin) & 15) return -10;
+  return gemm_pair_impl(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, 0, 0, EPI_BF16, nullptr, nullptr, 0, status, stream,
+                        cos_sin, seq, d, dh, ctx);
 }

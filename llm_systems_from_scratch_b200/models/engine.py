@@ -76,8 +76,7 @@ def block_forward(x, w: BlockWeights, cfg: EngineConfig, rope_cache, batch: int,
     """x (M, d) -> (y (M, d), saved activations or None).  ``gather`` is an optional pending all-gather
     (the next FSDP unit's weights) that the largest GEMM of the block carries."""
     h1, rstd1 = ops.rmsnorm_fwd(x, w.n1, cfg.eps)
-    qkv = ops.gemm(h1, w.wqkv, "nt")
-    ops.rope_(qkv, rope_cache, None, cfg.n_heads, False, seq)
+    qkv = ops.gemm_qkv_rope(h1, w.wqkv, rope_cache, seq, cfg.n_heads)     # RoPE in the GEMM epilogue
     o, lse = ops.attention_fwd(qkv, batch, seq, cfg.n_heads)
     x2 = ops.gemm(o, w.wo, "nt", residual=x)
     h2, rstd2 = ops.rmsnorm_fwd(x2, w.n2, cfg.eps)
@@ -105,9 +104,8 @@ def block_backward(dy, w: BlockWeights, s: BlockSaved, gw: BlockWeights, cfg: En
     # ---- attention half
     do = ops.gemm(dx2, w.wo, "nn")
     ops.gemm(dx2, s.o, "tn", out=gw.wo)
-    dqkv = ops.attention_bwd(do, s.qkv, s.o, s.lse, batch, seq, cfg.n_heads)
+    dqkv = ops.attention_bwd(do, s.qkv, s.o, s.lse, batch, seq, cfg.n_heads, rope_cache)   # dQ, dK rotated back
     del do
-    ops.rope_(dqkv, rope_cache, None, cfg.n_heads, True, seq)
     dh1 = ops.gemm(dqkv, w.wqkv, "nn")
     ops.gemm(dqkv, s.h1, "tn", out=gw.wqkv)
     del dqkv
@@ -347,17 +345,10 @@ class _HeadLossFn(torch.autograd.Function):
             logits = buf[:r1 - r0, :cfg.vocab]
             ops.gemm(hn[r0:r1], hw.lm, "nt", out=logits)
             tg = targets[r0:r1]
+            # every chunk is normalised by the global count of valid targets, so the parts simply add up
             if need_grad:
-                part = ops.xent_fwd_bwd(buf[:r1 - r0], tg, 1.0, -100, cfg.vocab)
-            else:
-                part = ops.xent_fwd(buf[:r1 - r0], tg, -100, cfg.vocab)
-            # each chunk normalised by its own valid count -> re-weight to the global mean
-            cnt = (tg != -100).sum().clamp(min=1).float()
-            wgt = cnt / n_valid
-            loss = loss + part * wgt
-            if need_grad:
-                if m > chunk_rows:
-                    ops.scale_(buf[:r1 - r0], wgt) if buf[:r1 - r0].is_contiguous() else buf[:r1 - r0].mul_(wgt)
+                ops.xent_fwd_bwd(buf[:r1 - r0], tg, 1.0, -100, cfg.vocab, loss_out=loss, accumulate_loss=(r0 > 0),
+                                 n_valid=n_valid)
                 ops.gemm(logits, hw.lm, "nn", out=dhn[r0:r1])
                 if gw.lm.dtype == torch.float32:
                     ops.gemm(logits, hn[r0:r1], "tn", out=gw.lm, accumulate=(r0 > 0))
@@ -365,6 +356,9 @@ class _HeadLossFn(torch.autograd.Function):
                     if lm_acc is None:
                         lm_acc = torch.empty(gw.lm.shape, dtype=torch.float32, device=x.device)
                     ops.gemm(logits, hn[r0:r1], "tn", out=lm_acc, accumulate=(r0 > 0))
+            else:
+                ops.xent_fwd(buf[:r1 - r0], tg, -100, cfg.vocab, loss_out=loss, accumulate_loss=(r0 > 0),
+                             n_valid=n_valid)
         if need_grad and lm_acc is not None:
             gw.lm.copy_(lm_acc)
         ctx.eng = eng

@@ -57,11 +57,27 @@ def attention_fwd(qkv, batch, seq, n_heads):
     return torch_impl.attention_fwd(qkv, batch, seq, n_heads)
 
 
-def attention_bwd(do, qkv, o, lse, batch, seq, n_heads):
+def attention_bwd(do, qkv, o, lse, batch, seq, n_heads, rope_cache=None):
+    """Gradient of packed qkv.  With ``rope_cache`` the Q / K in ``qkv`` are rotated and the result is the
+    gradient with respect to the un-rotated projections (inverse rotation fused on the GPU)."""
     if qkv.is_cuda:
         from . import attention
-        return attention.attention_bwd(do, qkv, o, lse, batch, seq, n_heads)
-    return torch_impl.attention_bwd(do, qkv, o, lse, batch, seq, n_heads)
+        return attention.attention_bwd(do, qkv, o, lse, batch, seq, n_heads, rope_cache)
+    dqkv = torch_impl.attention_bwd(do, qkv, o, lse, batch, seq, n_heads)
+    if rope_cache is not None:
+        rope_(dqkv, rope_cache, None, n_heads, True, seq)
+    return dqkv
+
+
+def gemm_qkv_rope(x, wqkv, cos_sin, seq, n_heads):
+    """QKV projection followed by the rotary embedding on Q and K (one kernel on the GPU when possible)."""
+    if x.is_cuda:
+        out = native.gemm_qkv_rope(x, wqkv, cos_sin, seq, n_heads)
+        if out is not None:
+            return out
+    qkv = gemm(x, wqkv, "nt")
+    rope_(qkv, cos_sin, None, n_heads, False, seq)
+    return qkv
 
 
 def clip_coef(sumsq_t, max_norm, coef_out=None, norm_out=None):

@@ -52,7 +52,9 @@ def attention_fwd(qkv, batch: int, seq: int, n_heads: int):
     return o, lse
 
 
-def attention_bwd(do, qkv, o, lse, batch: int, seq: int, n_heads: int):
+def attention_bwd(do, qkv, o, lse, batch: int, seq: int, n_heads: int, rope_cache=None):
+    """dqkv for packed qkv.  With ``rope_cache`` (qkv holds rotated Q / K) the kernels rotate dQ and dK back in
+    their epilogues, so no separate inverse-RoPE pass is needed."""
     lib = native.load()
     _req(do.dtype == torch.bfloat16 and do.is_contiguous() and o.is_contiguous(), "do / o must be contiguous bf16")
     rows, three_d = qkv.shape
@@ -67,11 +69,19 @@ def attention_bwd(do, qkv, o, lse, batch: int, seq: int, n_heads: int):
         qkv_p, do_p, o_p = qkv, do, o
     dqkv = torch.empty_like(qkv_p)
     delta = torch.empty((batch, n_heads, seq), dtype=torch.float32, device=qkv.device)
+    fused = rope_cache is not None and dhp == dh and native.has("b200_flash_bwd_rope")
+    if fused:
+        _check(lib.b200_flash_bwd_rope(_ptr(qkv_p), _ptr(o_p), _ptr(do_p), _ptr(lse), _ptr(delta), _ptr(dqkv), batch,
+                                       seq, n_heads, dhp, 1.0 / math.sqrt(dh), _ptr(rope_cache), rope_cache.shape[1],
+                                       _ptr(native.status_word(qkv.device)), _stream()), "flash_bwd")
+        return dqkv
     _check(lib.b200_flash_bwd(_ptr(qkv_p), _ptr(o_p), _ptr(do_p), _ptr(lse), _ptr(delta), _ptr(dqkv), batch, seq,
                               n_heads, dhp, 1.0 / math.sqrt(dh), _ptr(native.status_word(qkv.device)), _stream()),
            "flash_bwd")
     if dhp != dh:
         dqkv = _unpad_heads(dqkv, 3, n_heads, dh, dhp)
+    if rope_cache is not None:
+        native.rope_(dqkv if dqkv.is_contiguous() else dqkv.contiguous(), rope_cache, None, n_heads, True, seq)
     return dqkv
 
 

@@ -76,7 +76,7 @@ def _declare(lib):
         "b200_rope": [P, P, P, L, I, I, I, I, I, P],
         "b200_embedding_fwd": [P, P, P, L, I, I, P],
         "b200_embedding_bwd": [P, P, P, L, I, I, P],
-        "b200_xent": [P, P, P, P, L, L, I, I, F, I, I, P],
+        "b200_xent": [P, P, P, P, L, L, I, I, F, I, I, P, P],
         "b200_argmax": [P, L, L, I, P, P],
         "b200_adamw": [P, P, I, P, P, P, L, P, F, F, F, F, F, F, P],
         "b200_sumsq": [P, I, L, P, P],
@@ -89,6 +89,8 @@ def _declare(lib):
         "b200_flash_fwd": [P, P, P, I, I, I, I, F, P, P],
         "b200_flash_bwd": [P, P, P, P, P, P, I, I, I, I, F, P, P],
         "b200_flash_varlen_fwd": [P, P, P, I, I, I, I, I, F, P, P],
+        "b200_flash_bwd_rope": [P, P, P, P, P, P, I, I, I, I, F, P, I, P, P],
+        "b200_gemm_bf16_pair_rope": [P, P, P, I, I, I, L, L, L, P, I, I, I, I, P, P],
         "b200_paged_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P],
         "b200_kv_append": [P, P, P, P, L, I, P],
         "b200_sample": [P, L, L, I, F, I, P, P, P, P],
@@ -244,6 +246,28 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
     return out
 
 
+def gemm_qkv_rope(x, wqkv, cos_sin, seq: int, n_heads: int):
+    """qkv = x @ wqkv.T with the rotary embedding applied to the Q and K thirds in the GEMM epilogue.
+    Returns None when the fused kernel does not apply (the caller then runs GEMM + rope separately)."""
+    lib = load()
+    m, k = x.shape
+    n = wqkv.shape[0]
+    d = n // 3
+    dh = d // n_heads
+    ok = (USE_PAIR and m >= PAIR_MIN_M and dh % 32 == 0 and m % seq == 0 and seq <= cos_sin.shape[1]
+          and x.dtype == torch.bfloat16 and wqkv.dtype == torch.bfloat16 and x.stride(1) == 1 and wqkv.stride(1) == 1
+          and x.stride(0) % 8 == 0 and wqkv.stride(0) % 8 == 0 and cos_sin.is_contiguous()
+          and cos_sin.dtype == torch.float32 and cos_sin.shape[2] == dh // 2)
+    if not ok:
+        return None
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    rc = lib.b200_gemm_bf16_pair_rope(_ptr(x), _ptr(wqkv), _ptr(out), m, n, k, x.stride(0), wqkv.stride(0), n,
+                                      _ptr(cos_sin), seq, d, dh, cos_sin.shape[1], _ptr(status_word(x.device)),
+                                      _stream())
+    _check(rc, "b200_gemm_bf16_pair_rope")
+    return out
+
+
 # -------------------------------------------------------------------------- RMSNorm
 def rmsnorm_fwd(x, w, eps: float):
     lib = load()
@@ -352,7 +376,7 @@ def embedding_bwd(dx, tokens, grad_weight, accumulate=False):
 
 # -------------------------------------------------------------------- Cross entropy
 def xent_fwd_bwd(logits, targets, grad_scale: float = 1.0, ignore_index: int = -100, valid_cols=None,
-                 write_grad: bool = True, loss_out=None, accumulate_loss=False):
+                 write_grad: bool = True, loss_out=None, accumulate_loss=False, n_valid=None):
     lib = load()
     _req(logits.dtype == torch.bfloat16 and logits.dim() == 2 and logits.stride(1) == 1, "logits must be bf16 2-D")
     rows, cols = logits.shape
@@ -363,12 +387,15 @@ def xent_fwd_bwd(logits, targets, grad_scale: float = 1.0, ignore_index: int = -
     loss = loss_out if loss_out is not None else torch.empty((), dtype=torch.float32, device=logits.device)
     scratch = torch.empty(rows + 1, dtype=torch.float32, device=logits.device)
     _check(lib.b200_xent(_ptr(logits), _ptr(targets), _ptr(loss), _ptr(scratch), rows, ld, v, ignore_index,
-                         float(grad_scale), 1 if write_grad else 0, 1 if accumulate_loss else 0, _stream()), "xent")
+                         float(grad_scale), 1 if write_grad else 0, 1 if accumulate_loss else 0, _ptr(n_valid),
+                         _stream()), "xent")
     return loss
 
 
-def xent_fwd(logits, targets, ignore_index: int = -100, valid_cols=None):
-    return xent_fwd_bwd(logits, targets, 1.0, ignore_index, valid_cols, write_grad=False)
+def xent_fwd(logits, targets, ignore_index: int = -100, valid_cols=None, loss_out=None, accumulate_loss=False,
+             n_valid=None):
+    return xent_fwd_bwd(logits, targets, 1.0, ignore_index, valid_cols, write_grad=False, loss_out=loss_out,
+                        accumulate_loss=accumulate_loss, n_valid=n_valid)
 
 
 def argmax_rows(logits, valid_cols=None):

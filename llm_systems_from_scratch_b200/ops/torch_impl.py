@@ -161,7 +161,8 @@ def embedding_bwd(dx, tokens, grad_weight, accumulate=False):
 
 
 # -------------------------------------------------------------------- Cross entropy
-def xent_fwd_bwd(logits, targets, grad_scale: float = 1.0, ignore_index: int = -100, valid_cols=None):
+def xent_fwd_bwd(logits, targets, grad_scale: float = 1.0, ignore_index: int = -100, valid_cols=None,
+                 loss_out=None, accumulate_loss=False, n_valid=None):
     """Mean CE over non-ignored rows; overwrites ``logits`` with d(loss)/d(logits) * grad_scale.
 
     ``valid_cols`` limits the vocabulary to the first columns of a padded logits buffer.
@@ -170,7 +171,7 @@ def xent_fwd_bwd(logits, targets, grad_scale: float = 1.0, ignore_index: int = -
     v = valid_cols or logits.shape[-1]
     lf = _f(logits[:, :v])
     keep = targets != ignore_index
-    n = keep.sum().clamp(min=1).float()
+    n = keep.sum().clamp(min=1).float() if n_valid is None else n_valid.float()
     lse = torch.logsumexp(lf, dim=-1)
     tgt = targets.clamp(min=0).long()
     picked = lf.gather(-1, tgt.unsqueeze(-1)).squeeze(-1)
@@ -181,17 +182,31 @@ def xent_fwd_bwd(logits, targets, grad_scale: float = 1.0, ignore_index: int = -
     logits[:, :v] = p.to(logits.dtype)
     if v < logits.shape[-1]:
         logits[:, v:] = 0
+    if loss_out is not None:
+        if accumulate_loss:
+            loss_out.add_(loss)
+        else:
+            loss_out.copy_(loss)
+        return loss_out
     return loss
 
 
-def xent_fwd(logits, targets, ignore_index: int = -100, valid_cols=None):
+def xent_fwd(logits, targets, ignore_index: int = -100, valid_cols=None, loss_out=None, accumulate_loss=False,
+             n_valid=None):
     v = valid_cols or logits.shape[-1]
     lf = _f(logits[:, :v])
     keep = targets != ignore_index
-    n = keep.sum().clamp(min=1).float()
+    n = keep.sum().clamp(min=1).float() if n_valid is None else n_valid.float()
     lse = torch.logsumexp(lf, dim=-1)
     picked = lf.gather(-1, targets.clamp(min=0).long().unsqueeze(-1)).squeeze(-1)
-    return ((lse - picked) * keep).sum() / n
+    loss = ((lse - picked) * keep).sum() / n
+    if loss_out is not None:
+        if accumulate_loss:
+            loss_out.add_(loss)
+        else:
+            loss_out.copy_(loss)
+        return loss_out
+    return loss
 
 
 # ---------------------------------------------------------------------------- AdamW

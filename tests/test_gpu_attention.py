@@ -49,3 +49,29 @@ def test_flash_varlen_matches_per_sequence():
     native.check_status()
     ref = torch_impl.varlen_attention_fwd(qkv.float(), cu.cpu(), h)
     assert (o.float() - ref).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("b,s,h,dh", [(2, 1024, 4, 128), (4, 512, 4, 64)])
+def test_rope_fused_into_qkv_gemm_and_attention_backward(b, s, h, dh):
+    """QKV GEMM with RoPE in its epilogue, and attention backward that rotates dQ/dK back, against the separate kernels."""
+    from llm_systems_from_scratch_b200.models.transformer import RotaryEmbedding
+    from llm_systems_from_scratch_b200.ops import attention, native
+    d = h * dh
+    cache = RotaryEmbedding._build_cache(s + 7, dh, 10000.0).cuda().contiguous()
+    x = torch.randn(b * s, d, device="cuda").bfloat16()
+    w = (torch.randn(3 * d, d, device="cuda") / d ** 0.5).bfloat16()
+    fused = native.gemm_qkv_rope(x, w, cache, s, h)
+    assert fused is not None
+    ref = native.gemm(x, w, "nt")
+    native.rope_(ref, cache, None, h, False, s)
+    native.check_status()
+    assert (fused.float() - ref.float()).abs().max().item() < 3e-2
+    assert torch.equal(fused[:, 2 * d:], ref[:, 2 * d:])
+    o, lse = attention.attention_fwd(ref, b, s, h)
+    do = torch.randn_like(o)
+    a = attention.attention_bwd(do, ref, o, lse, b, s, h, rope_cache=cache)
+    plain = attention.attention_bwd(do, ref, o, lse, b, s, h)
+    native.rope_(plain, cache, None, h, True, s)
+    native.check_status()
+    assert (a.float() - plain.float()).abs().max().item() < 3e-2 * max(1.0, plain.float().abs().max().item())
+    assert torch.equal(a[:, 2 * d:], plain[:, 2 * d:])
