@@ -65,7 +65,8 @@ def test_rope_fused_into_qkv_gemm_and_attention_backward(b, s, h, dh):
     ref = native.gemm(x, w, "nt")
     native.rope_(ref, cache, None, h, False, s)
     native.check_status()
-    assert (fused.float() - ref.float()).abs().max().item() < 3e-2
+    # the fused epilogue rotates fp32 accumulators, the separate kernel rotates bf16-rounded values: <= 2 ulp apart
+    assert bool(((fused.float() - ref.float()).abs() <= 2e-2 * ref.float().abs().clamp(min=1.0)).all())
     assert torch.equal(fused[:, 2 * d:], ref[:, 2 * d:])
     o, lse = attention.attention_fwd(ref, b, s, h)
     do = torch.randn_like(o)
