@@ -36,6 +36,12 @@ struct GemmParams {
   // (2, rope_ctx, rope_dh/2) fp32 (cos, then sin).  Null = off.
   const float* rope_cs;
   int rope_seq, rope_d, rope_dh, rope_ctx;
+  // Optional SwiGLU fused into the epilogue of the merged gate|up projection (CTA-pair kernel only): B is
+  // (2F, K) with gate rows first; a tile then holds 128 gate columns and the matching 128 up columns, C
+  // receives both (they are needed by the backward pass) and H (M x F, bf16) receives silu(gate) * up.
+  int swiglu_f;        // F, 0 = off
+  void* H;
+  long long ldh;
   int M, N, K;
   void* C;
   long long ldc;

@@ -165,7 +165,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         int m_blk, n_blk;
         tile_coords(tile, p, m_blk, n_blk);
         const int m0 = m_blk * 256 + (int)rank * BM;
-        const int n0 = n_blk * P_BN + (int)rank * P_HALF;
+        // SwiGLU mode: the leader loads 128 gate rows, its peer the matching 128 up rows (F rows further down)
+        const int n0 = p.swiglu_f > 0 ? n_blk * P_HALF + (int)rank * p.swiglu_f : n_blk * P_BN + (int)rank * P_HALF;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word)) {
             report(p, abort_word, ERR_WAIT_EMPTY);
@@ -301,13 +302,45 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int row = m_blk * 256 + (int)rank * BM + quarter * 32 + lane;
       const int n0 = n_blk * P_BN;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * P_BN;
+      if (p.swiglu_f > 0) {
+        // accumulator columns [0,128) are gate_j, [128,256) the matching up_j
+        const int col = n_blk * P_HALF;
 #pragma unroll 1
-      for (int c = 0; c < P_BN / 32; ++c) {
-        if (n0 + c * 32 >= p.N) break;
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        epilogue_store(p, row, n0 + c * 32, r);
+        for (int c = 0; c < P_HALF / 32; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + c * 32, g);
+          tmem_ld_32x32(taddr + P_HALF + c * 32, u);
+          tmem_ld_wait();
+          if (row < p.M) {
+            __nv_bfloat16* cg = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col + c * 32;
+            __nv_bfloat16* cu = cg + p.swiglu_f;
+            __nv_bfloat16* ch = reinterpret_cast<__nv_bfloat16*>(p.H) + (long long)row * p.ldh + col + c * 32;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t og[4], ou[4], oh[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                og[t] = pack_bf16x2(__uint_as_float(g[j * 8 + 2 * t]), __uint_as_float(g[j * 8 + 2 * t + 1]));
+                ou[t] = pack_bf16x2(__uint_as_float(u[j * 8 + 2 * t]), __uint_as_float(u[j * 8 + 2 * t + 1]));
+                // same arithmetic as the stand-alone kernel: silu on the bf16-rounded gate, times the rounded up
+                const float2 gf = unpack_bf16x2(og[t]), uf = unpack_bf16x2(ou[t]);
+                oh[t] = pack_bf16x2(gf.x / (1.f + __expf(-gf.x)) * uf.x, gf.y / (1.f + __expf(-gf.y)) * uf.y);
+              }
+              *reinterpret_cast<uint4*>(cg + j * 8) = make_uint4(og[0], og[1], og[2], og[3]);
+              *reinterpret_cast<uint4*>(cu + j * 8) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+              *reinterpret_cast<uint4*>(ch + j * 8) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < P_BN / 32; ++c) {
+          if (n0 + c * 32 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          epilogue_store(p, row, n0 + c * 32, r);
+        }
       }
       tc_fence_before();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));   // the leader owns this barrier
@@ -338,7 +371,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
     configured = true;
   }
   p.num_m_tiles = (p.M + 255) / 256;
-  p.num_n_tiles = (p.N + P_BN - 1) / P_BN;
+  p.num_n_tiles = p.swiglu_f > 0 ? p.swiglu_f / P_HALF : (p.N + P_BN - 1) / P_BN;
   p.group_m = 8;
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   int pairs = sms / 2;
@@ -356,7 +389,8 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
                           long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int epi,
                           const GatherTask* gather, const uint32_t* wait_counter, uint32_t wait_value,
                           uint32_t* status, cudaStream_t stream, const float* rope_cs = nullptr, int rope_seq = 0,
-                          int rope_d = 0, int rope_dh = 0, int rope_ctx = 0) {
+                          int rope_d = 0, int rope_dh = 0, int rope_ctx = 0, int swiglu_f = 0, void* H = nullptr,
+                          long long ldh = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -10;
@@ -376,6 +410,7 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
   else { p.gather.dst = nullptr; p.gather.done = nullptr; p.gather.shard_vec = 0; p.gather.world = 0; p.gather.rank = 0; }
   p.wait_counter = wait_counter; p.wait_value = wait_value;
   p.rope_cs = rope_cs; p.rope_seq = rope_seq; p.rope_d = rope_d; p.rope_dh = rope_dh; p.rope_ctx = rope_ctx;
+  p.swiglu_f = swiglu_f; p.H = H; p.ldh = ldh;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -431,4 +466,27 @@ extern "C" int b200_gemm_bf16_pair_rope(const void* A, const void* B, void* C, i
   if (reinterpret_cast<uintptr_t>(cos_sin) & 15) return -10;
   return gemm_pair_impl(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, 0, 0, EPI_BF16, nullptr, nullptr, 0, status, stream,
                         cos_sin, seq, d, dh, ctx);
+}
+
+// Merged gate|up projection with SwiGLU in the epilogue: C (M x 2F) = A * B^T (gate columns, then up columns) and
+// H (M x F) = silu(gate) * up.  F must be a multiple of 128; bf16 outputs; ldc, ldh multiples of 8.  The launch
+// may carry an all-gather exactly like b200_gemm_bf16_pair_gather (pass world = 0 for none).
+extern "C" int b200_gemm_bf16_pair_swiglu(const void* A, const void* B, void* C, void* H, int M, int F, int K,
+                                          long long lda, long long ldb, long long ldc, long long ldh,
+                                          const unsigned long long* src_ptrs, void* gather_dst,
+                                          unsigned long long shard_bytes, int world, int rank, uint32_t* status,
+                                          cudaStream_t stream) {
+  if (F <= 0 || F % P_HALF || (ldc & 7) || (ldh & 7) || H == nullptr) return -12;
+  if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(H) & 15)) return -10;
+  GatherTask g;
+  const bool carry = world > 0 && gather_dst != nullptr;
+  if (carry) {
+    if (world > 16 || shard_bytes % 16 || (reinterpret_cast<uintptr_t>(gather_dst) & 15)) return -10;
+    for (int i = 0; i < 16; ++i) g.src[i] = i < world ? reinterpret_cast<const uint4*>(src_ptrs[i]) : nullptr;
+    g.dst = reinterpret_cast<uint4*>(gather_dst);
+    g.shard_vec = shard_bytes / 16;
+    g.world = world; g.rank = rank; g.done = nullptr;
+  }
+  return gemm_pair_impl(A, B, C, nullptr, M, 2 * F, K, lda, ldb, ldc, 0, 0, 0, EPI_BF16, carry ? &g : nullptr, nullptr, 0,
+                        status, stream, nullptr, 0, 0, 0, 0, F, H, ldh);
 }

@@ -80,8 +80,7 @@ def block_forward(x, w: BlockWeights, cfg: EngineConfig, rope_cache, batch: int,
     o, lse = ops.attention_fwd(qkv, batch, seq, cfg.n_heads)
     x2 = ops.gemm(o, w.wo, "nt", residual=x)
     h2, rstd2 = ops.rmsnorm_fwd(x2, w.n2, cfg.eps)
-    gu = ops.gemm(h2, w.wgu, "nt", gather=gather)
-    hh = ops.silu_mul_fwd(gu)
+    gu, hh = ops.gemm_swiglu(h2, w.wgu, gather=gather)                    # SiLU(gate) * up in the GEMM epilogue
     y = ops.gemm(hh, w.wdown, "nt", residual=x2)
     saved = BlockSaved(x, rstd1, h1, qkv, o, lse, x2, rstd2, h2, gu, hh) if keep else None
     return y, saved

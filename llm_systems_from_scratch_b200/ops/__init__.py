@@ -80,6 +80,16 @@ def gemm_qkv_rope(x, wqkv, cos_sin, seq, n_heads):
     return qkv
 
 
+def gemm_swiglu(x, wgu, gather=None):
+    """Merged gate|up projection and SwiGLU: returns (gu, silu(gate) * up); one kernel on the GPU when possible."""
+    if x.is_cuda:
+        out = native.gemm_swiglu(x, wgu, gather)
+        if out is not None:
+            return out
+    gu = gemm(x, wgu, "nt", gather=gather)
+    return gu, silu_mul_fwd(gu)
+
+
 def clip_coef(sumsq_t, max_norm, coef_out=None, norm_out=None):
     if sumsq_t.is_cuda:
         return native.clip_coef(sumsq_t, max_norm, coef_out, norm_out)

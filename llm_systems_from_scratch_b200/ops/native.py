@@ -91,6 +91,7 @@ def _declare(lib):
         "b200_flash_varlen_fwd": [P, P, P, I, I, I, I, I, F, P, P],
         "b200_flash_bwd_rope": [P, P, P, P, P, P, I, I, I, I, F, P, I, P, P],
         "b200_gemm_bf16_pair_rope": [P, P, P, I, I, I, L, L, L, P, I, I, I, I, P, P],
+        "b200_gemm_bf16_pair_swiglu": [P, P, P, P, I, I, I, L, L, L, L, P, P, ctypes.c_ulonglong, I, I, P, P],
         "b200_paged_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P],
         "b200_kv_append": [P, P, P, P, L, I, P],
         "b200_sample": [P, L, L, I, F, I, P, P, P, P],
@@ -266,6 +267,32 @@ def gemm_qkv_rope(x, wqkv, cos_sin, seq: int, n_heads: int):
                                       _stream())
     _check(rc, "b200_gemm_bf16_pair_rope")
     return out
+
+
+def gemm_swiglu(x, wgu, gather=None):
+    """(gu, h) with gu = x @ wgu.T (gate columns then up columns) and h = silu(gate) * up, in one kernel.
+    Returns None when the fused kernel does not apply.  A pending all-gather can ride on the launch."""
+    lib = load()
+    m, k = x.shape
+    two_f = wgu.shape[0]
+    f = two_f // 2
+    ok = (USE_PAIR and m >= PAIR_MIN_M and f % 128 == 0 and x.dtype == torch.bfloat16 and wgu.dtype == torch.bfloat16
+          and x.stride(1) == 1 and wgu.stride(1) == 1 and x.stride(0) % 8 == 0 and wgu.stride(0) % 8 == 0)
+    if not ok:
+        return None
+    gu = torch.empty((m, two_f), dtype=torch.bfloat16, device=x.device)
+    h = torch.empty((m, f), dtype=torch.bfloat16, device=x.device)
+    gargs = gather.native_args() if (gather is not None and not gather.done) else None
+    if gather is not None and not gather.done and gargs is None:
+        gather.run()
+    table, dst, nbytes, world, rank = gargs if gargs is not None else (None, None, 0, 0, 0)
+    rc = lib.b200_gemm_bf16_pair_swiglu(_ptr(x), _ptr(wgu), _ptr(gu), _ptr(h), m, f, k, x.stride(0), wgu.stride(0),
+                                        two_f, f, table, dst, nbytes, world, rank, _ptr(status_word(x.device)),
+                                        _stream())
+    _check(rc, "b200_gemm_bf16_pair_swiglu")
+    if gargs is not None:
+        gather.mark_done()
+    return gu, h
 
 
 # -------------------------------------------------------------------------- RMSNorm

@@ -115,3 +115,21 @@ def test_gemm_cta_pair_kernel(layout, shape):
     out16 = native.gemm(a, b, layout, residual=res, pair=True)
     native.check_status()
     _check(out16, _ref(a, b, layout) + res.float(), k)
+
+
+@pytest.mark.parametrize("m,f,k", [(1024, 1408, 512), (2048, 5504, 2048), (1100, 256, 264)])
+def test_gemm_swiglu_epilogue(m, f, k):
+    """gate|up projection with SiLU(gate)*up in the epilogue against GEMM followed by the stand-alone kernel."""
+    from llm_systems_from_scratch_b200.ops import native
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(2 * f, k, device="cuda") / k ** 0.5).bfloat16()
+    out = native.gemm_swiglu(x, w)
+    assert out is not None
+    gu, h = out
+    native.check_status()
+    ref_gu = native.gemm(x, w, "nt")
+    ref_h = native.silu_mul_fwd(ref_gu)
+    assert torch.allclose(gu.float(), ref_gu.float(), atol=2e-2, rtol=2e-2)
+    assert (gu.float() - (x.float() @ w.float().t())).abs().max().item() < 3e-2 * k ** 0.5 / 8
+    assert torch.allclose(h.float(), native.silu_mul_fwd(gu).float(), atol=1e-3, rtol=1e-2)
+    assert torch.allclose(h.float(), ref_h.float(), atol=3e-2, rtol=3e-2)
