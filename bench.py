@@ -38,6 +38,8 @@ CONFIGS = {
                       num_layers=24, num_heads=16, d_ff=5504, rope_theta=10000.0, micro_batch=8),
     "ddp_124m": dict(model="TransformerLM-124M-class", vocab_size=50257, context_length=1024, d_model=768,
                      num_layers=12, num_heads=12, d_ff=2048, rope_theta=10000.0, micro_batch=16),
+    "fsdp_7b": dict(model="TransformerLM-7B", vocab_size=32000, context_length=4096, d_model=4096, num_layers=32,
+                    num_heads=32, d_ff=11008, rope_theta=10000.0, micro_batch=2, activation_checkpointing=True),
     "tiny": dict(model="TransformerLM-tiny", vocab_size=10000, context_length=256, d_model=512, num_layers=4,
                  num_heads=8, d_ff=1344, rope_theta=10000.0, micro_batch=8),
 }
@@ -181,6 +183,7 @@ def run_native(args, cfg, rank, local_rank, world):
     mkeys = ("vocab_size", "context_length", "d_model", "num_layers", "num_heads", "d_ff", "rope_theta")
     with torch.device(dev):
         model = TransformerLM(**{k: cfg[k] for k in mkeys}, use_flash_attn=True, use_custom_triton=True)
+    model.activation_checkpointing = bool(cfg.get("activation_checkpointing", False))
     wrapped = FSDP(model, comm=args.comm) if args.parallel == "fsdp" else DDP(model, comm=args.comm)
     opt = FusedAdamW(wrapped.parameters(), lr=LR, weight_decay=WEIGHT_DECAY)
     arena = wrapped.shard_arena if args.parallel == "fsdp" else model.engine().provider.arena
