@@ -481,8 +481,30 @@ __global__ void clip_coef_kernel(const float* __restrict__ sumsq, float max_norm
 
 template <typename T>
 __global__ void scale_kernel(T* __restrict__ x, long long n, const float* __restrict__ coef) {
+  // 16-byte accesses over the aligned body, scalar head and tail
   const float c = *coef;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+  constexpr int V = 16 / sizeof(T);
+  const long long head = min(n, (long long)(((16 - (reinterpret_cast<uintptr_t>(x) & 15)) & 15) / sizeof(T)));
+  const long long nvec = (n - head) / V;
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x, nth = (long long)gridDim.x * blockDim.x;
+  uint4* xv = reinterpret_cast<uint4*>(x + head);
+  for (long long i = tid; i < nvec; i += nth) {
+    uint4 v = xv[i];
+    if constexpr (sizeof(T) == 4) {
+      v.x = __float_as_uint(__uint_as_float(v.x) * c); v.y = __float_as_uint(__uint_as_float(v.y) * c);
+      v.z = __float_as_uint(__uint_as_float(v.z) * c); v.w = __float_as_uint(__uint_as_float(v.w) * c);
+    } else {
+      float2 f;
+      f = unpack_bf16x2(v.x); v.x = pack_bf16x2(f.x * c, f.y * c);
+      f = unpack_bf16x2(v.y); v.y = pack_bf16x2(f.x * c, f.y * c);
+      f = unpack_bf16x2(v.z); v.z = pack_bf16x2(f.x * c, f.y * c);
+      f = unpack_bf16x2(v.w); v.w = pack_bf16x2(f.x * c, f.y * c);
+    }
+    xv[i] = v;
+  }
+  const long long rest = n - head - nvec * V;
+  if (tid < head + rest) {
+    const long long i = tid < head ? tid : head + nvec * V + (tid - head);
     if constexpr (sizeof(T) == 4) x[i] = x[i] * c; else x[i] = __float2bfloat16(__bfloat162float(x[i]) * c);
   }
 }

@@ -131,6 +131,14 @@ def test_sumsq_clip_scale_cast():
     y = x.clone()
     native.scale_(y, coef)
     assert torch.allclose(y, x * coef)
+    # unaligned starts and ragged lengths take the scalar head / tail of the vectorised kernel
+    for dtype in (torch.float32, torch.bfloat16):
+        for off, n in ((1, 1000), (3, 7), (5, 4099), (0, 5)):
+            base = torch.randn(8192, device="cuda").to(dtype)
+            want = base.clone()
+            want[off:off + n] = (base[off:off + n].float() * coef).to(dtype)
+            native.scale_(base[off:off + n], coef)
+            assert torch.equal(base, want)
     b = torch.empty(x.numel(), device="cuda", dtype=torch.bfloat16)
     native.cast_copy(b, x)
     assert torch.equal(b, x.bfloat16())
