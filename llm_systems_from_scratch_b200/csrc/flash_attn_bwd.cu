@@ -9,8 +9,8 @@
 //                          S^T = K Q_i^T, dP^T = V dO_i^T        (TMEM, double buffered)
 //                          P^T = exp2(S^T*c - lse), dS^T = P^T*(dP^T - delta)*scale -> swizzled smem
 //                          dV += P^T dO_i,  dK += dS^T Q_i        (TMEM accumulators)
-//   flash_dq_kernel      CTA = 128 queries; walks 64-key steps j <= diagonal:
-//                          S = Q K_j^T, dP = dO V_j^T ; dS -> smem ; dQ += dS K_j
+//   flash_dq_kernel      CTA = 128 queries; walks 128-key steps j <= diagonal:
+//                          S = Q K_j^T, dP = dO V_j^T ; dS -> tensor memory ; dQ += dS K_j
 //
 // Roles per CTA: warp 0 TMA producer, warp 1 tcgen05.mma issuer, warps 2-5 one tile row per thread.
 #include "ptx.cuh"
@@ -32,7 +32,17 @@ struct FlashBwdParams {
   // (2, rope_ctx, dh/2) fp32 table; null = off.
   const float* rope_cs;
   int rope_ctx;
+  // Optional timeline of one CTA (clock64 stamps per role, step and event) for tuning; null = off.
+  long long* trace;
+  int trace_cta;
 };
+
+// stamp[(role * 64 + step) * 8 + slot] = SM clock, written by one lane of the traced CTA
+#define BWD_TRACE(role, step, slot)                                                          \
+  do {                                                                                       \
+    if (p.trace != nullptr && (int)blockIdx.x == p.trace_cta && lane == 0 && (step) < 64)    \
+      p.trace[((role) * 64 + (step)) * 8 + (slot)] = clock64();                              \
+  } while (0)
 
 // Inverse interleaved-pair rotation of 32 consecutive head columns starting at column e of the head.
 template <int DH>
@@ -185,8 +195,11 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
   float* delta_s = lse_s + 128;                                  // [2][64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh = blockIdx.x % (p.batch * p.heads);
-  const int jblk = blockIdx.x / (p.batch * p.heads);   // 128-key block; small j = most work, scheduled first
+  // CTAs of one (b, h) are neighbours in the grid, so the tiles they share are read from HBM once and then hit in
+  // L2; inside a (b, h) the key block with the most work (small j) is scheduled first.
+  const int n_kblk = (p.seq + 127) / 128;
+  const int bh = blockIdx.x / n_kblk;
+  const int jblk = blockIdx.x % n_kblk;
   const int b = bh / p.heads, h = bh % p.heads;
   const int row_base = b * p.seq;
   const int k0 = jblk * 128;
@@ -228,7 +241,9 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
   const int col_q = h * DH, col_k = p.d + h * DH, col_v = 2 * p.d + h * DH;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {   // elect.sync keeps the issuing code warp-uniform (descriptors in uniform registers)
+      const int lane = 0;   // the tracing macro stamps from the issuing thread
+      (void)lane;
       mbar_expect_tx(kv_full, 2 * L::KV_TILE);
 #pragma unroll
       for (int pn = 0; pn < L::PANELS; ++pn) {
@@ -249,7 +264,9 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (elect_one()) {   // elect.sync keeps the issuing code warp-uniform (descriptors in uniform registers)
+      const int lane = 0;   // the tracing macro stamps from the issuing thread
+      (void)lane;
       constexpr uint32_t idesc_12 = make_idesc_bf16(128, 64, false, false);
       constexpr uint32_t idesc_34 = make_idesc_bf16(128, DH, false, true);
       const uint32_t k_addr = smem_u32(smem + L::OFF_K), v_addr = smem_u32(smem + L::OFF_V);
@@ -425,67 +442,80 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
 }
 
 // ----------------------------------------------------------------------------------- dQ
+// CTA = 128 queries of one (b, h); walks 128-key steps j up to the diagonal:
+//   S = Q K_j^T and dP = dO V_j^T  (128 x 128 fp32 each, single buffered in tensor memory)
+//   dS = P * (dP - delta) * scale   written by the compute warps as packed bf16 into tensor memory
+//   dQ += dS K_j                    A operand straight from tensor memory, B = K_j MN-major
+// dS never touches shared memory, which therefore holds Q, dO, three K stages and two V stages (a K tile
+// stays live until its dQ MMA, a V tile only until its dP MMA).  Tensor pipe order per step:
+// [S, dP of step t+1] [dQ of step t], so the element-wise work on step t+1 overlaps the dQ MMAs of step t.
+constexpr int DQ_KSTAGES = 3;
+constexpr int DQ_VSTAGES = 2;
+
 template <int DH>
 struct DqSmem {
   static constexpr int PANELS = DH / 64;
-  static constexpr int Q_TILE = 128 * DH * 2;   // Q_i or dO_i (128 queries)
-  static constexpr int KV_TILE = 64 * DH * 2;   // K_j or V_j (64 keys)
+  static constexpr int TILE = 128 * DH * 2;   // Q_i, dO_i, K_j or V_j (128 rows)
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_DO = OFF_Q + Q_TILE;
-  static constexpr int OFF_K = OFF_DO + Q_TILE;               // BWD_RING stages
-  static constexpr int OFF_V = OFF_K + BWD_RING * KV_TILE;    // BWD_RING stages
-  static constexpr int OFF_DS = OFF_V + BWD_RING * KV_TILE;   // 128 x 64 bf16
-  static constexpr int OFF_BAR = OFF_DS + 2 * 16384;   // dS is double buffered
-  static constexpr int NUM_BARS = 1 + 2 * BWD_RING + 8;
+  static constexpr int OFF_DO = OFF_Q + TILE;
+  static constexpr int OFF_K = OFF_DO + TILE;                 // DQ_KSTAGES stages
+  static constexpr int OFF_V = OFF_K + DQ_KSTAGES * TILE;     // DQ_VSTAGES stages
+  static constexpr int OFF_BAR = OFF_V + DQ_VSTAGES * TILE;
+  static constexpr int NUM_BARS = 1 + 2 * DQ_KSTAGES + 2 * DQ_VSTAGES + 2 + 2 + 1;
   static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
 };
 
 template <int DH>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
-flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 over qkv
-                const __grid_constant__ CUtensorMap tm_do,   // box 64 x 128 over dO
-                const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 64 over qkv
+flash_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box 64 x 128 over qkv
+                const __grid_constant__ CUtensorMap tm_do,    // box 64 x 128 over dO
                 const FlashBwdParams p) {
   using L = DqSmem<DH>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* qd_full = bars;
-  uint64_t* kv_full = bars + 1;                    // [BWD_RING]
-  uint64_t* kv_empty = kv_full + BWD_RING;         // [BWD_RING]
-  uint64_t* s_full = kv_empty + BWD_RING;          // [2]
-  uint64_t* s_empty = s_full + 2;                  // [2]
-  uint64_t* p_full = s_empty + 2;                  // [2]
-  uint64_t* p_empty = p_full + 2;                  // [2]
+  uint64_t* k_full = bars + 1;                     // [DQ_KSTAGES]
+  uint64_t* k_empty = k_full + DQ_KSTAGES;         // [DQ_KSTAGES]  dQ MMAs of the step have completed
+  uint64_t* v_full = k_empty + DQ_KSTAGES;         // [DQ_VSTAGES]
+  uint64_t* v_empty = v_full + DQ_VSTAGES;         // [DQ_VSTAGES]  dP MMAs of the step have completed
+  uint64_t* s_full = v_empty + DQ_VSTAGES;         // S_t and dP_t are in tensor memory
+  uint64_t* s_empty = s_full + 1;                  // every compute thread has S_t and dP_t in registers
+  uint64_t* p_full = s_empty + 1;                  // [2] dS_t is in tensor memory
+  uint64_t* dq_done = p_full + 2;                  // all MMAs of the CTA have completed
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
   volatile uint32_t* abort_word = tmem_holder + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qblk = (p.seq + 127) / 128;
-  const int bh = blockIdx.x % (p.batch * p.heads);
-  const int iblk = n_qblk - 1 - blockIdx.x / (p.batch * p.heads);   // latest (heaviest) query tiles first
+  // CTAs of one (b, h) are neighbours in the grid and walk the same K / V tiles at about the same time, so those
+  // are read from HBM once and then hit in L2; inside a (b, h) the latest (heaviest) query tile goes first.
+  const int bh = blockIdx.x / n_qblk;
+  const int iblk = n_qblk - 1 - blockIdx.x % n_qblk;
   const int b = bh / p.heads, h = bh % p.heads;
   const int row_base = b * p.seq;
   const int q0 = iblk * 128;
-  const int n_steps = min((p.seq + 63) / 64, 2 * iblk + 2);   // 64-key steps up to the diagonal
+  const int n_steps = iblk + 1;   // 128-key steps up to and including the diagonal tile
 
   if (threadIdx.x == 0) {
     mbar_init(qd_full, 1);
-    for (int i = 0; i < BWD_RING; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+    for (int i = 0; i < DQ_KSTAGES; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], BWD_COMPUTE_THREADS);
-      mbar_init(&p_full[i], BWD_COMPUTE_THREADS);
-      mbar_init(&p_empty[i], 1);
+    for (int i = 0; i < DQ_VSTAGES; ++i) {
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
     }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, BWD_COMPUTE_THREADS);
+    mbar_init(&p_full[0], BWD_COMPUTE_THREADS);
+    mbar_init(&p_full[1], BWD_COMPUTE_THREADS);
+    mbar_init(dq_done, 1);
     *abort_word = 0;
     fence_barrier_init();
-    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_qkv);
     prefetch_tensormap(&tm_do);
-    prefetch_tensormap(&tm_kv);
   }
   if (warp == 1) {
     tmem_alloc(tmem_holder, 512);
@@ -495,85 +525,101 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tm_s = tmem_base;          // 2 x 64
-  const uint32_t tm_dp = tmem_base + 128;   // 2 x 64
-  const uint32_t tm_dq = tmem_base + 256;   // DH
+  const uint32_t tm_s = tmem_base;           // 128 columns
+  const uint32_t tm_dp = tmem_base + 128;    // 128 columns
+  const uint32_t tm_ds = tmem_base + 256;    // 2 x 64 columns of packed bf16 pairs
+  const uint32_t tm_dq = tmem_base + 384;    // DH columns
 
   const int col_q = h * DH, col_k = p.d + h * DH, col_v = 2 * p.d + h * DH;
 
   if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(qd_full, 2 * L::Q_TILE);
+    if (elect_one()) {   // elect.sync keeps the issuing code warp-uniform (descriptors in uniform registers)
+      const int lane = 0;   // the tracing macro stamps from the issuing thread
+      (void)lane;
+      mbar_expect_tx(qd_full, 2 * L::TILE);
 #pragma unroll
       for (int pn = 0; pn < L::PANELS; ++pn) {
-        tma_load_2d(smem + L::OFF_Q + pn * 16384, &tm_q, qd_full, col_q + pn * 64, row_base + q0);
+        tma_load_2d(smem + L::OFF_Q + pn * 16384, &tm_qkv, qd_full, col_q + pn * 64, row_base + q0);
         tma_load_2d(smem + L::OFF_DO + pn * 16384, &tm_do, qd_full, h * DH + pn * 64, row_base + q0);
       }
       for (int t = 0; t < n_steps; ++t) {
-        const int st = t % BWD_RING;
-        const uint32_t ph = (t / BWD_RING) & 1;
-        const int krow = row_base + t * 64;
-        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_word)) { *abort_word = ERR_WAIT_EMPTY; break; }
-        mbar_expect_tx(&kv_full[st], 2 * L::KV_TILE);
+        const int ks = t % DQ_KSTAGES, vs = t % DQ_VSTAGES;
+        const int krow = row_base + t * 128;
+        if (!mbar_wait(&k_empty[ks], ((t / DQ_KSTAGES) & 1) ^ 1, abort_word)) { *abort_word = ERR_WAIT_EMPTY; break; }
+        BWD_TRACE(0, t, 0);
+        mbar_expect_tx(&k_full[ks], L::TILE);
 #pragma unroll
-        for (int pn = 0; pn < L::PANELS; ++pn) {
-          tma_load_2d(smem + L::OFF_K + st * L::KV_TILE + pn * 8192, &tm_kv, &kv_full[st], col_k + pn * 64, krow);
-          tma_load_2d(smem + L::OFF_V + st * L::KV_TILE + pn * 8192, &tm_kv, &kv_full[st], col_v + pn * 64, krow);
-        }
+        for (int pn = 0; pn < L::PANELS; ++pn)
+          tma_load_2d(smem + L::OFF_K + ks * L::TILE + pn * 16384, &tm_qkv, &k_full[ks], col_k + pn * 64, krow);
+        if (!mbar_wait(&v_empty[vs], ((t / DQ_VSTAGES) & 1) ^ 1, abort_word)) { *abort_word = ERR_WAIT_EMPTY; break; }
+        BWD_TRACE(0, t, 1);
+        mbar_expect_tx(&v_full[vs], L::TILE);
+#pragma unroll
+        for (int pn = 0; pn < L::PANELS; ++pn)
+          tma_load_2d(smem + L::OFF_V + vs * L::TILE + pn * 16384, &tm_qkv, &v_full[vs], col_v + pn * 64, krow);
+      }
+    } else if (lane == 1 && p.trace != nullptr && (int)blockIdx.x == p.trace_cta) {
+      // tuning aid: arrival time of every K and V tile
+      for (int t = 0; t < n_steps && t < 64; ++t) {
+        if (!mbar_wait(&k_full[t % DQ_KSTAGES], (t / DQ_KSTAGES) & 1, abort_word)) break;
+        p.trace[(0 * 64 + t) * 8 + 2] = clock64();
+        if (!mbar_wait(&v_full[t % DQ_VSTAGES], (t / DQ_VSTAGES) & 1, abort_word)) break;
+        p.trace[(0 * 64 + t) * 8 + 3] = clock64();
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_12 = make_idesc_bf16(128, 64, false, false);
+    // elect.sync keeps the issuing code warp-uniform for the compiler (descriptors in uniform registers)
+    if (elect_one()) {
+      const int lane = 0;   // the tracing macro stamps from the issuing thread
+      (void)lane;
+      constexpr uint32_t idesc_12 = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_3 = make_idesc_bf16(128, DH, false, true);
-      const uint32_t q_addr = smem_u32(smem + L::OFF_Q), do_addr = smem_u32(smem + L::OFF_DO);
-      const uint32_t ds_base = smem_u32(smem + L::OFF_DS);
+      const uint64_t q_desc = make_smem_desc(smem_u32(smem + L::OFF_Q), 16, 1024);
+      const uint64_t do_desc = make_smem_desc(smem_u32(smem + L::OFF_DO), 16, 1024);
       auto issue12 = [&](int t) {
-        const int st = t & 1, rs = t % BWD_RING;
-        const uint32_t k_addr = smem_u32(smem + L::OFF_K + rs * L::KV_TILE);
-        const uint32_t v_addr = smem_u32(smem + L::OFF_V + rs * L::KV_TILE);
+        const uint64_t k_desc = make_smem_desc(smem_u32(smem + L::OFF_K + (t % DQ_KSTAGES) * L::TILE), 16, 1024);
+        const uint64_t v_desc = make_smem_desc(smem_u32(smem + L::OFF_V + (t % DQ_VSTAGES) * L::TILE), 16, 1024);
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k) {
-          const uint32_t offa = (k / 4) * 16384 + (k % 4) * 32;
-          const uint32_t offb = (k / 4) * 8192 + (k % 4) * 32;
-          umma_f16_ss(tm_s + st * 64, make_smem_desc(q_addr + offa, 16, 1024), make_smem_desc(k_addr + offb, 16, 1024),
-                      idesc_12, k > 0 ? 1u : 0u);
+          const uint32_t off = ((k / 4) * 16384 + (k % 4) * 32) >> 4;
+          umma_f16_ss(tm_s, q_desc + off, k_desc + off, idesc_12, k > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k) {
-          const uint32_t offa = (k / 4) * 16384 + (k % 4) * 32;
-          const uint32_t offb = (k / 4) * 8192 + (k % 4) * 32;
-          umma_f16_ss(tm_dp + st * 64, make_smem_desc(do_addr + offa, 16, 1024),
-                      make_smem_desc(v_addr + offb, 16, 1024), idesc_12, k > 0 ? 1u : 0u);
+          const uint32_t off = ((k / 4) * 16384 + (k % 4) * 32) >> 4;
+          umma_f16_ss(tm_dp, do_desc + off, v_desc + off, idesc_12, k > 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[st]);
+        umma_commit(s_full);
+        umma_commit(&v_empty[t % DQ_VSTAGES]);
       };
-      bool ok = mbar_wait(qd_full, 0, abort_word) && mbar_wait(&kv_full[0], 0, abort_word);
+      bool ok = mbar_wait(qd_full, 0, abort_word) && mbar_wait(&k_full[0], 0, abort_word) &&
+                mbar_wait(&v_full[0], 0, abort_word);
       if (ok) { tc_fence_after(); issue12(0); }
       for (int t = 0; t < n_steps && ok; ++t) {
-        const int st = t & 1;
         if (t + 1 < n_steps) {
-          const int st1 = (t + 1) & 1;
-          const uint32_t ph1 = ((t + 1) >> 1) & 1;
-          ok = mbar_wait(&kv_full[(t + 1) % BWD_RING], ((t + 1) / BWD_RING) & 1, abort_word) &&
-               mbar_wait(&s_empty[st1], ph1 ^ 1, abort_word);
+          ok = mbar_wait(&k_full[(t + 1) % DQ_KSTAGES], ((t + 1) / DQ_KSTAGES) & 1, abort_word) &&
+               mbar_wait(&v_full[(t + 1) % DQ_VSTAGES], ((t + 1) / DQ_VSTAGES) & 1, abort_word) &&
+               mbar_wait(s_empty, t & 1, abort_word);
           if (!ok) break;
           tc_fence_after();
+          BWD_TRACE(1, t, 0);
           issue12(t + 1);
+          BWD_TRACE(1, t, 1);
         }
-        ok = mbar_wait(&p_full[st], (t >> 1) & 1, abort_word);
+        ok = mbar_wait(&p_full[t & 1], (t >> 1) & 1, abort_word);
         if (!ok) break;
         tc_fence_after();
-        const int rs = t % BWD_RING;
-        const uint32_t k_addr = smem_u32(smem + L::OFF_K + rs * L::KV_TILE);
-        const uint32_t ds_addr = ds_base + st * 16384;
+        BWD_TRACE(1, t, 2);
+        // K = 128 keys; A = dS_t from tensor memory (16 keys = 8 packed columns); B = K_t MN-major: 16 keys are
+        // 2048 B apart inside a 64-column panel, the dh panels 16384 B apart.
+        const uint64_t kmn_desc = make_smem_desc(smem_u32(smem + L::OFF_K + (t % DQ_KSTAGES) * L::TILE), 16384, 1024);
+        const uint32_t a_tmem = tm_ds + (t & 1) * 64;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {   // K = 64 keys; B = K_j MN-major (dh contiguous)
-          umma_f16_ss(tm_dq, make_smem_desc(ds_addr + k * 32, 16, 1024), make_smem_desc(k_addr + k * 2048, 8192, 1024),
-                      idesc_3, (t > 0 || k > 0) ? 1u : 0u);
-        }
-        umma_commit(&p_empty[st]);
-        umma_commit(&kv_empty[rs]);
+        for (int k = 0; k < 8; ++k)
+          umma_f16_ts(tm_dq, a_tmem + k * 8, kmn_desc + ((k * 2048) >> 4), idesc_3, (t > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&k_empty[t % DQ_KSTAGES]);
+        if (t == n_steps - 1) umma_commit(dq_done);
+        BWD_TRACE(1, t, 3);
       }
       if (!ok) *abort_word = ERR_WAIT_FULL;
     }
@@ -581,50 +627,68 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_q,    // box 64 x 128 ove
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int q_idx = q0 + r;
-    const int cg = (warp - 2) >> 2;
+    const int cg = (warp - 2) >> 2;          // this thread's 64 of the step's 128 keys
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const bool valid = q_idx < p.seq;
     const size_t vec = ((size_t)b * p.heads + h) * p.seq + q_idx;
-    const float lse2 = valid ? p.lse[vec] * 1.4426950408889634f : INFINITY;
+    const float lse2 = valid ? p.lse[vec] * 1.4426950408889634f : INFINITY;   // +inf: padded rows get P = 0
     const float dlt_scaled = valid ? p.delta[vec] * p.scale : 0.f;
     bool ok = true;
     for (int t = 0; t < n_steps; ++t) {
-      const int st = t & 1;
-      const uint32_t ph = (t >> 1) & 1;
-      const int kb = t * 64;
-      if (!mbar_wait(&s_full[st], ph, abort_word)) { ok = false; break; }
+      const int trole = warp;
+      BWD_TRACE(trole, t, 0);
+      if (!mbar_wait(s_full, t & 1, abort_word)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sreg[BWD_COLS], dreg[BWD_COLS];
-      tmem_ld_32x32(tm_s + lane_addr + st * 64 + cg * BWD_COLS, sreg);
-      tmem_ld_32x32(tm_dp + lane_addr + st * 64 + cg * BWD_COLS, dreg);
+      BWD_TRACE(trole, t, 1);
+      uint32_t sreg[2][32], dreg[2][32];
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        tmem_ld_32x32(tm_s + lane_addr + cg * 64 + hf * 32, sreg[hf]);
+        tmem_ld_32x32(tm_dp + lane_addr + cg * 64 + hf * 32, dreg[hf]);
+      }
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&s_empty[st]);
-      const bool need_mask = (kb + 64 > q0);
-      float dsv[BWD_COLS];
-      // lse2 is +inf for padded query rows, so their probabilities are exactly zero
-      if (need_mask) {
+      mbar_arrive(s_empty);      // S and dP may be overwritten by the MMAs of step t+1
+      BWD_TRACE(trole, t, 2);
+      const int kb = t * 128 + cg * 64;
+      uint32_t packed[32];
+      if (t == n_steps - 1) {   // diagonal tile: causal mask
 #pragma unroll
-        for (int c = 0; c < BWD_COLS; ++c) {
-          const int col = cg * BWD_COLS + c;
-          float pe = fast_exp2(__uint_as_float(sreg[c]) * p.scale_log2 - lse2);
-          pe = (kb + col > q_idx) ? 0.f : pe;
-          dsv[c] = pe * (__uint_as_float(dreg[c]) * p.scale - dlt_scaled);
-        }
+        for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            float ds[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              float pe = fast_exp2(__uint_as_float(sreg[hf][c + e]) * p.scale_log2 - lse2);
+              pe = (kb + hf * 32 + c + e > q_idx) ? 0.f : pe;
+              ds[e] = pe * (__uint_as_float(dreg[hf][c + e]) * p.scale - dlt_scaled);
+            }
+            packed[hf * 16 + c / 2] = pack_bf16x2(ds[0], ds[1]);
+          }
       } else {
 #pragma unroll
-        for (int c = 0; c < BWD_COLS; ++c) {
-          const float pe = fast_exp2(__uint_as_float(sreg[c]) * p.scale_log2 - lse2);
-          dsv[c] = pe * (__uint_as_float(dreg[c]) * p.scale - dlt_scaled);
-        }
+        for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            float ds[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float pe = fast_exp2(__uint_as_float(sreg[hf][c + e]) * p.scale_log2 - lse2);
+              ds[e] = pe * (__uint_as_float(dreg[hf][c + e]) * p.scale - dlt_scaled);
+            }
+            packed[hf * 16 + c / 2] = pack_bf16x2(ds[0], ds[1]);
+          }
       }
-      if (!mbar_wait(&p_empty[st], ph ^ 1, abort_word)) { ok = false; break; }
-      store_row16_swizzled(smem + L::OFF_DS + st * 16384, r, cg, dsv);
-      fence_proxy_async_smem();
+      BWD_TRACE(trole, t, 3);
+      // Buffer t&1 was last read by the dQ MMAs of step t-2, which precede the S MMAs of step t in the tensor pipe.
+      tmem_st_32x32(tm_ds + lane_addr + (t & 1) * 64 + cg * 32, packed);
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&p_full[st]);
+      mbar_arrive(&p_full[t & 1]);
+      BWD_TRACE(trole, t, 4);
     }
-    if (ok) ok = mbar_wait(&p_empty[(n_steps - 1) & 1], ((n_steps - 1) >> 1) & 1, abort_word);
+    if (ok) ok = mbar_wait(dq_done, 0, abort_word);
     if (ok) {
       tc_fence_after();
       __nv_bfloat16* dq_row = p.dqkv + (size_t)(row_base + q_idx) * 3 * p.d + col_q;
@@ -682,13 +746,23 @@ static int launch_flash_bwd(const void* qkv, const void* dout, const FlashBwdPar
   }
   const int n_kblk = (p.seq + 127) / 128;
   k1<<<p.batch * p.heads * n_kblk, BWD_THREADS, DkDvSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_qkv64, tm_do64, p);
-  k2<<<p.batch * p.heads * n_kblk, BWD_THREADS, DqSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_do128, tm_qkv64, p);
+  k2<<<p.batch * p.heads * n_kblk, BWD_THREADS, DqSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_do128, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace b200
 
 using namespace b200;
+
+static long long* g_bwd_trace = nullptr;
+static int g_bwd_trace_cta = 0;
+
+// Tuning aid: record the timeline of CTA `cta` of the next backward launches into `buf`
+// (device memory, 10 roles x 64 steps x 8 stamps of 8 bytes); null switches it off.
+extern "C" void b200_flash_bwd_set_trace(long long* buf, int cta) {
+  g_bwd_trace = buf;
+  g_bwd_trace_cta = cta;
+}
 
 // qkv (rows, 3d), o / dout (rows, d) bf16; lse (batch, heads, seq) from the forward; delta: scratch of the
 // same shape (fp32); dqkv (rows, 3d) bf16 receives dQ | dK | dV.  dh must be 64 or 128.
@@ -719,6 +793,7 @@ static int flash_bwd_impl(const void* qkv, const void* o, const void* dout, cons
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   p.rope_cs = rope_cs; p.rope_ctx = rope_ctx;
+  p.trace = g_bwd_trace; p.trace_cta = g_bwd_trace_cta;
   return dh == 64 ? launch_flash_bwd<64>(qkv, dout, p, stream) : launch_flash_bwd<128>(qkv, dout, p, stream);
 }
 

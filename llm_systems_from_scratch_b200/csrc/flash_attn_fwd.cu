@@ -41,7 +41,16 @@ struct FlashFwdParams {
   int n_qblk;
   float scale_log2;      // softmax scale * log2(e)
   uint32_t* status;
+  long long* trace;      // optional timeline of CTA `trace_cta` (tuning aid); null = off
+  int trace_cta;
 };
+
+// stamp[(role * 64 + step) * 8 + slot] = SM clock, written by one lane of the traced CTA
+#define FWD_TRACE(role, step, slot)                                                          \
+  do {                                                                                       \
+    if (p.trace != nullptr && (int)blockIdx.x == p.trace_cta && lane == 0 && (step) < 64)    \
+      p.trace[((role) * 64 + (step)) * 8 + (slot)] = clock64();                              \
+  } while (0)
 
 template <int DH>
 struct FlashFwdSmem {
@@ -79,9 +88,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // Work assignment: heaviest (latest) query tiles first.
-  const int bh = blockIdx.x % (p.batch * p.heads);
-  const int qblk = p.n_qblk - 1 - blockIdx.x / (p.batch * p.heads);
+  // Work assignment: the query tiles of one (b, h) are neighbours in the grid and walk the same K / V tiles at about
+  // the same time (one HBM read, then L2 hits); inside a (b, h) the heaviest (latest) query tile goes first.
+  const int bh = blockIdx.x / p.n_qblk;
+  const int qblk = p.n_qblk - 1 - blockIdx.x % p.n_qblk;
   const int b = bh / p.heads, h = bh % p.heads;
   int row_base, seq_len;
   if (p.cu_seqlens != nullptr) {
@@ -125,7 +135,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
   const int col_q = h * DH, col_k = p.d + h * DH, col_v = 2 * p.d + h * DH;
 
   if (warp == 0) {
-    if (lane == 0 && active) {
+    if (active && elect_one()) {   // elect.sync keeps the issuing code warp-uniform (descriptors in uniform registers)
+      const int lane = 0;   // the tracing macro stamps from the issuing thread
+      (void)lane;
       mbar_expect_tx(q_full, L::TILE_BYTES);
 #pragma unroll
       for (int pn = 0; pn < L::PANELS; ++pn)
@@ -147,7 +159,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && active) {
+    if (active && elect_one()) {   // elect.sync keeps the issuing code warp-uniform (descriptors in uniform registers)
+      const int lane = 0;   // the tracing macro stamps from the issuing thread
+      (void)lane;
       constexpr uint32_t idesc_qk = make_idesc_bf16(128, FA_BK, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, DH, false, true);
       const uint32_t q_addr = smem_u32(smem + L::OFF_Q);
@@ -178,11 +192,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
           ok = mbar_wait(&k_full[st1], ph1, abort_word) && mbar_wait(&s_empty[st1], ph1 ^ 1, abort_word);
           if (!ok) break;
           tc_fence_after();
+          FWD_TRACE(1, j, 0);
           issue_s(j + 1);
+          FWD_TRACE(1, j, 1);
         }
         ok = mbar_wait(p_full, j & 1, abort_word) && mbar_wait(&v_full[st], ph, abort_word);
         if (!ok) break;
         tc_fence_after();
+        FWD_TRACE(1, j, 2);
         const uint32_t v_addr = smem_u32(smem + L::OFF_V + st * L::TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < FA_BK / 16; ++k) {
@@ -194,6 +211,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
         }
         umma_commit(p_empty);
         umma_commit(&v_empty[st]);
+        FWD_TRACE(1, j, 3);
       }
       if (!ok) *abort_word = ERR_WAIT_FULL;
     }
@@ -217,12 +235,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
       const uint32_t ph = (j >> 1) & 1;
       float mx = -INFINITY;
       uint32_t s[2][32];
+      const int trole = warp;
+      FWD_TRACE(trole, j, 0);
       if (ok && !mbar_wait(&s_full[st], ph, abort_word)) ok = false;
       if (ok) {
         tc_fence_after();
+        FWD_TRACE(trole, j, 1);
 #pragma unroll
         for (int c = 0; c < 2; ++c) tmem_ld_32x32(tmem_s + lane_addr + st * 128 + wg * 64 + c * 32, s[c]);
         tmem_ld_wait();
+        FWD_TRACE(trole, j, 2);
         tc_fence_before();
         mbar_arrive(&s_empty[st]);
         const bool diag = (j == n_kv - 1);
@@ -245,8 +267,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
         mx *= p.scale_log2;
         xch[(st * 2 + wg) * 128 + r] = mx;
       }
+      FWD_TRACE(trole, j, 3);
       named_barrier_sync(1, 256);               // reached by all 256 softmax threads every step
       if (!ok) continue;
+      FWD_TRACE(trole, j, 4);
       mx = fmaxf(mx, xch[(st * 2 + (wg ^ 1)) * 128 + r]);
       // Lazy rescale: keep the old reference max unless it moved by more than 8 (a factor 256).
       float m_new = m_run;
@@ -265,9 +289,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
       l_run = l_run * (need ? alpha : 1.f) + sum;
       m_run = m_new;
       // P_{j-1} V_{j-1} must have finished before P is overwritten or O is rescaled.
+      FWD_TRACE(trole, j, 5);
       if (j > 0) {
         if (!mbar_wait(p_empty, (j - 1) & 1, abort_word)) { ok = false; continue; }
         tc_fence_after();
+        FWD_TRACE(trole, j, 6);
         if (__any_sync(0xffffffffu, need)) {
           const float f = need ? alpha : 1.f;
 #pragma unroll 1
@@ -298,6 +324,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
+      FWD_TRACE(trole, j, 7);
     }
     // ------------------------------------------------------------------- epilogue
     xch[512 + wg * 128 + r] = l_run;            // combine the two partial row sums (own buffer: no reuse hazard)
@@ -365,6 +392,16 @@ static int launch_flash_fwd(const CUtensorMap& tm, const FlashFwdParams& p, cuda
 
 using namespace b200;
 
+static long long* g_fwd_trace = nullptr;
+static int g_fwd_trace_cta = 0;
+
+// Tuning aid: record the timeline of CTA `cta` of the next forward launches into `buf`
+// (device memory, 10 roles x 64 steps x 8 stamps of 8 bytes); null switches it off.
+extern "C" void b200_flash_fwd_set_trace(long long* buf, int cta) {
+  g_fwd_trace = buf;
+  g_fwd_trace_cta = cta;
+}
+
 // qkv: (rows, 3*heads*dh) bf16 row-major, rows = batch*seq (or cu_seqlens[batch] when packed).
 // o: (rows, heads*dh) bf16.  lse: (batch, heads, seq) fp32 or null.  dh must be 64 or 128.
 extern "C" int b200_flash_fwd(const void* qkv, void* o, float* lse, int batch, int seq, int heads, int dh,
@@ -381,6 +418,7 @@ extern "C" int b200_flash_fwd(const void* qkv, void* o, float* lse, int batch, i
   p.n_qblk = (seq + FA_BQ - 1) / FA_BQ;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.trace = g_fwd_trace; p.trace_cta = g_fwd_trace_cta;
   return dh == 64 ? launch_flash_fwd<64>(tm, p, stream) : launch_flash_fwd<128>(tm, p, stream);
 }
 
@@ -401,5 +439,6 @@ extern "C" int b200_flash_varlen_fwd(const void* qkv, void* o, const int* cu_seq
   p.n_qblk = (max_seq + FA_BQ - 1) / FA_BQ;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.trace = g_fwd_trace; p.trace_cta = g_fwd_trace_cta;
   return dh == 64 ? launch_flash_fwd<64>(tm, p, stream) : launch_flash_fwd<128>(tm, p, stream);
 }

@@ -75,7 +75,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (elect_one()) {   // elect.sync keeps the issuing code warp-uniform (descriptors in uniform registers)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -114,7 +114,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (elect_one()) {   // elect.sync keeps the issuing code warp-uniform (descriptors in uniform registers)
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;

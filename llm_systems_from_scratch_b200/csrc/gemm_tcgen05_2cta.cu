@@ -144,7 +144,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {   // elect.sync keeps the issuing code warp-uniform (descriptors in uniform registers)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -198,7 +198,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && leader) {
+    if (leader && elect_one()) {
       constexpr uint32_t idesc = make_idesc_bf16(256, P_BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0, acc_phase[2] = {0, 0};
