@@ -37,6 +37,21 @@ struct FlashBwdParams {
   int trace_cta;
 };
 
+// CTA log (trace_cta == BWD_CTA_LOG): every CTA records its SM, start / end time and step count
+constexpr int BWD_CTA_LOG = 100000;
+__device__ __forceinline__ uint32_t smid() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+  return r;
+}
+#define BWD_CTA_LOG_END(kernel_id, t_start, steps)                                             \
+  do {                                                                                         \
+    if (p.trace != nullptr && p.trace_cta == BWD_CTA_LOG && threadIdx.x == 0) {                \
+      long long* rec = p.trace + ((kernel_id) * 4096 + blockIdx.x) * 4;                        \
+      rec[0] = smid(); rec[1] = (long long)(t_start); rec[2] = (long long)globaltimer_ns(); rec[3] = (steps); \
+    }                                                                                          \
+  } while (0)
+
 // stamp[(role * 64 + step) * 8 + slot] = SM clock, written by one lane of the traced CTA
 #define BWD_TRACE(role, step, slot)                                                          \
   do {                                                                                       \
@@ -115,7 +130,8 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
 // The element-wise stage of both kernels is spread over BWD_CG warpgroups: warpgroup g handles
 // columns [g*BWD_COLS, (g+1)*BWD_COLS) of every 64-column step, so 8 warps (2 per scheduler) hide each
 // other's TMEM-load, exp2 and shared-memory latencies instead of one warp per scheduler.
-constexpr int BWD_RING = 3;   // TMA ring depth for the per-step tiles: the load of step t+2 is in flight during step t
+constexpr int BWD_RING = 4;   // TMA ring depth of the dK/dV kernel's per-step Q / dO tiles
+constexpr int DKDV_VEC_STEPS = 32;   // steps whose lse / delta are staged in shared memory at a time
 constexpr int BWD_CG = 2;
 constexpr int BWD_COLS = 64 / BWD_CG;                 // 32 columns per thread and step
 constexpr int BWD_COMPUTE_THREADS = 128 * BWD_CG;     // 256
@@ -131,30 +147,10 @@ __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-// Write BWD_COLS bf16 values (this column group's 16-byte chunks of one 128-byte row of a 128B-swizzled panel).
-__device__ __forceinline__ void store_row16_swizzled(uint8_t* panel, int r, int cg, const float (&v)[BWD_COLS]) {
-  uint8_t* row = panel + r * 128;
-#pragma unroll
-  for (int j = 0; j < BWD_COLS / 8; ++j) {
-    const int c16 = cg * (BWD_COLS / 8) + j;
-    uint4 u = make_uint4(pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]), pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]),
-                         pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]), pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]));
-    *reinterpret_cast<uint4*>(row + ((c16 ^ (r & 7)) << 4)) = u;
-  }
-}
-
-// Write 64 bf16 values (one 128-byte row of a 128B-swizzled panel) from fp32 registers.
-__device__ __forceinline__ void store_row64_swizzled(uint8_t* panel, int r, const float (&v)[64]) {
-  uint8_t* row = panel + r * 128;
-#pragma unroll
-  for (int c16 = 0; c16 < 8; ++c16) {
-    uint4 u = make_uint4(pack_bf16x2(v[c16 * 8 + 0], v[c16 * 8 + 1]), pack_bf16x2(v[c16 * 8 + 2], v[c16 * 8 + 3]),
-                         pack_bf16x2(v[c16 * 8 + 4], v[c16 * 8 + 5]), pack_bf16x2(v[c16 * 8 + 6], v[c16 * 8 + 7]));
-    *reinterpret_cast<uint4*>(row + ((c16 ^ (r & 7)) << 4)) = u;
-  }
-}
-
 // ------------------------------------------------------------------------------ dK / dV
+// P^T and dS^T never touch shared memory: the compute warps write them as packed bf16 over the S^T / dP^T
+// columns they have just read (tcgen05.st) and the dV / dK MMAs take their A operand from tensor memory.
+// The shared memory that frees holds a five-stage Q / dO ring.
 template <int DH>
 struct DkDvSmem {
   static constexpr int PANELS = DH / 64;
@@ -164,11 +160,9 @@ struct DkDvSmem {
   static constexpr int OFF_V = OFF_K + KV_TILE;
   static constexpr int OFF_Q = OFF_V + KV_TILE;                // BWD_RING stages
   static constexpr int OFF_DO = OFF_Q + BWD_RING * Q_TILE;     // BWD_RING stages
-  static constexpr int OFF_PT = OFF_DO + BWD_RING * Q_TILE;    // 128 x 64 bf16
-  static constexpr int OFF_DST = OFF_PT + 2 * 16384;     // P^T and dS^T are double buffered
-  static constexpr int OFF_VEC = OFF_DST + 2 * 16384;    // lse[2][64], delta[2][64] floats
-  static constexpr int OFF_BAR = OFF_VEC + 4 * 64 * 4;
-  static constexpr int NUM_BARS = 1 + 2 * BWD_RING + 8;
+  static constexpr int OFF_VEC = OFF_DO + BWD_RING * Q_TILE;   // lse and delta of DKDV_VEC_STEPS steps (floats)
+  static constexpr int OFF_BAR = OFF_VEC + 2 * DKDV_VEC_STEPS * 64 * 4;
+  static constexpr int NUM_BARS = 1 + 2 * BWD_RING + 5;
   static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
 };
 
@@ -179,27 +173,26 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
                   const __grid_constant__ CUtensorMap tm_do,   // box 64 x 64 over dO
                   const FlashBwdParams p) {
   using L = DkDvSmem<DH>;
+  const uint64_t t_cta_start = globaltimer_ns();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* kv_full = bars;
   uint64_t* qd_full = bars + 1;                    // [BWD_RING]
   uint64_t* qd_empty = qd_full + BWD_RING;         // [BWD_RING]
-  uint64_t* s_full = qd_empty + BWD_RING;          // [2]
-  uint64_t* s_empty = s_full + 2;                  // [2]
-  uint64_t* p_full = s_empty + 2;                  // [2]
-  uint64_t* p_empty = p_full + 2;                  // [2]
+  uint64_t* s_full = qd_empty + BWD_RING;          // [2]  S^T_t and dP^T_t are in tensor memory
+  uint64_t* p_full = s_full + 2;                   // [2]  P^T_t and dS^T_t are in tensor memory
+  uint64_t* all_done = p_full + 2;                 // every MMA of the CTA has completed
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
   volatile uint32_t* abort_word = tmem_holder + 1;
-  float* lse_s = reinterpret_cast<float*>(smem + L::OFF_VEC);   // [2][64]
-  float* delta_s = lse_s + 128;                                  // [2][64]
+  float* lse_s = reinterpret_cast<float*>(smem + L::OFF_VEC);   // [DKDV_VEC_STEPS * 64]
+  float* delta_s = lse_s + DKDV_VEC_STEPS * 64;                 // [DKDV_VEC_STEPS * 64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // CTAs of one (b, h) are neighbours in the grid, so the tiles they share are read from HBM once and then hit in
-  // L2; inside a (b, h) the key block with the most work (small j) is scheduled first.
-  const int n_kblk = (p.seq + 127) / 128;
-  const int bh = blockIdx.x / n_kblk;
-  const int jblk = blockIdx.x % n_kblk;
+  // Longest-first order over the whole grid (small j = most query steps), so the tail of the launch is made of
+  // short CTAs; the (b, h) index varies fastest.
+  const int bh = blockIdx.x % (p.batch * p.heads);
+  const int jblk = blockIdx.x / (p.batch * p.heads);
   const int b = bh / p.heads, h = bh % p.heads;
   const int row_base = b * p.seq;
   const int k0 = jblk * 128;
@@ -215,10 +208,9 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], BWD_COMPUTE_THREADS);
       mbar_init(&p_full[i], BWD_COMPUTE_THREADS);
-      mbar_init(&p_empty[i], 1);
     }
+    mbar_init(all_done, 1);
     *abort_word = 0;
     fence_barrier_init();
     prefetch_tensormap(&tm_kv);
@@ -270,7 +262,6 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
       constexpr uint32_t idesc_12 = make_idesc_bf16(128, 64, false, false);
       constexpr uint32_t idesc_34 = make_idesc_bf16(128, DH, false, true);
       const uint32_t k_addr = smem_u32(smem + L::OFF_K), v_addr = smem_u32(smem + L::OFF_V);
-      const uint32_t pt_base = smem_u32(smem + L::OFF_PT), dst_base = smem_u32(smem + L::OFF_DST);
       auto issue12 = [&](int t) {
         const int st = t & 1, rs = t % BWD_RING;
         const uint32_t q_addr = smem_u32(smem + L::OFF_Q + rs * L::Q_TILE);
@@ -296,34 +287,40 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
       for (int t = 0; t < n_steps && ok; ++t) {
         const int st = t & 1;
         if (t + 1 < n_steps) {
-          const int st1 = (t + 1) & 1;
-          const uint32_t ph1 = ((t + 1) >> 1) & 1;
-          ok = mbar_wait(&qd_full[(t + 1) % BWD_RING], ((t + 1) / BWD_RING) & 1, abort_word) &&
-               mbar_wait(&s_empty[st1], ph1 ^ 1, abort_word);
+          // Buffer (t+1)&1 is free: its last readers, the compute warps of step t-1, arrived on p_full before the
+          // dV / dK MMAs of step t-1 were issued, and those MMAs precede this issue in the tensor pipe.
+          ok = mbar_wait(&qd_full[(t + 1) % BWD_RING], ((t + 1) / BWD_RING) & 1, abort_word);
           if (!ok) break;
           tc_fence_after();
+          BWD_TRACE(1, t, 0);
           issue12(t + 1);
+          BWD_TRACE(1, t, 1);
         }
         ok = mbar_wait(&p_full[st], (t >> 1) & 1, abort_word);
         if (!ok) break;
         tc_fence_after();
+        BWD_TRACE(1, t, 2);
         const int rs = t % BWD_RING;
         const uint32_t q_addr = smem_u32(smem + L::OFF_Q + rs * L::Q_TILE);
         const uint32_t do_addr = smem_u32(smem + L::OFF_DO + rs * L::Q_TILE);
-        const uint32_t pt_addr = pt_base + st * 16384, dst_addr = dst_base + st * 16384;
+        // K = 64 queries.  A: column group g of the compute warps left queries [32g, 32g+32) as 16 packed columns
+        // at column 32g of the S^T / dP^T buffer.  B operands are MN-major: dh contiguous, 16 queries = 2048 B per
+        // step, dh panels 8192 B apart.
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {   // K = 64 queries
-          // B operands are MN-major: dh contiguous, 16 queries = 2048 B per step, dh panels 8192 B apart
-          umma_f16_ss(tm_dv, make_smem_desc(pt_addr + k * 32, 16, 1024), make_smem_desc(do_addr + k * 2048, 8192, 1024),
-                      idesc_34, (t > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t a_off = st * 64 + (k >> 1) * BWD_COLS + (k & 1) * 8;
+          umma_f16_ts(tm_dv, tm_st + a_off, make_smem_desc(do_addr + k * 2048, 8192, 1024), idesc_34,
+                      (t > 0 || k > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          umma_f16_ss(tm_dk, make_smem_desc(dst_addr + k * 32, 16, 1024), make_smem_desc(q_addr + k * 2048, 8192, 1024),
-                      idesc_34, (t > 0 || k > 0) ? 1u : 0u);
+          const uint32_t a_off = st * 64 + (k >> 1) * BWD_COLS + (k & 1) * 8;
+          umma_f16_ts(tm_dk, tm_dpt + a_off, make_smem_desc(q_addr + k * 2048, 8192, 1024), idesc_34,
+                      (t > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(&p_empty[st]);
         umma_commit(&qd_empty[rs]);
+        if (t == n_steps - 1) umma_commit(all_done);
+        BWD_TRACE(1, t, 3);
       }
       if (!ok) *abort_word = ERR_WAIT_FULL;
     }
@@ -337,62 +334,78 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
     const float* lse_g = p.lse + ((size_t)b * p.heads + h) * p.seq;
     const float* delta_g = p.delta + ((size_t)b * p.heads + h) * p.seq;
     bool ok = true;
-    // threads 0-63 carry lse, 64-127 carry delta; +inf lse zeroes the probabilities of padded queries
-    auto fetch_vec = [&](int t) -> float {
-      const int qi = (i0 + t) * 64 + (tid & 63);
-      if (tid < 64) return (qi < p.seq) ? lse_g[qi] * 1.4426950408889634f : INFINITY;
-      if (tid < 128) return (qi < p.seq) ? delta_g[qi] : 0.f;
-      return 0.f;
-    };
-    float staged = fetch_vec(0);
+    // lse (in log2 units; +inf zeroes the probabilities of padded queries) and delta * scale of the next
+    // DKDV_VEC_STEPS steps are staged in shared memory by all compute threads together, so no step waits on a
+    // global load; the two barriers around a refill are reached by every compute thread, also after a failed wait.
     for (int t = 0; t < n_steps; ++t) {
       const int st = t & 1;
       const uint32_t ph = (t >> 1) & 1;
       const int qb = (i0 + t) * 64;
-      // lse (in log2 units) and delta of this step's 64 queries were fetched one step ahead
-      if (tid < 64) lse_s[st * 64 + tid] = staged;
-      else if (tid < 128) delta_s[st * 64 + (tid - 64)] = staged;
-      named_barrier_sync(1, BWD_COMPUTE_THREADS);   // reached by every compute thread each step, also after a failed wait
-      if (t + 1 < n_steps) staged = fetch_vec(t + 1);   // in flight while this step computes
+      BWD_TRACE(warp, t, 0);
+      if (t % DKDV_VEC_STEPS == 0) {
+        if (t > 0) named_barrier_sync(1, BWD_COMPUTE_THREADS);   // everyone is done with the previous chunk
+        const int q_first = (i0 + t) * 64;
+        constexpr int PER = DKDV_VEC_STEPS * 64 / BWD_COMPUTE_THREADS;
+        float lv[PER], dv[PER];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {   // all loads in flight before the first store
+          const int qi = q_first + tid + i * BWD_COMPUTE_THREADS;
+          lv[i] = (qi < p.seq) ? lse_g[qi] : INFINITY;
+          dv[i] = (qi < p.seq) ? delta_g[qi] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+          lse_s[tid + i * BWD_COMPUTE_THREADS] = lv[i] * 1.4426950408889634f;
+          delta_s[tid + i * BWD_COMPUTE_THREADS] = dv[i] * p.scale;
+        }
+        named_barrier_sync(1, BWD_COMPUTE_THREADS);
+      }
       if (!ok) continue;
+      BWD_TRACE(warp, t, 1);
       if (!mbar_wait(&s_full[st], ph, abort_word)) { ok = false; continue; }
       tc_fence_after();
+      BWD_TRACE(warp, t, 2);
       uint32_t sreg[BWD_COLS], dreg[BWD_COLS];
       tmem_ld_32x32(tm_st + lane_addr + st * 64 + cg * BWD_COLS, sreg);
       tmem_ld_32x32(tm_dpt + lane_addr + st * 64 + cg * BWD_COLS, dreg);
       tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&s_empty[st]);
+      BWD_TRACE(warp, t, 3);
       const bool need_mask = (qb < k0 + 128);   // tile touches the diagonal
-      float pv[BWD_COLS], dsv[BWD_COLS];
-      const float* lse_v = lse_s + st * 64 + cg * BWD_COLS;       // lse * log2(e); +inf marks a padded query
-      const float* dlt_v = delta_s + st * 64 + cg * BWD_COLS;
-      if (need_mask) {
+      const float* lse_v = lse_s + (t % DKDV_VEC_STEPS) * 64 + cg * BWD_COLS;   // lse * log2(e); +inf marks a padded query
+      const float* dlt_v = delta_s + (t % DKDV_VEC_STEPS) * 64 + cg * BWD_COLS;  // delta * scale
+      // Eight columns at a time: two 16-byte broadcast reads each of lse and delta, eight independent
+      // exp2 / multiply chains, four packed results each of P^T and dS^T (bf16 packing on the integer pipe).
+      uint32_t pk[BWD_COLS / 2], dk[BWD_COLS / 2];
 #pragma unroll
-        for (int c = 0; c < BWD_COLS; ++c) {
-          const int col = cg * BWD_COLS + c;
-          float pe = fast_exp2(__uint_as_float(sreg[c]) * p.scale_log2 - lse_v[c]);   // exp2(-inf) = 0 for padded queries
-          pe = (qb + col < key_idx) ? 0.f : pe;
-          pv[c] = pe;
-          dsv[c] = pe * (__uint_as_float(dreg[c]) - dlt_v[c]) * p.scale;
+      for (int c0 = 0; c0 < BWD_COLS; c0 += 8) {
+        float lr[8], dr[8], pe[8], ds[8];
+        *reinterpret_cast<float4*>(lr) = *reinterpret_cast<const float4*>(lse_v + c0);
+        *reinterpret_cast<float4*>(lr + 4) = *reinterpret_cast<const float4*>(lse_v + c0 + 4);
+        *reinterpret_cast<float4*>(dr) = *reinterpret_cast<const float4*>(dlt_v + c0);
+        *reinterpret_cast<float4*>(dr + 4) = *reinterpret_cast<const float4*>(dlt_v + c0 + 4);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) pe[e] = fast_exp2(__uint_as_float(sreg[c0 + e]) * p.scale_log2 - lr[e]);
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) pe[e] = (qb + cg * BWD_COLS + c0 + e < key_idx) ? 0.f : pe[e];
         }
-      } else {
 #pragma unroll
-        for (int c = 0; c < BWD_COLS; ++c) {
-          const float pe = fast_exp2(__uint_as_float(sreg[c]) * p.scale_log2 - lse_v[c]);
-          pv[c] = pe;
-          dsv[c] = pe * (__uint_as_float(dreg[c]) - dlt_v[c]) * p.scale;
+        for (int e = 0; e < 8; ++e) ds[e] = pe[e] * (__uint_as_float(dreg[c0 + e]) * p.scale - dr[e]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          pk[c0 / 2 + e] = pack_bf16x2_alu(pe[2 * e], pe[2 * e + 1]);
+          dk[c0 / 2 + e] = pack_bf16x2_alu(ds[2 * e], ds[2 * e + 1]);
         }
       }
-      // buffer st was last read by the MMAs of step t-2
-      if (!mbar_wait(&p_empty[st], ph ^ 1, abort_word)) { ok = false; continue; }
-      store_row16_swizzled(smem + L::OFF_PT + st * 16384, r, cg, pv);
-      store_row16_swizzled(smem + L::OFF_DST + st * 16384, r, cg, dsv);
-      fence_proxy_async_smem();
+      BWD_TRACE(warp, t, 4);
+      tmem_st_32x16(tm_st + lane_addr + st * 64 + cg * BWD_COLS, pk);
+      tmem_st_32x16(tm_dpt + lane_addr + st * 64 + cg * BWD_COLS, dk);
+      tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_full[st]);
+      BWD_TRACE(warp, t, 5);
     }
-    if (ok) ok = mbar_wait(&p_empty[(n_steps - 1) & 1], ((n_steps - 1) >> 1) & 1, abort_word);
+    if (ok) ok = mbar_wait(all_done, 0, abort_word);
     if (ok) {
       tc_fence_after();
       const bool valid = key_idx < p.seq;
@@ -439,6 +452,7 @@ flash_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kv,   // box 64 x 128 o
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+  BWD_CTA_LOG_END(0, t_cta_start, n_steps);
 }
 
 // ----------------------------------------------------------------------------------- dQ
@@ -471,6 +485,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box 64 x 128 ov
                 const __grid_constant__ CUtensorMap tm_do,    // box 64 x 128 over dO
                 const FlashBwdParams p) {
   using L = DqSmem<DH>;
+  const uint64_t t_cta_start = globaltimer_ns();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
@@ -488,10 +503,10 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box 64 x 128 ov
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qblk = (p.seq + 127) / 128;
-  // CTAs of one (b, h) are neighbours in the grid and walk the same K / V tiles at about the same time, so those
-  // are read from HBM once and then hit in L2; inside a (b, h) the latest (heaviest) query tile goes first.
-  const int bh = blockIdx.x / n_qblk;
-  const int iblk = n_qblk - 1 - blockIdx.x % n_qblk;
+  // Longest-first order over the whole grid (latest query tile = most key steps), so the tail of the launch is
+  // made of short CTAs; the (b, h) index varies fastest.
+  const int bh = blockIdx.x % (p.batch * p.heads);
+  const int iblk = n_qblk - 1 - blockIdx.x / (p.batch * p.heads);
   const int b = bh / p.heads, h = bh % p.heads;
   const int row_base = b * p.seq;
   const int q0 = iblk * 128;
@@ -664,7 +679,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box 64 x 128 ov
               pe = (kb + hf * 32 + c + e > q_idx) ? 0.f : pe;
               ds[e] = pe * (__uint_as_float(dreg[hf][c + e]) * p.scale - dlt_scaled);
             }
-            packed[hf * 16 + c / 2] = pack_bf16x2(ds[0], ds[1]);
+            packed[hf * 16 + c / 2] = pack_bf16x2_alu(ds[0], ds[1]);
           }
       } else {
 #pragma unroll
@@ -677,7 +692,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box 64 x 128 ov
               const float pe = fast_exp2(__uint_as_float(sreg[hf][c + e]) * p.scale_log2 - lse2);
               ds[e] = pe * (__uint_as_float(dreg[hf][c + e]) * p.scale - dlt_scaled);
             }
-            packed[hf * 16 + c / 2] = pack_bf16x2(ds[0], ds[1]);
+            packed[hf * 16 + c / 2] = pack_bf16x2_alu(ds[0], ds[1]);
           }
       }
       BWD_TRACE(trole, t, 3);
@@ -726,6 +741,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box 64 x 128 ov
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+  BWD_CTA_LOG_END(1, t_cta_start, n_steps);
 }
 
 template <int DH>
@@ -745,8 +761,13 @@ static int launch_flash_bwd(const void* qkv, const void* dout, const FlashBwdPar
     configured = true;
   }
   const int n_kblk = (p.seq + 127) / 128;
-  k1<<<p.batch * p.heads * n_kblk, BWD_THREADS, DkDvSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_qkv64, tm_do64, p);
-  k2<<<p.batch * p.heads * n_kblk, BWD_THREADS, DqSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_do128, p);
+  // tracing (tuning aid): CTA c >= 0 selects the dQ kernel's CTA c, c < 0 the dK/dV kernel's CTA -c-1
+  FlashBwdParams p1 = p, p2 = p;
+  if (p.trace_cta == BWD_CTA_LOG) { }
+  else if (p.trace_cta >= 0) p1.trace = nullptr;
+  else { p2.trace = nullptr; p1.trace_cta = -p.trace_cta - 1; }
+  k1<<<p.batch * p.heads * n_kblk, BWD_THREADS, DkDvSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_qkv64, tm_do64, p1);
+  k2<<<p.batch * p.heads * n_kblk, BWD_THREADS, DqSmem<DH>::TOTAL, stream>>>(tm_qkv128, tm_do128, p2);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

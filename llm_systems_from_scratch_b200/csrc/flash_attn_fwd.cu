@@ -88,10 +88,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // Work assignment: the query tiles of one (b, h) are neighbours in the grid and walk the same K / V tiles at about
-  // the same time (one HBM read, then L2 hits); inside a (b, h) the heaviest (latest) query tile goes first.
-  const int bh = blockIdx.x / p.n_qblk;
-  const int qblk = p.n_qblk - 1 - blockIdx.x % p.n_qblk;
+  // Work assignment: longest-first over the whole grid (latest query tile = most key steps), so the tail of the
+  // launch is made of short CTAs; the (b, h) index varies fastest.
+  const int bh = blockIdx.x % (p.batch * p.heads);
+  const int qblk = p.n_qblk - 1 - blockIdx.x / (p.batch * p.heads);
   const int b = bh / p.heads, h = bh % p.heads;
   int row_base, seq_len;
   if (p.cu_seqlens != nullptr) {
@@ -315,10 +315,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int c16 = c * 4 + q;
-          uint4 v = make_uint4(pack_bf16x2(__uint_as_float(s[c][q * 8 + 0]), __uint_as_float(s[c][q * 8 + 1])),
-                               pack_bf16x2(__uint_as_float(s[c][q * 8 + 2]), __uint_as_float(s[c][q * 8 + 3])),
-                               pack_bf16x2(__uint_as_float(s[c][q * 8 + 4]), __uint_as_float(s[c][q * 8 + 5])),
-                               pack_bf16x2(__uint_as_float(s[c][q * 8 + 6]), __uint_as_float(s[c][q * 8 + 7])));
+          uint4 v = make_uint4(pack_bf16x2_alu(__uint_as_float(s[c][q * 8 + 0]), __uint_as_float(s[c][q * 8 + 1])),
+                               pack_bf16x2_alu(__uint_as_float(s[c][q * 8 + 2]), __uint_as_float(s[c][q * 8 + 3])),
+                               pack_bf16x2_alu(__uint_as_float(s[c][q * 8 + 4]), __uint_as_float(s[c][q * 8 + 5])),
+                               pack_bf16x2_alu(__uint_as_float(s[c][q * 8 + 6]), __uint_as_float(s[c][q * 8 + 7])));
           *reinterpret_cast<uint4*>(p_row + ((c16 ^ (r & 7)) << 4)) = v;
         }
       fence_proxy_async_smem();
