@@ -4,7 +4,9 @@
     python -m llm_systems_from_scratch_b200.ops.bench_ops attention       # FlashAttention fwd/bwd vs SDPA
     python -m llm_systems_from_scratch_b200.ops.bench_ops elementwise     # bandwidth-bound kernels vs the copy roofline
     python -m llm_systems_from_scratch_b200.ops.bench_ops gemm-small      # one small GEMM, three launches (for ncu)
+    python -m llm_systems_from_scratch_b200.ops.bench_ops gemm-pair-small # three launches of the CTA-pair GEMM (for ncu)
     python -m llm_systems_from_scratch_b200.ops.bench_ops attention-small # one small attention fwd+bwd (for ncu)
+    python -m llm_systems_from_scratch_b200.ops.bench_ops attention-trace # in-kernel timeline of one CTA per kernel
 
 Each line of output is one JSON record.  The "-small" modes exist so that a profiler capture ends by
 itself in seconds: inputs are larger than L2 but only a few hundred MB.
@@ -124,6 +126,16 @@ def gemm_small():
     print(json.dumps({"op": "gemm-small", "ok": True}))
 
 
+def gemm_pair_small():
+    a, b = _operands("nt", 8192, 6144, 2048)
+    out = torch.empty(8192, 6144, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        native.gemm(a, b, "nt", out=out, pair=True)
+    torch.cuda.synchronize()
+    native.check_status()
+    print(json.dumps({"op": "gemm-pair-small", "ok": True}))
+
+
 def attention_small():
     b, s, h, dh = 4, 2048, 16, 128
     qkv = torch.randn(b * s, 3 * h * dh, device="cuda").bfloat16()
@@ -137,10 +149,45 @@ def attention_small():
     print(json.dumps({"op": "attention-small", "ok": True}))
 
 
+def attention_trace():
+    """Per-step timeline (SM clock stamps) of one CTA of each attention kernel: where each role waits."""
+    import ctypes
+    lib = native.load()
+    b, s, h, dh = 8, 2048, 16, 128
+    qkv = torch.randn(b * s, 3 * h * dh, device="cuda").bfloat16()
+    o, lse = attention.attention_fwd(qkv, b, s, h)
+    do = torch.randn_like(o)
+    attention.attention_bwd(do, qkv, o, lse, b, s, h)
+    torch.cuda.synchronize()
+
+    def capture(setter, cta, fn):
+        buf = torch.zeros(10 * 64 * 8, dtype=torch.int64, device="cuda")
+        setter(ctypes.c_void_p(buf.data_ptr()), cta)
+        fn()
+        torch.cuda.synchronize()
+        setter(ctypes.c_void_p(0), 0)
+        t = buf.cpu().view(10, 64, 8)
+        base = int(t[t > 0].min())
+        return [[[int(v) - base if v > 0 else None for v in t[role, step]] for step in range(20)] for role in range(10)]
+
+    fwd = lambda: attention.attention_fwd(qkv, b, s, h)
+    bwd = lambda: attention.attention_bwd(do, qkv, o, lse, b, s, h)
+    # CTA 200 is a mid-grid CTA with many steps in all three kernels; a negative index selects the dK/dV kernel
+    for name, setter, cta, fn, roles in (("flash_fwd", lib.b200_flash_fwd_set_trace, 200, fwd, (1, 2, 6)),
+                                         ("flash_dq", lib.b200_flash_bwd_set_trace, 200, bwd, (0, 1, 2, 6)),
+                                         ("flash_dkdv", lib.b200_flash_bwd_set_trace, -201, bwd, (1, 2, 6))):
+        rec = capture(setter, cta, fn)
+        for role in roles:
+            for step in (6, 7, 8):
+                print(json.dumps({"op": "attention-trace", "kernel": name, "role": role, "step": step,
+                                  "clk": rec[role][step]}), flush=True)
+    native.check_status()
+
+
 def main(argv=None):
     argv = argv if argv is not None else sys.argv[1:]
     mode = argv[0] if argv else "gemm"
-    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "gemm-small": gemm_small,
+    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "gemm-small": gemm_small, "gemm-pair-small": gemm_pair_small, "attention-trace": attention_trace,
      "attention-small": attention_small}[mode]()
 
 

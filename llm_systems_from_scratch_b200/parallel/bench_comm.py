@@ -8,7 +8,9 @@ maximum over ranks, (1) the pull all-gather of bf16 weight shards, (2) the reduc
 and sum of squares, (3) the reduce-scatter fused with the AdamW update, (4) the in-place two-shot
 all-reduce of an fp32 bucket, and the NCCL collective each one replaces.  The roofline of a kernel is the
 slower of its NVLink ingress bytes over the measured 770 GB/s per direction and its HBM bytes over the
-measured copy bandwidth; rank 0 prints one JSON line per kernel with achieved / roofline.
+measured copy bandwidth; rank 0 prints one JSON line per kernel with achieved / roofline.  It also times
+the CTA-pair GEMM that carries the all-gather on its copy warps against the slower of the GEMM at the
+measured cuBLAS peak and the gather's NVLink time.
 """
 from __future__ import annotations
 
@@ -32,7 +34,19 @@ def _hbm_gbs() -> float:
         return 6650.0
 
 
-def _time(fn, iters=10, warm=3):
+def _bf16_tflops() -> float:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                        "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"])
+    except Exception:
+        return 1590.0
+
+
+def _time(fn, iters=10, warm=3, reps=4):
+    """Median over ``iters`` of the time of ``reps`` back-to-back calls divided by ``reps`` (the ranks' launch
+    skew after a host synchronisation is paid once per group, as in a training step), max over ranks."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
@@ -42,10 +56,11 @@ def _time(fn, iters=10, warm=3):
     for _ in range(iters):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        fn()
+        for _ in range(reps):
+            fn()
         b.record()
         torch.cuda.synchronize()
-        best.append(a.elapsed_time(b))
+        best.append(a.elapsed_time(b) / reps)
     best.sort()
     t = torch.tensor([best[len(best) // 2]], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -84,6 +99,36 @@ def main():
     t = _time(lambda: comm.all_gather(full, shard))
     t_n = _time(lambda: dist.all_gather_into_tensor(full, shard))
     report("peer_allgather (bf16 shards)", t, (ws - 1) * n * 2, padded * 2 + n * 2, t_n)
+
+    # ---- the same gather carried by the consumer GEMM (QKV projection shape of the 1.3B block): two copy
+    # warps per CTA pull the shards while the MMA warps run.  Roofline: the slower of the GEMM at the measured
+    # cuBLAS burst peak and the gather's NVLink bytes; the plain GEMM and gather-then-GEMM are the baselines.
+    from .comm import GatherTask
+    m_, n_, k_ = 16384, 6144, 2048
+    xa = torch.randn(m_, k_, device="cuda").bfloat16()
+    wb = torch.randn(n_, k_, device="cuda").bfloat16()
+    yc = torch.empty(m_, n_, device="cuda", dtype=torch.bfloat16)
+    peak = _bf16_tflops()
+    comm.barrier()
+    t_plain = _time(lambda: native.gemm(xa, wb, "nt", out=yc, pair=True))
+
+    def fused():
+        comm.pre_gather_sync()
+        native.gemm(xa, wb, "nt", out=yc, pair=True, gather=GatherTask(comm, full, shard))
+
+    def unfused():
+        comm.pre_gather_sync()
+        dist.all_gather_into_tensor(full, shard)
+        native.gemm(xa, wb, "nt", out=yc, pair=True)
+    t_sync = _time(lambda: comm.pre_gather_sync())
+    t_f = _time(fused) - t_sync
+    t_u = _time(unfused) - t_sync
+    flops = 2.0 * m_ * n_ * k_
+    roof = max(flops / (peak * 1e12), (ws - 1) * n * 2 / (NVLINK_GBS * 1e9)) * 1e3
+    if rank == 0:
+        out.append({"kernel": "gemm_bf16_pair carrying the all-gather (16384x6144x2048 + 50.6M bf16 gather)", "world": ws,
+                    "ms": round(t_f, 4), "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / t_f, 3),
+                    "gemm_alone_ms": round(t_plain, 4), "nccl_gather_then_gemm_ms": round(t_u, 4)})
 
     # ---- reduce-scatter + scale + sumsq, and reduce-scatter + AdamW
     stage = comm.alloc(padded, torch.bfloat16)

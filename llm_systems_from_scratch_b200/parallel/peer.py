@@ -162,12 +162,17 @@ class PeerComm(Communicator):
     def pre_gather_sync(self):
         self.barrier()
 
+    def _ctas(self) -> int:
+        """CTAs of a bandwidth kernel: with few peers each thread has few remote loads in flight, so more threads
+        are needed to cover the NVLink latency."""
+        return {2: 296, 4: 192}.get(self.world_size, 128)
+
     def all_gather(self, full, shard):
         table = self._peer_table(shard)
         nbytes = shard.numel() * shard.element_size()
         if table is None or nbytes % 16 or full.data_ptr() % 16:
             return self.fallback.all_gather(full, shard)
-        native._check(self.lib.b200_peer_allgather(table, full.data_ptr(), nbytes, self.world_size, self.rank, 128,
+        native._check(self.lib.b200_peer_allgather(table, full.data_ptr(), nbytes, self.world_size, self.rank, self._ctas(),
                                                    self._stream()), "peer_allgather")
 
     def gather_args(self, full, shard):
@@ -191,7 +196,7 @@ class PeerComm(Communicator):
             self.world_size, self.rank, e, mode, ptr(a.get("master")), ptr(a.get("m")), ptr(a.get("v")),
             ptr(a.get("mirror")), ptr(a.get("gscale")), a.get("lr", 0.0), a.get("b1", 0.0), a.get("b2", 0.0),
             a.get("eps", 0.0), a.get("wd", 0.0), a.get("alpha_t", 0.0), self.limit_ns, self._counter_slot().data_ptr(),
-            self._status(), 128, self._stream()), "peer_reduce_scatter")
+            self._status(), self._ctas(), self._stream()), "peer_reduce_scatter")
 
     def reduce_scatter_mean(self, out_shard, full, key: str | None = None, sumsq=None):
         ok = (self._find(full) is not None and full.dtype == torch.bfloat16 and out_shard.dtype == torch.float32
