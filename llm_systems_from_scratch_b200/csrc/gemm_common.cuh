@@ -13,6 +13,9 @@ enum GemmEpilogue : int {
   EPI_F32 = 1,        // C = acc (fp32)
   EPI_BF16_RES = 2,   // C = bf16(acc + R)   (R bf16, may alias C)
   EPI_F32_ACC = 3,    // C += acc (fp32 read-modify-write)
+  // Backward of h = silu(gate) * up fused into the GEMM that produces dh = acc (M x N): R holds gate | up
+  // (M x 2N, bf16) and C (M x 2N, bf16) receives d(gate) | d(up).
+  EPI_SWIGLU_BWD = 4,
 };
 
 // Optional all-gather carried by a GEMM launch: while the MMA warps work, two copy warps per CTA pull
@@ -93,6 +96,33 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int
   const int ncols = min(32, p.N - col0);
   if (ncols <= 0) return;
   if (p.rope_cs != nullptr && col0 < 2 * p.rope_d && ncols == 32) epilogue_rope(p, row, col0, acc);
+  if (p.epi == EPI_SWIGLU_BWD) {
+    // same arithmetic as the stand-alone kernel: dh is rounded to bf16 first, gate and up are read as bf16
+    const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)row * p.ldr + col0;
+    const __nv_bfloat16* up = gp + p.N;
+    __nv_bfloat16* dgp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+    __nv_bfloat16* dup = dgp + p.N;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j * 8 >= ncols) break;          // N, ldr and ldc are multiples of 8 (checked on the host)
+      const uint4 gv = *reinterpret_cast<const uint4*>(gp + j * 8);
+      const uint4 uv = *reinterpret_cast<const uint4*>(up + j * 8);
+      const uint32_t gg[4] = {gv.x, gv.y, gv.z, gv.w}, uu[4] = {uv.x, uv.y, uv.z, uv.w};
+      uint32_t og[4], ou[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 g = unpack_bf16x2(gg[t]), u = unpack_bf16x2(uu[t]);
+        const float2 d = unpack_bf16x2(pack_bf16x2(__uint_as_float(acc[j * 8 + 2 * t]), __uint_as_float(acc[j * 8 + 2 * t + 1])));
+        const float s0 = 1.f / (1.f + __expf(-g.x)), s1 = 1.f / (1.f + __expf(-g.y));
+        const float l0 = g.x * s0, l1 = g.y * s1;
+        og[t] = pack_bf16x2(d.x * u.x * (s0 + l0 * (1.f - s0)), d.y * u.y * (s1 + l1 * (1.f - s1)));
+        ou[t] = pack_bf16x2(d.x * l0, d.y * l1);
+      }
+      *reinterpret_cast<uint4*>(dgp + j * 8) = make_uint4(og[0], og[1], og[2], og[3]);
+      *reinterpret_cast<uint4*>(dup + j * 8) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+    }
+    return;
+  }
   if (p.epi == EPI_BF16 || p.epi == EPI_BF16_RES) {
     __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
     const bool vec_ok = (ncols == 32) && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);

@@ -288,6 +288,9 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -10;
   if (epi == EPI_BF16_RES && R == nullptr) return -11;
+  if (epi == EPI_SWIGLU_BWD &&
+      (R == nullptr || (N & 7) || (ldr & 7) || (ldc & 7) || ((reinterpret_cast<uintptr_t>(R) | reinterpret_cast<uintptr_t>(C)) & 15)))
+    return -11;
   int bn = bn_hint;
   const bool small_ok = !a_mn && !b_mn;   // narrow tiles exist for the K-major (decode) layout only
   if (small_ok && (bn == 32 || bn == 64)) {

@@ -395,6 +395,9 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -10;
   if (epi == EPI_BF16_RES && R == nullptr) return -11;
+  if (epi == EPI_SWIGLU_BWD &&
+      (R == nullptr || (N & 7) || (ldr & 7) || (ldc & 7) || ((reinterpret_cast<uintptr_t>(R) | reinterpret_cast<uintptr_t>(C)) & 15)))
+    return -11;
   CUtensorMap tmA, tmB;
   int rc = a_mn ? make_tmap_bf16_2d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 64)
                 : make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BM);

@@ -91,10 +91,8 @@ def block_backward(dy, w: BlockWeights, s: BlockSaved, gw: BlockWeights, cfg: En
     """Returns dx; writes every weight gradient of the block into the views in ``gw``.  ``gather`` (the
     previous unit's weights, needed next) rides on the first GEMM."""
     # ---- feed-forward half
-    dhh = ops.gemm(dy, w.wdown, "nn", gather=gather)
+    dgu = ops.gemm_swiglu_bwd(dy, w.wdown, s.gu, gather=gather)          # SiLU*mul backward in the GEMM epilogue
     ops.gemm(dy, s.hh, "tn", out=gw.wdown)
-    dgu = ops.silu_mul_bwd(dhh, s.gu)
-    del dhh
     dh2 = ops.gemm(dgu, w.wgu, "nn")
     ops.gemm(dgu, s.h2, "tn", out=gw.wgu)
     del dgu

@@ -90,6 +90,15 @@ def gemm_swiglu(x, wgu, gather=None):
     return gu, silu_mul_fwd(gu)
 
 
+def gemm_swiglu_bwd(dy, wdown, gu, gather=None):
+    """d(gate | up) for h = silu(gate) * up and dh = dy @ wdown; one kernel on the GPU when possible."""
+    if dy.is_cuda:
+        out = native.gemm_swiglu_bwd(dy, wdown, gu, gather)
+        if out is not None:
+            return out
+    return silu_mul_bwd(gemm(dy, wdown, "nn", gather=gather), gu)
+
+
 def clip_coef(sumsq_t, max_norm, coef_out=None, norm_out=None):
     if sumsq_t.is_cuda:
         return native.clip_coef(sumsq_t, max_norm, coef_out, norm_out)

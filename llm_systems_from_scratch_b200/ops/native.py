@@ -168,7 +168,7 @@ def _rowmajor(t: torch.Tensor, name: str):
 
 
 # ----------------------------------------------------------------------------- GEMM
-EPI_BF16, EPI_F32, EPI_BF16_RES, EPI_F32_ACC = 0, 1, 2, 3
+EPI_BF16, EPI_F32, EPI_BF16_RES, EPI_F32_ACC, EPI_SWIGLU_BWD = 0, 1, 2, 3, 4
 
 
 # Problems at least this large (rows of the output) run on CTA pairs (cta_group::2, 256 x 256 tiles).
@@ -293,6 +293,38 @@ def gemm_swiglu(x, wgu, gather=None):
     if gargs is not None:
         gather.mark_done()
     return gu, h
+
+
+def gemm_swiglu_bwd(dy, wdown, gu, gather=None):
+    """d(gate | up) of h = silu(gate) * up for dh = dy @ wdown, with the element-wise backward done in the
+    GEMM epilogue (dh is never written).  dy (M, d), wdown (d, F), gu (M, 2F) -> (M, 2F), all bf16.
+    Returns None when the fused kernel does not apply.  A pending all-gather can ride on the launch."""
+    lib = load()
+    m, k = dy.shape
+    kb, f = wdown.shape
+    ok = (USE_PAIR and m >= PAIR_MIN_M and f >= 256 and f % 8 == 0 and k == kb and tuple(gu.shape) == (m, 2 * f)
+          and dy.dtype == torch.bfloat16 and wdown.dtype == torch.bfloat16 and gu.dtype == torch.bfloat16
+          and dy.stride(1) == 1 and wdown.stride(1) == 1 and gu.stride(1) == 1 and dy.stride(0) % 8 == 0
+          and wdown.stride(0) % 8 == 0 and gu.stride(0) % 8 == 0 and gu.data_ptr() % 16 == 0
+          and dy.data_ptr() % 16 == 0 and wdown.data_ptr() % 16 == 0)
+    if not ok:
+        return None
+    dgu = torch.empty((m, 2 * f), dtype=torch.bfloat16, device=dy.device)
+    gargs = gather.native_args() if (gather is not None and not gather.done) else None
+    if gather is not None and not gather.done and gargs is None:
+        gather.run()
+    if gargs is not None:
+        table, dst, nbytes, world, rank = gargs
+        rc = lib.b200_gemm_bf16_pair_gather(_ptr(dy), _ptr(wdown), _ptr(dgu), _ptr(gu), m, f, k, dy.stride(0),
+                                            wdown.stride(0), 2 * f, gu.stride(0), 0, 1, EPI_SWIGLU_BWD, table, dst, nbytes,
+                                            world, rank, None, None, None, 0, _ptr(status_word(dy.device)), _stream())
+        _check(rc, "b200_gemm_bf16_pair_gather")
+        gather.mark_done()
+    else:
+        rc = lib.b200_gemm_bf16_pair(_ptr(dy), _ptr(wdown), _ptr(dgu), _ptr(gu), m, f, k, dy.stride(0), wdown.stride(0),
+                                     2 * f, gu.stride(0), 0, 1, EPI_SWIGLU_BWD, _ptr(status_word(dy.device)), _stream())
+        _check(rc, "b200_gemm_bf16_pair")
+    return dgu
 
 
 # -------------------------------------------------------------------------- RMSNorm

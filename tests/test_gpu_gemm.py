@@ -133,3 +133,23 @@ def test_gemm_swiglu_epilogue(m, f, k):
     assert (gu.float() - (x.float() @ w.float().t())).abs().max().item() < 3e-2 * k ** 0.5 / 8
     assert torch.allclose(h.float(), native.silu_mul_fwd(gu).float(), atol=1e-3, rtol=1e-2)
     assert torch.allclose(h.float(), ref_h.float(), atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("m,f,k", [(1024, 1408, 512), (2048, 5504, 2048), (1100, 264, 136)])
+def test_gemm_swiglu_backward_epilogue(m, f, k):
+    """dh = dy @ W2 with the SiLU*mul backward in the epilogue against the fp32 statement of the same op and
+    against GEMM followed by the stand-alone kernel."""
+    from llm_systems_from_scratch_b200.ops import native
+    dy = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(k, f, device="cuda") / k ** 0.5).bfloat16()
+    gu = torch.randn(m, 2 * f, device="cuda").bfloat16()
+    out = native.gemm_swiglu_bwd(dy, w, gu)
+    assert out is not None
+    native.check_status()
+    two_step = native.silu_mul_bwd(native.gemm(dy, w, "nn"), gu)
+    assert torch.allclose(out.float(), two_step.float(), atol=2e-2, rtol=2e-2)
+    dh = dy.float() @ w.float()
+    g, u = gu[:, :f].float(), gu[:, f:].float()
+    s = torch.sigmoid(g)
+    ref = torch.cat([dh * u * (s + g * s * (1 - s)), dh * g * s], dim=1)
+    assert (out.float() - ref).abs().max().item() < 4e-2 * max(1.0, ref.abs().max().item()) / 4
