@@ -358,7 +358,18 @@ class TransformerLM(nn.Module):
         new: list[Tensor] = []
         for _ in range(max_new_tokens):
             window = ids[:, -self.context_length:]
-            last = self.forward(window)[:, -1].float()
+            logits = self.forward(window)[:, -1]
+            if logits.is_cuda and logits.dtype == torch.bfloat16 and temperature != 0:
+                # filter, softmax and draw in one kernel (no sort, no probabilities in memory)
+                from ..ops import native
+                u = torch.rand(logits.shape[0], device=logits.device)
+                nxt = native.sample_topk(logits.contiguous(), u, temperature, top_k).unsqueeze(-1)
+                if eos_token_id is not None and int(nxt) == eos_token_id:
+                    break
+                ids = torch.cat((ids, nxt), dim=-1)
+                new.append(nxt)
+                continue
+            last = logits.float()
             if temperature == 0:
                 nxt = last.argmax(dim=-1, keepdim=True)
             else:

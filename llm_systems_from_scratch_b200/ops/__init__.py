@@ -35,6 +35,7 @@ embedding_bwd = _dispatch("embedding_bwd")
 xent_fwd_bwd = _dispatch("xent_fwd_bwd")
 xent_fwd = _dispatch("xent_fwd")
 argmax_rows = _dispatch("argmax_rows")
+sample_topk = _dispatch("sample_topk")
 adamw_step = _dispatch("adamw_step")
 sumsq = _dispatch("sumsq")
 scale_ = _dispatch("scale_")

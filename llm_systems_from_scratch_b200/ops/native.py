@@ -78,6 +78,7 @@ def _declare(lib):
         "b200_embedding_bwd": [P, P, P, L, I, I, P],
         "b200_xent": [P, P, P, P, L, L, I, I, F, I, I, P, P],
         "b200_argmax": [P, L, L, I, P, P],
+        "b200_sample_topk": [P, L, L, I, P, F, I, P, P],
         "b200_adamw": [P, P, I, P, P, P, L, P, F, F, F, F, F, F, P],
         "b200_sumsq": [P, I, L, P, P],
         "b200_clip_coef": [P, F, P, P, P],
@@ -467,6 +468,20 @@ def argmax_rows(logits, valid_cols=None):
 
 
 # ---------------------------------------------------------------------------- AdamW
+def sample_topk(logits, uniforms, temperature: float, top_k: int | None = None, valid_cols=None):
+    """One token id per row: softmax(logits / temperature) restricted to the top-k logits (ties kept), drawn by
+    inverse CDF with the caller's uniforms in [0, 1).  logits (rows, cols) bf16, uniforms (rows,) fp32 -> int64."""
+    lib = load()
+    _req(logits.dtype == torch.bfloat16 and logits.dim() == 2 and logits.stride(1) == 1, "logits must be bf16 2-D")
+    rows, cols = logits.shape
+    _req(uniforms.dtype == torch.float32 and uniforms.numel() == rows and uniforms.is_contiguous(), "bad uniforms")
+    _req(temperature > 0, "temperature must be positive (use argmax_rows for greedy decoding)")
+    out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    _check(lib.b200_sample_topk(_ptr(logits), rows, logits.stride(0), valid_cols or cols, _ptr(uniforms),
+                                float(temperature), int(top_k or 0), _ptr(out), _stream()), "sample_topk")
+    return out
+
+
 def adamw_step(master, grad, m, v, mirror, lr, beta1, beta2, eps, weight_decay, step: int, grad_scale=None):
     lib = load()
     n = master.numel()

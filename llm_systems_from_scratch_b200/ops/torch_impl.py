@@ -293,3 +293,15 @@ def varlen_attention_fwd(qkv, cu_seqlens, n_heads: int):
 def argmax_rows(logits, valid_cols=None):
     v = valid_cols or logits.shape[-1]
     return logits[:, :v].float().argmax(dim=-1)
+
+
+def sample_topk(logits, uniforms, temperature: float, top_k=None, valid_cols=None):
+    """Inverse-CDF draw from softmax(logits / temperature) restricted to the top-k logits (ties kept)."""
+    x = logits[:, :valid_cols].float() if valid_cols else logits.float()
+    if top_k and top_k < x.shape[1]:
+        kth = torch.topk(x, top_k, dim=1).values[:, -1:]
+        x = x.masked_fill(x < kth, float("-inf"))
+    p = torch.softmax(x / temperature, dim=1)
+    cdf = p.cumsum(dim=1)
+    idx = (cdf <= uniforms.float()[:, None] * cdf[:, -1:]).sum(dim=1)
+    return idx.clamp(max=x.shape[1] - 1)

@@ -145,3 +145,35 @@ def test_sumsq_clip_scale_cast():
     f = torch.empty_like(x)
     native.cast_copy(f, b)
     assert torch.equal(f, b.float())
+
+
+def test_sample_topk_kernel():
+    """Top-k / temperature sampling: support, greedy limit and distribution against the fp32 statement."""
+    from llm_systems_from_scratch_b200.ops import native, torch_impl
+    torch.manual_seed(0)
+    rows, vocab, ld = 64, 50257, 50264
+    buf = torch.randn(rows, ld, device="cuda").mul_(3).bfloat16()
+    logits = buf[:, :vocab]
+    u = torch.rand(rows, device="cuda")
+    # top_k = 1 is the argmax whatever the uniform
+    top1 = native.sample_topk(logits, u, 0.7, 1)
+    assert torch.equal(logits.gather(1, top1[:, None]), logits.gather(1, native.argmax_rows(logits)[:, None]))
+    # every draw lies in the top-k set (ties of the k-th value included)
+    k = 50
+    got = native.sample_topk(logits, u, 1.0, k)
+    kth = torch.topk(logits.float(), k, dim=1).values[:, -1]
+    assert (logits.float().gather(1, got[:, None])[:, 0] >= kth).all()
+    # same inverse-CDF rule as the fp32 statement: identical tokens except where u falls within rounding of a boundary
+    ref = torch_impl.sample_topk(logits, u, 1.0, k)
+    assert (got == ref).float().mean().item() > 0.9
+    # distribution on a small vocabulary: empirical frequencies against softmax probabilities
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0, 3.0, 0.5, -2.0, 1.5]], device="cuda").bfloat16()
+    n = 20000
+    draws = native.sample_topk(small.expand(n, 8).contiguous(), torch.rand(n, device="cuda"), 0.8, 5)
+    freq = torch.bincount(draws, minlength=8).float() / n
+    x = small[0].float() / 0.8
+    keep = x >= torch.topk(x, 5).values[-1]
+    p = torch.softmax(x.masked_fill(~keep, float("-inf")), dim=0)
+    assert (freq - p).abs().max().item() < 0.015
+    assert freq[~keep].sum().item() == 0
+    native.check_status()
