@@ -177,6 +177,16 @@ PAIR_MIN_M = int(os.environ.get("B200_GEMM_PAIR_MIN_M", "1024"))
 USE_PAIR = os.environ.get("B200_GEMM_PAIR", "1") == "1"
 
 
+def _pair_pays(m: int, n: int, sms: int = 148) -> bool:
+    """Wave model of the two tensor-core kernels.  A 256x256 tile on a CTA pair is the unit of time; a 128x128
+    tile on one SM is a quarter of the work on half the hardware at about 0.8 of the efficiency.  Small weight
+    gradients (a few dozen pair tiles) fill the GPU better with the single-CTA kernel."""
+    waves = lambda tiles, slots: -(-tiles // slots)
+    cost_pair = waves(-(-m // 256) * -(-n // 256), sms // 2)
+    cost_single = waves(-(-m // 128) * -(-n // 128), sms) * 0.625
+    return cost_pair <= cost_single
+
+
 def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, bn_hint=0, max_ctas=0,
          pair=None, gather=None):
     """bf16 tensor-core GEMM (tcgen05).  layout 'nt' | 'nn' | 'tn' as in ``torch_impl.gemm``.
@@ -224,7 +234,7 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
         _req(residual.dtype == torch.bfloat16 and tuple(residual.shape) == (m, n), "residual must be bf16 (M,N)")
         ldr = residual.stride(0)
     if pair is None:
-        pair = USE_PAIR and bn_hint == 0 and max_ctas == 0 and m >= PAIR_MIN_M and n >= 256
+        pair = USE_PAIR and bn_hint == 0 and max_ctas == 0 and m >= PAIR_MIN_M and n >= 256 and _pair_pays(m, n)
     gargs = gather.native_args() if (gather is not None and not gather.done) else None
     if gather is not None and not gather.done and (gargs is None or not pair):
         gather.run()           # this launch cannot carry it: stand-alone collective
