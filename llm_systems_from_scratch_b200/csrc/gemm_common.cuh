@@ -97,7 +97,7 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int
   if (ncols <= 0) return;
   if (p.rope_cs != nullptr && col0 < 2 * p.rope_d && ncols == 32) epilogue_rope(p, row, col0, acc);
   if (p.epi == EPI_SWIGLU_BWD) {
-    // same arithmetic as the stand-alone kernel: dh is rounded to bf16 first, gate and up are read as bf16
+    // as the stand-alone kernel (fast division apart): dh is rounded to bf16 first, gate and up are read as bf16
     const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)row * p.ldr + col0;
     const __nv_bfloat16* up = gp + p.N;
     __nv_bfloat16* dgp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
@@ -113,7 +113,7 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int
       for (int t = 0; t < 4; ++t) {
         const float2 g = unpack_bf16x2(gg[t]), u = unpack_bf16x2(uu[t]);
         const float2 d = unpack_bf16x2(pack_bf16x2(__uint_as_float(acc[j * 8 + 2 * t]), __uint_as_float(acc[j * 8 + 2 * t + 1])));
-        const float s0 = 1.f / (1.f + __expf(-g.x)), s1 = 1.f / (1.f + __expf(-g.y));
+        const float s0 = __fdividef(1.f, 1.f + __expf(-g.x)), s1 = __fdividef(1.f, 1.f + __expf(-g.y));
         const float l0 = g.x * s0, l1 = g.y * s1;
         og[t] = pack_bf16x2(d.x * u.x * (s0 + l0 * (1.f - s0)), d.y * u.y * (s1 + l1 * (1.f - s1)));
         ou[t] = pack_bf16x2(d.x * l0, d.y * l1);

@@ -322,9 +322,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
               for (int t = 0; t < 4; ++t) {
                 og[t] = pack_bf16x2(__uint_as_float(g[j * 8 + 2 * t]), __uint_as_float(g[j * 8 + 2 * t + 1]));
                 ou[t] = pack_bf16x2(__uint_as_float(u[j * 8 + 2 * t]), __uint_as_float(u[j * 8 + 2 * t + 1]));
-                // same arithmetic as the stand-alone kernel: silu on the bf16-rounded gate, times the rounded up
+                // as the stand-alone kernel: silu on the bf16-rounded gate, times the rounded up (fast division)
                 const float2 gf = unpack_bf16x2(og[t]), uf = unpack_bf16x2(ou[t]);
-                oh[t] = pack_bf16x2(gf.x / (1.f + __expf(-gf.x)) * uf.x, gf.y / (1.f + __expf(-gf.y)) * uf.y);
+                oh[t] = pack_bf16x2(__fdividef(gf.x, 1.f + __expf(-gf.x)) * uf.x, __fdividef(gf.y, 1.f + __expf(-gf.y)) * uf.y);
               }
               *reinterpret_cast<uint4*>(cg + j * 8) = make_uint4(og[0], og[1], og[2], og[3]);
               *reinterpret_cast<uint4*>(cu + j * 8) = make_uint4(ou[0], ou[1], ou[2], ou[3]);

@@ -174,6 +174,7 @@ EPI_BF16, EPI_F32, EPI_BF16_RES, EPI_F32_ACC, EPI_SWIGLU_BWD = 0, 1, 2, 3, 4
 
 # Problems at least this large (rows of the output) run on CTA pairs (cta_group::2, 256 x 256 tiles).
 PAIR_MIN_M = int(os.environ.get("B200_GEMM_PAIR_MIN_M", "1024"))
+FUSE_SWIGLU_BWD = os.environ.get("B200_FUSE_SWIGLU_BWD", "1") == "1"
 USE_PAIR = os.environ.get("B200_GEMM_PAIR", "1") == "1"
 
 
@@ -313,7 +314,7 @@ def gemm_swiglu_bwd(dy, wdown, gu, gather=None):
     lib = load()
     m, k = dy.shape
     kb, f = wdown.shape
-    ok = (USE_PAIR and m >= PAIR_MIN_M and f >= 256 and f % 8 == 0 and k == kb and tuple(gu.shape) == (m, 2 * f)
+    ok = (USE_PAIR and FUSE_SWIGLU_BWD and m >= PAIR_MIN_M and f >= 256 and f % 8 == 0 and k == kb and tuple(gu.shape) == (m, 2 * f)
           and dy.dtype == torch.bfloat16 and wdown.dtype == torch.bfloat16 and gu.dtype == torch.bfloat16
           and dy.stride(1) == 1 and wdown.stride(1) == 1 and gu.stride(1) == 1 and dy.stride(0) % 8 == 0
           and wdown.stride(0) % 8 == 0 and gu.stride(0) % 8 == 0 and gu.data_ptr() % 16 == 0

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -165,6 +166,9 @@ class PeerComm(Communicator):
     def _ctas(self) -> int:
         """CTAs of a bandwidth kernel: with few peers each thread has few remote loads in flight, so more threads
         are needed to cover the NVLink latency."""
+        env = os.environ.get("B200_COMM_CTAS")
+        if env:
+            return int(env)
         return {2: 296, 4: 192}.get(self.world_size, 128)
 
     def all_gather(self, full, shard):

@@ -195,3 +195,39 @@ def test_heartbeat_detects_silent_rank_and_step_watchdog():
     time.sleep(0.4)
     assert w.expired
     w.stop()
+
+
+def test_fused_op_front_ends_on_cpu():
+    """The fused front ends fall back to their fp32 statements on CPU tensors."""
+    import torch
+    from llm_systems_from_scratch_b200 import ops
+    torch.manual_seed(0)
+    m, d, f = 12, 16, 24
+    dy, w2, gu = torch.randn(m, d), torch.randn(d, f), torch.randn(m, 2 * f)
+    got = ops.gemm_swiglu_bwd(dy, w2, gu)
+    dh = dy @ w2
+    g, u = gu[:, :f], gu[:, f:]
+    s = torch.sigmoid(g)
+    want = torch.cat([dh * u * (s + g * s * (1 - s)), dh * g * s], dim=1)
+    assert torch.allclose(got, want, atol=1e-5)
+    x, wgu = torch.randn(m, d), torch.randn(2 * f, d)
+    gu2, h = ops.gemm_swiglu(x, wgu)
+    assert torch.allclose(gu2, x @ wgu.t(), atol=1e-5)
+    assert torch.allclose(h, torch.nn.functional.silu(gu2[:, :f]) * gu2[:, f:], atol=1e-5)
+
+
+def test_sample_topk_statement():
+    """Inverse-CDF top-k sampling: support is the top-k set and frequencies follow the softmax."""
+    import torch
+    from llm_systems_from_scratch_b200 import ops
+    torch.manual_seed(1)
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 3.0, 0.5, -2.0, 1.5]])
+    n = 20000
+    draws = ops.sample_topk(logits.expand(n, 8), torch.rand(n), 0.8, 5)
+    freq = torch.bincount(draws, minlength=8).float() / n
+    x = logits[0] / 0.8
+    keep = x >= torch.topk(x, 5).values[-1]
+    p = torch.softmax(x.masked_fill(~keep, float("-inf")), dim=0)
+    assert freq[~keep].sum().item() == 0
+    assert (freq - p).abs().max().item() < 0.015
+    assert torch.equal(ops.sample_topk(logits, torch.tensor([0.3]), 1.0, 1), torch.tensor([4]))
