@@ -22,6 +22,7 @@ from typing import NamedTuple
 import torch
 
 from .. import ops
+from ..utils.metrics import nvtx_range
 
 
 class BlockWeights(NamedTuple):
@@ -216,8 +217,9 @@ class _BlockFn(torch.autograd.Function):
         w = eng.provider.block_weights(i)
         keep = torch.is_grad_enabled() or ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
         cfg = eng.cfg
-        y, saved = block_forward(x, w, cfg, eng.rope_cache, batch, seq, keep and not cfg.recompute,
-                                 gather=eng.provider.take_gather("fwd", i))
+        with nvtx_range(f"block{i}.fwd"):
+            y, saved = block_forward(x, w, cfg, eng.rope_cache, batch, seq, keep and not cfg.recompute,
+                                     gather=eng.provider.take_gather("fwd", i))
         ctx.eng, ctx.i, ctx.batch, ctx.seq = eng, i, batch, seq
         ctx.saved = saved
         ctx.x_in = x if cfg.recompute else None
@@ -232,9 +234,11 @@ class _BlockFn(torch.autograd.Function):
         w = prov.block_weights(i, backward=True)
         saved = ctx.saved
         if saved is None:
-            _, saved = block_forward(ctx.x_in, w, eng.cfg, eng.rope_cache, ctx.batch, ctx.seq, True)
-        dx = block_backward(dy.contiguous(), w, saved, prov.block_grads(i), eng.cfg, eng.rope_cache, ctx.batch, ctx.seq,
-                            gather=prov.take_gather("bwd", i))
+            with nvtx_range(f"block{i}.recompute"):
+                _, saved = block_forward(ctx.x_in, w, eng.cfg, eng.rope_cache, ctx.batch, ctx.seq, True)
+        with nvtx_range(f"block{i}.bwd"):
+            dx = block_backward(dy.contiguous(), w, saved, prov.block_grads(i), eng.cfg, eng.rope_cache, ctx.batch,
+                                ctx.seq, gather=prov.take_gather("bwd", i))
         ctx.saved = None
         ctx.x_in = None
         prov.post_backward("block", i)

@@ -31,6 +31,7 @@ from torch import nn
 from .. import ops
 from ..models.arena import ParamArena, Segment
 from ..models.engine import block_views, head_views
+from ..utils.metrics import nvtx_range
 from .comm import Communicator, GatherTask, make_communicator
 
 
@@ -339,7 +340,7 @@ class FSDP(nn.Module):
             u.slot = slot
             self._slot_owner[slot] = u
             return
-        with self._on_comm():
+        with self._on_comm(), nvtx_range(f"fsdp.all_gather.unit{u.index}"):
             if slot is not None and self._slot_free_ev[slot] is not None:
                 self.comm_stream.wait_event(self._slot_free_ev[slot])
             self.comm.all_gather(buf[:u.padded_numel], u.mirror_shard)
@@ -426,7 +427,7 @@ class FSDP(nn.Module):
         if self.cuda:
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream())
-        with self._on_comm():
+        with self._on_comm(), nvtx_range(f"fsdp.reduce_scatter.unit{u.index}"):
             if self.cuda:
                 self.comm_stream.wait_event(ready)
             key = "stage_head" if u is self.head_unit else f"stage{u.index % self.n_slots}"

@@ -10,6 +10,7 @@ file, and serving counters.
 from __future__ import annotations
 
 import contextlib
+import os
 import json
 import subprocess
 import time
@@ -28,17 +29,25 @@ def get_gpu_stats() -> list[list[str]]:
     return [ln.split(", ") for ln in lines if ln]
 
 
+NVTX_ENABLED = os.environ.get("B200_NVTX", "0") == "1"
+_NULL = contextlib.nullcontext()
+
+
 @contextlib.contextmanager
-def nvtx_range(name: str):
-    """NVTX range on CUDA builds, no-op elsewhere."""
-    on = torch.cuda.is_available()
-    if on:
-        torch.cuda.nvtx.range_push(name)
+def _nvtx(name: str):
+    torch.cuda.nvtx.range_push(name)
     try:
         yield
     finally:
-        if on:
-            torch.cuda.nvtx.range_pop()
+        torch.cuda.nvtx.range_pop()
+
+
+def nvtx_range(name: str):
+    """NVTX range (per block, phase and collective) when ``B200_NVTX=1`` and CUDA is present; otherwise a shared
+    no-op context, so the annotations cost nothing in normal runs."""
+    if NVTX_ENABLED and torch.cuda.is_available():
+        return _nvtx(name)
+    return _NULL
 
 
 class StepTimer:

@@ -131,3 +131,19 @@ def test_fsdp_world_size_one_aliases_shards():
         assert torch.allclose(got[k], ref[k], atol=3e-4, rtol=1e-4), k
     logits = f(x)
     assert logits.shape == (2, 16, CFG["vocab_size"])
+
+
+def test_flag_protocol_model_checker():
+    """Random interleavings of the ready / done flag protocol of the peer reduce-scatter: no read of a stale or
+    overwritten staging buffer, no deadlock; without the wait on `done` (one unit, so nothing else orders the
+    next write after the peers' reads) the checker must find the race."""
+    from llm_systems_from_scratch_b200.parallel.protocol_check import ProtocolViolation, check_reduce_scatter_protocol
+    for seed in range(200):
+        check_reduce_scatter_protocol(world=2 + seed % 4, units=1 + seed % 3, steps=3, seed=seed)
+    found = 0
+    for seed in range(200):
+        try:
+            check_reduce_scatter_protocol(world=4, units=1, steps=3, seed=seed, use_wait_readers=False)
+        except ProtocolViolation:
+            found += 1
+    assert found > 0

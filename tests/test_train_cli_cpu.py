@@ -67,3 +67,14 @@ def test_config_validation_rejects_indivisible_batch(tmp_path):
         validate(cfg)
     for name in ("sample", "cpu_tiny", "ddp_124m", "fsdp_1p3b", "fsdp_7b", "serve_1p3b"):
         validate(load_config(os.path.join(ROOT, "configures", f"{name}.yaml")), world_size=8)
+
+
+def test_profile_flag_writes_chrome_trace(tmp_path, monkeypatch):
+    """B200_PROFILE_STEPS (set by --profile N) wraps N steps in torch.profiler and writes a trace per rank."""
+    sys.path.insert(0, ROOT)
+    import train
+    cfg = _config(tmp_path, max_steps=7)
+    monkeypatch.setenv("B200_PROFILE_STEPS", "2")
+    train.train_worker(0, 1, [], cfg, False, False, False, True)
+    trace = tmp_path / "ckpt" / "trace_rank0.json"
+    assert trace.exists() and trace.stat().st_size > 1000

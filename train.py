@@ -33,7 +33,7 @@ from llm_systems_from_scratch_b200.ops.functional import clip_gradient, cross_en
 from llm_systems_from_scratch_b200.optim.adamw import AdamW, FusedAdamW, cosine_lr_schedule  # noqa: E402
 from llm_systems_from_scratch_b200.utils import checkpoint as ckpt_io  # noqa: E402
 from llm_systems_from_scratch_b200.utils.config import load_config, validate  # noqa: E402
-from llm_systems_from_scratch_b200.utils.metrics import MetricsLogger, StepTimer, get_gpu_stats  # noqa: E402,F401
+from llm_systems_from_scratch_b200.utils.metrics import MetricsLogger, StepTimer, get_gpu_stats, nvtx_range  # noqa: E402,F401
 from llm_systems_from_scratch_b200.utils.watchdog import Heartbeat  # noqa: E402
 
 
@@ -156,21 +156,38 @@ def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None 
             logits = model(x)
             return cross_entropy(logits.view(-1, logits.size(-1)).float(), y.view(-1))
 
+    # optional torch.profiler trace of a few steps (B200_PROFILE_STEPS=N, set by --profile N): Chrome trace per rank
+    profile_steps = int(os.environ.get("B200_PROFILE_STEPS", "0"))
+    profiler = None
     for step in range(start_step, max_steps):
         if heartbeat is not None:
             heartbeat.check()          # between steps: nothing of this rank is in flight
+        if profile_steps and step == start_step + 3:
+            from torch.profiler import ProfilerActivity, profile
+            acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+            profiler = profile(activities=acts)
+            profiler.__enter__()
+        if profiler is not None and step == start_step + 3 + profile_steps:
+            profiler.__exit__(None, None, None)
+            os.makedirs(checkpoint_dir, exist_ok=True)
+            profiler.export_chrome_trace(os.path.join(checkpoint_dir, f"trace_rank{rank}.json"))
+            profiler = None
         timer.start()
         lr = cosine_lr_schedule(step, lr_max, lr_min, optim_cfg["warmup_steps"], optim_cfg["decay_steps"])
         for group in optimizer.param_groups:
             group["lr"] = lr
-        x, y = sample_batch(train_data, local_batch, context_length, device)
+        with nvtx_range("data"):
+            x, y = sample_batch(train_data, local_batch, context_length, device)
         model.zero_grad()
-        loss = loss_of(x, y)
-        loss.backward()
-        if distributed:
-            model.finish_gradient_synchronization()
-        clip_gradient(model.parameters(), max_grad_norm)
-        optimizer.step()
+        with nvtx_range("forward"):
+            loss = loss_of(x, y)
+        with nvtx_range("backward"):
+            loss.backward()
+            if distributed:
+                model.finish_gradient_synchronization()
+        with nvtx_range("optimizer"):
+            clip_gradient(model.parameters(), max_grad_norm)
+            optimizer.step()
         loss_value = loss.item()
         step_time = timer.stop()
         logger.step_line(step, loss_value, lr, step_time, batch_size * context_length / step_time)
@@ -229,7 +246,14 @@ def main():
     ap.add_argument("--parallel", nargs="+", default=[], choices=["ddp", "fsdp"])
     ap.add_argument("--world-size", type=int, default=2)
     ap.add_argument("--resume", type=str, default=None, help="checkpoint file or sharded checkpoint directory")
+    ap.add_argument("--profile", type=int, default=0, metavar="N",
+                    help="torch.profiler Chrome trace of N steps (after 3 warm-up steps) into the checkpoint directory")
+    ap.add_argument("--nvtx", action="store_true", help="NVTX ranges per block, phase and collective")
     args = ap.parse_args()
+    if args.profile:
+        os.environ["B200_PROFILE_STEPS"] = str(args.profile)   # inherited by spawned ranks
+    if args.nvtx:
+        os.environ["B200_NVTX"] = "1"
     if "ddp" in args.parallel and "fsdp" in args.parallel:
         raise ValueError("--parallel ddp and fsdp are mutually exclusive (both are data parallelism)")
     if "fsdp" in args.parallel and args.compile:
