@@ -292,6 +292,57 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ tokens, const
   }
 }
 
+// Deterministic variant: `order` lists the token rows sorted by token id (stable), `sorted_tokens` the ids in that
+// order.  The warp at the first position of every run of equal ids adds the run's dx rows in order in fp32
+// registers and writes (or accumulates into) the table row once: no atomics, bitwise reproducible.
+template <int CHUNKS>   // 256-column chunks per launch: columns [col0, col0 + 256 * CHUNKS) of every row
+__global__ void embedding_bwd_sorted_kernel(const long long* __restrict__ sorted_tokens,
+                                            const long long* __restrict__ order,
+                                            const __nv_bfloat16* __restrict__ dx, float* __restrict__ grad_table,
+                                            long long rows, int d, int vocab, int accumulate, int col0) {
+  const int lane = threadIdx.x & 31;
+  const long long j0 = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (j0 >= rows) return;
+  const long long t = sorted_tokens[j0];
+  if (t < 0 || t >= vocab) return;
+  if (j0 > 0 && sorted_tokens[j0 - 1] == t) return;   // not the head of its run
+  float acc[CHUNKS][8];
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
+  for (long long j = j0; j < rows && sorted_tokens[j] == t; ++j) {
+    const __nv_bfloat16* src = dx + (size_t)order[j] * d;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = col0 + lane * 8 + k * 256;
+      if (c < d) {
+        float f[8];
+        load8(src + c, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[k][e] += f[e];
+      }
+    }
+  }
+  float* dst = grad_table + (size_t)t * d;
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) {
+    const int c = col0 + lane * 8 + k * 256;
+    if (c < d) {
+      float4* o = reinterpret_cast<float4*>(dst + c);
+      float4 a = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+      float4 b = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
+      if (accumulate) {
+        const float4 pa = o[0], pb = o[1];
+        a.x += pa.x; a.y += pa.y; a.z += pa.z; a.w += pa.w;
+        b.x += pb.x; b.y += pb.y; b.z += pb.z; b.w += pb.w;
+      }
+      o[0] = a;
+      o[1] = b;
+    }
+  }
+}
+
 // -------------------------------------------------------------------- Cross entropy
 // One block per row of logits (rows, ld) bf16 with `vocab` valid columns.  Pass 1: online max / sum.
 // Pass 2: overwrite the row with (softmax - onehot) * grad_scale / n_valid.  Row losses go to
@@ -614,6 +665,26 @@ extern "C" int b200_embedding_bwd(const long long* tokens, const void* dx, float
   if (rows == 0) return 0;
   embedding_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(tokens, (const __nv_bfloat16*)dx, grad_table, rows, d,
                                                                    vocab);
+  CHECK_LAUNCH();
+}
+
+// Deterministic embedding backward.  sorted_tokens / order: the token ids sorted ascending (stable) and the row
+// index of each; the table rows of tokens that occur are overwritten (accumulate = 0: the caller zeroes the rest)
+// or added to (accumulate = 1).  d must be a multiple of 8.
+extern "C" int b200_embedding_bwd_sorted(const long long* sorted_tokens, const long long* order, const void* dx,
+                                         float* grad_table, long long rows, int d, int vocab, int accumulate,
+                                         cudaStream_t st) {
+  if (d % 8 || !ALIGNED16(dx) || !ALIGNED16(grad_table)) return -10;
+  if (rows == 0) return 0;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+#define EMB_LAUNCH(C_, COL0_)                                                                                    \
+  embedding_bwd_sorted_kernel<C_><<<grid, 256, 0, st>>>(sorted_tokens, order, (const __nv_bfloat16*)dx, grad_table, \
+                                                       rows, d, vocab, accumulate, COL0_)
+  if (d <= 1024) EMB_LAUNCH(4, 0);
+  else if (d <= 2048) EMB_LAUNCH(8, 0);
+  else
+    for (int col0 = 0; col0 < d; col0 += 4096) EMB_LAUNCH(16, col0);   // wide rows: one launch per 4096 columns
+#undef EMB_LAUNCH
   CHECK_LAUNCH();
 }
 

@@ -76,6 +76,7 @@ def _declare(lib):
         "b200_rope": [P, P, P, L, I, I, I, I, I, P],
         "b200_embedding_fwd": [P, P, P, L, I, I, P],
         "b200_embedding_bwd": [P, P, P, L, I, I, P],
+        "b200_embedding_bwd_sorted": [P, P, P, P, L, I, I, I, P],
         "b200_xent": [P, P, P, P, L, L, I, I, F, I, I, P, P],
         "b200_argmax": [P, L, L, I, P, P],
         "b200_sample_topk": [P, L, L, I, P, F, I, P, P],
@@ -431,7 +432,10 @@ def embedding_fwd(tokens, weight, out_dtype=None):
     return out
 
 
-def embedding_bwd(dx, tokens, grad_weight, accumulate=False):
+def embedding_bwd(dx, tokens, grad_weight, accumulate=False, deterministic=True):
+    """Scatter-add of dx rows into the fp32 gradient table.  The default sorts the token ids (stable device sort)
+    and adds every run of equal ids in order inside one warp: no atomics, bitwise reproducible.
+    ``deterministic=False`` uses 16-byte vector atomics instead (one launch, no sort)."""
     lib = load()
     _req(dx.dtype == torch.bfloat16 and dx.is_contiguous(), "dx must be contiguous bf16")
     _req(grad_weight.dtype == torch.float32 and grad_weight.is_contiguous(), "grad table must be fp32")
@@ -441,6 +445,12 @@ def embedding_bwd(dx, tokens, grad_weight, accumulate=False):
     _req(dx.numel() == rows * d, "dx shape mismatch")
     if not accumulate:
         grad_weight.zero_()
+    if deterministic:
+        flat = tokens.reshape(-1)
+        sorted_tokens, order = torch.sort(flat, stable=True)
+        _check(lib.b200_embedding_bwd_sorted(_ptr(sorted_tokens), _ptr(order), _ptr(dx), _ptr(grad_weight), rows, d, v,
+                                             1 if accumulate else 0, _stream()), "embedding_bwd_sorted")
+        return grad_weight
     _check(lib.b200_embedding_bwd(_ptr(tokens), _ptr(dx), _ptr(grad_weight), rows, d, v, _stream()), "embedding_bwd")
     return grad_weight
 

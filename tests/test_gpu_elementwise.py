@@ -72,6 +72,24 @@ def test_embedding():
     native.embedding_bwd(dx, tok, g)
     ref = torch.zeros(v, d, device="cuda").index_add_(0, tok, dx.float())
     _close(g, ref, 1e-3, 1e-4)
+    # the default path is free of atomics: repeated runs are bitwise identical, also with heavy duplication,
+    # accumulation and rows wider than one launch covers
+    hot = torch.randint(0, 7, (rows,), device="cuda")
+    g1, g2 = torch.empty(v, d, device="cuda"), torch.empty(v, d, device="cuda")
+    native.embedding_bwd(dx, hot, g1)
+    native.embedding_bwd(dx, hot, g2)
+    assert torch.equal(g1, g2)
+    _close(g1, torch.zeros(v, d, device="cuda").index_add_(0, hot, dx.float()), 2e-2, 1e-4)
+    native.embedding_bwd(dx, tok, g1, accumulate=True)
+    _close(g1, g2 + ref, 2e-2, 1e-4)
+    ga = torch.empty(v, d, device="cuda")
+    native.embedding_bwd(dx, tok, ga, deterministic=False)
+    _close(ga, ref, 1e-3, 1e-4)
+    wide = torch.randn(64, 5120, device="cuda").bfloat16()
+    tw = torch.randint(0, 20, (64,), device="cuda")
+    gw = torch.empty(20, 5120, device="cuda")
+    native.embedding_bwd(wide, tw, gw)
+    _close(gw, torch.zeros(20, 5120, device="cuda").index_add_(0, tw, wide.float()), 1e-2, 1e-4)
 
 
 @pytest.mark.parametrize("rows,v,ld", [(64, 1000, 1000), (128, 50257, 50264), (16, 10000, 10048)])
