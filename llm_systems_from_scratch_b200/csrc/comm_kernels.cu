@@ -373,6 +373,27 @@ extern "C" int b200_peer_reduce_scatter(const unsigned long long* staging_ptrs, 
   COMM_CHECK();
 }
 
+// Plain pull copy (init-time broadcast: every rank reads the source rank's buffer through its peer mapping).
+__global__ void __launch_bounds__(512) peer_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                                        size_t n_vec, unsigned char* __restrict__ dst_tail,
+                                                        const unsigned char* __restrict__ src_tail, int tail) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_vec; i += stride) dst[i] = src[i];
+  if (blockIdx.x == 0 && (int)threadIdx.x < tail) dst_tail[threadIdx.x] = src_tail[threadIdx.x];
+}
+
+// dst (local) <- src (any address this process can read, e.g. a peer's IPC-mapped buffer); both 16-byte aligned.
+extern "C" int b200_peer_copy(void* dst, const void* src, unsigned long long nbytes, int ctas, cudaStream_t st) {
+  if ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) return -10;
+  if (nbytes == 0) return 0;
+  const size_t n_vec = nbytes / 16;
+  const int tail = (int)(nbytes % 16);
+  peer_copy_kernel<<<ctas > 0 ? ctas : 128, 512, 0, st>>>(reinterpret_cast<uint4*>(dst), reinterpret_cast<const uint4*>(src),
+                                                          n_vec, reinterpret_cast<unsigned char*>(dst) + n_vec * 16,
+                                                          reinterpret_cast<const unsigned char*>(src) + n_vec * 16, tail);
+  COMM_CHECK();
+}
+
 extern "C" int b200_peer_wait(const uint32_t* flags, int world, unsigned int epoch, unsigned long long limit_ns,
                               uint32_t* status, cudaStream_t st) {
   if (world > MAX_WORLD) return -10;

@@ -45,9 +45,10 @@ def _declare(lib):
                                              I, P]
     lib.b200_peer_wait.argtypes = [P, I, U, L, P, P]
     lib.b200_peer_allreduce.argtypes = [P, P, L, L, L, I, I, U, L, P, P, I, P]
+    lib.b200_peer_copy.argtypes = [P, P, L, I, P]
     for n in ("b200_ipc_alloc", "b200_ipc_free", "b200_ipc_get_handle", "b200_ipc_open", "b200_ipc_close",
               "b200_peer_barrier", "b200_peer_allgather", "b200_peer_reduce_scatter", "b200_peer_wait",
-              "b200_peer_allreduce"):
+              "b200_peer_allreduce", "b200_peer_copy"):
         getattr(lib, n).restype = I
 
 
@@ -245,5 +246,27 @@ class PeerComm(Communicator):
     def all_reduce_sum(self, flat):
         self.fallback.all_reduce_sum(flat)      # scalars (norms, counters): plumbing
 
+    BOUNCE_BYTES = 64 << 20
+
     def broadcast(self, t, src=0):
-        self.fallback.broadcast(t, src)
+        """Every rank pulls ``t`` from rank ``src`` through a peer-visible bounce buffer (init-time weights)."""
+        if not (t.is_cuda and t.is_contiguous()) or t.numel() == 0:
+            return self.fallback.broadcast(t, src)
+        if not hasattr(self, "_bounce"):
+            self._bounce = self.alloc(self.BOUNCE_BYTES, torch.uint8)    # collective: all ranks broadcast together
+        raw = t.view(-1).view(torch.uint8)
+        src_ptr = self._find(self._bounce)["peers"][src]
+        for off in range(0, raw.numel(), self.BOUNCE_BYTES):
+            n = min(self.BOUNCE_BYTES, raw.numel() - off)
+            if self.rank == src:
+                self._bounce[:n].copy_(raw[off:off + n])
+            self.barrier()                  # the source's bounce buffer is complete
+            if self.rank != src:
+                dst = raw[off:off + n]
+                if dst.data_ptr() % 16:
+                    tmp = torch.empty(n, dtype=torch.uint8, device=t.device)
+                    native._check(self.lib.b200_peer_copy(tmp.data_ptr(), src_ptr, n, 0, self._stream()), "peer_copy")
+                    dst.copy_(tmp)
+                else:
+                    native._check(self.lib.b200_peer_copy(dst.data_ptr(), src_ptr, n, 0, self._stream()), "peer_copy")
+            self.barrier()                  # every reader is done before the next chunk overwrites it

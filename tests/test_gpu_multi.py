@@ -109,6 +109,14 @@ def _collectives(rank, world, port):
             want /= world
             comm.all_reduce_mean(buf)
             assert torch.allclose(buf, want, atol=1e-6)
+        # init-time broadcast: every rank pulls rank 0's tensor (odd byte counts and unaligned views included)
+        for numel, dtype, off in ((1 << 20, torch.float32, 0), (12345, torch.bfloat16, 1), (7, torch.float32, 0)):
+            base = torch.randn(numel + off, device="cuda", generator=g).to(dtype)
+            t = base[off:]
+            want = t.clone()
+            dist.broadcast(want, src=0)
+            comm.broadcast(t, src=0)
+            assert torch.equal(t, want)
         torch.cuda.synchronize()
         native.check_status()
     finally:
