@@ -247,10 +247,11 @@ class PeerComm(Communicator):
         self.fallback.all_reduce_sum(flat)      # scalars (norms, counters): plumbing
 
     BOUNCE_BYTES = 64 << 20
+    PEER_BROADCAST = os.environ.get("B200_PEER_BROADCAST", "0") == "1"   # off: NCCL broadcast (init only)
 
     def broadcast(self, t, src=0):
         """Every rank pulls ``t`` from rank ``src`` through a peer-visible bounce buffer (init-time weights)."""
-        if not (t.is_cuda and t.is_contiguous()) or t.numel() == 0:
+        if not (t.is_cuda and t.is_contiguous()) or t.numel() == 0 or not self.PEER_BROADCAST:
             return self.fallback.broadcast(t, src)
         if not hasattr(self, "_bounce"):
             self._bounce = self.alloc(self.BOUNCE_BYTES, torch.uint8)    # collective: all ranks broadcast together

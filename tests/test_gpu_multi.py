@@ -115,6 +115,7 @@ def _collectives(rank, world, port):
             t = base[off:]
             want = t.clone()
             dist.broadcast(want, src=0)
+            comm.PEER_BROADCAST = True
             comm.broadcast(t, src=0)
             assert torch.equal(t, want)
         torch.cuda.synchronize()
