@@ -175,7 +175,9 @@ EPI_BF16, EPI_F32, EPI_BF16_RES, EPI_F32_ACC, EPI_SWIGLU_BWD = 0, 1, 2, 3, 4
 
 # Problems at least this large (rows of the output) run on CTA pairs (cta_group::2, 256 x 256 tiles).
 PAIR_MIN_M = int(os.environ.get("B200_GEMM_PAIR_MIN_M", "1024"))
-FUSE_SWIGLU_BWD = os.environ.get("B200_FUSE_SWIGLU_BWD", "1") == "1"
+# The SiLU*mul backward can run in the epilogue of the W2 dgrad GEMM, but measured on the 1.3B step it is 1.3 %
+# slower than GEMM + stand-alone kernel (the 128 epilogue threads of a CTA become the bottleneck), so it is opt-in.
+FUSE_SWIGLU_BWD = os.environ.get("B200_FUSE_SWIGLU_BWD", "0") == "1"
 USE_PAIR = os.environ.get("B200_GEMM_PAIR", "1") == "1"
 
 

@@ -143,7 +143,11 @@ def test_gemm_swiglu_backward_epilogue(m, f, k):
     dy = torch.randn(m, k, device="cuda").bfloat16()
     w = (torch.randn(k, f, device="cuda") / k ** 0.5).bfloat16()
     gu = torch.randn(m, 2 * f, device="cuda").bfloat16()
-    out = native.gemm_swiglu_bwd(dy, w, gu)
+    native.FUSE_SWIGLU_BWD = True       # opt-in path (off by default: slower than the two-kernel path end to end)
+    try:
+        out = native.gemm_swiglu_bwd(dy, w, gu)
+    finally:
+        native.FUSE_SWIGLU_BWD = False
     assert out is not None
     native.check_status()
     two_step = native.silu_mul_bwd(native.gemm(dy, w, "nn"), gu)
