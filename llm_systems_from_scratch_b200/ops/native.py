@@ -175,6 +175,8 @@ EPI_BF16, EPI_F32, EPI_BF16_RES, EPI_F32_ACC, EPI_SWIGLU_BWD = 0, 1, 2, 3, 4
 
 # Problems at least this large (rows of the output) run on CTA pairs (cta_group::2, 256 x 256 tiles).
 PAIR_MIN_M = int(os.environ.get("B200_GEMM_PAIR_MIN_M", "1024"))
+FUSE_ROPE = os.environ.get("B200_FUSE_ROPE", "1") == "1"                # RoPE in the QKV GEMM epilogue
+FUSE_SWIGLU_FWD = os.environ.get("B200_FUSE_SWIGLU_FWD", "1") == "1"    # SiLU*mul in the gate|up GEMM epilogue
 # The SiLU*mul backward can run in the epilogue of the W2 dgrad GEMM, but measured on the 1.3B step it is 1.3 %
 # slower than GEMM + stand-alone kernel (the 128 epilogue threads of a CTA become the bottleneck), so it is opt-in.
 FUSE_SWIGLU_BWD = os.environ.get("B200_FUSE_SWIGLU_BWD", "0") == "1"
@@ -270,7 +272,7 @@ def gemm_qkv_rope(x, wqkv, cos_sin, seq: int, n_heads: int):
     n = wqkv.shape[0]
     d = n // 3
     dh = d // n_heads
-    ok = (USE_PAIR and m >= PAIR_MIN_M and dh % 32 == 0 and m % seq == 0 and seq <= cos_sin.shape[1]
+    ok = (USE_PAIR and FUSE_ROPE and m >= PAIR_MIN_M and dh % 32 == 0 and m % seq == 0 and seq <= cos_sin.shape[1]
           and x.dtype == torch.bfloat16 and wqkv.dtype == torch.bfloat16 and x.stride(1) == 1 and wqkv.stride(1) == 1
           and x.stride(0) % 8 == 0 and wqkv.stride(0) % 8 == 0 and cos_sin.is_contiguous()
           and cos_sin.dtype == torch.float32 and cos_sin.shape[2] == dh // 2)
@@ -291,7 +293,7 @@ def gemm_swiglu(x, wgu, gather=None):
     m, k = x.shape
     two_f = wgu.shape[0]
     f = two_f // 2
-    ok = (USE_PAIR and m >= PAIR_MIN_M and f % 128 == 0 and x.dtype == torch.bfloat16 and wgu.dtype == torch.bfloat16
+    ok = (USE_PAIR and FUSE_SWIGLU_FWD and m >= PAIR_MIN_M and f % 128 == 0 and x.dtype == torch.bfloat16 and wgu.dtype == torch.bfloat16
           and x.stride(1) == 1 and wgu.stride(1) == 1 and x.stride(0) % 8 == 0 and wgu.stride(0) % 8 == 0)
     if not ok:
         return None
