@@ -21,6 +21,8 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 BUILD_DIR = PKG_DIR / "csrc" / "build"
 LIB_PATH = PKG_DIR / "_b200_kernels.so"
+HOST_SRC = CSRC / "host" / "host_runtime.cpp"
+HOST_LIB_PATH = PKG_DIR / "_b200_host.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -58,8 +60,31 @@ def needs_build() -> bool:
     return stamp.read_text().strip() != _digest(deps)
 
 
+def build_host(force: bool = False) -> Path | None:
+    """Compile the host-side runtime (loader gather, KV page allocator) with g++; returns None without a compiler."""
+    if not HOST_SRC.exists():
+        return None
+    stamp = BUILD_DIR / "host_stamp.txt"
+    digest = hashlib.sha256(HOST_SRC.read_bytes()).hexdigest()
+    if not force and HOST_LIB_PATH.exists() and stamp.exists() and stamp.read_text().strip() == digest:
+        return HOST_LIB_PATH
+    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        return None
+    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    tmp = HOST_LIB_PATH.with_suffix(".so.tmp")
+    proc = subprocess.run([cxx, "-O3", "-std=c++17", "-shared", "-fPIC", "-pthread", "-o", str(tmp), str(HOST_SRC)],
+                          capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"host runtime build failed:\n{proc.stdout}\n{proc.stderr}")
+    os.replace(tmp, HOST_LIB_PATH)
+    stamp.write_text(digest)
+    return HOST_LIB_PATH
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every ``csrc/*.cu`` for sm_100a and link ``_b200_kernels.so``."""
+    """Compile every ``csrc/*.cu`` for sm_100a and link ``_b200_kernels.so``; also builds the host runtime."""
+    build_host(force)
     if not force and not needs_build():
         return LIB_PATH
     nvcc = _nvcc()

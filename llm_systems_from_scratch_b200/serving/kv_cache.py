@@ -12,17 +12,30 @@ import torch
 
 
 class PageAllocator:
-    """LIFO free list over page ids with reservation accounting."""
+    """LIFO free list over page ids.  The list lives in the C++ host runtime when that library is available
+    (``utils.host_runtime``), otherwise in a Python list; both hand pages out in the same order."""
 
-    def __init__(self, num_pages: int):
+    def __init__(self, num_pages: int, native: bool | None = None):
         self.num_pages = num_pages
-        self._free = list(range(num_pages - 1, -1, -1))
+        self._pool = None
+        if native is not False:
+            try:
+                from ..utils import host_runtime
+                if host_runtime.available():
+                    self._pool = host_runtime.NativePagePool(num_pages)
+            except Exception:
+                self._pool = None
+        if native is True and self._pool is None:
+            raise RuntimeError("host runtime library is not available")
+        self._free = list(range(num_pages - 1, -1, -1)) if self._pool is None else None
 
     @property
     def free(self) -> int:
-        return len(self._free)
+        return self._pool.free if self._pool is not None else len(self._free)
 
     def take(self, n: int) -> list[int]:
+        if self._pool is not None:
+            return self._pool.take(n)
         if n > len(self._free):
             raise MemoryError(f"out of KV pages: want {n}, have {len(self._free)}")
         out = self._free[-n:][::-1] if n else []
@@ -30,6 +43,8 @@ class PageAllocator:
         return out
 
     def give(self, pages: list[int]):
+        if self._pool is not None:
+            return self._pool.give(pages)
         self._free.extend(reversed(pages))
 
 

@@ -73,3 +73,41 @@ def test_poisson_trace_statistics():
     assert abs(sum(gaps) / len(gaps) - 0.05) < 0.005
     assert min(len(r.prompt) for r in tr) >= 128 and max(len(r.prompt) for r in tr) <= 2048
     assert min(r.max_new_tokens for r in tr) >= 64 and max(r.max_new_tokens for r in tr) <= 512
+
+
+def test_host_runtime_matches_python_paths():
+    """C++ host runtime: window gather, page pool order, slot and block-table arithmetic against the Python code."""
+    import numpy as np
+    import pytest
+    import torch
+    from llm_systems_from_scratch_b200.serving.kv_cache import PageAllocator
+    from llm_systems_from_scratch_b200.utils import host_runtime as hr
+    if not hr.available():
+        pytest.skip("no C++ compiler for the host runtime")
+    rng = np.random.default_rng(0)
+    tokens = rng.integers(0, 50000, size=1 << 18, dtype=np.uint32)
+    starts = rng.integers(0, len(tokens) - 513, size=256, dtype=np.int64)
+    out = torch.empty(256, 513, dtype=torch.int64)
+    hr.gather_windows(tokens, starts, 513, out)
+    want = tokens[np.arange(513)[None, :] + starts[:, None]].astype(np.int64)
+    assert np.array_equal(out.numpy(), want)
+    with pytest.raises(IndexError):
+        hr.gather_windows(tokens, np.array([len(tokens) - 10], dtype=np.int64), 513, torch.empty(1, 513, dtype=torch.int64))
+    a, b = PageAllocator(64, native=True), PageAllocator(64, native=False)
+    held_a, held_b = [], []
+    for step in range(200):
+        if rng.random() < 0.6 and a.free >= 5:
+            n = int(rng.integers(1, 6))
+            held_a.append(a.take(n))
+            held_b.append(b.take(n))
+        elif held_a:
+            i = int(rng.integers(0, len(held_a)))
+            a.give(held_a.pop(i))
+            b.give(held_b.pop(i))
+        assert held_a == held_b and a.free == b.free
+    with pytest.raises(MemoryError):
+        a.take(a.free + 1)
+    pages = [7, 3, 9]
+    assert hr.slots(pages, 16, 14, 20) == [pages[t // 16] * 16 + t % 16 for t in range(14, 34)]
+    table = hr.block_table([[1, 2, 3], [4], []], 4, pad=-1)
+    assert table.tolist() == [[1, 2, 3, -1], [4, -1, -1, -1], [-1, -1, -1, -1]]
