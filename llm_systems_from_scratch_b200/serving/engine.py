@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import time
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -57,6 +58,11 @@ class ServingEngine:
         self.max_batch = max_batch
         self.use_graphs = use_cuda_graphs and self.cuda
         self._graphs: dict[int, dict] = {}
+        try:
+            from ..utils import host_runtime
+            self._host_rt = host_runtime if host_runtime.available() else None
+        except Exception:
+            self._host_rt = None
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "prefill_steps": 0}
 
     # ------------------------------------------------------------------ model pieces
@@ -163,20 +169,34 @@ class ServingEngine:
         bucket = self._bucket(n)
         st = self._graph_for(bucket)
         ps = self.page_size
-        tok = torch.zeros(bucket, dtype=torch.int64)
-        pos = torch.zeros(bucket, dtype=torch.int32)
-        slots = torch.full((bucket,), -1, dtype=torch.int64)
-        ctx = torch.ones(bucket, dtype=torch.int32)
-        tables = torch.zeros((bucket, self.max_pages_per_req), dtype=torch.int32)
-        for i, r in enumerate(reqs):
-            p = r.context_len - 1                 # position of the token being fed (the last generated one)
-            tok[i] = r.output[-1]
-            pos[i] = p
-            slots[i] = r.pages[p // ps] * ps + p % ps
-            ctx[i] = p + 1
-            tables[i, :len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
-        for name, host in (("tokens", tok), ("positions", pos), ("slots", slots), ("ctx", ctx), ("tables", tables)):
-            st[name].copy_(host.pin_memory() if self.cuda else host, non_blocking=True)
+        # Host staging is pinned once per bucket and refilled in place through numpy views (the previous step ended
+        # with a device-to-host read, so no copy from these buffers is still in flight).
+        host = st.get("host")
+        if host is None:
+            mk = lambda shape, dt: torch.zeros(shape, dtype=dt, pin_memory=self.cuda)
+            host = st["host"] = {"tokens": mk(bucket, torch.int64), "positions": mk(bucket, torch.int32),
+                                 "slots": mk(bucket, torch.int64), "ctx": mk(bucket, torch.int32),
+                                 "tables": mk((bucket, self.max_pages_per_req), torch.int32)}
+            st["host_np"] = {k: v.numpy() for k, v in host.items()}
+        hn = st["host_np"]
+        p = np.fromiter((r.context_len - 1 for r in reqs), dtype=np.int64, count=n)   # position of the token being fed
+        hn["tokens"][:n] = np.fromiter((r.output[-1] for r in reqs), dtype=np.int64, count=n)
+        hn["tokens"][n:] = 0
+        hn["positions"][:n] = p
+        hn["positions"][n:] = 0
+        hn["slots"][:n] = np.fromiter((r.pages[q // ps] for r, q in zip(reqs, p)), dtype=np.int64, count=n) * ps + p % ps
+        hn["slots"][n:] = -1
+        hn["ctx"][:n] = p + 1
+        hn["ctx"][n:] = 1
+        if self._host_rt is not None:
+            self._host_rt.block_table_into([r.pages for r in reqs], host["tables"], 0)
+        else:
+            tb = hn["tables"]
+            tb[:] = 0
+            for i, r in enumerate(reqs):
+                tb[i, :len(r.pages)] = r.pages
+        for name in ("tokens", "positions", "slots", "ctx", "tables"):
+            st[name].copy_(host[name], non_blocking=True)
         if self.use_graphs:
             st["graph"].replay()
             out = st["out"]

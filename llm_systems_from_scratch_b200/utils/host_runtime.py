@@ -115,3 +115,18 @@ def block_table(page_lists: list[list[int]], width: int, pad: int = 0) -> torch.
     if lib.b200h_block_table(pg, of, len(page_lists), width, pad, table.data_ptr()) != 0:
         raise ValueError("a request has more pages than the table is wide")
     return table
+
+
+def block_table_into(page_lists: list[list[int]], table: torch.Tensor, pad: int = 0):
+    """Fill the first ``len(page_lists)`` rows of a preallocated int32 CPU table in place; the other rows get ``pad``."""
+    lib = _load()
+    rows, width = table.shape
+    lists = list(page_lists) + [[]] * (rows - len(page_lists))
+    flat = [p for pl in lists for p in pl]
+    offs = [0]
+    for pl in lists:
+        offs.append(offs[-1] + len(pl))
+    pg = (ctypes.c_int32 * max(len(flat), 1))(*flat)
+    of = (ctypes.c_int32 * len(offs))(*offs)
+    if lib.b200h_block_table(pg, of, rows, width, pad, table.data_ptr()) != 0:
+        raise ValueError("a request has more pages than the table is wide")
