@@ -70,4 +70,7 @@ class PagedKVCache:
     def slots(self, pages: list[int], start: int, count: int) -> list[int]:
         """Flat cache slots (page * page_size + offset) of token positions [start, start + count)."""
         ps = self.page_size
+        if self.allocator._pool is not None and count > 64:
+            from ..utils import host_runtime
+            return host_runtime.slots(pages, ps, start, count)
         return [pages[t // ps] * ps + t % ps for t in range(start, start + count)]
