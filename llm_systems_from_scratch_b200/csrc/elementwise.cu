@@ -88,49 +88,6 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
   }
 }
 
-// Register-resident variant for d <= 256 * CHUNKS: every 16-byte load of the row is in flight at once and the
-// row is read from memory a single time.
-template <int CHUNKS>
-__global__ void __launch_bounds__(256) rmsnorm_fwd_reg_kernel(const __nv_bfloat16* __restrict__ x,
-                                                              const __nv_bfloat16* __restrict__ w,
-                                                              __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
-                                                              int rows, int d, float eps) {
-  const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const __nv_bfloat16* xr = x + (size_t)row * d;
-  float f[CHUNKS][8];
-  float ss = 0.f;
-#pragma unroll
-  for (int k = 0; k < CHUNKS; ++k) {
-    const int c = lane * 8 + k * 256;
-    if (c < d) load8(xr + c, f[k]);
-  }
-#pragma unroll
-  for (int k = 0; k < CHUNKS; ++k) {
-    const int c = lane * 8 + k * 256;
-    if (c < d) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ss += f[k][i] * f[k][i];
-    }
-  }
-  ss = warp_sum(ss);
-  const float r = rsqrtf(ss / (float)d + eps);
-  if (lane == 0 && rstd != nullptr) rstd[row] = r;
-  __nv_bfloat16* yr = y + (size_t)row * d;
-#pragma unroll
-  for (int k = 0; k < CHUNKS; ++k) {
-    const int c = lane * 8 + k * 256;
-    if (c < d) {
-      float g[8];
-      load8(w + c, g);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) f[k][i] = f[k][i] * r * g[i];
-      store8(yr + c, f[k]);
-    }
-  }
-}
-
 // ------------------------------------------------------------------------ RMSNorm bwd
 // dx = [dres +] rstd * (dy*w) - rstd^3/d * sum(dy*w*x) * x ;  dw += dy * x * rstd.
 // Each block walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a thread owns up to MAXC groups of
@@ -161,7 +118,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     const __nv_bfloat16* dyr = dy + (size_t)row * d;
     const __nv_bfloat16* xr = x + (size_t)row * d;
     const float r = rstd[row];
-    float g[RMS_BWD_MAXC][8], xv[RMS_BWD_MAXC][8], ev[RMS_BWD_MAXC][8];
+    float g[RMS_BWD_MAXC][8], xv[RMS_BWD_MAXC][8];
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < RMS_BWD_MAXC; ++j) {
@@ -170,8 +127,6 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         float dyv[8];
         load8(dyr + c, dyv);
         load8(xr + c, xv[j]);
-        // the residual-branch gradient is fetched with the other operands, not after the row reduction
-        if (dres != nullptr) load8(dres + (size_t)row * d + c, ev[j]);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           dwacc[j][i] += dyv[i] * xv[j][i] * r;
@@ -191,8 +146,10 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = r * g[j][i] - coef * xv[j][i];
         if (dres != nullptr) {  // gradient arriving through the residual branch
+          float e[8];
+          load8(dres + (size_t)row * d + c, e);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] += ev[j][i];
+          for (int i = 0; i < 8; ++i) o[i] += e[i];
         }
         store8(dxr + c, o);
       }
@@ -636,15 +593,8 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* w, void* y, float* rs
                                 cudaStream_t st) {
   if (d % 8 || !ALIGNED16(x) || !ALIGNED16(w) || !ALIGNED16(y)) return -10;
   if (rows == 0) return 0;
-#define RMS_FWD_REG(C_)                                                                                      \
-  rmsnorm_fwd_reg_kernel<C_><<<(rows + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, \
-                                                            (__nv_bfloat16*)y, rstd, rows, d, eps)
-  if (d <= 1024) RMS_FWD_REG(4);
-  else if (d <= 2048) RMS_FWD_REG(8);
-  else
-    rmsnorm_fwd_kernel<<<(rows + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                                       (__nv_bfloat16*)y, rstd, rows, d, eps);
-#undef RMS_FWD_REG
+  rmsnorm_fwd_kernel<<<(rows + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                                     (__nv_bfloat16*)y, rstd, rows, d, eps);
   CHECK_LAUNCH();
 }
 
