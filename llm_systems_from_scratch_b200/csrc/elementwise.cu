@@ -508,6 +508,29 @@ __global__ void adamw_kernel(float* __restrict__ p, const GradT* __restrict__ g,
   }
 }
 
+// Deterministic two-step variant: per-block partials to `partials[blockIdx.x]`, then one block adds them in index
+// order (fixed summation order => bitwise reproducible gradient norm).
+template <typename T>
+__global__ void sumsq_partials_kernel(const T* __restrict__ x, long long n, float* __restrict__ partials) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float f;
+    if constexpr (sizeof(T) == 4) f = x[i]; else f = __bfloat162float(x[i]);
+    s += f * f;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) partials[blockIdx.x] = s;
+}
+
+__global__ void sumsq_finish_kernel(const float* __restrict__ partials, int n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += partials[i];   // fixed assignment of partials to threads
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) *out += s;
+}
+
 // out += sum(x^2).  fp32 or bf16 input.  Per-block partials are combined with one atomic per block.
 template <typename T>
 __global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __restrict__ out) {
@@ -726,6 +749,20 @@ extern "C" int b200_adamw(float* p, const void* g, int grad_is_bf16, float* m, f
   else
     adamw_kernel<float><<<grid, 256, 0, st>>>(p, (const float*)g, m, v, (__nv_bfloat16*)mirror, n, gscale, lr, b1, b2, eps,
                                               wd, alpha_t);
+  CHECK_LAUNCH();
+}
+
+// Number of floats of scratch that b200_sumsq_det needs.
+extern "C" int b200_sumsq_scratch() { return 148 * 4; }
+
+// out += sum(x^2) with a fixed summation order (scratch: b200_sumsq_scratch() floats, used only by this call's stream).
+extern "C" int b200_sumsq_det(const void* x, int is_bf16, long long n, float* out, float* scratch, cudaStream_t st) {
+  if (n == 0) return 0;
+  if (scratch == nullptr) return -10;
+  const int grid = grid_for(n, 512, 148 * 4);
+  if (is_bf16) sumsq_partials_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>((const __nv_bfloat16*)x, n, scratch);
+  else sumsq_partials_kernel<float><<<grid, 512, 0, st>>>((const float*)x, n, scratch);
+  sumsq_finish_kernel<<<1, 256, 0, st>>>(scratch, grid, out);
   CHECK_LAUNCH();
 }
 

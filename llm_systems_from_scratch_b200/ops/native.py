@@ -82,6 +82,8 @@ def _declare(lib):
         "b200_sample_topk": [P, L, L, I, P, F, I, P, P],
         "b200_adamw": [P, P, I, P, P, P, L, P, F, F, F, F, F, F, P],
         "b200_sumsq": [P, I, L, P, P],
+        "b200_sumsq_det": [P, I, L, P, P, P],
+        "b200_sumsq_scratch": [],
         "b200_clip_coef": [P, F, P, P, P],
         "b200_scale": [P, I, L, P, P],
         "b200_cast_f32_bf16": [P, P, L, P],
@@ -529,7 +531,10 @@ def sumsq(x, out=None):
     _req(x.is_contiguous() and x.dtype in (torch.float32, torch.bfloat16), "sumsq needs contiguous fp32/bf16")
     if out is None:
         out = torch.zeros((), dtype=torch.float32, device=x.device)
-    _check(lib.b200_sumsq(_ptr(x), 1 if x.dtype == torch.bfloat16 else 0, x.numel(), _ptr(out), _stream()), "sumsq")
+    # per-block partials added in index order: the gradient norm is bitwise reproducible
+    scratch = torch.empty(lib.b200_sumsq_scratch(), dtype=torch.float32, device=x.device)
+    _check(lib.b200_sumsq_det(_ptr(x), 1 if x.dtype == torch.bfloat16 else 0, x.numel(), _ptr(out), _ptr(scratch),
+                              _stream()), "sumsq")
     return out
 
 

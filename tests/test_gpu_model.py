@@ -89,3 +89,37 @@ def test_activation_checkpointing_matches():
 def test_smoke_entry():
     import __graft_entry__
     __graft_entry__.smoke()
+
+
+def test_training_is_bitwise_reproducible():
+    """Every reduction on the training path has a fixed order (no float atomics), so two runs from the same seed end
+    with identical parameters; a race between kernels or streams would show up here as a difference."""
+    from llm_systems_from_scratch_b200.models.transformer import TransformerLM
+    from llm_systems_from_scratch_b200.ops import native as nat
+    from llm_systems_from_scratch_b200.optim import FusedAdamW
+    from llm_systems_from_scratch_b200.parallel import FSDP
+    cfg = dict(vocab_size=1003, context_length=512, d_model=512, num_layers=3, num_heads=4, d_ff=1408, rope_theta=10000.0)
+
+    def run():
+        torch.manual_seed(0)
+        model = TransformerLM(**cfg, use_flash_attn=True, use_custom_triton=True).cuda()
+        wrapped = FSDP(model)
+        opt = FusedAdamW(wrapped.parameters(), lr=1e-3, weight_decay=0.1)
+        g = torch.Generator(device="cuda").manual_seed(1)
+        losses = []
+        for _ in range(4):
+            x = torch.randint(0, cfg["vocab_size"], (4, 512), device="cuda", generator=g)   # 2048 rows: CTA-pair GEMMs
+            y = torch.randint(0, cfg["vocab_size"], (4, 512), device="cuda", generator=g)
+            loss = wrapped.loss(x, y)
+            loss.backward()
+            wrapped.finish_gradient_synchronization()
+            opt.set_grad_scale(wrapped.shard_arena.clip_coef(1.0))
+            opt.step()
+            losses.append(loss.item())
+        nat.check_status()
+        return losses, [p.detach().clone() for p in wrapped.parameters()]
+
+    l1, p1 = run()
+    l2, p2 = run()
+    assert l1 == l2
+    assert all(torch.equal(a, b) for a, b in zip(p1, p2))
