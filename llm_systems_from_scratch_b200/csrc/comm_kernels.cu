@@ -130,6 +130,11 @@ struct AdamArgs {
   float lr, b1, b2, eps, wd, alpha_t;
 };
 
+// Per-CTA partial sums of squares of one reduce-scatter launch.  Launches that share the array must be ordered on
+// one stream (FSDP issues all of them on its communication stream).
+constexpr int RS_MAX_CTAS = 1024;
+__device__ float g_rs_sumsq_partials[RS_MAX_CTAS];
+
 // mode 0: grad_out[i] = mean_p staging_p[rank*n + i]  (fp32), sumsq += sum(grad^2) when sumsq != null
 // mode 1: the same mean feeds AdamW directly (grad_out may be null)
 template <int MODE, int WORLD>
@@ -212,7 +217,7 @@ peer_reduce_scatter_kernel(PeerPtrs staging, PeerPtrs flag_bases, size_t ready_r
       ss = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) atomicAdd(sumsq, ss);
+      if (lane == 0) g_rs_sumsq_partials[blockIdx.x] = ss;   // added up in block order by the last CTA (below)
     }
   }
   // last CTA to finish tells every peer that this rank no longer reads their staging for this unit
@@ -224,7 +229,14 @@ peer_reduce_scatter_kernel(PeerPtrs staging, PeerPtrs flag_bases, size_t ready_r
   }
   __syncthreads();
   if (last) {
-    if (threadIdx.x == 0) *counter = 0;
+    if (threadIdx.x == 0) {
+      *counter = 0;
+      if (sumsq != nullptr) {   // fixed summation order: the gradient norm is bitwise reproducible
+        float t = 0.f;
+        for (unsigned b = 0; b < gridDim.x; ++b) t += __ldcg(&g_rs_sumsq_partials[b]);
+        *sumsq += t;
+      }
+    }
     signal_peers(flag_bases, done_row, world, rank, epoch);
   }
 }
@@ -354,7 +366,7 @@ extern "C" int b200_peer_reduce_scatter(const unsigned long long* staging_ptrs, 
   if (mode == 0 && grad_out == nullptr) return -11;
   if (mode == 1 && (master == nullptr || m == nullptr || v == nullptr)) return -11;
   AdamArgs a{master, m, v, (__nv_bfloat16*)mirror, gscale, lr, b1, b2, eps, wd, alpha_t};
-  const int grid = ctas > 0 ? ctas : 96;
+  const int grid = ctas > 0 ? (ctas > RS_MAX_CTAS ? RS_MAX_CTAS : ctas) : 96;
 #define RS_LAUNCH(MODE_, WORLD_)                                                                                  \
   peer_reduce_scatter_kernel<MODE_, WORLD_><<<grid, 512, 0, st>>>(make_ptrs(staging_ptrs, world),                 \
                                                                   make_ptrs(flag_bases, world), ready_row, done_row, \
