@@ -247,7 +247,7 @@ class PeerComm(Communicator):
         self.fallback.all_reduce_sum(flat)      # scalars (norms, counters): plumbing
 
     BOUNCE_BYTES = 64 << 20
-    PEER_BROADCAST = os.environ.get("B200_PEER_BROADCAST", "0") == "1"   # off: NCCL broadcast (init only)
+    PEER_BROADCAST = os.environ.get("B200_PEER_BROADCAST", "1") == "1"   # 0: NCCL broadcast instead (init only)
 
     def broadcast(self, t, src=0):
         """Every rank pulls ``t`` from rank ``src`` through a peer-visible bounce buffer (init-time weights)."""
