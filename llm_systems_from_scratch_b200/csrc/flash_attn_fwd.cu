@@ -295,20 +295,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
       FWD_TRACE(trole, j, 1);
       const int k0 = j * FA_BK;
       const bool diag = (k0 + FA_BK - 1 > q0);   // tile touches the diagonal (warp-uniform)
-      // pass 1: row maximum over the raw scores (the softmax scale is positive, so it is applied afterwards)
+      // pass 1: row maximum over the raw scores (the softmax scale is positive, so it is applied afterwards).
+      // The load of chunk c+1 is in flight while chunk c is reduced.
       float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < FA_BK / 32; ++c) {
-        uint32_t s[32];
-        tmem_ld_32x32(tm_s + c * 32, s);
+      {
+        uint32_t sa[32], sb[32];
+        tmem_ld_32x32(tm_s, sa);
         tmem_ld_wait();
-        if (diag) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k0 + c * 32 + i > q_idx) s[i] = 0xff800000u;   // -inf
+        for (int c = 0; c < FA_BK / 32; ++c) {
+          uint32_t (&cur)[32] = (c & 1) ? sb : sa;
+          uint32_t (&nxt)[32] = (c & 1) ? sa : sb;
+          if (c + 1 < FA_BK / 32) tmem_ld_32x32(tm_s + (c + 1) * 32, nxt);
+          if (diag) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (k0 + c * 32 + i > q_idx) cur[i] = 0xff800000u;   // -inf
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) mx = fmax3(mx, __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]));
+          if (c + 1 < FA_BK / 32) tmem_ld_wait();
         }
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) mx = fmax3(mx, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
       }
       mx *= p.scale_log2;
       FWD_TRACE(trole, j, 2);
@@ -334,30 +341,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FlashFwdParam
       // pass 2: P = exp2(S * scale - m), row sum, bf16 pack; P chunk c (16 packed columns) lands on S columns
       // [16c, 16c+16), all of which this thread has already read.
       float sum = 0.f, sum1 = 0.f;
-#pragma unroll
-      for (int c = 0; c < FA_BK / 32; ++c) {
-        uint32_t s[32], pk[16];
-        tmem_ld_32x32(tm_s + c * 32, s);
+      {
+        uint32_t sa[32], sb[32];
+        tmem_ld_32x32(tm_s, sa);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float x0, x1;
-          fma2(x0, x1, __uint_as_float(s[i]), __uint_as_float(s[i + 1]), p.scale_log2, -m_new);
-          // a fixed share of the exponentials runs on the FMA pipe so that the special-function unit is not the limit
-          float e0 = ((i & 7) < FA_POLY_PER_8) ? fa_exp2_poly(x0) : fa_exp2(x0);
-          float e1 = (((i + 1) & 7) < FA_POLY_PER_8) ? fa_exp2_poly(x1) : fa_exp2(x1);
-          if (diag) {
-            e0 = (k0 + c * 32 + i > q_idx) ? 0.f : e0;
-            e1 = (k0 + c * 32 + i + 1 > q_idx) ? 0.f : e1;
+        for (int c = 0; c < FA_BK / 32; ++c) {
+          uint32_t (&s)[32] = (c & 1) ? sb : sa;
+          uint32_t (&nxt)[32] = (c & 1) ? sa : sb;
+          uint32_t pk[16];
+          if (c + 1 < FA_BK / 32) tmem_ld_32x32(tm_s + (c + 1) * 32, nxt);   // in flight while this chunk is processed
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0, x1;
+            fma2(x0, x1, __uint_as_float(s[i]), __uint_as_float(s[i + 1]), p.scale_log2, -m_new);
+            float e0 = ((i & 7) < FA_POLY_PER_8) ? fa_exp2_poly(x0) : fa_exp2(x0);
+            float e1 = (((i + 1) & 7) < FA_POLY_PER_8) ? fa_exp2_poly(x1) : fa_exp2(x1);
+            if (diag) {
+              e0 = (k0 + c * 32 + i > q_idx) ? 0.f : e0;
+              e1 = (k0 + c * 32 + i + 1 > q_idx) ? 0.f : e1;
+            }
+            add2(sum, sum1, e0, e1);
+            pk[i / 2] = pack_bf16x2(e0, e1);
           }
-          add2(sum, sum1, e0, e1);
-          pk[i / 2] = pack_bf16x2(e0, e1);
-        }
-        tmem_st_32x16(tm_s + c * 16, pk);
-        if (c == 1 || c == 3) {   // publish this half of P
-          tmem_st_wait();
-          tc_fence_before();
-          mbar_arrive(&p_full[2 * x + (c >> 1)]);
+          if (c + 1 < FA_BK / 32) tmem_ld_wait();   // before the store below: wait::ld covers the prefetched chunk
+          tmem_st_32x16(tm_s + c * 16, pk);
+          if (c == 1 || c == 3) {   // publish this half of P
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&p_full[2 * x + (c >> 1)]);
+          }
         }
       }
       l_run = l_run * (need ? alpha : 1.f) + (sum + sum1);
