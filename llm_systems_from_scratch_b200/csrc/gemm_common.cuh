@@ -16,6 +16,9 @@ enum GemmEpilogue : int {
   // Backward of h = silu(gate) * up fused into the GEMM that produces dh = acc (M x N): R holds gate | up
   // (M x 2N, bf16) and C (M x 2N, bf16) receives d(gate) | d(up).
   EPI_SWIGLU_BWD = 4,
+  // Flag or-ed into the epilogue code by the caller (CTA-pair kernel): output columns from N up to the next 16-byte
+  // boundary lie inside the row pitch and may be overwritten with zeros.
+  EPI_PAD_WRITABLE = 0x100,
 };
 
 // Optional all-gather carried by a GEMM launch: while the MMA warps work, two copy warps per CTA pull
@@ -51,6 +54,7 @@ struct GemmParams {
   const void* R;
   long long ldr;
   int epi;
+  int tma_store;       // CTA-pair kernel: the epilogue stages tiles in shared memory and writes them with TMA stores
   int num_m_tiles, num_n_tiles, group_m;
   uint32_t* status;
 };
@@ -144,8 +148,9 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int
           *reinterpret_cast<uint4*>(c + j * 8) = make_uint4(o[0], o[1], o[2], o[3]);
         }
       } else {
-        for (int j = 0; j < ncols; ++j)
-          c[j] = __float2bfloat16(__uint_as_float(acc[j]) + __bfloat162float(r[j]));
+#pragma unroll
+        for (int j = 0; j < 32; ++j)    // static register indices keep the accumulator chunk out of local memory
+          if (j < ncols) c[j] = __float2bfloat16(__uint_as_float(acc[j]) + __bfloat162float(r[j]));
       }
     } else if (vec_ok) {
 #pragma unroll
@@ -157,7 +162,9 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int
         *reinterpret_cast<uint4*>(c + j * 8) = make_uint4(o[0], o[1], o[2], o[3]);
       }
     } else {
-      for (int j = 0; j < ncols; ++j) c[j] = __float2bfloat16(__uint_as_float(acc[j]));
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) c[j] = __float2bfloat16(__uint_as_float(acc[j]));
     }
   } else {
     float* c = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
@@ -168,7 +175,9 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int
         for (int j = 0; j < 8; ++j)
           *reinterpret_cast<uint4*>(c + j * 4) = make_uint4(acc[j * 4], acc[j * 4 + 1], acc[j * 4 + 2], acc[j * 4 + 3]);
       } else {
-        for (int j = 0; j < ncols; ++j) c[j] = __uint_as_float(acc[j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) c[j] = __uint_as_float(acc[j]);
       }
     } else {  // EPI_F32_ACC
       if (vec_ok) {
@@ -182,7 +191,9 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, int row, int
           *reinterpret_cast<float4*>(c + j * 4) = v;
         }
       } else {
-        for (int j = 0; j < ncols; ++j) c[j] += __uint_as_float(acc[j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) c[j] += __uint_as_float(acc[j]);
       }
     }
   }

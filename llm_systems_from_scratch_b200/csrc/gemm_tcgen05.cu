@@ -239,6 +239,23 @@ int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+// Output matrix (bf16 or fp32) for TMA stores: box = (box_cols, box_rows) with box_cols * element size == 128 bytes,
+// 128-byte swizzle.  Boxes that reach past the matrix are clipped by the hardware, so edge tiles need no predication.
+int make_tmap_out_2d(CUtensorMap* tm, bool f32, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                     uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  const uint64_t esz = f32 ? 4 : 2;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * esz};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
 static int g_num_sms = 0;
 static int num_sms() {
   if (g_num_sms == 0) {

@@ -17,6 +17,8 @@ namespace b200 {
 
 int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
                       uint32_t box_rows);
+int make_tmap_out_2d(CUtensorMap* tm, bool f32, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                     uint32_t box_cols, uint32_t box_rows);
 
 constexpr int P_BN = 256;        // tile columns of the pair
 constexpr int P_HALF = 128;      // B rows held by one CTA
@@ -30,8 +32,13 @@ constexpr int P_THREADS = 256;    // TMA warp, MMA warp, 4 epilogue warps, 2 gat
 constexpr int P_A_BYTES = BM * BK * 2;       // 16 KB
 constexpr int P_B_BYTES = P_HALF * BK * 2;   // 16 KB
 constexpr int P_DATA = P_STAGES * (P_A_BYTES + P_B_BYTES);
+// Output staging: every epilogue warp owns two slabs of 32 rows x 128 bytes (128-byte swizzle) that it fills from
+// registers and hands to a TMA store, so global writes are whole 128-byte lines issued by the copy engine.
+constexpr int P_SLAB = 32 * 128;
+constexpr int P_STAGING = 4 * 2 * P_SLAB;   // 32 KB
 constexpr int P_BARS = 2 * P_STAGES + 4;
-constexpr int P_SMEM = P_DATA + P_BARS * 8 + 16 + 1024;
+constexpr int P_SMEM = P_DATA + P_STAGING + P_BARS * 8 + 16 + 1024;
+static_assert(P_SMEM <= 232448, "shared memory budget of one CTA");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -98,12 +105,13 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const GemmParams p) {
+                      const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + P_STAGES * P_A_BYTES;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_DATA);
+  uint8_t* smem_out = smem + P_DATA;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_DATA + P_STAGING);
   uint64_t* empty_bar = full_bar + P_STAGES;
   uint64_t* tmem_full = empty_bar + P_STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -128,6 +136,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     fence_barrier_init();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
+    if (p.tma_store) prefetch_tensormap(&tmC);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_holder, TMEM_COLS);
@@ -287,6 +296,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int quarter = warp & 3;
     uint32_t acc_phase[2] = {0, 0};
     int local = 0;
+    uint32_t out_slab = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
       int m_blk, n_blk;
@@ -332,6 +342,78 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             }
           }
         }
+      } else if (p.tma_store) {
+        // registers -> swizzled slab in shared memory -> TMA store (or TMA add for EPI_F32_ACC).  Row `lane` of the
+        // slab is one 128-byte line; its 16-byte pieces are permuted by (row & 7) as the 128-byte swizzle of the
+        // tensor map expects, which also makes the st.shared.v4 of a quarter warp conflict-free.
+        const int row0 = m_blk * 256 + (int)rank * BM + quarter * 32;
+        const bool out_f32 = p.epi == EPI_F32 || p.epi == EPI_F32_ACC;
+        const int cols_per_chunk = out_f32 ? 32 : 64;
+        const int nchunks = P_BN / cols_per_chunk;
+#pragma unroll 1
+        for (int c = 0; c < nchunks; ++c) {
+          const int col = n0 + c * cols_per_chunk;
+          if (col >= p.N) break;
+          uint32_t o[32];
+          if (out_f32) {
+            tmem_ld_32x32(taddr + c * 32, o);
+            tmem_ld_wait();
+          } else {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(taddr + c * 64, r0);
+            tmem_ld_32x32(taddr + c * 64 + 32, r1);
+            tmem_ld_wait();
+            if (p.rope_cs != nullptr && col < 2 * p.rope_d) {      // N = 3 * rope_d, heads are multiples of 32 columns
+              epilogue_rope(p, row, col, r0);
+              epilogue_rope(p, row, col + 32, r1);
+            }
+            if (p.epi == EPI_BF16_RES && row < p.M) {
+              const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)row * p.ldr + col;
+              if (col + 64 <= p.N && (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.R) & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const uint4 rv = *reinterpret_cast<const uint4*>(rp + j * 8);
+                  const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w};
+                  uint32_t* a = j < 4 ? r0 + j * 8 : r1 + (j - 4) * 8;
+#pragma unroll
+                  for (int t = 0; t < 4; ++t) {
+                    const float2 f = unpack_bf16x2(rr[t]);
+                    a[2 * t] = __float_as_uint(__uint_as_float(a[2 * t]) + f.x);
+                    a[2 * t + 1] = __float_as_uint(__uint_as_float(a[2 * t + 1]) + f.y);
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {      // static register indices; the column test predicates the loads
+                  if (col + j < p.N) r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __bfloat162float(rp[j]));
+                  if (col + 32 + j < p.N) r1[j] = __float_as_uint(__uint_as_float(r1[j]) + __bfloat162float(rp[32 + j]));
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              o[j] = pack_bf16x2(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+              o[16 + j] = pack_bf16x2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+            }
+          }
+          uint8_t* slab = smem_out + ((warp - 2) * 2 + (out_slab & 1)) * P_SLAB;
+          ++out_slab;
+          if (lane == 0) tma_store_wait_read<1>();     // the store that last used this slab has read it
+          __syncwarp();
+          uint8_t* line = slab + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(line + ((j ^ (lane & 7)) << 4)) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < p.M) {
+              if (p.epi == EPI_F32_ACC) tma_reduce_add_2d(&tmC, slab, col, row0);
+              else tma_store_2d(&tmC, slab, col, row0);
+            }
+            tma_store_commit();
+          }
+        }
       } else {
 #pragma unroll 1
         for (int c = 0; c < P_BN / 32; ++c) {
@@ -345,6 +427,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_before();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));   // the leader owns this barrier
     }
+    if (p.tma_store && lane == 0) tma_store_wait<0>();   // shared memory stays valid until the last store has left
   }
 
   __syncwarp();
@@ -363,7 +446,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 }
 
 template <bool A_MN, bool B_MN>
-static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int sms, cudaStream_t stream) {
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, GemmParams p, int sms,
+                       cudaStream_t stream) {
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
@@ -376,13 +460,27 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   int pairs = sms / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<pairs * 2, P_THREADS, P_SMEM, stream>>>(tmA, tmB, p);
+  kern<<<pairs * 2, P_THREADS, P_SMEM, stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace b200
 
 using namespace b200;
+
+#include <stdlib.h>
+#include <string.h>
+// B200_GEMM_TMA_STORE=0 (or b200_gemm_set_tma_store(0)) keeps the direct register stores in every epilogue: the
+// switch exists for A/B measurements and for tests that compare the two epilogues bit for bit.
+static int g_pair_tma_store = []() {
+  const char* e = getenv("B200_GEMM_TMA_STORE");
+  return (e == nullptr || e[0] != '0') ? 1 : 0;
+}();
+extern "C" int b200_gemm_set_tma_store(int on) {
+  const int old = g_pair_tma_store;
+  g_pair_tma_store = on ? 1 : 0;
+  return old;
+}
 
 // Same contract as b200_gemm_bf16 (gemm_tcgen05.cu); tiles are 256 x 256 on CTA pairs.
 static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
@@ -394,6 +492,8 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -10;
+  const bool pad_writable = (epi & EPI_PAD_WRITABLE) != 0;
+  epi &= ~EPI_PAD_WRITABLE;
   if (epi == EPI_BF16_RES && R == nullptr) return -11;
   if (epi == EPI_SWIGLU_BWD &&
       (R == nullptr || (N & 7) || (ldr & 7) || (ldc & 7) || ((reinterpret_cast<uintptr_t>(R) | reinterpret_cast<uintptr_t>(C)) & 15)))
@@ -414,13 +514,31 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
   p.wait_counter = wait_counter; p.wait_value = wait_value;
   p.rope_cs = rope_cs; p.rope_seq = rope_seq; p.rope_d = rope_d; p.rope_dh = rope_dh; p.rope_ctx = rope_ctx;
   p.swiglu_f = swiglu_f; p.H = H; p.ldh = ldh;
+  // TMA-store epilogue: needs a 16-byte aligned output whose row pitch is a multiple of 16 bytes.  A TMA store
+  // clips a box at the matrix edge in whole 16-byte pieces (measured: with N = 1001 bf16 columns it also writes
+  // columns 1001..1007), so a row must end on a 16-byte boundary unless the caller declared the rest of the last
+  // piece writable (EPI_PAD_WRITABLE: it lies inside the row pitch and receives zeros, because B rows beyond N are
+  // zero-filled by the loads).  The SwiGLU epilogues (three outputs per tile) and outputs that do not qualify keep
+  // the direct register stores.
+  CUtensorMap tmC;
+  memset(&tmC, 0, sizeof(tmC));
+  p.tma_store = 0;
+  const bool out_f32 = epi == EPI_F32 || epi == EPI_F32_ACC;
+  const long long esz = out_f32 ? 4 : 2;
+  const long long per16 = 16 / esz;
+  const bool row_end_ok = (N % per16 == 0) || (pad_writable && (N + per16 - 1) / per16 * per16 <= ldc);
+  if (g_pair_tma_store && swiglu_f == 0 && epi != EPI_SWIGLU_BWD && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+      (ldc * esz) % 16 == 0 && row_end_ok && (rope_cs == nullptr || (N == 3 * rope_d && rope_dh % 32 == 0))) {
+    if (make_tmap_out_2d(&tmC, out_f32, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, out_f32 ? 32 : 64, 32) == 0)
+      p.tma_store = 1;
+  }
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (a_mn && b_mn) return launch_pair<true, true>(tmA, tmB, p, sms, stream);
-  if (a_mn) return launch_pair<true, false>(tmA, tmB, p, sms, stream);
-  if (b_mn) return launch_pair<false, true>(tmA, tmB, p, sms, stream);
-  return launch_pair<false, false>(tmA, tmB, p, sms, stream);
+  if (a_mn && b_mn) return launch_pair<true, true>(tmA, tmB, tmC, p, sms, stream);
+  if (a_mn) return launch_pair<true, false>(tmA, tmB, tmC, p, sms, stream);
+  if (b_mn) return launch_pair<false, true>(tmA, tmB, tmC, p, sms, stream);
+  return launch_pair<false, false>(tmA, tmB, tmC, p, sms, stream);
 }
 
 extern "C" int b200_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N, int K,

@@ -278,7 +278,7 @@ class _HeadFn(torch.autograd.Function):
         hn, rstd = ops.rmsnorm_fwd(x, hw.norm, cfg.eps)
         buf = torch.empty((x.shape[0], cfg.vocab_padded), dtype=x.dtype, device=x.device)
         logits = buf[:, :cfg.vocab]
-        ops.gemm(hn, hw.lm, "nt", out=logits)
+        ops.gemm(hn, hw.lm, "nt", out=logits, pad_writable=True)
         ctx.eng = eng
         ctx.saved = (x, rstd, hn)
         return logits
@@ -344,7 +344,7 @@ class _HeadLossFn(torch.autograd.Function):
         for r0 in range(0, m, chunk_rows):
             r1 = min(m, r0 + chunk_rows)
             logits = buf[:r1 - r0, :cfg.vocab]
-            ops.gemm(hn[r0:r1], hw.lm, "nt", out=logits)
+            ops.gemm(hn[r0:r1], hw.lm, "nt", out=logits, pad_writable=True)
             tg = targets[r0:r1]
             # every chunk is normalised by the global count of valid targets, so the parts simply add up
             if need_grad:

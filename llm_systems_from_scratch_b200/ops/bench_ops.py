@@ -62,6 +62,11 @@ def bench_gemm():
         out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
         t = timeit(lambda: native.gemm(a, b, layout, out=out, pair=False))
         t_pair = timeit(lambda: native.gemm(a, b, layout, out=out, pair=True)) if m >= 256 else float("nan")
+        t_direct = float("nan")
+        if m >= 256:        # the same kernel with direct register stores in the epilogue instead of TMA stores
+            prev = native.set_gemm_tma_store(False)
+            t_direct = timeit(lambda: native.gemm(a, b, layout, out=out, pair=True))
+            native.set_gemm_tma_store(prev)
         ref = {"nt": lambda: torch.matmul(a, b.t(), out=out), "nn": lambda: torch.matmul(a, b, out=out),
                "tn": lambda: torch.matmul(a.t(), b, out=out)}[layout]
         t2 = timeit(ref)
@@ -69,7 +74,8 @@ def bench_gemm():
         flops = 2.0 * m * n * k
         print(json.dumps({"op": "gemm", "layout": layout, "m": m, "n": n, "k": k, "ms": round(t, 4),
                           "tflops": round(flops / t / 1e9, 1), "pair_ms": round(t_pair, 4),
-                          "pair_tflops": round(flops / t_pair / 1e9, 1), "cublas_ms": round(t2, 4),
+                          "pair_tflops": round(flops / t_pair / 1e9, 1),
+                          "pair_direct_store_tflops": round(flops / t_direct / 1e9, 1), "cublas_ms": round(t2, 4),
                           "cublas_tflops": round(flops / t2 / 1e9, 1)}), flush=True)
 
 

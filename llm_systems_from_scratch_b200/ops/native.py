@@ -173,6 +173,7 @@ def _rowmajor(t: torch.Tensor, name: str):
 
 # ----------------------------------------------------------------------------- GEMM
 EPI_BF16, EPI_F32, EPI_BF16_RES, EPI_F32_ACC, EPI_SWIGLU_BWD = 0, 1, 2, 3, 4
+EPI_PAD_WRITABLE = 0x100
 
 
 # Problems at least this large (rows of the output) run on CTA pairs (cta_group::2, 256 x 256 tiles).
@@ -195,11 +196,23 @@ def _pair_pays(m: int, n: int, sms: int = 148) -> bool:
     return cost_pair <= cost_single
 
 
+def set_gemm_tma_store(on: bool) -> bool:
+    """Switch the CTA-pair GEMM epilogue between TMA stores from shared memory (default) and direct register
+    stores; returns the previous setting."""
+    lib = load()
+    lib.b200_gemm_set_tma_store.argtypes = [c_int]
+    lib.b200_gemm_set_tma_store.restype = c_int
+    return bool(lib.b200_gemm_set_tma_store(1 if on else 0))
+
+
 def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, bn_hint=0, max_ctas=0,
-         pair=None, gather=None):
+         pair=None, gather=None, pad_writable=False):
     """bf16 tensor-core GEMM (tcgen05).  layout 'nt' | 'nn' | 'tn' as in ``torch_impl.gemm``.
 
-    ``pair`` forces (True) or forbids (False) the CTA-pair kernel; by default large problems use it."""
+    ``pair`` forces (True) or forbids (False) the CTA-pair kernel; by default large problems use it.
+    ``pad_writable``: ``out`` is a column slice of a wider buffer and the columns from N up to the next 16-byte
+    boundary (inside the row pitch) may be overwritten with zeros; this lets a row count that is not a multiple of
+    16 bytes (a vocabulary of 50,257) use the TMA-store epilogue."""
     lib = load()
     _req(a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "gemm inputs must be bf16")
     _rowmajor(a, "a")
@@ -247,6 +260,10 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
     if gather is not None and not gather.done and (gargs is None or not pair):
         gather.run()           # this launch cannot carry it: stand-alone collective
         gargs = None
+    if pair and pad_writable:
+        per16 = 16 // out.element_size()
+        if -(-n // per16) * per16 <= out.stride(0):
+            epi |= EPI_PAD_WRITABLE
     if pair and gargs is not None:
         table, dst, nbytes, world, rank = gargs
         rc = lib.b200_gemm_bf16_pair_gather(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb,

@@ -117,6 +117,64 @@ def test_gemm_cta_pair_kernel(layout, shape):
     _check(out16, _ref(a, b, layout) + res.float(), k)
 
 
+@pytest.mark.parametrize("layout", ["nt", "tn"])
+@pytest.mark.parametrize("shape", [(1024, 1001, 256), (1000, 1336, 520), (2048, 5504, 512), (300, 264, 72)])
+def test_gemm_pair_tma_store_matches_direct_store(layout, shape):
+    """The TMA-store epilogue (tile staged in shared memory) writes exactly what the direct register stores write:
+    bf16, bf16 + residual, fp32 and fp32 accumulate, into a padded output view whose columns beyond N stay untouched."""
+    from llm_systems_from_scratch_b200.ops import native
+    m, n, k = shape
+    a, b = _make(layout, m, n, k, "cuda")
+    ld = -(-n // 8) * 8 + 8
+    res = torch.randn(m, n, device="cuda").bfloat16()
+    outs = {}
+    for tma in (True, False):
+        prev = native.set_gemm_tma_store(tma)
+        try:
+            o16 = torch.full((m, ld), 7.0, device="cuda", dtype=torch.bfloat16)
+            native.gemm(a, b, layout, out=o16[:, :n], pair=True)
+            r16 = torch.full((m, ld), 7.0, device="cuda", dtype=torch.bfloat16)
+            native.gemm(a, b, layout, out=r16[:, :n], residual=res, pair=True)
+            o32 = torch.full((m, ld), 7.0, device="cuda", dtype=torch.float32)
+            native.gemm(a, b, layout, out=o32[:, :n], pair=True)
+            acc = torch.full((m, ld), 3.0, device="cuda", dtype=torch.float32)
+            native.gemm(a, b, layout, out=acc[:, :n], accumulate=True, pair=True)
+            native.gemm(a, b, layout, out=acc[:, :n], accumulate=True, pair=True)
+            native.check_status()
+        finally:
+            native.set_gemm_tma_store(prev)
+        outs[tma] = (o16, r16, o32, acc)
+    ref = _ref(a, b, layout)
+    o16, r16, o32, acc = outs[True]
+    _check(o16[:, :n], ref, k)
+    _check(r16[:, :n], ref + res.float(), k)
+    _check(o32[:, :n], ref, k)
+    _check(acc[:, :n], 2 * ref + 3.0, 4 * k)
+    for t, d in zip(outs[True], outs[False]):
+        assert torch.equal(t[:, :n], d[:, :n])
+        assert (t[:, n:] == (3.0 if t is acc else 7.0)).all()      # padding columns are never written
+
+
+def test_gemm_pair_pad_writable_rows_not_ending_on_16_bytes():
+    """A vocabulary-like N (1001): with ``pad_writable`` the TMA-store epilogue runs and may zero columns up to the
+    next 16-byte boundary, nothing beyond; without it the padding is untouched."""
+    from llm_systems_from_scratch_b200.ops import native
+    m, n, k = 1024, 1001, 256
+    a, b = _make("nt", m, n, k, "cuda")
+    ref = _ref(a, b, "nt")
+    for dtype, edge in ((torch.bfloat16, 1008), (torch.float32, 1004)):
+        buf = torch.full((m, 1024), 7.0, device="cuda", dtype=dtype)
+        native.gemm(a, b, "nt", out=buf[:, :n], pair=True, pad_writable=True)
+        native.check_status()
+        _check(buf[:, :n], ref, k)
+        pad = buf[:, n:edge]
+        assert ((pad == 0) | (pad == 7.0)).all()
+        assert (buf[:, edge:] == 7.0).all()
+        keep = torch.full((m, 1024), 7.0, device="cuda", dtype=dtype)
+        native.gemm(a, b, "nt", out=keep[:, :n], pair=True)
+        assert torch.equal(keep[:, :n], buf[:, :n]) and (keep[:, n:] == 7.0).all()
+
+
 @pytest.mark.parametrize("m,f,k", [(1024, 1408, 512), (2048, 5504, 2048), (1100, 256, 264)])
 def test_gemm_swiglu_epilogue(m, f, k):
     """gate|up projection with SiLU(gate)*up in the epilogue against GEMM followed by the stand-alone kernel."""
