@@ -105,7 +105,8 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+                      const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmH,
+                      const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
@@ -137,6 +138,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
     if (p.tma_store) prefetch_tensormap(&tmC);
+    if (p.tma_store && p.swiglu_f > 0) prefetch_tensormap(&tmH);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_holder, TMEM_COLS);
@@ -312,7 +314,69 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int row = m_blk * 256 + (int)rank * BM + quarter * 32 + lane;
       const int n0 = n_blk * P_BN;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * P_BN;
-      if (p.swiglu_f > 0) {
+      // registers -> swizzled slab in shared memory -> TMA store (or TMA add).  Row `lane` of a slab is one 128-byte
+      // line; its 16-byte pieces are permuted by (row & 7) as the 128-byte swizzle of the tensor maps expects, which
+      // also makes the st.shared.v4 of a quarter warp conflict-free.  A warp alternates between its two slabs and
+      // waits, before refilling one, until the store that last used it has read it.
+      const int row0 = m_blk * 256 + (int)rank * BM + quarter * 32;
+      auto emit = [&](const CUtensorMap* tm, int x, const uint32_t (&o)[32], bool add) {
+        uint8_t* slab = smem_out + ((warp - 2) * 2 + (out_slab & 1)) * P_SLAB;
+        ++out_slab;
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* line = slab + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(line + ((j ^ (lane & 7)) << 4)) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (row0 < p.M) {
+            if (add) tma_reduce_add_2d(tm, slab, x, row0);
+            else tma_store_2d(tm, slab, x, row0);
+          }
+          tma_store_commit();
+        }
+      };
+      if (p.swiglu_f > 0 && p.tma_store) {
+        // accumulator columns [0,128) are gate_j, [128,256) the matching up_j; three outputs per 64 columns
+        const int col = n_blk * P_HALF;
+#pragma unroll 1
+        for (int c = 0; c < P_HALF / 64; ++c) {
+          uint32_t og[32], ou[32];
+          {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(taddr + c * 64, r0);
+            tmem_ld_32x32(taddr + c * 64 + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              og[j] = pack_bf16x2(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+              og[16 + j] = pack_bf16x2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+            }
+          }
+          emit(&tmC, col + c * 64, og, false);
+          {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(taddr + P_HALF + c * 64, r0);
+            tmem_ld_32x32(taddr + P_HALF + c * 64 + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              ou[j] = pack_bf16x2(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+              ou[16 + j] = pack_bf16x2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+            }
+          }
+          emit(&tmC, p.swiglu_f + col + c * 64, ou, false);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            // as the stand-alone kernel: silu on the bf16-rounded gate, times the rounded up (fast division)
+            const float2 gf = unpack_bf16x2(og[j]), uf = unpack_bf16x2(ou[j]);
+            og[j] = pack_bf16x2(__fdividef(gf.x, 1.f + __expf(-gf.x)) * uf.x, __fdividef(gf.y, 1.f + __expf(-gf.y)) * uf.y);
+          }
+          emit(&tmH, col + c * 64, og, false);
+        }
+      } else if (p.swiglu_f > 0) {
         // accumulator columns [0,128) are gate_j, [128,256) the matching up_j
         const int col = n_blk * P_HALF;
 #pragma unroll 1
@@ -343,10 +407,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
         }
       } else if (p.tma_store) {
-        // registers -> swizzled slab in shared memory -> TMA store (or TMA add for EPI_F32_ACC).  Row `lane` of the
-        // slab is one 128-byte line; its 16-byte pieces are permuted by (row & 7) as the 128-byte swizzle of the
-        // tensor map expects, which also makes the st.shared.v4 of a quarter warp conflict-free.
-        const int row0 = m_blk * 256 + (int)rank * BM + quarter * 32;
         const bool out_f32 = p.epi == EPI_F32 || p.epi == EPI_F32_ACC;
         const int cols_per_chunk = out_f32 ? 32 : 64;
         const int nchunks = P_BN / cols_per_chunk;
@@ -396,23 +456,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
               o[16 + j] = pack_bf16x2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
             }
           }
-          uint8_t* slab = smem_out + ((warp - 2) * 2 + (out_slab & 1)) * P_SLAB;
-          ++out_slab;
-          if (lane == 0) tma_store_wait_read<1>();     // the store that last used this slab has read it
-          __syncwarp();
-          uint8_t* line = slab + lane * 128;
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(line + ((j ^ (lane & 7)) << 4)) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (row0 < p.M) {
-              if (p.epi == EPI_F32_ACC) tma_reduce_add_2d(&tmC, slab, col, row0);
-              else tma_store_2d(&tmC, slab, col, row0);
-            }
-            tma_store_commit();
-          }
+          emit(&tmC, col, o, p.epi == EPI_F32_ACC);
         }
       } else {
 #pragma unroll 1
@@ -446,8 +490,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 }
 
 template <bool A_MN, bool B_MN>
-static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, GemmParams p, int sms,
-                       cudaStream_t stream) {
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmH,
+                       GemmParams p, int sms, cudaStream_t stream) {
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
@@ -460,7 +504,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   int pairs = sms / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<pairs * 2, P_THREADS, P_SMEM, stream>>>(tmA, tmB, tmC, p);
+  kern<<<pairs * 2, P_THREADS, P_SMEM, stream>>>(tmA, tmB, tmC, tmH, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -520,14 +564,21 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
   // piece writable (EPI_PAD_WRITABLE: it lies inside the row pitch and receives zeros, because B rows beyond N are
   // zero-filled by the loads).  The SwiGLU epilogues (three outputs per tile) and outputs that do not qualify keep
   // the direct register stores.
-  CUtensorMap tmC;
+  CUtensorMap tmC, tmH;
   memset(&tmC, 0, sizeof(tmC));
+  memset(&tmH, 0, sizeof(tmH));
   p.tma_store = 0;
   const bool out_f32 = epi == EPI_F32 || epi == EPI_F32_ACC;
   const long long esz = out_f32 ? 4 : 2;
   const long long per16 = 16 / esz;
   const bool row_end_ok = (N % per16 == 0) || (pad_writable && (N + per16 - 1) / per16 * per16 <= ldc);
-  if (g_pair_tma_store && swiglu_f == 0 && epi != EPI_SWIGLU_BWD && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+  if (g_pair_tma_store && swiglu_f > 0) {
+    // gate | up (M x 2F) and h (M x F): F is a multiple of 128, so no 64-column box straddles the gate / up border
+    if ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (reinterpret_cast<uintptr_t>(H) & 15) == 0 && (ldc & 7) == 0 &&
+        (ldh & 7) == 0 && make_tmap_out_2d(&tmC, false, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, 64, 32) == 0 &&
+        make_tmap_out_2d(&tmH, false, H, (uint64_t)M, (uint64_t)swiglu_f, (uint64_t)ldh, 64, 32) == 0)
+      p.tma_store = 1;
+  } else if (g_pair_tma_store && swiglu_f == 0 && epi != EPI_SWIGLU_BWD && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
       (ldc * esz) % 16 == 0 && row_end_ok && (rope_cs == nullptr || (N == 3 * rope_d && rope_dh % 32 == 0))) {
     if (make_tmap_out_2d(&tmC, out_f32, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, out_f32 ? 32 : 64, 32) == 0)
       p.tma_store = 1;
@@ -535,10 +586,10 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (a_mn && b_mn) return launch_pair<true, true>(tmA, tmB, tmC, p, sms, stream);
-  if (a_mn) return launch_pair<true, false>(tmA, tmB, tmC, p, sms, stream);
-  if (b_mn) return launch_pair<false, true>(tmA, tmB, tmC, p, sms, stream);
-  return launch_pair<false, false>(tmA, tmB, tmC, p, sms, stream);
+  if (a_mn && b_mn) return launch_pair<true, true>(tmA, tmB, tmC, tmH, p, sms, stream);
+  if (a_mn) return launch_pair<true, false>(tmA, tmB, tmC, tmH, p, sms, stream);
+  if (b_mn) return launch_pair<false, true>(tmA, tmB, tmC, tmH, p, sms, stream);
+  return launch_pair<false, false>(tmA, tmB, tmC, tmH, p, sms, stream);
 }
 
 extern "C" int b200_gemm_bf16_pair(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
