@@ -17,52 +17,19 @@
 // wait is bounded: when the limit runs out the kernel records ERR_WAIT_FLAG in the status word and
 // returns without touching the data, leaving the context usable.  Loads from peers are plain
 // vector loads (no TMA, no multicast).
-#include "ptx.cuh"
+#include "comm_device.cuh"
 #include <string.h>
 
 namespace b200 {
 
-constexpr int MAX_WORLD = 16;
-
-struct PeerPtrs {
-  void* p[MAX_WORLD];
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
-  return v;
-}
-
-// Wait until flags[i] >= epoch for every i < world (wrap-safe comparison).  One thread polls each flag.
-// Returns false when the time limit ran out.
+// Block-wide forms of the flag helpers (all threads of the CTA call them).
 __device__ __forceinline__ bool wait_flags(const uint32_t* flags, int world, uint32_t epoch, uint64_t limit_ns) {
-  bool ok = true;
-  if (threadIdx.x < world) {
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t spins = 0;
-    while ((int32_t)(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
-      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > limit_ns) {
-        ok = false;
-        break;
-      }
-      __nanosleep(64);
-    }
-  }
+  const bool ok = poll_flag(flags, world, epoch, limit_ns, threadIdx.x);
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
-
-// rank `rank` announces `epoch` in slot row `flag_row` (an array of `world` words) on every peer.
 __device__ __forceinline__ void signal_peers(const PeerPtrs& flag_bases, size_t row_offset, int world, int rank,
                                              uint32_t epoch) {
-  if (threadIdx.x < world) {
-    __threadfence_system();
-    uint32_t* dst = reinterpret_cast<uint32_t*>(flag_bases.p[threadIdx.x]) + row_offset + rank;
-    st_release_sys(dst, epoch);
-  }
+  signal_row(flag_bases, row_offset, world, rank, epoch, threadIdx.x);
 }
 
 __global__ void peer_barrier_kernel(PeerPtrs flag_bases, size_t row_offset, int world, int rank, uint32_t epoch,
@@ -121,124 +88,21 @@ __global__ void peer_allgather_kernel(PeerPtrs src, uint4* __restrict__ dst, siz
              (size_t)gridDim.x * blockDim.x);
 }
 
-struct AdamArgs {
-  float* master;
-  float* m;
-  float* v;
-  __nv_bfloat16* mirror;
-  const float* gscale;   // device clip coefficient or null
-  float lr, b1, b2, eps, wd, alpha_t;
-};
-
-// Per-CTA partial sums of squares of one reduce-scatter launch.  Launches that share the array must be ordered on
-// one stream (FSDP issues all of them on its communication stream).
+// Per-group partial sums of squares of one reduce-scatter launch.  Launches that share an array must be ordered
+// on one stream: stand-alone launches (FSDP issues them on its communication stream) use the first array,
+// reduce-scatters carried by a GEMM (compute stream) the second.
 constexpr int RS_MAX_CTAS = 1024;
-__device__ float g_rs_sumsq_partials[RS_MAX_CTAS];
+__device__ float g_rs_sumsq_partials[2][RS_MAX_CTAS];
 
-// mode 0: grad_out[i] = mean_p staging_p[rank*n + i]  (fp32), sumsq += sum(grad^2) when sumsq != null
-// mode 1: the same mean feeds AdamW directly (grad_out may be null)
-template <int MODE, int WORLD>
-__global__ void __launch_bounds__(512)
-peer_reduce_scatter_kernel(PeerPtrs staging, PeerPtrs flag_bases, size_t ready_row, size_t done_row, float* grad_out,
-                           float* sumsq, AdamArgs adam, size_t n, int world, int rank, uint32_t epoch,
-                           uint64_t limit_ns, uint32_t* counter, uint32_t* status) {
-  __shared__ float red[32];
-  // "my staging for this unit is complete" (this kernel is stream-ordered after the unit's backward)
-  if (blockIdx.x == 0) signal_peers(flag_bases, ready_row, world, rank, epoch);
-  const uint32_t* ready = reinterpret_cast<const uint32_t*>(flag_bases.p[rank]) + ready_row;
-  if (!wait_flags(ready, world, epoch, limit_ns)) {
-    if (threadIdx.x == 0 && status) atomicCAS(status, 0u, ERR_WAIT_FLAG | (1u << 8));
-    return;
-  }
-  const float inv = 1.f / (float)world;
-  const float gs = (MODE == 1 && adam.gscale) ? *adam.gscale : 1.f;
-  const size_t n_vec = n / 8;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  float ss = 0.f;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_vec; i += stride) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    uint4 in[WORLD > 0 ? WORLD : 1];
-    if (WORLD > 0) {                    // all peer loads are issued before the first one is consumed
-#pragma unroll
-      for (int p = 0; p < WORLD; ++p) in[p] = reinterpret_cast<const uint4*>(staging.p[p])[(size_t)rank * n_vec + i];
-    }
-#pragma unroll
-    for (int p = 0; p < (WORLD > 0 ? WORLD : world); ++p) {   // fixed order: bitwise reproducible
-      const uint4 u = WORLD > 0 ? in[p] : reinterpret_cast<const uint4*>(staging.p[p])[(size_t)rank * n_vec + i];
-      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
-      acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
-    }
-#pragma unroll
-    for (int k = 0; k < 8; ++k) acc[k] *= inv;
-    if (MODE == 0) {
-      float4* g = reinterpret_cast<float4*>(grad_out) + 2 * i;
-      g[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      g[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) ss += acc[k] * acc[k];
-    } else {
-      float4* pm = reinterpret_cast<float4*>(adam.master) + 2 * i;
-      float4* mm = reinterpret_cast<float4*>(adam.m) + 2 * i;
-      float4* vv = reinterpret_cast<float4*>(adam.v) + 2 * i;
-      float pw[8], mw[8], vw[8];
-      *reinterpret_cast<float4*>(pw) = pm[0]; *reinterpret_cast<float4*>(pw + 4) = pm[1];
-      *reinterpret_cast<float4*>(mw) = mm[0]; *reinterpret_cast<float4*>(mw + 4) = mm[1];
-      *reinterpret_cast<float4*>(vw) = vv[0]; *reinterpret_cast<float4*>(vw + 4) = vv[1];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const float g = acc[k] * gs;
-        mw[k] = adam.b1 * mw[k] + (1.f - adam.b1) * g;
-        vw[k] = adam.b2 * vw[k] + (1.f - adam.b2) * g * g;
-        pw[k] -= adam.alpha_t * mw[k] / (sqrtf(vw[k]) + adam.eps);
-        pw[k] -= adam.lr * adam.wd * pw[k];
-        ss += acc[k] * acc[k];
-      }
-      pm[0] = *reinterpret_cast<float4*>(pw); pm[1] = *reinterpret_cast<float4*>(pw + 4);
-      mm[0] = *reinterpret_cast<float4*>(mw); mm[1] = *reinterpret_cast<float4*>(mw + 4);
-      vv[0] = *reinterpret_cast<float4*>(vw); vv[1] = *reinterpret_cast<float4*>(vw + 4);
-      if (adam.mirror)
-        reinterpret_cast<uint4*>(adam.mirror)[i] = make_uint4(pack_bf16x2(pw[0], pw[1]), pack_bf16x2(pw[2], pw[3]),
-                                                             pack_bf16x2(pw[4], pw[5]), pack_bf16x2(pw[6], pw[7]));
-      if (grad_out) {
-        float4* g = reinterpret_cast<float4*>(grad_out) + 2 * i;
-        g[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        g[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-      }
-    }
-  }
-  if (sumsq != nullptr) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    if (warp == 0) {
-      ss = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) g_rs_sumsq_partials[blockIdx.x] = ss;   // added up in block order by the last CTA (below)
-    }
-  }
-  // last CTA to finish tells every peer that this rank no longer reads their staging for this unit
-  __syncthreads();
-  __shared__ uint32_t last;
-  if (threadIdx.x == 0) {
-    __threadfence();
-    last = (atomicAdd(counter, 1u) == gridDim.x - 1) ? 1u : 0u;
-  }
-  __syncthreads();
-  if (last) {
-    if (threadIdx.x == 0) {
-      *counter = 0;
-      if (sumsq != nullptr) {   // fixed summation order: the gradient norm is bitwise reproducible
-        float t = 0.f;
-        for (unsigned b = 0; b < gridDim.x; ++b) t += __ldcg(&g_rs_sumsq_partials[b]);
-        *sumsq += t;
-      }
-    }
-    signal_peers(flag_bases, done_row, world, rank, epoch);
-  }
+template <int MODE>
+__global__ void __launch_bounds__(512) peer_reduce_scatter_kernel(const ReduceTask t) {
+  __shared__ ReduceSmem sm;
+  reduce_scatter_any<MODE>(t, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x, 1, &sm);
+}
+
+// Rank `rank` publishes `epoch` in one flag row on every peer and returns (no wait).
+__global__ void peer_signal_kernel(PeerPtrs flag_bases, size_t row_offset, int world, int rank, uint32_t epoch) {
+  signal_peers(flag_bases, row_offset, world, rank, epoch);
 }
 
 // Wait for a row of flags (used before a staging buffer is overwritten).
@@ -253,11 +117,11 @@ peer_allreduce_kernel(PeerPtrs bufs, PeerPtrs flag_bases, size_t ready_row, size
                       int rank, uint32_t epoch, uint64_t limit_ns, uint32_t* counter, uint32_t* status) {
   if (blockIdx.x == 0) signal_peers(flag_bases, ready_row, world, rank, epoch);
   const uint32_t* ready = reinterpret_cast<const uint32_t*>(flag_bases.p[rank]) + ready_row;
-  if (!wait_flags(ready, world, epoch, limit_ns)) {
-    if (threadIdx.x == 0 && status) atomicCAS(status, 0u, ERR_WAIT_FLAG | (3u << 8));
-    return;
-  }
-  const size_t n_vec = n / 4;
+  // A CTA whose wait ran out reports, skips the data and still takes part in the CTA count below, so that the
+  // counter is back at zero for the next launch.
+  const bool ok = wait_flags(ready, world, epoch, limit_ns);
+  if (!ok && threadIdx.x == 0 && status) atomicCAS(status, 0u, ERR_WAIT_FLAG | (3u << 8));
+  const size_t n_vec = ok ? n / 4 : 0;
   const size_t chunk = (n_vec + world - 1) / world;
   const size_t lo = (size_t)rank * chunk;
   const size_t hi = lo + chunk < n_vec ? lo + chunk : n_vec;
@@ -354,34 +218,48 @@ extern "C" int b200_peer_allgather(const unsigned long long* src_ptrs, void* dst
   COMM_CHECK();
 }
 
-// mode 0: reduce into grad_out (+ sumsq).  mode 1: fused AdamW on master/m/v/mirror (grad_out, sumsq optional).
-extern "C" int b200_peer_reduce_scatter(const unsigned long long* staging_ptrs, const unsigned long long* flag_bases,
-                                        unsigned long long ready_row, unsigned long long done_row, float* grad_out,
-                                        float* sumsq, unsigned long long n, int world, int rank, unsigned int epoch,
-                                        int mode, float* master, float* m, float* v, void* mirror, const float* gscale,
-                                        float lr, float b1, float b2, float eps, float wd, float alpha_t,
-                                        unsigned long long limit_ns, uint32_t* counter, uint32_t* status, int ctas,
-                                        cudaStream_t st) {
-  if (world > MAX_WORLD || n % 8) return -10;
-  if (mode == 0 && grad_out == nullptr) return -11;
-  if (mode == 1 && (master == nullptr || m == nullptr || v == nullptr)) return -11;
-  AdamArgs a{master, m, v, (__nv_bfloat16*)mirror, gscale, lr, b1, b2, eps, wd, alpha_t};
+float* b200_rs_partials(int which) {
+  float* p = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rs_sumsq_partials) != cudaSuccess) return nullptr;
+  return p + (which ? RS_MAX_CTAS : 0);
+}
+
+extern "C" int b200_peer_signal(const unsigned long long* flag_bases, unsigned long long row_offset, int world,
+                                int rank, unsigned int epoch, cudaStream_t st) {
+  if (world > MAX_WORLD) return -10;
+  peer_signal_kernel<<<1, 32, 0, st>>>(make_ptrs(flag_bases, world), row_offset, world, rank, epoch);
+  COMM_CHECK();
+}
+
+// Validates a description and turns it into the device-side task.  `carried`: the task will run on the copy warps
+// of a GEMM (it then uses the second array of partial sums).
+int b200_make_reduce_task(const B200ReduceDesc* d, uint32_t* status, bool carried, ReduceTask* out) {
+  if (d->world > MAX_WORLD || d->world < 1 || d->n % 8 || d->counter == nullptr) return -10;
+  if (d->mode == 0 && d->grad_out == nullptr) return -11;
+  if (d->mode == 1 && (d->master == nullptr || d->m == nullptr || d->v == nullptr)) return -11;
+  ReduceTask t;
+  t.staging = make_ptrs(d->staging, d->world);
+  t.flag_bases = make_ptrs(d->flag_bases, d->world);
+  t.ready_row = d->ready_row; t.done_row = d->done_row;
+  t.grad_out = d->grad_out; t.sumsq = d->sumsq;
+  t.adam = AdamArgs{d->master, d->m, d->v, (__nv_bfloat16*)d->mirror, d->gscale, d->lr, d->b1, d->b2, d->eps, d->wd,
+                    d->alpha_t};
+  t.n = d->n; t.world = d->world; t.rank = d->rank; t.mode = d->mode; t.epoch = d->epoch;
+  t.limit_ns = d->limit_ns; t.counter = d->counter; t.status = status;
+  t.partials = b200_rs_partials(carried ? 1 : 0);
+  if (t.partials == nullptr) return -12;
+  *out = t;
+  return 0;
+}
+
+// Stand-alone launch.  mode 0: reduce into grad_out (+ sumsq).  mode 1: fused AdamW on master/m/v/mirror.
+extern "C" int b200_peer_reduce_scatter_desc(const B200ReduceDesc* d, uint32_t* status, int ctas, cudaStream_t st) {
+  ReduceTask t;
+  const int rc = b200_make_reduce_task(d, status, false, &t);
+  if (rc) return rc;
   const int grid = ctas > 0 ? (ctas > RS_MAX_CTAS ? RS_MAX_CTAS : ctas) : 96;
-#define RS_LAUNCH(MODE_, WORLD_)                                                                                  \
-  peer_reduce_scatter_kernel<MODE_, WORLD_><<<grid, 512, 0, st>>>(make_ptrs(staging_ptrs, world),                 \
-                                                                  make_ptrs(flag_bases, world), ready_row, done_row, \
-                                                                  grad_out, sumsq, a, n, world, rank, epoch, limit_ns, \
-                                                                  counter, status)
-#define RS_WORLD(MODE_)                        \
-  switch (world) {                             \
-    case 2: RS_LAUNCH(MODE_, 2); break;        \
-    case 4: RS_LAUNCH(MODE_, 4); break;        \
-    case 8: RS_LAUNCH(MODE_, 8); break;        \
-    default: RS_LAUNCH(MODE_, 0); break;       \
-  }
-  if (mode == 0) { RS_WORLD(0) } else { RS_WORLD(1) }
-#undef RS_WORLD
-#undef RS_LAUNCH
+  if (d->mode == 0) peer_reduce_scatter_kernel<0><<<grid, 512, 0, st>>>(t);
+  else peer_reduce_scatter_kernel<1><<<grid, 512, 0, st>>>(t);
   COMM_CHECK();
 }
 

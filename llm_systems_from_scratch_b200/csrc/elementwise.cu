@@ -295,10 +295,12 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ tokens, const
 // Deterministic variant: `order` lists the token rows sorted by token id (stable), `sorted_tokens` the ids in that
 // order.  The warp at the first position of every run of equal ids adds the run's dx rows in order in fp32
 // registers and writes (or accumulates into) the table row once: no atomics, bitwise reproducible.
-template <int CHUNKS>   // 256-column chunks per launch: columns [col0, col0 + 256 * CHUNKS) of every row
+// OUT = float: the fp32 gradient table; OUT = __nv_bfloat16: a bf16 staging table (multi-GPU gradient staging),
+// written once per row from the fp32 sum of the run (accumulate is not offered there).
+template <int CHUNKS, typename OUT>   // 256-column chunks per launch: columns [col0, col0 + 256 * CHUNKS) of every row
 __global__ void embedding_bwd_sorted_kernel(const long long* __restrict__ sorted_tokens,
                                             const long long* __restrict__ order,
-                                            const __nv_bfloat16* __restrict__ dx, float* __restrict__ grad_table,
+                                            const __nv_bfloat16* __restrict__ dx, OUT* __restrict__ grad_table,
                                             long long rows, int d, int vocab, int accumulate, int col0) {
   const int lane = threadIdx.x & 31;
   const long long j0 = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -324,11 +326,16 @@ __global__ void embedding_bwd_sorted_kernel(const long long* __restrict__ sorted
       }
     }
   }
-  float* dst = grad_table + (size_t)t * d;
+  OUT* dst = grad_table + (size_t)t * d;
 #pragma unroll
   for (int k = 0; k < CHUNKS; ++k) {
     const int c = col0 + lane * 8 + k * 256;
     if (c < d) {
+      if constexpr (sizeof(OUT) == 2) {
+        *reinterpret_cast<uint4*>(dst + c) = make_uint4(pack_bf16x2(acc[k][0], acc[k][1]), pack_bf16x2(acc[k][2], acc[k][3]),
+                                                        pack_bf16x2(acc[k][4], acc[k][5]), pack_bf16x2(acc[k][6], acc[k][7]));
+        continue;
+      }
       float4* o = reinterpret_cast<float4*>(dst + c);
       float4 a = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
       float4 b = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
@@ -701,12 +708,30 @@ extern "C" int b200_embedding_bwd_sorted(const long long* sorted_tokens, const l
   if (rows == 0) return 0;
   const unsigned grid = (unsigned)((rows + 7) / 8);
 #define EMB_LAUNCH(C_, COL0_)                                                                                    \
-  embedding_bwd_sorted_kernel<C_><<<grid, 256, 0, st>>>(sorted_tokens, order, (const __nv_bfloat16*)dx, grad_table, \
-                                                       rows, d, vocab, accumulate, COL0_)
+  embedding_bwd_sorted_kernel<C_, float><<<grid, 256, 0, st>>>(sorted_tokens, order, (const __nv_bfloat16*)dx,        \
+                                                              grad_table, rows, d, vocab, accumulate, COL0_)
   if (d <= 1024) EMB_LAUNCH(4, 0);
   else if (d <= 2048) EMB_LAUNCH(8, 0);
   else
     for (int col0 = 0; col0 < d; col0 += 4096) EMB_LAUNCH(16, col0);   // wide rows: one launch per 4096 columns
+#undef EMB_LAUNCH
+  CHECK_LAUNCH();
+}
+
+// The same with a bf16 table (gradient staging that a reduce-scatter reads): rows of tokens that occur are
+// overwritten with the rounded fp32 sum of their run; the caller zeroes the table first.
+extern "C" int b200_embedding_bwd_sorted_bf16(const long long* sorted_tokens, const long long* order, const void* dx,
+                                              void* grad_table, long long rows, int d, int vocab, cudaStream_t st) {
+  if (d % 8 || !ALIGNED16(dx) || !ALIGNED16(grad_table)) return -10;
+  if (rows == 0) return 0;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+#define EMB_LAUNCH(C_, COL0_)                                                                                          \
+  embedding_bwd_sorted_kernel<C_, __nv_bfloat16><<<grid, 256, 0, st>>>(sorted_tokens, order, (const __nv_bfloat16*)dx, \
+                                                                      (__nv_bfloat16*)grad_table, rows, d, vocab, 0, COL0_)
+  if (d <= 1024) EMB_LAUNCH(4, 0);
+  else if (d <= 2048) EMB_LAUNCH(8, 0);
+  else
+    for (int col0 = 0; col0 < d; col0 += 4096) EMB_LAUNCH(16, col0);
 #undef EMB_LAUNCH
   CHECK_LAUNCH();
 }

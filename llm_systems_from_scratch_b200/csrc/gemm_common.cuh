@@ -1,5 +1,6 @@
 // Shared pieces of the tcgen05 GEMM kernels: problem description, tile order and the fused epilogue.
 #pragma once
+#include "comm_device.cuh"
 #include "ptx.cuh"
 
 namespace b200 {
@@ -35,6 +36,9 @@ struct GatherTask {
 
 struct GemmParams {
   GatherTask gather;
+  // Optional reduce-scatter (+ scale + sum of squares, or + AdamW) of an earlier FSDP unit's gradient staging, run
+  // by the same copy warps after the gather (CTA-pair kernel only); reduce.n == 0 = none.
+  ReduceTask reduce;
   const uint32_t* wait_counter;  // optional: do not touch operand B before *wait_counter >= wait_value
   uint32_t wait_value;
   // Optional rotary embedding fused into the epilogue of the QKV projection: output columns [0, 2*rope_d)

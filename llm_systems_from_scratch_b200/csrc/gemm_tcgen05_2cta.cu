@@ -37,7 +37,7 @@ constexpr int P_DATA = P_STAGES * (P_A_BYTES + P_B_BYTES);
 constexpr int P_SLAB = 32 * 128;
 constexpr int P_STAGING = 4 * 2 * P_SLAB;   // 32 KB
 constexpr int P_BARS = 2 * P_STAGES + 4;
-constexpr int P_SMEM = P_DATA + P_STAGING + P_BARS * 8 + 16 + 1024;
+constexpr int P_SMEM = P_DATA + P_STAGING + P_BARS * 8 + 16 + 160 + 1024;   // 160: ReduceSmem of the copy warps
 static_assert(P_SMEM <= 232448, "shared memory budget of one CTA");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -118,6 +118,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile uint32_t* abort_word = tmem_holder + 1;
+  ReduceSmem* reduce_smem = reinterpret_cast<ReduceSmem*>(tmem_holder + 4);
+  static_assert(sizeof(ReduceSmem) <= 144, "ReduceSmem must fit the space reserved behind the barriers");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -138,7 +140,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
     if (p.tma_store) prefetch_tensormap(&tmC);
-    if (p.tma_store && p.swiglu_f > 0) prefetch_tensormap(&tmH);
+    if (p.tma_store && (p.swiglu_f > 0 || p.epi == EPI_SWIGLU_BWD)) prefetch_tensormap(&tmH);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_holder, TMEM_COLS);
@@ -294,6 +296,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         atomicAdd(g.done, 1u);
       }
     }
+    // ---------------------------------------------------------------- carried reduce-scatter
+    // The gradient staging of an earlier unit is reduced over all peers (and optionally fed to AdamW) by the same
+    // 64 threads of every CTA while the tensor cores of this kernel keep working.
+    if (p.reduce.n > 0) {
+      const int t = (warp - 6) * 32 + lane;
+      if (p.reduce.mode == 0) reduce_scatter_any<0>(p.reduce, t, 64, blockIdx.x, gridDim.x, 3, reduce_smem);
+      else reduce_scatter_any<1>(p.reduce, t, 64, blockIdx.x, gridDim.x, 3, reduce_smem);
+    }
   } else {
     const int quarter = warp & 3;
     uint32_t acc_phase[2] = {0, 0};
@@ -406,6 +416,75 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             }
           }
         }
+      } else if (p.tma_store && p.epi == EPI_SWIGLU_BWD) {
+        // acc = dh (this row, 256 columns); R holds gate | up; d(gate) goes out through tmC, d(up) through tmH.
+        // The gate / up pieces of the next 32 columns are fetched while the current 32 are computed, so that the
+        // row-strided loads are off the critical path; two 32-column halves fill one 64-column slab per output.
+        const __nv_bfloat16* grow = reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)row * p.ldr;
+        uint8_t* slab_g = smem_out + (warp - 2) * 2 * P_SLAB;
+        uint8_t* slab_u = slab_g + P_SLAB;
+        const bool row_ok = row < p.M;
+        uint4 gq[4], uq[4];
+        auto load_gu = [&](int col, uint4 (&g)[4], uint4 (&u)[4]) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const bool in = row_ok && col + j * 8 < p.N;     // N is a multiple of 8
+            g[j] = in ? __ldg(reinterpret_cast<const uint4*>(grow + col + j * 8)) : make_uint4(0, 0, 0, 0);
+            u[j] = in ? __ldg(reinterpret_cast<const uint4*>(grow + p.N + col + j * 8)) : make_uint4(0, 0, 0, 0);
+          }
+        };
+        load_gu(n0, gq, uq);
+#pragma unroll
+        for (int h = 0; h < P_BN / 32; ++h) {
+          const int col = n0 + h * 32;
+          if (col >= p.N) break;
+          uint4 gn[4], un[4];
+          if (h + 1 < P_BN / 32) load_gu(col + 32, gn, un);
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + h * 32, r);
+          tmem_ld_wait();
+          if ((h & 1) == 0) {
+            if (lane == 0) tma_store_wait_read<0>();      // both slabs have been read by the previous stores
+            __syncwarp();
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t gg[4] = {gq[j].x, gq[j].y, gq[j].z, gq[j].w}, uu[4] = {uq[j].x, uq[j].y, uq[j].z, uq[j].w};
+            uint32_t og[4], ou[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              // as the stand-alone kernel: dh is rounded to bf16 first, gate and up are read as bf16
+              const float2 g = unpack_bf16x2(gg[t]), u = unpack_bf16x2(uu[t]);
+              const float2 d = unpack_bf16x2(pack_bf16x2(__uint_as_float(r[j * 8 + 2 * t]), __uint_as_float(r[j * 8 + 2 * t + 1])));
+              const float s0 = __fdividef(1.f, 1.f + __expf(-g.x)), s1 = __fdividef(1.f, 1.f + __expf(-g.y));
+              const float l0 = g.x * s0, l1 = g.y * s1;
+              og[t] = pack_bf16x2(d.x * u.x * (s0 + l0 * (1.f - s0)), d.y * u.y * (s1 + l1 * (1.f - s1)));
+              ou[t] = pack_bf16x2(d.x * l0, d.y * l1);
+            }
+            const int piece = (((h & 1) * 4 + j) ^ (lane & 7)) << 4;
+            *reinterpret_cast<uint4*>(slab_g + lane * 128 + piece) = make_uint4(og[0], og[1], og[2], og[3]);
+            *reinterpret_cast<uint4*>(slab_u + lane * 128 + piece) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+          }
+          if ((h & 1) == 1 || col + 32 >= p.N) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (row0 < p.M) {
+                tma_store_2d(&tmC, slab_g, n0 + (h >> 1) * 64, row0);
+                tma_store_2d(&tmH, slab_u, n0 + (h >> 1) * 64, row0);
+              }
+              tma_store_commit();
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            gq[j] = gn[j];
+            uq[j] = un[j];
+          }
+        }
+        out_slab = 0;     // both slabs are in flight: the next emit() must wait for them (it waits for all but one)
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
       } else if (p.tma_store) {
         const bool out_f32 = p.epi == EPI_F32 || p.epi == EPI_F32_ACC;
         const int cols_per_chunk = out_f32 ? 32 : 64;
@@ -532,7 +611,7 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
                           const GatherTask* gather, const uint32_t* wait_counter, uint32_t wait_value,
                           uint32_t* status, cudaStream_t stream, const float* rope_cs = nullptr, int rope_seq = 0,
                           int rope_d = 0, int rope_dh = 0, int rope_ctx = 0, int swiglu_f = 0, void* H = nullptr,
-                          long long ldh = 0) {
+                          long long ldh = 0, const ReduceTask* reduce = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -10;
@@ -555,6 +634,8 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
   p.num_m_tiles = p.num_n_tiles = p.group_m = 0;
   if (gather != nullptr) p.gather = *gather;
   else { p.gather.dst = nullptr; p.gather.done = nullptr; p.gather.shard_vec = 0; p.gather.world = 0; p.gather.rank = 0; }
+  if (reduce != nullptr) p.reduce = *reduce;
+  else p.reduce.n = 0;
   p.wait_counter = wait_counter; p.wait_value = wait_value;
   p.rope_cs = rope_cs; p.rope_seq = rope_seq; p.rope_d = rope_d; p.rope_dh = rope_dh; p.rope_ctx = rope_ctx;
   p.swiglu_f = swiglu_f; p.H = H; p.ldh = ldh;
@@ -578,7 +659,14 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
         (ldh & 7) == 0 && make_tmap_out_2d(&tmC, false, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, 64, 32) == 0 &&
         make_tmap_out_2d(&tmH, false, H, (uint64_t)M, (uint64_t)swiglu_f, (uint64_t)ldh, 64, 32) == 0)
       p.tma_store = 1;
-  } else if (g_pair_tma_store && swiglu_f == 0 && epi != EPI_SWIGLU_BWD && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+  } else if (g_pair_tma_store && epi == EPI_SWIGLU_BWD) {
+    // d(gate) and d(up) are the two halves of C (M x 2N); one map each, so that a box at the right edge of the gate
+    // half is clipped instead of running into the up half
+    const __nv_bfloat16* cu = reinterpret_cast<const __nv_bfloat16*>(C) + N;
+    if (make_tmap_out_2d(&tmC, false, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, 64, 32) == 0 &&
+        make_tmap_out_2d(&tmH, false, cu, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, 64, 32) == 0)
+      p.tma_store = 1;
+  } else if (g_pair_tma_store && swiglu_f == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
       (ldc * esz) % 16 == 0 && row_end_ok && (rope_cs == nullptr || (N == 3 * rope_d && rope_dh % 32 == 0))) {
     if (make_tmap_out_2d(&tmC, out_f32, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, out_f32 ? 32 : 64, 32) == 0)
       p.tma_store = 1;
@@ -661,4 +749,41 @@ extern "C" int b200_gemm_bf16_pair_swiglu(const void* A, const void* B, void* C,
   }
   return gemm_pair_impl(A, B, C, nullptr, M, 2 * F, K, lda, ldb, ldc, 0, 0, 0, EPI_BF16, carry ? &g : nullptr, nullptr, 0,
                         status, stream, nullptr, 0, 0, 0, 0, F, H, ldh);
+}
+
+int b200_make_reduce_task(const B200ReduceDesc* d, uint32_t* status, bool carried, ReduceTask* out);
+
+// Host description of a carried all-gather (same meaning as the arguments of b200_gemm_bf16_pair_gather).
+struct B200GatherDesc {
+  unsigned long long src[16];
+  void* dst;
+  unsigned long long shard_bytes;
+  int world, rank;
+};
+
+// The CTA-pair GEMM with optional carried collectives: `gather` (all-gather of the next unit's weight shards) and
+// `reduce` (reduce-scatter of an earlier unit's gradient staging, optionally fused with AdamW) run on the two copy
+// warps of every CTA, the gather first.  Either may be null.  epi as in b200_gemm_bf16 (EPI_SWIGLU_BWD included).
+extern "C" int b200_gemm_bf16_pair_tasks(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                                         long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int b_mn,
+                                         int epi, const B200GatherDesc* gather, const B200ReduceDesc* reduce,
+                                         uint32_t* status, cudaStream_t stream) {
+  GatherTask g;
+  if (gather != nullptr) {
+    if (gather->world > 16 || gather->shard_bytes % 16 || (reinterpret_cast<uintptr_t>(gather->dst) & 15) ||
+        gather->dst == nullptr)
+      return -10;
+    for (int i = 0; i < 16; ++i) g.src[i] = i < gather->world ? reinterpret_cast<const uint4*>(gather->src[i]) : nullptr;
+    g.dst = reinterpret_cast<uint4*>(gather->dst);
+    g.shard_vec = gather->shard_bytes / 16;
+    g.world = gather->world; g.rank = gather->rank; g.done = nullptr;
+  }
+  ReduceTask r;
+  if (reduce != nullptr) {
+    const int rc = b200_make_reduce_task(reduce, status, true, &r);
+    if (rc) return rc;
+    // one partial sum per CTA: the grid of this kernel never exceeds the SM count
+  }
+  return gemm_pair_impl(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, epi, gather ? &g : nullptr, nullptr, 0,
+                        status, stream, nullptr, 0, 0, 0, 0, 0, nullptr, 0, reduce ? &r : nullptr);
 }

@@ -88,13 +88,14 @@ def block_forward(x, w: BlockWeights, cfg: EngineConfig, rope_cache, batch: int,
 
 
 def block_backward(dy, w: BlockWeights, s: BlockSaved, gw: BlockWeights, cfg: EngineConfig, rope_cache,
-                   batch: int, seq: int, gather=None):
+                   batch: int, seq: int, gather=None, reduce=None):
     """Returns dx; writes every weight gradient of the block into the views in ``gw``.  ``gather`` (the
-    previous unit's weights, needed next) rides on the first GEMM."""
+    previous unit's weights, needed next) rides on the first GEMM, ``reduce`` (the reduce-scatter of the unit
+    whose backward has just finished) on the third."""
     # ---- feed-forward half
     dgu = ops.gemm_swiglu_bwd(dy, w.wdown, s.gu, gather=gather)          # SiLU*mul backward in the GEMM epilogue
     ops.gemm(dy, s.hh, "tn", out=gw.wdown)
-    dh2 = ops.gemm(dgu, w.wgu, "nn")
+    dh2 = ops.gemm(dgu, w.wgu, "nn", reduce=reduce)
     ops.gemm(dgu, s.h2, "tn", out=gw.wgu)
     del dgu
     dx2 = _norm_bwd(dh2, s.x2, w.n2, s.rstd2, gw.n2, dy)
@@ -147,6 +148,7 @@ def block_views(by_name, names: dict, flat: torch.Tensor, base: int) -> BlockWei
 
 
 def head_views(by_name, names: dict, flat: torch.Tensor, base: int) -> HeadWeights:
+    """Embedding table, final norm and lm_head as views of ``flat`` (element 0 = arena offset ``base``)."""
     return HeadWeights(_seg_view(by_name, flat, names["emb"], base), _seg_view(by_name, flat, names["norm"], base),
                        _seg_view(by_name, flat, names["lm"], base))
 
@@ -182,6 +184,12 @@ class LocalProvider:
     def head_weights(self, backward: bool = False) -> HeadWeights:
         return self._w_cache[1]
 
+    def embed_weight(self) -> torch.Tensor:
+        return self._w_cache[1].emb
+
+    def embed_grad(self) -> torch.Tensor:
+        return self._grads()[1].emb
+
     def _grads(self):
         if self._g_cache is None:
             self.arena.bind_grads()
@@ -202,6 +210,9 @@ class LocalProvider:
         pass
 
     def take_gather(self, kind: str, i: int):
+        return None
+
+    def take_reduce(self, kind: str, i: int):
         return None
 
     def post_backward(self, kind: str, i: int):
@@ -238,7 +249,7 @@ class _BlockFn(torch.autograd.Function):
                 _, saved = block_forward(ctx.x_in, w, eng.cfg, eng.rope_cache, ctx.batch, ctx.seq, True)
         with nvtx_range(f"block{i}.bwd"):
             dx = block_backward(dy.contiguous(), w, saved, prov.block_grads(i), eng.cfg, eng.rope_cache, ctx.batch,
-                                ctx.seq, gather=prov.take_gather("bwd", i))
+                                ctx.seq, gather=prov.take_gather("bwd", i), reduce=prov.take_reduce("bwd", i))
         ctx.saved = None
         ctx.x_in = None
         prov.post_backward("block", i)
@@ -248,22 +259,20 @@ class _BlockFn(torch.autograd.Function):
 class _EmbedFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, tokens, anchor, eng):
-        w = eng.provider.head_weights().emb
+        w = eng.provider.embed_weight()
         ctx.eng = eng
         ctx.tokens = tokens
-        return ops.embedding_fwd(tokens, w)
+        out = ops.embedding_fwd(tokens, w)
+        eng.provider.post_forward("embed", 0)
+        return out
 
     @staticmethod
     def backward(ctx, dx):
         prov = ctx.eng.provider
         prov.pre_backward("embed", 0)
-        g = prov.head_grads().emb
-        if g.dtype == torch.float32:
-            ops.embedding_bwd(dx.contiguous(), ctx.tokens, g)
-        else:
-            tmp = torch.zeros(g.shape, dtype=torch.float32, device=g.device)
-            ops.embedding_bwd(dx.contiguous(), ctx.tokens, tmp)
-            g.copy_(tmp)
+        # fp32 gradient table, or the bf16 gradient staging of a multi-GPU run: each row is written once from the
+        # fp32 sum of its token run, so no fp32 temporary of the table's size is needed
+        ops.embedding_bwd(dx.contiguous(), ctx.tokens, prov.embed_grad())
         prov.post_backward("embed", 0)
         return None, None, None
 

@@ -313,6 +313,8 @@ class TransformerLM(nn.Module):
         ordered += [(head_names["emb"], self.token_embeddings.weight), (head_names["norm"], self.final_norm.weight),
                     (head_names["lm"], self.lm_head.weight)]
         groups.append(("head", first, len(ordered) - 1))
+        groups.append(("embed", first, first))                     # FSDP shards the table and the head separately
+        groups.append(("lmhead", first + 1, len(ordered) - 1))
         dev = ordered[0][1].device
         if any(p.device != dev or p.dtype != torch.float32 for _, p in ordered):
             raise RuntimeError("the native engine needs all parameters in fp32 on one device")

@@ -184,6 +184,9 @@ FUSE_SWIGLU_FWD = os.environ.get("B200_FUSE_SWIGLU_FWD", "1") == "1"    # SiLU*m
 # slower than GEMM + stand-alone kernel (the 128 epilogue threads of a CTA become the bottleneck), so it is opt-in.
 FUSE_SWIGLU_BWD = os.environ.get("B200_FUSE_SWIGLU_BWD", "0") == "1"
 USE_PAIR = os.environ.get("B200_GEMM_PAIR", "1") == "1"
+# Tests of the GEMM-carried collectives run tiny models: this switch sends every GEMM whose default would be the
+# single-CTA kernel to the CTA-pair kernel as well (it handles any shape; small ones just fill fewer SMs).
+FORCE_PAIR = os.environ.get("B200_GEMM_FORCE_PAIR", "0") == "1"
 
 
 def _pair_pays(m: int, n: int, sms: int = 148) -> bool:
@@ -205,11 +208,41 @@ def set_gemm_tma_store(on: bool) -> bool:
     return bool(lib.b200_gemm_set_tma_store(1 if on else 0))
 
 
+def _task_descs(gather, reduce):
+    """ctypes descriptions of the collectives a CTA-pair GEMM launch is about to carry (None where there is none)."""
+    from ..parallel.peer import GatherDesc
+    gdesc = None
+    if gather is not None:
+        table, dst, nbytes, world, rank = gather
+        gdesc = GatherDesc()
+        for r in range(world):
+            gdesc.src[r] = table[r]
+        gdesc.dst, gdesc.shard_bytes, gdesc.world, gdesc.rank = dst, nbytes, world, rank
+    return gdesc, (reduce.desc if reduce is not None else None)
+
+
+def _gemm_pair_tasks(lib, a, b, out, r, m, n, k, lda, ldb, ldc, ldr, a_mn, b_mn, epi, gargs, reduce):
+    gdesc, rdesc = _task_descs(gargs, reduce)
+    fn = lib.b200_gemm_bf16_pair_tasks
+    if not getattr(fn, "_declared", False):
+        P, I, L = c_void_p, c_int, c_ll
+        fn.argtypes = [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P, P, P]
+        fn.restype = I
+        fn._declared = True
+    rc = fn(_ptr(a), _ptr(b), _ptr(out), _ptr(r), m, n, k, lda, ldb, ldc, ldr, a_mn, b_mn, epi,
+            ctypes.byref(gdesc) if gdesc is not None else None, ctypes.byref(rdesc) if rdesc is not None else None,
+            _ptr(status_word(a.device)), _stream())
+    _check(rc, "b200_gemm_bf16_pair_tasks")
+
+
 def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, bn_hint=0, max_ctas=0,
-         pair=None, gather=None, pad_writable=False):
+         pair=None, gather=None, pad_writable=False, reduce=None):
     """bf16 tensor-core GEMM (tcgen05).  layout 'nt' | 'nn' | 'tn' as in ``torch_impl.gemm``.
 
     ``pair`` forces (True) or forbids (False) the CTA-pair kernel; by default large problems use it.
+    ``gather`` / ``reduce``: a pending all-gather / reduce-scatter (``parallel.comm.GatherTask`` /
+    ``ReduceScatterTask``) that the CTA-pair kernel carries on its copy warps; a launch that cannot carry them
+    performs them first as collectives of their own.
     ``pad_writable``: ``out`` is a column slice of a wider buffer and the columns from N up to the next 16-byte
     boundary (inside the row pitch) may be overwritten with zeros; this lets a row count that is not a multiple of
     16 bytes (a vocabulary of 50,257) use the TMA-store epilogue."""
@@ -255,22 +288,26 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
         _req(residual.dtype == torch.bfloat16 and tuple(residual.shape) == (m, n), "residual must be bf16 (M,N)")
         ldr = residual.stride(0)
     if pair is None:
-        pair = USE_PAIR and bn_hint == 0 and max_ctas == 0 and m >= PAIR_MIN_M and n >= 256 and _pair_pays(m, n)
+        pair = USE_PAIR and bn_hint == 0 and max_ctas == 0 and (
+            FORCE_PAIR or (m >= PAIR_MIN_M and n >= 256 and _pair_pays(m, n)))
     gargs = gather.native_args() if (gather is not None and not gather.done) else None
     if gather is not None and not gather.done and (gargs is None or not pair):
         gather.run()           # this launch cannot carry it: stand-alone collective
         gargs = None
+    if reduce is not None and not reduce.done and (reduce.desc is None or not pair):
+        reduce.run()
     if pair and pad_writable:
         per16 = 16 // out.element_size()
         if -(-n // per16) * per16 <= out.stride(0):
             epi |= EPI_PAD_WRITABLE
-    if pair and gargs is not None:
-        table, dst, nbytes, world, rank = gargs
-        rc = lib.b200_gemm_bf16_pair_gather(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb,
-                                            out.stride(0), ldr, a_mn, b_mn, epi, table, dst, nbytes, world, rank,
-                                            None, None, None, 0, _ptr(status_word(a.device)), _stream())
-        _check(rc, "b200_gemm_bf16_pair_gather")
-        gather.mark_done()
+    carry_reduce = reduce if (reduce is not None and not reduce.done) else None
+    if pair and (gargs is not None or carry_reduce is not None):
+        _gemm_pair_tasks(lib, a, b, out, residual, m, n, k, lda, ldb, out.stride(0), ldr, a_mn, b_mn, epi, gargs,
+                         carry_reduce)
+        if gargs is not None:
+            gather.mark_done()
+        if carry_reduce is not None:
+            carry_reduce.mark_done()
         return out
     if pair:
         rc = lib.b200_gemm_bf16_pair(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb, out.stride(0),
@@ -291,7 +328,7 @@ def gemm_qkv_rope(x, wqkv, cos_sin, seq: int, n_heads: int):
     n = wqkv.shape[0]
     d = n // 3
     dh = d // n_heads
-    ok = (USE_PAIR and FUSE_ROPE and m >= PAIR_MIN_M and dh % 32 == 0 and m % seq == 0 and seq <= cos_sin.shape[1]
+    ok = (USE_PAIR and FUSE_ROPE and (m >= PAIR_MIN_M or FORCE_PAIR) and dh % 32 == 0 and m % seq == 0 and seq <= cos_sin.shape[1]
           and x.dtype == torch.bfloat16 and wqkv.dtype == torch.bfloat16 and x.stride(1) == 1 and wqkv.stride(1) == 1
           and x.stride(0) % 8 == 0 and wqkv.stride(0) % 8 == 0 and cos_sin.is_contiguous()
           and cos_sin.dtype == torch.float32 and cos_sin.shape[2] == dh // 2)
@@ -312,7 +349,7 @@ def gemm_swiglu(x, wgu, gather=None):
     m, k = x.shape
     two_f = wgu.shape[0]
     f = two_f // 2
-    ok = (USE_PAIR and FUSE_SWIGLU_FWD and m >= PAIR_MIN_M and f % 128 == 0 and x.dtype == torch.bfloat16 and wgu.dtype == torch.bfloat16
+    ok = (USE_PAIR and FUSE_SWIGLU_FWD and (m >= PAIR_MIN_M or FORCE_PAIR) and f % 128 == 0 and x.dtype == torch.bfloat16 and wgu.dtype == torch.bfloat16
           and x.stride(1) == 1 and wgu.stride(1) == 1 and x.stride(0) % 8 == 0 and wgu.stride(0) % 8 == 0)
     if not ok:
         return None
@@ -338,7 +375,7 @@ def gemm_swiglu_bwd(dy, wdown, gu, gather=None):
     lib = load()
     m, k = dy.shape
     kb, f = wdown.shape
-    ok = (USE_PAIR and FUSE_SWIGLU_BWD and m >= PAIR_MIN_M and f >= 256 and f % 8 == 0 and k == kb and tuple(gu.shape) == (m, 2 * f)
+    ok = (USE_PAIR and FUSE_SWIGLU_BWD and (m >= PAIR_MIN_M or FORCE_PAIR) and f >= 256 and f % 8 == 0 and k == kb and tuple(gu.shape) == (m, 2 * f)
           and dy.dtype == torch.bfloat16 and wdown.dtype == torch.bfloat16 and gu.dtype == torch.bfloat16
           and dy.stride(1) == 1 and wdown.stride(1) == 1 and gu.stride(1) == 1 and dy.stride(0) % 8 == 0
           and wdown.stride(0) % 8 == 0 and gu.stride(0) % 8 == 0 and gu.data_ptr() % 16 == 0
@@ -350,11 +387,8 @@ def gemm_swiglu_bwd(dy, wdown, gu, gather=None):
     if gather is not None and not gather.done and gargs is None:
         gather.run()
     if gargs is not None:
-        table, dst, nbytes, world, rank = gargs
-        rc = lib.b200_gemm_bf16_pair_gather(_ptr(dy), _ptr(wdown), _ptr(dgu), _ptr(gu), m, f, k, dy.stride(0),
-                                            wdown.stride(0), 2 * f, gu.stride(0), 0, 1, EPI_SWIGLU_BWD, table, dst, nbytes,
-                                            world, rank, None, None, None, 0, _ptr(status_word(dy.device)), _stream())
-        _check(rc, "b200_gemm_bf16_pair_gather")
+        _gemm_pair_tasks(lib, dy, wdown, dgu, gu, m, f, k, dy.stride(0), wdown.stride(0), 2 * f, gu.stride(0), 0, 1,
+                         EPI_SWIGLU_BWD, gargs, None)
         gather.mark_done()
     else:
         rc = lib.b200_gemm_bf16_pair(_ptr(dy), _ptr(wdown), _ptr(dgu), _ptr(gu), m, f, k, dy.stride(0), wdown.stride(0),
@@ -461,11 +495,23 @@ def embedding_bwd(dx, tokens, grad_weight, accumulate=False, deterministic=True)
     ``deterministic=False`` uses 16-byte vector atomics instead (one launch, no sort)."""
     lib = load()
     _req(dx.dtype == torch.bfloat16 and dx.is_contiguous(), "dx must be contiguous bf16")
-    _req(grad_weight.dtype == torch.float32 and grad_weight.is_contiguous(), "grad table must be fp32")
     _req(tokens.dtype == torch.int64 and tokens.is_contiguous(), "tokens must be contiguous int64")
     v, d = grad_weight.shape
     rows = tokens.numel()
     _req(dx.numel() == rows * d, "dx shape mismatch")
+    if grad_weight.dtype == torch.bfloat16:
+        # bf16 gradient staging (multi-GPU): each row is written once from the fp32 sum of its run
+        _req(grad_weight.is_contiguous() and deterministic and not accumulate,
+             "a bf16 gradient table is written by the deterministic kernel only, without accumulation")
+        grad_weight.zero_()
+        sorted_tokens, order = torch.sort(tokens.reshape(-1), stable=True)
+        fn = lib.b200_embedding_bwd_sorted_bf16
+        fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]
+        fn.restype = c_int
+        _check(fn(_ptr(sorted_tokens), _ptr(order), _ptr(dx), _ptr(grad_weight), rows, d, v, _stream()),
+               "embedding_bwd_sorted")
+        return grad_weight
+    _req(grad_weight.dtype == torch.float32 and grad_weight.is_contiguous(), "grad table must be fp32")
     if not accumulate:
         grad_weight.zero_()
     if deterministic:

@@ -50,6 +50,29 @@ class GatherTask:
             self.mark_done()
 
 
+class ReduceScatterTask:
+    """A reduce-scatter (optionally fused with AdamW) that has been decided but not launched yet.
+
+    A CTA-pair GEMM launch can carry it (``ops.gemm(..., reduce=task)``): after the carried all-gather, if any, the
+    copy warps of every CTA read the peers' gradient staging, add it up and store the shard gradient or apply the
+    optimizer update while the MMA warps compute.  Anywhere else ``run()`` launches it as a collective of its own
+    on the current stream.  ``desc`` is the native description (None when only ``run`` can perform it)."""
+
+    def __init__(self, run_fn, desc, on_carried=None):
+        self._run, self.desc, self._on_carried = run_fn, desc, on_carried
+        self.done = False
+
+    def mark_done(self):
+        self.done = True
+        if self._on_carried is not None:
+            self._on_carried()
+
+    def run(self):
+        if not self.done:
+            self._run()
+            self.done = True
+
+
 class Communicator:
     rank: int = 0
     world_size: int = 1
@@ -60,8 +83,43 @@ class Communicator:
     def reduce_scatter_mean(self, out_shard: torch.Tensor, full: torch.Tensor, key=None, sumsq=None):
         raise NotImplementedError
 
-    def pre_gather_sync(self):
+    def reduce_scatter_adamw(self, full, key, master, m, v, mirror, lr, beta1, beta2, eps, weight_decay, step,
+                             grad_scale=None, grad_out=None, sumsq=None):
+        """Mean reduce-scatter of ``full`` whose result feeds the AdamW update of this rank's shard (``master``,
+        ``m``, ``v`` fp32; ``mirror`` the compute-dtype copy of the weights or None).  ``grad_scale`` is a 0-d clip
+        coefficient, ``sumsq`` a 0-d accumulator of the squared norm of the (unclipped) shard gradient.  This
+        statement of the op runs on any back end; ``PeerComm`` does all of it in one kernel."""
+        g = torch.empty(master.numel(), dtype=torch.float32, device=master.device) if grad_out is None else grad_out
+        self.reduce_scatter_mean(g, full, key=key)
+        if sumsq is not None:
+            sumsq.add_((g.double() ** 2).sum().to(sumsq.dtype))
+        gs = g if grad_scale is None else g * grad_scale
+        alpha_t = lr * (1 - beta2 ** step) ** 0.5 / (1 - beta1 ** step)
+        m.mul_(beta1).add_(gs, alpha=1 - beta1)
+        v.mul_(beta2).addcmul_(gs, gs, value=1 - beta2)
+        master.addcdiv_(m, v.sqrt().add_(eps), value=-alpha_t)
+        master.mul_(1 - lr * weight_decay)
+        if mirror is not None and mirror.data_ptr() != master.data_ptr():
+            mirror.copy_(master)
+
+    def reduce_task(self, full, key, out_shard=None, sumsq=None, adamw: dict | None = None) -> "ReduceScatterTask":
+        """A pending reduce-scatter (see ``ReduceScatterTask``).  Back ends without native descriptions can only
+        ``run`` it."""
+        if adamw is not None:
+            return ReduceScatterTask(lambda: self.reduce_scatter_adamw(full, key, grad_out=out_shard, sumsq=sumsq,
+                                                                       **adamw), None)
+        return ReduceScatterTask(lambda: self.reduce_scatter_mean(out_shard, full, key=key, sumsq=sumsq), None)
+
+    def publish_weights(self):
+        """Stream-ordered: this rank's weight shards are final for the coming step (its optimizer has run)."""
+
+    def await_weights(self):
         """Stream-ordered point after which every rank's weight shards are safe to read."""
+
+    def pre_gather_sync(self):
+        """``publish_weights`` followed by ``await_weights``."""
+        self.publish_weights()
+        self.await_weights()
 
     def wait_readers(self, staging: torch.Tensor, key=None):
         """Stream-ordered point after which ``staging`` may be overwritten."""
@@ -116,6 +174,11 @@ class TorchDistComm(Communicator):
             dist.all_gather_into_tensor(full[:n * self.world_size], shard, group=self.group)
 
     def reduce_scatter_mean(self, out_shard, full, key=None, sumsq=None):
+        self._reduce_scatter_mean(out_shard, full)
+        if sumsq is not None:
+            sumsq.add_((out_shard.double() ** 2).sum().to(sumsq.dtype))
+
+    def _reduce_scatter_mean(self, out_shard, full):
         n = out_shard.numel()
         ws = self.world_size
         if self.backend == "gloo":
@@ -145,6 +208,11 @@ class TorchDistComm(Communicator):
     def barrier(self):
         dist.barrier(group=self.group)
 
+    def await_weights(self):
+        # torch.distributed collectives of one group are ordered among themselves and every rank enqueues its
+        # optimizer before its next gather, so a gather can never overtake a peer's weight update: nothing to do.
+        pass
+
 
 def make_communicator(group=None, kind: str = "auto") -> Communicator:
     """``kind``: 'auto' | 'torch' | 'peer'.  'auto' picks peer-memory kernels when every rank of an
@@ -154,10 +222,12 @@ def make_communicator(group=None, kind: str = "auto") -> Communicator:
     if dist.get_world_size(group) == 1 and kind != "peer":
         return SingleProcessComm()
     if kind in ("auto", "peer") and dist.get_backend(group) == "nccl":
-        try:
-            from .peer import PeerComm
+        from .peer import PeerComm, peer_access_everywhere
+        # Every rank must take the same decision: probe locally (no collective inside), then agree.
+        ok = torch.tensor([1 if peer_access_everywhere(dist.get_world_size(group)) else 0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 1:
             return PeerComm(group)
-        except Exception:
-            if kind == "peer":
-                raise
+        if kind == "peer":
+            raise RuntimeError("peer-memory communicator requested but not every GPU pair has peer access")
     return TorchDistComm(group)

@@ -31,6 +31,23 @@ class _CudaArray:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
+class ReduceDesc(ctypes.Structure):
+    """Mirror of ``B200ReduceDesc`` (csrc/comm_device.cuh): one reduce-scatter of a unit's gradient staging."""
+    _fields_ = [("staging", _ULL * 16), ("flag_bases", _ULL * 16), ("ready_row", _ULL), ("done_row", _ULL),
+                ("grad_out", ctypes.c_void_p), ("sumsq", ctypes.c_void_p), ("master", ctypes.c_void_p),
+                ("m", ctypes.c_void_p), ("v", ctypes.c_void_p), ("mirror", ctypes.c_void_p),
+                ("gscale", ctypes.c_void_p), ("lr", ctypes.c_float), ("b1", ctypes.c_float), ("b2", ctypes.c_float),
+                ("eps", ctypes.c_float), ("wd", ctypes.c_float), ("alpha_t", ctypes.c_float), ("n", _ULL),
+                ("world", ctypes.c_int), ("rank", ctypes.c_int), ("mode", ctypes.c_int), ("epoch", ctypes.c_uint),
+                ("limit_ns", _ULL), ("counter", ctypes.c_void_p)]
+
+
+class GatherDesc(ctypes.Structure):
+    """Mirror of ``B200GatherDesc`` (csrc/gemm_tcgen05_2cta.cu): an all-gather carried by a GEMM."""
+    _fields_ = [("src", _ULL * 16), ("dst", ctypes.c_void_p), ("shard_bytes", _ULL), ("world", ctypes.c_int),
+                ("rank", ctypes.c_int)]
+
+
 def _declare(lib):
     P, I, L, F = ctypes.c_void_p, ctypes.c_int, _ULL, ctypes.c_float
     U = ctypes.c_uint
@@ -41,20 +58,34 @@ def _declare(lib):
     lib.b200_ipc_close.argtypes = [L]
     lib.b200_peer_barrier.argtypes = [P, L, I, I, U, L, P, P]
     lib.b200_peer_allgather.argtypes = [P, P, L, I, I, I, P]
-    lib.b200_peer_reduce_scatter.argtypes = [P, P, L, L, P, P, L, I, I, U, I, P, P, P, P, P, F, F, F, F, F, F, L, P, P,
-                                             I, P]
+    lib.b200_peer_reduce_scatter_desc.argtypes = [ctypes.POINTER(ReduceDesc), P, I, P]
+    lib.b200_peer_signal.argtypes = [P, L, I, I, U, P]
     lib.b200_peer_wait.argtypes = [P, I, U, L, P, P]
     lib.b200_peer_allreduce.argtypes = [P, P, L, L, L, I, I, U, L, P, P, I, P]
     lib.b200_peer_copy.argtypes = [P, P, L, I, P]
     for n in ("b200_ipc_alloc", "b200_ipc_free", "b200_ipc_get_handle", "b200_ipc_open", "b200_ipc_close",
-              "b200_peer_barrier", "b200_peer_allgather", "b200_peer_reduce_scatter", "b200_peer_wait",
+              "b200_peer_barrier", "b200_peer_allgather", "b200_peer_reduce_scatter_desc", "b200_peer_signal",
+              "b200_peer_wait",
               "b200_peer_allreduce", "b200_peer_copy"):
         getattr(lib, n).restype = I
 
 
+def peer_access_everywhere(world_size: int) -> bool:
+    """True when this process's GPU can map the memory of every other GPU of a one-node job of ``world_size`` ranks
+    (rank r on device r).  Purely local: no collective, no allocation."""
+    if not torch.cuda.is_available() or world_size > torch.cuda.device_count() or world_size > 16:
+        return False
+    me = torch.cuda.current_device()
+    try:
+        return all(d == me or torch.cuda.can_device_access_peer(me, d) for d in range(world_size))
+    except Exception:
+        return False
+
+
 class PeerComm(Communicator):
-    FLAG_ROWS = 64          # rows of `world` uint32 flags
+    FLAG_ROWS = 1024        # rows of `world` uint32 flags: two per logical buffer (a DDP bucket, an FSDP staging slot)
     ROW_BARRIER = 0
+    COUNTER_SLOTS = 256     # CTA counters handed out in turn; a slot is reused only 256 collective launches later
     WAIT_LIMIT_NS = 5_000_000_000   # a peer that is 5 s late is reported, never waited for indefinitely
 
     def __init__(self, group=None, wait_limit_s: float | None = None):
@@ -72,12 +103,14 @@ class PeerComm(Communicator):
         self.limit_ns = int((wait_limit_s * 1e9) if wait_limit_s else self.WAIT_LIMIT_NS)
         self._allocs: list[dict] = []      # {"base", "nbytes", "peers": [ptr per rank]}
         self._epochs: dict[int, int] = {}
-        self._next_row = 1
+        self._next_row = 2          # row 0: barrier, row 1: "weights published"
         self._rows: dict[str, tuple[int, int]] = {}
         flags = self.alloc(self.FLAG_ROWS * self.world_size, torch.int32)
         self.flags = flags
-        self._flag_bases = self._table(self._find(flags)["peers"])
-        self._counter = torch.zeros(64, dtype=torch.int32, device=self.device)
+        self._flag_peers = list(self._find(flags)["peers"])
+        self._flag_bases = self._table(self._flag_peers)
+        self.launches: dict[str, int] = {}      # peer-memory kernels launched, by kind
+        self._counter = torch.zeros(self.COUNTER_SLOTS, dtype=torch.int32, device=self.device)
         self._counter_used = 0
         self.barrier()
 
@@ -142,7 +175,7 @@ class PeerComm(Communicator):
         return e
 
     def _counter_slot(self):
-        i = self._counter_used % 64
+        i = self._counter_used % self.COUNTER_SLOTS
         self._counter_used += 1
         return self._counter[i:i + 1]
 
@@ -160,9 +193,33 @@ class PeerComm(Communicator):
         native._check(self.lib.b200_peer_barrier(self._flag_bases, self.ROW_BARRIER * self.world_size, self.world_size,
                                                  self.rank, e, self.limit_ns, self._status(), self._stream()),
                       "peer_barrier")
+        self._count("barrier")
 
     def pre_gather_sync(self):
         self.barrier()
+
+    ROW_WEIGHTS = 1
+
+    def publish_weights(self):
+        """Tell every peer (a flag store from a one-warp kernel on the current stream, no wait) that this rank's
+        weight shards are final for the coming step."""
+        e = self._bump(self.ROW_WEIGHTS)
+        native._check(self.lib.b200_peer_signal(self._flag_bases, self.ROW_WEIGHTS * self.world_size, self.world_size,
+                                                self.rank, e, self._stream()), "peer_signal")
+        self._count("signal")
+
+    def await_weights(self):
+        """Make the current stream wait (bounded) until every peer has published the weights of this step."""
+        e = self._epochs.get(self.ROW_WEIGHTS, 0)
+        if e == 0:
+            return
+        flags = self.flags.data_ptr() + self.ROW_WEIGHTS * self.world_size * 4
+        native._check(self.lib.b200_peer_wait(flags, self.world_size, e, self.limit_ns, self._status(), self._stream()),
+                      "peer_wait")
+        self._count("wait")
+
+    def _count(self, kind: str):
+        self.launches[kind] = self.launches.get(kind, 0) + 1
 
     def _ctas(self) -> int:
         """CTAs of a bandwidth kernel: with few peers each thread has few remote loads in flight, so more threads
@@ -179,6 +236,7 @@ class PeerComm(Communicator):
             return self.fallback.all_gather(full, shard)
         native._check(self.lib.b200_peer_allgather(table, full.data_ptr(), nbytes, self.world_size, self.rank, self._ctas(),
                                                    self._stream()), "peer_allgather")
+        self._count("all_gather")
 
     def gather_args(self, full, shard):
         """Arguments for a GEMM-carried all-gather of ``shard`` into ``full`` (see ``comm.GatherTask``)."""
@@ -186,37 +244,77 @@ class PeerComm(Communicator):
         nbytes = shard.numel() * shard.element_size()
         if table is None or nbytes % 16 or full.data_ptr() % 16:
             return None
+        self._count("all_gather_carried")
         return table, full.data_ptr(), nbytes, self.world_size, self.rank
 
-    def _reduce_scatter(self, staging, key, mode, grad_out, sumsq, adam):
-        table = self._peer_table(staging)
+    def _reduce_desc(self, staging, key, mode, grad_out, sumsq, adam) -> ReduceDesc:
+        """Fill the description of one reduce-scatter and advance the epoch of its flag rows.  Descriptions of one
+        ``key`` must be launched in the order in which they were made."""
+        a = self._find(staging)
+        off = staging.data_ptr() - a["base"]
         ready, done = self._rows_for(key)
         e = self._bump(ready)
         self._epochs[done] = e
-        n = staging.numel() // self.world_size
-        a = adam or {}
-        ptr = lambda t: 0 if t is None else t.data_ptr()
-        native._check(self.lib.b200_peer_reduce_scatter(
-            table, self._flag_bases, ready * self.world_size, done * self.world_size, ptr(grad_out), ptr(sumsq), n,
-            self.world_size, self.rank, e, mode, ptr(a.get("master")), ptr(a.get("m")), ptr(a.get("v")),
-            ptr(a.get("mirror")), ptr(a.get("gscale")), a.get("lr", 0.0), a.get("b1", 0.0), a.get("b2", 0.0),
-            a.get("eps", 0.0), a.get("wd", 0.0), a.get("alpha_t", 0.0), self.limit_ns, self._counter_slot().data_ptr(),
-            self._status(), self._ctas(), self._stream()), "peer_reduce_scatter")
+        ad = adam or {}
+        ptr = lambda t: None if t is None else t.data_ptr()
+        d = ReduceDesc()
+        for r in range(self.world_size):
+            d.staging[r] = a["peers"][r] + off
+            d.flag_bases[r] = self._flag_peers[r]
+        d.ready_row, d.done_row = ready * self.world_size, done * self.world_size
+        d.grad_out, d.sumsq = ptr(grad_out), ptr(sumsq)
+        d.master, d.m, d.v, d.mirror = ptr(ad.get("master")), ptr(ad.get("m")), ptr(ad.get("v")), ptr(ad.get("mirror"))
+        d.gscale = ptr(ad.get("gscale"))
+        d.lr, d.b1, d.b2 = ad.get("lr", 0.0), ad.get("b1", 0.0), ad.get("b2", 0.0)
+        d.eps, d.wd, d.alpha_t = ad.get("eps", 0.0), ad.get("wd", 0.0), ad.get("alpha_t", 0.0)
+        d.n = staging.numel() // self.world_size
+        d.world, d.rank, d.mode, d.epoch = self.world_size, self.rank, mode, e
+        d.limit_ns = self.limit_ns
+        d.counter = self._counter_slot().data_ptr()
+        return d
+
+    def _launch_reduce(self, desc: ReduceDesc):
+        native._check(self.lib.b200_peer_reduce_scatter_desc(ctypes.byref(desc), self._status(), self._ctas(),
+                                                             self._stream()), "peer_reduce_scatter")
+        self._count("reduce_scatter")
+
+    def _rs_ok(self, out_shard, full) -> bool:
+        return (self._find(full) is not None and full.dtype == torch.bfloat16
+                and (out_shard is None or out_shard.dtype == torch.float32)
+                and (full.numel() // self.world_size) % 8 == 0)
 
     def reduce_scatter_mean(self, out_shard, full, key: str | None = None, sumsq=None):
-        ok = (self._find(full) is not None and full.dtype == torch.bfloat16 and out_shard.dtype == torch.float32
-              and (full.numel() // self.world_size) % 8 == 0)
-        if not ok:
-            return self.fallback.reduce_scatter_mean(out_shard, full)
-        self._reduce_scatter(full, key or f"rs{full.data_ptr()}", 0, out_shard, sumsq, None)
+        if not self._rs_ok(out_shard, full):
+            return self.fallback.reduce_scatter_mean(out_shard, full, sumsq=sumsq)
+        self._launch_reduce(self._reduce_desc(full, key or f"rs{full.data_ptr()}", 0, out_shard, sumsq, None))
 
     def reduce_scatter_adamw(self, full, key, master, m, v, mirror, lr, beta1, beta2, eps, weight_decay, step,
                              grad_scale=None, grad_out=None, sumsq=None):
         """Reduce-scatter fused with the AdamW update of this rank's shard (one kernel)."""
+        self._launch_reduce(self._adamw_desc(full, key, master, m, v, mirror, lr, beta1, beta2, eps, weight_decay, step,
+                                             grad_scale, grad_out, sumsq))
+
+    def _adamw_desc(self, full, key, master, m, v, mirror, lr, beta1, beta2, eps, weight_decay, step, grad_scale,
+                    grad_out, sumsq) -> ReduceDesc:
         alpha_t = lr * math.sqrt(1 - beta2 ** step) / (1 - beta1 ** step)
-        self._reduce_scatter(full, key, 1, grad_out, sumsq,
-                             dict(master=master, m=m, v=v, mirror=mirror, gscale=grad_scale, lr=lr, b1=beta1, b2=beta2,
-                                  eps=eps, wd=weight_decay, alpha_t=alpha_t))
+        return self._reduce_desc(full, key, 1, grad_out, sumsq,
+                                 dict(master=master, m=m, v=v, mirror=mirror, gscale=grad_scale, lr=lr, b1=beta1,
+                                      b2=beta2, eps=eps, wd=weight_decay, alpha_t=alpha_t))
+
+    def reduce_task(self, full, key, out_shard=None, sumsq=None, adamw: dict | None = None):
+        """A reduce-scatter that a later GEMM launch can carry on its copy warps (``ReduceScatterTask``); ``adamw``
+        holds the keyword arguments of ``reduce_scatter_adamw`` when the update is to be fused."""
+        from .comm import ReduceScatterTask
+        if not self._rs_ok(out_shard, full):
+            return ReduceScatterTask(lambda: self.fallback.reduce_scatter_mean(out_shard, full, sumsq=sumsq), None)
+        if adamw is not None:
+            desc = self._adamw_desc(full, key, grad_out=out_shard, sumsq=sumsq, **adamw)
+        else:
+            desc = self._reduce_desc(full, key, 0, out_shard, sumsq, None)
+
+        def carried():
+            self._count("reduce_scatter_carried")
+        return ReduceScatterTask(lambda: self._launch_reduce(desc), desc, on_carried=carried)
 
     def wait_readers(self, staging, key: str | None = None):
         """Before overwriting ``staging``: wait until every peer has finished reading its last contents."""
@@ -230,6 +328,7 @@ class PeerComm(Communicator):
         flags = self.flags.data_ptr() + done * self.world_size * 4
         native._check(self.lib.b200_peer_wait(flags, self.world_size, e, self.limit_ns, self._status(), self._stream()),
                       "peer_wait")
+        self._count("wait")
 
     def all_reduce_mean(self, flat):
         table = self._peer_table(flat)
@@ -242,6 +341,7 @@ class PeerComm(Communicator):
                                                    done * self.world_size, flat.numel(), self.world_size, self.rank, e,
                                                    self.limit_ns, self._counter_slot().data_ptr(), self._status(), 96,
                                                    self._stream()), "peer_allreduce")
+        self._count("all_reduce")
 
     def all_reduce_sum(self, flat):
         self.fallback.all_reduce_sum(flat)      # scalars (norms, counters): plumbing

@@ -66,8 +66,12 @@ def save_sharded(fsdp, optimizer, iteration: int, directory: str) -> None:
     fsdp.comm.barrier()
 
 
-def _unit_full(shards: list[dict], key: str, unit_idx: int) -> torch.Tensor:
-    """Concatenate one unit's slices from every saved rank and drop the padding."""
+def _unit_full(shards: list[dict], key: str, name: str) -> torch.Tensor:
+    """Concatenate the slices of the unit called ``name`` from every saved rank and drop the padding."""
+    names = [u["name"] for u in shards[0]["units"]]
+    if name not in names:
+        raise KeyError(f"sharded checkpoint has no unit {name!r} (it holds {names})")
+    unit_idx = names.index(name)
     parts = []
     for sh in shards:
         off = sum(u["shard_numel"] for u in sh["units"][:unit_idx])
@@ -89,7 +93,7 @@ def load_sharded(fsdp, optimizer, directory: str) -> int:
     for ui, (u, seg) in enumerate(zip(fsdp.fsdp_units, sa.segments)):
         lo = fsdp.rank * u.shard_numel
         for key, dst in (("master", sa.master),) + ((("m", st["m"]), ("v", st["v"])) if has_opt else ()):
-            full = _unit_full(shards, key, ui)
+            full = _unit_full(shards, key, u.name)
             piece = full[lo:lo + u.shard_numel]
             d = dst[seg.start:seg.start + seg.numel]
             d.zero_()

@@ -116,8 +116,8 @@ def test_fsdp_world_size_one_aliases_shards():
     model = TransformerLM(**CFG, use_custom_triton=True)
     ref = _single_process_reference(1, 2, True, 0.0)
     f = FSDP(model)
-    assert len(f.fsdp_units) == CFG["num_layers"] + 1
-    assert len(list(f.parameters())) == CFG["num_layers"] + 1
+    assert len(f.fsdp_units) == CFG["num_layers"] + 2      # blocks, embedding table, final norm + lm_head
+    assert len(list(f.parameters())) == CFG["num_layers"] + 2
     assert all(p.numel() == 0 for p in model.parameters())       # unsharded weights are really released
     opt = FusedAdamW(f.parameters(), lr=1e-2, weight_decay=0.1)
     for s in range(2):
