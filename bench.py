@@ -111,6 +111,9 @@ def parse_args():
     ap.add_argument("--config", choices=sorted(CONFIGS), default="fsdp_1p3b")
     ap.add_argument("--parallel", choices=["fsdp", "ddp"], default="fsdp")
     ap.add_argument("--comm", choices=["auto", "torch", "peer"], default="auto")
+    ap.add_argument("--fused-optimizer", choices=["auto", "on", "off"], default="auto",
+                    help="FSDP on 2+ GPUs: run AdamW inside each unit's reduce-scatter (clip coefficient from the previous "
+                         "step's norm); auto = on.  off = reduce-scatter, exact global-norm clip, then one AdamW launch")
     ap.add_argument("--seed", type=int, default=0)
     return ap.parse_args()
 
@@ -196,6 +199,8 @@ def run_native(args, cfg, rank, local_rank, world):
     model.activation_checkpointing = bool(cfg.get("activation_checkpointing", False))
     wrapped = FSDP(model, comm=args.comm) if args.parallel == "fsdp" else DDP(model, comm=args.comm)
     opt = FusedAdamW(wrapped.parameters(), lr=LR, weight_decay=WEIGHT_DECAY)
+    fused = (args.parallel == "fsdp" and world > 1 and args.fused_optimizer != "off"
+             and wrapped.attach_optimizer(opt, MAX_GRAD_NORM))
     arena = wrapped.shard_arena if args.parallel == "fsdp" else model.engine().provider.arena
     b, s = cfg["micro_batch"], cfg["context_length"]
     tokens = synthetic_tokens(cfg["vocab_size"], 1 << 24, args.seed + 1)
@@ -208,7 +213,10 @@ def run_native(args, cfg, rank, local_rank, world):
         loss = wrapped.loss(x, y)
         loss.backward()
         wrapped.finish_gradient_synchronization()
-        opt.set_grad_scale(arena.clip_coef(MAX_GRAD_NORM))   # global-norm clip folded into the update
+        if fused:
+            wrapped.finish_fused_step()      # the updates ran inside the reduce-scatters; this step's norm clips the next
+        else:
+            opt.set_grad_scale(arena.clip_coef(MAX_GRAD_NORM))   # global-norm clip folded into the update
         opt.step()
         return loss
 
@@ -222,9 +230,14 @@ def run_native(args, cfg, rank, local_rank, world):
         last["loss"] = train_step(x, y)
 
     native.reset_launch_count()
+    comm_counts = getattr(wrapped.comm, "launches", None)
+    if comm_counts is not None:
+        comm_counts.clear()
     ms, wall, clocks = timed_region(step_resident, args.steps, args.warmup, world, local_rank if rank == 0 else None)
     launches = native.launch_count()
-    launches_timed = launches * args.steps // max(1, args.steps + args.warmup)
+    per_step = lambda n: n * args.steps // max(1, args.steps + args.warmup)
+    launches_timed = per_step(launches)
+    comm_launches = {k: per_step(v) for k, v in sorted((comm_counts or {}).items())}
     native.check_status()
     loss_a = float(last["loss"].item())
 
@@ -248,7 +261,10 @@ def run_native(args, cfg, rank, local_rank, world):
     return dict(ms=ms, ms_e2e=ms_e2e, wall=wall, clocks=clocks, tokens_per_step=tokens_per_step,
                 launches=launches_timed, loss=loss_a, h2d=sampler.bytes_per_batch(), d2h=4,
                 mem_gb=torch.cuda.max_memory_allocated() / 2 ** 30,
-                parallelism=f"{args.parallel}{world}", comm=type(wrapped.comm).__name__)
+                parallelism=f"{args.parallel}{world}", comm=type(wrapped.comm).__name__, comm_launches=comm_launches,
+                optimizer=("AdamW fp32 sharded state, update fused into each unit's reduce-scatter, global-norm clip 1.0 "
+                           "with the previous step's norm" if fused else
+                           "AdamW fp32 state, one launch, exact global-norm clip 1.0"))
 
 
 def run_reference(args, cfg, rank, local_rank, world):
@@ -319,7 +335,10 @@ def run_reference(args, cfg, rank, local_rank, world):
     os.unlink(tmp.name)
     return dict(ms=ms, ms_e2e=ms_e2e, wall=wall, clocks=clocks, tokens_per_step=b * s * world, launches=None,
                 loss=loss_a, h2d=2 * b * s * 8, d2h=4, mem_gb=torch.cuda.max_memory_allocated() / 2 ** 30,
-                parallelism=f"{args.parallel}{world}", comm="NCCL"), None
+                parallelism=f"{args.parallel}{world}", comm="NCCL", comm_launches=None,
+                optimizer="reference FusedAdamW (Triton), clip 1.0 by each rank's local shard norm (the reference's "
+                          "clip_gradient over its FSDP shards)" if args.parallel == "fsdp" and world > 1 else
+                          "reference FusedAdamW (Triton), global-norm clip 1.0"), None
 
 
 def main():
@@ -357,9 +376,8 @@ def main():
             "config": {"model": cfg["model"], "global_batch": cfg["micro_batch"] * world, "seq_len": cfg["context_length"],
                        "parallelism": res["parallelism"], "micro_batch_per_gpu": cfg["micro_batch"],
                        "vocab": cfg["vocab_size"], "d_model": cfg["d_model"], "layers": cfg["num_layers"],
-                       "heads": cfg["num_heads"], "d_ff": cfg["d_ff"], "optimizer": "AdamW fp32 state, global-norm clip 1.0",
-                       "comm": res["comm"],
-                       "l2_policy": l2_policy(cfg)},
+                       "heads": cfg["num_heads"], "d_ff": cfg["d_ff"], "l2_policy": l2_policy(cfg)},
+            "optimizer": res["optimizer"], "comm": res["comm"], "comm_launches_per_step": res["comm_launches"],
             "clocks": res["clocks"],
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(res["ms_e2e"] / args.steps, 3),
                     "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"]},

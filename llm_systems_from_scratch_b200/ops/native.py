@@ -305,7 +305,7 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
         _gemm_pair_tasks(lib, a, b, out, residual, m, n, k, lda, ldb, out.stride(0), ldr, a_mn, b_mn, epi, gargs,
                          carry_reduce)
         if gargs is not None:
-            gather.mark_done()
+            gather.mark_done(carried=True)
         if carry_reduce is not None:
             carry_reduce.mark_done()
         return out
@@ -364,7 +364,7 @@ def gemm_swiglu(x, wgu, gather=None):
                                         _stream())
     _check(rc, "b200_gemm_bf16_pair_swiglu")
     if gargs is not None:
-        gather.mark_done()
+        gather.mark_done(carried=True)
     return gu, h
 
 
@@ -389,7 +389,7 @@ def gemm_swiglu_bwd(dy, wdown, gu, gather=None):
     if gargs is not None:
         _gemm_pair_tasks(lib, dy, wdown, dgu, gu, m, f, k, dy.stride(0), wdown.stride(0), 2 * f, gu.stride(0), 0, 1,
                          EPI_SWIGLU_BWD, gargs, None)
-        gather.mark_done()
+        gather.mark_done(carried=True)
     else:
         rc = lib.b200_gemm_bf16_pair(_ptr(dy), _ptr(wdown), _ptr(dgu), _ptr(gu), m, f, k, dy.stride(0), wdown.stride(0),
                                      2 * f, gu.stride(0), 0, 1, EPI_SWIGLU_BWD, _ptr(status_word(dy.device)), _stream())

@@ -7,10 +7,12 @@ For one FSDP unit of the 1.3B model (50.6 M parameters by default) it times, wit
 maximum over ranks, (1) the pull all-gather of bf16 weight shards, (2) the reduce-scatter fused with scale
 and sum of squares, (3) the reduce-scatter fused with the AdamW update, (4) the in-place two-shot
 all-reduce of an fp32 bucket, and the NCCL collective each one replaces.  The roofline of a kernel is the
-slower of its NVLink ingress bytes over the measured 770 GB/s per direction and its HBM bytes over the
-measured copy bandwidth; rank 0 prints one JSON line per kernel with achieved / roofline.  It also times
-the CTA-pair GEMM that carries the all-gather on its copy warps against the slower of the GEMM at the
-measured cuBLAS peak and the gather's NVLink time.
+slower of its NVLink ingress bytes over the link bandwidth and its HBM bytes over the measured copy
+bandwidth; rank 0 prints one JSON line per kernel with achieved / roofline against two link figures: the
+peer-copy bandwidth measured by this same program (first row: every rank pulls 256 MiB from its right-hand
+neighbour, once with the copy engine and once with this package's copy kernel) and the nominal 900 GB/s per
+direction.  It also times the CTA-pair GEMMs that carry the all-gather or the reduce-scatter (+ AdamW) on
+their copy warps against the slower of the GEMM at the measured cuBLAS peak and the collective's NVLink time.
 """
 from __future__ import annotations
 
@@ -21,7 +23,7 @@ import os
 import torch
 import torch.distributed as dist
 
-NVLINK_GBS = 770.0
+NVLINK_NOMINAL_GBS = 900.0
 
 
 def _hbm_gbs() -> float:
@@ -84,12 +86,40 @@ def main():
     hbm = _hbm_gbs()
     out = []
 
-    def report(name, ms, link_bytes, hbm_bytes, nccl_ms):
-        roof_ms = max(link_bytes / NVLINK_GBS, hbm_bytes / hbm) / 1e6
+    # ---- link bandwidth as this box delivers it: every rank pulls 256 MiB from its right-hand neighbour
+    probe_n = 256 << 20
+    probe_src = comm.alloc(probe_n, torch.uint8)
+    probe_dst = torch.empty(probe_n, dtype=torch.uint8, device="cuda")
+    peer_ptr = comm._find(probe_src)["peers"][(rank + 1) % ws]
+    comm.barrier()
+    import ctypes
+    cudart = ctypes.CDLL("libcudart.so.12") if ws > 1 else None
+
+    def copy_engine():
+        # cudaMemcpyAsync(dst, src, n, cudaMemcpyDefault = 4, stream)
+        rc = cudart.cudaMemcpyAsync(ctypes.c_void_p(probe_dst.data_ptr()), ctypes.c_void_p(peer_ptr),
+                                    ctypes.c_size_t(probe_n), 4, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0, rc
+
+    def copy_kernel():
+        native._check(comm.lib.b200_peer_copy(probe_dst.data_ptr(), peer_ptr, probe_n, 296, comm._stream()), "peer_copy")
+    t_ce = _time(copy_engine, reps=2)
+    t_ck = _time(copy_kernel, reps=2)
+    link_ce, link_sm = probe_n / t_ce / 1e6, probe_n / t_ck / 1e6
+    link = max(link_ce, link_sm)          # GB/s per direction per GPU, measured here
+    if rank == 0:
+        out.append({"kernel": "peer copy probe (256 MiB pulled from the neighbour)", "world": ws,
+                    "copy_engine_gbs": round(link_ce, 1), "copy_kernel_gbs": round(link_sm, 1),
+                    "nominal_gbs": NVLINK_NOMINAL_GBS})
+
+    def report(name, ms, link_bytes, hbm_bytes, nccl_ms, **extra):
+        roof_ms = max(link_bytes / link, hbm_bytes / hbm) / 1e6
+        roof_nom = max(link_bytes / NVLINK_NOMINAL_GBS, hbm_bytes / hbm) / 1e6
         if rank == 0:
             out.append({"kernel": name, "world": ws, "ms": round(ms, 4), "roofline_ms": round(roof_ms, 4),
-                        "fraction_of_roofline": round(roof_ms / ms, 3), "nccl_ms": round(nccl_ms, 4),
-                        "nvlink_ingress_mb": round(link_bytes / 1e6, 1)})
+                        "fraction_of_roofline": round(roof_ms / ms, 3),
+                        "fraction_of_roofline_nominal_900": round(roof_nom / ms, 3), "nccl_ms": round(nccl_ms, 4),
+                        "nvlink_ingress_mb": round(link_bytes / 1e6, 1), **extra})
 
     # ---- all-gather of bf16 shards
     shard = comm.alloc(n, torch.bfloat16)
@@ -124,7 +154,7 @@ def main():
     t_f = _time(fused) - t_sync
     t_u = _time(unfused) - t_sync
     flops = 2.0 * m_ * n_ * k_
-    roof = max(flops / (peak * 1e12), (ws - 1) * n * 2 / (NVLINK_GBS * 1e9)) * 1e3
+    roof = max(flops / (peak * 1e12), (ws - 1) * n * 2 / (link * 1e9)) * 1e3
     if rank == 0:
         out.append({"kernel": "gemm_bf16_pair carrying the all-gather (16384x6144x2048 + 50.6M bf16 gather)", "world": ws,
                     "ms": round(t_f, 4), "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / t_f, 3),
@@ -150,6 +180,34 @@ def main():
         native.adamw_step(p, tmp, m, v, mirror, 1e-4, 0.9, 0.95, 1e-8, 0.1, 5)
     t_n = _time(nccl_then_adamw)
     report("peer_reduce_scatter + AdamW (one kernel)", t, (ws - 1) * n * 2, n * 2 + n * 26, t_n)
+
+    # ---- the same two reduce-scatters carried by the GEMM that follows a block's backward in FSDP (the dgrad of the
+    # gate|up projection, 16384 x 2048 x 11008): one kernel, the copy warps reduce while the MMA warps compute.
+    # Roofline: the slower of the GEMM at the measured cuBLAS burst peak and the reduce-scatter's NVLink time.
+    m2, n2, k2 = 16384, 2048, 11008
+    xa2 = torch.randn(m2, k2, device="cuda").bfloat16()
+    wb2 = torch.randn(k2, n2, device="cuda").bfloat16()
+    yc2 = torch.empty(m2, n2, device="cuda", dtype=torch.bfloat16)
+    comm.barrier()
+    t_plain2 = _time(lambda: native.gemm(xa2, wb2, "nn", out=yc2, pair=True))
+    flops2 = 2.0 * m2 * n2 * k2
+    adam_kw = dict(master=p, m=m, v=v, mirror=mirror, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=5)
+    for label, mk, nccl_fn in (
+            ("reduce-scatter + scale + sumsq", lambda: comm.reduce_task(stage, "bench", out_shard=grad, sumsq=ss),
+             lambda: dist.reduce_scatter_tensor(tmp, stage, op=dist.ReduceOp.AVG)),
+            ("reduce-scatter + AdamW", lambda: comm.reduce_task(stage, "bench", sumsq=ss, adamw=adam_kw), nccl_then_adamw)):
+        t_c = _time(lambda: native.gemm(xa2, wb2, "nn", out=yc2, pair=True, reduce=mk()))
+
+        def nccl_then_gemm():
+            nccl_fn()
+            native.gemm(xa2, wb2, "nn", out=yc2, pair=True)
+        t_n2 = _time(nccl_then_gemm)
+        roof2 = max(flops2 / (peak * 1e12), (ws - 1) * n * 2 / (link * 1e9)) * 1e3
+        if rank == 0:
+            out.append({"kernel": f"gemm_bf16_pair carrying the {label} (16384x2048x11008 GEMM + 50.6M-parameter unit)",
+                        "world": ws, "ms": round(t_c, 4), "roofline_ms": round(roof2, 4),
+                        "fraction_of_roofline": round(roof2 / t_c, 3), "gemm_alone_ms": round(t_plain2, 4),
+                        "nccl_then_gemm_ms": round(t_n2, 4)})
 
     # ---- two-shot all-reduce of an fp32 bucket (25 MiB)
     nb = 25 * 1024 * 1024 // 4

@@ -39,8 +39,10 @@ class GatherTask:
         fn = getattr(self.comm, "gather_args", None)
         return fn(self.full, self.shard) if fn is not None else None
 
-    def mark_done(self):
+    def mark_done(self, carried: bool = False):
         self.done = True
+        if carried and hasattr(self.comm, "_count"):
+            self.comm._count("all_gather_carried")
         if self.on_done is not None:
             self.on_done()
 

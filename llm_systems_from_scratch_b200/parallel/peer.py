@@ -244,7 +244,6 @@ class PeerComm(Communicator):
         nbytes = shard.numel() * shard.element_size()
         if table is None or nbytes % 16 or full.data_ptr() % 16:
             return None
-        self._count("all_gather_carried")
         return table, full.data_ptr(), nbytes, self.world_size, self.rank
 
     def _reduce_desc(self, staging, key, mode, grad_out, sumsq, adam) -> ReduceDesc:

@@ -3,8 +3,8 @@
 Required sections and keys are those the reference indexes without defaults: ``model``,
 ``training``, ``optimizer``, ``dataset``.  Extra keys the reference lacks are optional here and get
 defaults: ``training.seed``, ``training.dtype``, ``training.activation_checkpointing``,
-``training.resume``, ``optimizer.betas``, ``optimizer.eps``, ``fsdp.comm``, ``ddp.bucket_size_mb``,
-and a whole optional ``serving`` section.
+``training.resume``, ``training.step_timeout_s``, ``optimizer.betas``, ``optimizer.eps``, ``fsdp.comm``,
+``fsdp.fused_optimizer``, ``ddp.bucket_size_mb``, and a whole optional ``serving`` section.
 """
 from __future__ import annotations
 
@@ -21,9 +21,11 @@ REQUIRED = {
 
 DEFAULTS = {
     "training": {"seed": None, "dtype": "bf16", "activation_checkpointing": False, "resume": None,
-                 "val_last_position_only": True, "metrics_file": None},
+                 "val_last_position_only": True, "metrics_file": None, "step_timeout_s": 600.0},
     "optimizer": {"betas": [0.9, 0.95], "eps": 1e-8},
-    "fsdp": {"comm": "auto"},
+    # fused_optimizer: "off" = reduce-scatter, exact global-norm clip, one AdamW launch; "delayed_clip" = AdamW inside
+    # each unit's reduce-scatter, clipping with the coefficient of the previous step's gradient norm
+    "fsdp": {"comm": "auto", "fused_optimizer": "off"},
     "ddp": {"bucket_size_mb": 25.0, "comm": "auto"},
     "serving": {"page_size": 16, "max_batch": 64, "max_context": 2560, "num_pages": 0, "arrival_rate": 20.0,
                 "num_requests": 1024, "prompt_len": [128, 2048], "output_len": [64, 512], "seed": 0},
@@ -57,6 +59,8 @@ def validate(cfg: dict, world_size: int = 1, require_dataset: bool = True) -> di
     if world_size > 1 and bs % world_size:
         raise ValueError(f"training.batch_size ({bs}) must be divisible by the world size ({world_size}); "
                          "the reference silently floors it")
+    if out["fsdp"]["fused_optimizer"] not in ("off", "delayed_clip"):
+        raise ValueError("fsdp.fused_optimizer must be 'off' or 'delayed_clip'")
     m = out["model"]
     if m["d_model"] % m["num_heads"]:
         raise ValueError("model.d_model must be divisible by model.num_heads")

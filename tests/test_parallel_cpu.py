@@ -26,24 +26,33 @@ def _batch(world, per_rank=2, seq=16, seed=5):
     return x, y
 
 
-def _single_process_reference(world, steps, native, clip):
+def _single_process_reference(world, steps, native, clip, delayed=False):
+    """Full-batch training in one process.  ``delayed``: scale each step's gradients by the clip coefficient of the
+    *previous* step's norm (1 at the first step), which is what the fused reduce-scatter -> AdamW path does."""
     from llm_systems_from_scratch_b200.models.transformer import TransformerLM
     from llm_systems_from_scratch_b200.ops import functional as Fn
     from llm_systems_from_scratch_b200.optim import FusedAdamW
     torch.manual_seed(0)
     model = TransformerLM(**CFG, use_custom_triton=native)
     opt = FusedAdamW(model.parameters(), lr=1e-2, weight_decay=0.1)
+    coef = 1.0
     for s in range(steps):
         x, y = _batch(world, seed=5 + s)
         model.zero_grad()
         model.loss(x, y).backward()
-        if clip:
+        if clip and delayed:
+            grads = [p.grad for p in model.parameters() if p.grad is not None]
+            norm = torch.sqrt(sum((g.double() ** 2).sum() for g in grads)).item()
+            for g in grads:
+                g.mul_(coef)
+            coef = min(1.0, clip / (norm + 1e-6))
+        elif clip:
             Fn.clip_gradient(model.parameters(), clip)
         opt.step()
     return {k: v.clone() for k, v in model.state_dict().items()}
 
 
-def _worker(rank, world, port, mode, native, steps, clip, out_path):
+def _worker(rank, world, port, mode, native, steps, clip, out_path, fused=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -60,6 +69,8 @@ def _worker(rank, world, port, mode, native, steps, clip, out_path):
         # fuse_gather=True exercises the deferred-gather bookkeeping (on CPU the GEMM simply runs the gather first)
         wrapped = DDP(model, bucket_size_mb=0.05) if mode == "ddp" else FSDP(model, fuse_gather=(world == 3))
         opt = FusedAdamW(wrapped.parameters(), lr=1e-2, weight_decay=0.1)
+        if fused:
+            assert wrapped.attach_optimizer(opt, clip or None)
         per = 2
         for s in range(steps):
             x, y = _batch(world, seed=5 + s)
@@ -67,7 +78,10 @@ def _worker(rank, world, port, mode, native, steps, clip, out_path):
             wrapped.zero_grad()
             wrapped.loss(xs, ys).backward()
             wrapped.finish_gradient_synchronization()
-            if clip:
+            if fused:
+                norm = wrapped.finish_fused_step()
+                assert torch.isfinite(norm)
+            elif clip:
                 Fn.clip_gradient(wrapped.parameters(), clip)
             opt.step()
         sd = wrapped.full_state_dict() if mode == "fsdp" else model.state_dict()
@@ -80,16 +94,17 @@ def _worker(rank, world, port, mode, native, steps, clip, out_path):
         dist.destroy_process_group()
 
 
-def _run(mode, native, world, steps=3, clip=0.0):
+def _run(mode, native, world, steps=3, clip=0.0, fused=False):
     port = _free_port()
     with tempfile.TemporaryDirectory() as d:
         out = os.path.join(d, "sd.pt")
-        mp.spawn(_worker, args=(world, port, mode, native, steps, clip, out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, mode, native, steps, clip, out, fused), nprocs=world, join=True)
         got = torch.load(out)
-    ref = _single_process_reference(world, steps, native, clip)
+    ref = _single_process_reference(world, steps, native, clip, delayed=fused)
     assert set(got) == set(ref)
     for k in ref:
         assert torch.allclose(got[k], ref[k], atol=3e-4, rtol=1e-4), (k, (got[k] - ref[k]).abs().max().item())
+    return got
 
 
 def test_ddp_arena_mode_matches_single_process():
@@ -106,6 +121,24 @@ def test_fsdp_matches_single_process():
 
 def test_fsdp_three_ranks_with_global_clipping():
     _run("fsdp", native=True, world=3, steps=2, clip=0.25)
+
+
+def test_fsdp_fused_optimizer_matches_single_process():
+    """AdamW inside each unit's reduce-scatter (host statement of the fused kernel on gloo ranks), no clipping:
+    the same weights as single-process training."""
+    _run("fsdp", native=True, world=2, steps=3, fused=True)
+
+
+def test_fsdp_fused_optimizer_delayed_clip():
+    """With clipping the fused path scales step t by the coefficient of step t-1's norm: it must match a
+    single-process run that does exactly that (20 steps, 3 ranks), and stay close to exact clipping."""
+    got = _run("fsdp", native=True, world=3, steps=20, clip=0.5, fused=True)
+    exact = _single_process_reference(3, 20, True, 0.5, delayed=False)
+    worst = max((got[k] - exact[k]).abs().max().item() for k in exact)
+    mean = sum((got[k] - exact[k]).abs().sum().item() for k in exact) / sum(v.numel() for v in exact.values())
+    # lr 1e-2 for 20 Adam steps can move a weight by 0.2; the one-step lag of the clip factor moves single weights by
+    # about half of that at most and the average weight by far less
+    assert 0 < worst < 0.2 and mean < 0.03, (worst, mean)
 
 
 def test_fsdp_world_size_one_aliases_shards():

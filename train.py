@@ -6,8 +6,10 @@ Command line and behaviour follow the reference driver (train.py:75-353):
     python train.py --config configures/sample.yaml [--amp] [--compile] [--flash-attn]
                     [--custom-triton] [--parallel ddp|fsdp] [--world-size N] [--resume PATH]
 
-``--custom-triton`` selects the hand-written sm_100a kernel path (fused engine, fused AdamW, fused
-chunked loss); the flag name is kept so existing command lines work.  Distributed runs spawn one
+On a CUDA device the hand-written sm_100a kernel path (fused engine, fused AdamW, fused chunked loss)
+is the default; ``--eager`` selects the plain PyTorch modules instead (the oracle the kernels are tested
+against).  ``--custom-triton`` is accepted so that the reference's command lines keep working; on CPU it
+selects the same fused engine running on its fp32 PyTorch statement.  Distributed runs spawn one
 process per GPU and rendezvous on 127.0.0.1.  YAML ``batch_size`` is global; each rank takes
 ``batch_size // world_size`` (validated to divide evenly).  Checkpoints use the reference's
 single-file format; FSDP additionally writes sharded optimizer state so that runs can resume.
@@ -34,7 +36,7 @@ from llm_systems_from_scratch_b200.optim.adamw import AdamW, FusedAdamW, cosine_
 from llm_systems_from_scratch_b200.utils import checkpoint as ckpt_io  # noqa: E402
 from llm_systems_from_scratch_b200.utils.config import load_config, validate  # noqa: E402
 from llm_systems_from_scratch_b200.utils.metrics import MetricsLogger, StepTimer, get_gpu_stats, nvtx_range  # noqa: E402,F401
-from llm_systems_from_scratch_b200.utils.watchdog import Heartbeat  # noqa: E402
+from llm_systems_from_scratch_b200.utils.watchdog import Heartbeat, StepWatchdog  # noqa: E402
 
 
 def save_checkpoint(model, optimizer, iteration: int, path, save_optimizer: bool = True) -> None:
@@ -71,7 +73,7 @@ def _init_wandb(train_cfg, model_cfg, batch_size, lr_max, parallel, world_size):
 def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None = None,
                  config_path: str = "./configures/sample.yaml", use_amp: bool = False, use_compile: bool = False,
                  use_flash_attn: bool = False, use_custom_triton: bool = False, resume: str | None = None,
-                 backend: str | None = None):
+                 backend: str | None = None, eager: bool = False):
     parallel = parallel or []
     distributed = len(parallel) > 0
     use_fsdp, use_ddp = "fsdp" in parallel, "ddp" in parallel
@@ -103,6 +105,8 @@ def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None 
     else:
         device = detect_device() if train_cfg["device"] == "auto" else train_cfg["device"]
     amp_device_type = device.split(":")[0]
+    if amp_device_type == "cuda" and not eager:
+        use_custom_triton = True        # the kernels of this package are the default path on a GPU
     if train_cfg.get("seed") is not None:
         torch.manual_seed(int(train_cfg["seed"]) + rank)
 
@@ -134,6 +138,27 @@ def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None 
     opt_cls = FusedAdamW if (use_custom_triton or use_fsdp) else AdamW
     optimizer = opt_cls(params=model.parameters(), lr=lr_max, weight_decay=optim_cfg["weight_decay"],
                         betas=tuple(optim_cfg["betas"]), eps=optim_cfg["eps"])
+    # AdamW inside each unit's reduce-scatter (clips with the previous step's coefficient): fsdp.fused_optimizer
+    fused_opt = (use_fsdp and cfg["fsdp"]["fused_optimizer"] == "delayed_clip"
+                 and model.attach_optimizer(optimizer, max_grad_norm))
+    if use_fsdp:
+        print(f"[Rank {rank}] fsdp: comm={type(model.comm).__name__} fused_optimizer="
+              f"{'delayed_clip' if fused_opt else 'off'}")
+    on_gpu = amp_device_type == "cuda"
+    if on_gpu:
+        from llm_systems_from_scratch_b200.ops import native as native_ops
+    # A step that takes longer than training.step_timeout_s (a stuck collective, a hung peer) is reported from the
+    # watchdog thread; the loop raises at the next step boundary.
+    watchdog = StepWatchdog(float(train_cfg["step_timeout_s"]),
+                            on_timeout=lambda: print(f"[Rank {rank}] step watchdog: step exceeded "
+                                                     f"{train_cfg['step_timeout_s']} s", flush=True))
+
+    def rejoin():
+        """After host work that only some ranks do (rank 0 writing a checkpoint): meet on the host before any device
+        collective resumes, so that the bounded device waits never see the skew."""
+        if distributed:
+            dist.barrier()
+
     start_step = 0
     if resume:
         if use_fsdp and os.path.isdir(resume):
@@ -162,6 +187,9 @@ def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None 
     for step in range(start_step, max_steps):
         if heartbeat is not None:
             heartbeat.check()          # between steps: nothing of this rank is in flight
+        if watchdog.expired:
+            raise RuntimeError(f"step {step - 1} exceeded training.step_timeout_s; restart from the last checkpoint")
+        watchdog.arm()
         if profile_steps and step == start_step + 3:
             from torch.profiler import ProfilerActivity, profile
             acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
@@ -186,9 +214,17 @@ def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None 
             if distributed:
                 model.finish_gradient_synchronization()
         with nvtx_range("optimizer"):
-            clip_gradient(model.parameters(), max_grad_norm)
+            if fused_opt:
+                model.finish_fused_step()      # the update ran inside the reduce-scatters; this norm clips the next step
+            else:
+                clip_gradient(model.parameters(), max_grad_norm)
             optimizer.step()
         loss_value = loss.item()
+        if on_gpu:
+            # the loss read-back has synchronised the device: a bounded device wait that gave up during this step
+            # (a peer more than the limit late) left its collective undone - stop here rather than train on
+            native_ops.check_status()
+        watchdog.disarm()
         step_time = timer.stop()
         logger.step_line(step, loss_value, lr, step_time, batch_size * context_length / step_time)
         logger.log({"train/loss": loss_value, "train/lr": lr, "step": step, "step_time_s": step_time})
@@ -209,6 +245,9 @@ def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None 
                 ckpt_io.save_sharded(model, optimizer, step, os.path.join(checkpoint_dir, f"sharded_{step}"))
             elif not distributed or rank == 0:
                 save_checkpoint(inner_model, optimizer, step, os.path.join(checkpoint_dir, f"ckpt_{step}.pt"))
+            rejoin()
+            if on_gpu:
+                native_ops.check_status()
 
         if wandb_run is not None and step % gpu_log_interval == 0 and torch.cuda.is_available():
             rec = {"allocated_memory": int(torch.cuda.memory_allocated() / 1024 ** 2),
@@ -227,6 +266,7 @@ def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None 
     elif not distributed or rank == 0:
         save_checkpoint(inner_model, optimizer, max_steps, final)
     logger.close()
+    watchdog.stop()
     if heartbeat is not None:
         heartbeat.mark_done()
         heartbeat.stop()
@@ -242,7 +282,9 @@ def main():
     ap.add_argument("--compile", action="store_true", help="torch.compile the eager model (ignored on the native path)")
     ap.add_argument("--flash-attn", action="store_true", help="fused attention on the eager path")
     ap.add_argument("--custom-triton", "--native", dest="custom_triton", action="store_true",
-                    help="run the hand-written sm_100a kernel path")
+                    help="run the fused engine (the default on a CUDA device; on CPU its fp32 PyTorch statement)")
+    ap.add_argument("--eager", action="store_true",
+                    help="plain PyTorch modules on the GPU instead of this package's kernels (the test oracle)")
     ap.add_argument("--parallel", nargs="+", default=[], choices=["ddp", "fsdp"])
     ap.add_argument("--world-size", type=int, default=2)
     ap.add_argument("--resume", type=str, default=None, help="checkpoint file or sharded checkpoint directory")
@@ -258,7 +300,9 @@ def main():
         raise ValueError("--parallel ddp and fsdp are mutually exclusive (both are data parallelism)")
     if "fsdp" in args.parallel and args.compile:
         raise ValueError("--parallel fsdp and --compile are not compatible: FSDP always runs the fused engine")
-    common = (args.config, args.amp, args.compile, args.flash_attn, args.custom_triton, args.resume)
+    if args.eager and ("fsdp" in args.parallel or args.custom_triton):
+        raise ValueError("--eager excludes --custom-triton and --parallel fsdp (FSDP always runs the fused engine)")
+    common = (args.config, args.amp, args.compile, args.flash_attn, args.custom_triton, args.resume, None, args.eager)
     if args.parallel:
         mp.set_start_method("spawn", force=True)
         mp.spawn(train_worker, args=(args.world_size, args.parallel, *common), nprocs=args.world_size, join=True)
