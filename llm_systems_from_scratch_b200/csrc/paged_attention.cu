@@ -24,12 +24,19 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,        // (R, 3d) packe
                     const int* __restrict__ block_tables, const int* __restrict__ context_lens,
                     float* __restrict__ part_o,                  // (R, H, splits, DH)
                     float* __restrict__ part_ml,                 // (R, H, splits, 2)
-                    int q_ld, int heads, int page_size, int max_pages, int splits, float scale_log2) {
+                    int q_ld, int heads, int page_size, int max_pages, int splits, float scale_log2, int num_pages,
+                    uint32_t* __restrict__ status) {
   constexpr int LPT = DH / 8;            // lanes per token (16-byte loads)
   constexpr int TPW = 32 / LPT;          // tokens per warp iteration
   const int r = blockIdx.x / heads, h = blockIdx.x % heads;
   const int split = blockIdx.y;
-  const int ctx = context_lens[r];
+  // The tables come from the host scheduler; a length beyond the table or a page id beyond the cache is reported
+  // through the status word and skipped, never dereferenced.
+  int ctx = context_lens[r];
+  if (ctx < 0 || ctx > max_pages * page_size) {
+    if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0u, ERR_BAD_ARG | (1u << 8));
+    ctx = ctx < 0 ? 0 : max_pages * page_size;
+  }
   const int d = heads * DH;
   const int per = (ctx + splits - 1) / splits;
   const int t0 = split * per;
@@ -51,13 +58,18 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,        // (R, 3d) packe
   // a token group whose index runs past the end of the split only skips its loads and its update.
   for (int tb = t0 + warp * TPW; tb < t1; tb += (PD_THREADS / 32) * TPW) {
     const int t = tb + sub;
-    const bool valid = t < t1;
     uint4 ku = make_uint4(0, 0, 0, 0), vu = make_uint4(0, 0, 0, 0);
+    bool valid = t < t1;
     if (valid) {
       const int page = table[t / page_size];
-      const size_t row = ((size_t)page * page_size + (t % page_size)) * d + h * DH + li * 8;
-      ku = *reinterpret_cast<const uint4*>(k_cache + row);
-      vu = *reinterpret_cast<const uint4*>(v_cache + row);
+      if ((unsigned)page >= (unsigned)num_pages) {
+        if (status != nullptr) atomicCAS(status, 0u, ERR_BAD_ARG | (2u << 8));
+        valid = false;
+      } else {
+        const size_t row = ((size_t)page * page_size + (t % page_size)) * d + h * DH + li * 8;
+        ku = *reinterpret_cast<const uint4*>(k_cache + row);
+        vu = *reinterpret_cast<const uint4*>(v_cache + row);
+      }
     }
     const float2 k0 = unpack_bf16x2(ku.x), k1 = unpack_bf16x2(ku.y), k2 = unpack_bf16x2(ku.z), k3 = unpack_bf16x2(ku.w);
     float s = qv[0] * k0.x + qv[1] * k0.y + qv[2] * k1.x + qv[3] * k1.y + qv[4] * k2.x + qv[5] * k2.y + qv[6] * k3.x +
@@ -122,12 +134,16 @@ __global__ void paged_decode_merge_kernel(const float* __restrict__ part_o, cons
 // cache[slot] = K (V) row of qkv for every request row; slot = page * page_size + offset (negative: skip).
 __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ k_cache,
                                  __nv_bfloat16* __restrict__ v_cache, const long long* __restrict__ slots, long long rows,
-                                 int d) {
+                                 int d, long long num_slots, uint32_t* __restrict__ status) {
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const long long slot = slots[row];
   if (slot < 0) return;
+  if (slot >= num_slots) {      // beyond the cache: report, do not write
+    if (lane == 0 && status != nullptr) atomicCAS(status, 0u, ERR_BAD_ARG | (3u << 8));
+    return;
+  }
   const __nv_bfloat16* src = qkv + (size_t)row * 3 * d;
   for (int c = lane * 8; c < d; c += 256) {
     *reinterpret_cast<uint4*>(k_cache + (size_t)slot * d + c) = *reinterpret_cast<const uint4*>(src + d + c);
@@ -144,8 +160,9 @@ using namespace b200;
 extern "C" int b200_paged_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
                                  const int* context_lens, void* out, float* part_o, float* part_ml, int rows, int q_ld,
                                  int heads, int dh, int page_size, int max_pages, int splits, float scale,
-                                 cudaStream_t st) {
+                                 int num_pages, uint32_t* status, cudaStream_t st) {
   if (dh != 64 && dh != 128) return -10;
+  if (page_size <= 0 || max_pages <= 0 || num_pages <= 0) return -11;
   if (q_ld % 8 || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
       (reinterpret_cast<uintptr_t>(v_cache) & 15))
     return -10;
@@ -156,24 +173,26 @@ extern "C" int b200_paged_decode(const void* q, const void* k_cache, const void*
   if (dh == 128) {
     paged_decode_kernel<128><<<grid, PD_THREADS, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
                                                           (const __nv_bfloat16*)v_cache, block_tables, context_lens,
-                                                          part_o, part_ml, q_ld, heads, page_size, max_pages, splits, sl2);
+                                                          part_o, part_ml, q_ld, heads, page_size, max_pages, splits, sl2,
+                                                          num_pages, status);
     paged_decode_merge_kernel<128><<<rows * heads, 128, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, heads, splits);
   } else {
     paged_decode_kernel<64><<<grid, PD_THREADS, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
                                                          (const __nv_bfloat16*)v_cache, block_tables, context_lens,
-                                                         part_o, part_ml, q_ld, heads, page_size, max_pages, splits, sl2);
+                                                         part_o, part_ml, q_ld, heads, page_size, max_pages, splits, sl2,
+                                                          num_pages, status);
     paged_decode_merge_kernel<64><<<rows * heads, 64, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, heads, splits);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int b200_kv_append(const void* qkv, void* k_cache, void* v_cache, const long long* slots, long long rows,
-                              int d, cudaStream_t st) {
+                              int d, long long num_slots, uint32_t* status, cudaStream_t st) {
   if (d % 8 || (reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
       (reinterpret_cast<uintptr_t>(v_cache) & 15))
     return -10;
   if (rows <= 0) return 0;
   kv_append_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)k_cache,
-                                                               (__nv_bfloat16*)v_cache, slots, rows, d);
+                                                               (__nv_bfloat16*)v_cache, slots, rows, d, num_slots, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -355,8 +355,22 @@ class TransformerLM(nn.Module):
     @torch.no_grad()
     def generate(self, prompt_ids: Tensor, max_new_tokens: int, temperature: float = 1.0,
                  top_k: int | None = None, eos_token_id: int | None = None) -> Tensor:
-        """Sample up to ``max_new_tokens`` continuation ids; returns only the new ids, shape (1, n)."""
+        """Sample up to ``max_new_tokens`` continuation ids; returns only the new ids, shape (1, n).
+
+        With the fused engine a single prompt that fits the context window runs through the paged-KV serving engine
+        (one prefill, then one cached decode step per token) instead of re-running the whole context for every
+        token as the reference does (llm-core/llm_core/model.py:210-233); longer generations slide the window with
+        the re-forward loop below, which is also what the eager model uses."""
         ids = prompt_ids.unsqueeze(0) if prompt_ids.dim() == 1 else prompt_ids
+        if (self.native_supported() and ids.shape[0] == 1 and max_new_tokens > 0
+                and 0 < ids.shape[1] and ids.shape[1] + max_new_tokens <= self.context_length):
+            from ..serving import ServingEngine
+            need = -(-(ids.shape[1] + max_new_tokens) // 16) + 1
+            eng = ServingEngine(self, num_pages=need, page_size=16, max_batch=1, use_cuda_graphs=False)
+            out = eng.generate([ids[0].tolist()], max_new_tokens, eos_token_id, temperature, top_k)[0]
+            if eos_token_id is not None and out and out[-1] == eos_token_id:
+                out = out[:-1]                       # the contract of this method: the stop token is not returned
+            return torch.tensor([out], dtype=torch.long, device=ids.device).reshape(1, -1)
         new: list[Tensor] = []
         for _ in range(max_new_tokens):
             window = ids[:, -self.context_length:]

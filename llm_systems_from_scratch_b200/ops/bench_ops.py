@@ -7,6 +7,7 @@
     python -m llm_systems_from_scratch_b200.ops.bench_ops gemm-pair-small # three launches of the CTA-pair GEMM (for ncu)
     python -m llm_systems_from_scratch_b200.ops.bench_ops attention-small # one small attention fwd+bwd (for ncu)
     python -m llm_systems_from_scratch_b200.ops.bench_ops attention-trace # in-kernel timeline of one CTA per kernel
+    python -m llm_systems_from_scratch_b200.ops.bench_ops decode [ctx]    # serving decode step vs its memory roofline
 
 Each line of output is one JSON record.  The "-small" modes exist so that a profiler capture ends by
 itself in seconds: inputs are larger than L2 but only a few hundred MB.
@@ -190,9 +191,85 @@ def attention_trace():
     native.check_status()
 
 
+def bench_decode(argv=()):
+    """Decode step of the 1.3B serving model against its memory roofline, per batch bucket.
+
+    A decode step must read every weight once (2.84 GB in bf16) and every cached K / V byte of the running requests
+    once; roofline = those bytes over the measured copy bandwidth.  Reports the whole engine step (host preparation,
+    H2D of the step's inputs, graph replay, D2H of the sampled tokens), the device time of the graph alone, and the
+    paged-attention kernel and the small-M GEMMs on their own."""
+    import os
+    from ..models.transformer import TransformerLM
+    from ..serving import Request, ServingEngine
+    from . import serving_ops
+    ctx = int(argv[0]) if argv else 1200
+    hbm = 6541.8
+    try:
+        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            hbm = float(json.load(f)["hbm_gbs"])
+    except Exception:
+        pass
+    cfg = dict(vocab_size=50257, context_length=2048, d_model=2048, num_layers=24, num_heads=16, d_ff=5504, rope_theta=10000.0)
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = TransformerLM(**cfg, use_flash_attn=True, use_custom_triton=True)
+    model.eval()
+    eng = ServingEngine(model, page_size=16, max_batch=256, max_context=2048)
+    weight_bytes = 2 * (cfg["num_layers"] * (4 * 2048 * 2048 + 3 * 2048 * 5504) + 50257 * 2048)
+    g = torch.Generator().manual_seed(1)
+    for batch in (32, 64, 128, 256):
+        reqs = [Request(i, torch.randint(0, 50257, (ctx,), generator=g).tolist(), 8) for i in range(batch)]
+        for r in reqs:
+            eng.sched.add(r)
+        eng._realtime, eng._virtual = False, float("inf")
+        while eng.sched.waiting:
+            eng.step(float("inf"))
+        running = list(eng.sched.running)
+        assert len(running) == batch, (len(running), batch)
+        for _ in range(3):
+            eng.decode(running)
+        torch.cuda.synchronize()
+        import time
+        t0 = time.perf_counter()
+        n_it = 20
+        for _ in range(n_it):
+            eng.decode(running)
+        torch.cuda.synchronize()
+        step_ms = (time.perf_counter() - t0) / n_it * 1e3
+        st = eng._graphs[eng._bucket(batch)]
+        dev_ms = timeit(lambda: st["graph"].replay(), iters=10, warm=2, flush=False)
+        kv_bytes = sum(r.context_len for r in running) * 2 * 2048 * 2 * cfg["num_layers"]
+        roof_ms = (weight_bytes + kv_bytes) / hbm / 1e6
+        # the attention kernel of one layer on the same tables
+        qkv = torch.randn(eng._bucket(batch), 3 * 2048, device="cuda").bfloat16()
+        att_ms = timeit(lambda: serving_ops.paged_decode_attention(qkv, eng.cache.k[0], eng.cache.v[0], st["tables"],
+                                                                   st["ctx"], 16, st["splits"]), iters=10, warm=2)
+        print(json.dumps({"op": "decode-step", "batch": batch, "context": ctx, "step_ms": round(step_ms, 3),
+                          "graph_ms": round(dev_ms, 3), "roofline_ms": round(roof_ms, 3),
+                          "fraction_of_roofline": round(roof_ms / step_ms, 3), "tok_per_s": round(batch / step_ms * 1e3),
+                          "paged_attention_layer_ms": round(att_ms, 4),
+                          "paged_attention_gbs": round(kv_bytes / cfg["num_layers"] / att_ms / 1e6, 1)}), flush=True)
+        for r in running:
+            r.output.extend([0] * 8)
+        eng.sched.retire(0.0)
+    for m in (32, 64, 128, 256):
+        for n, k in ((6144, 2048), (2048, 2048), (11008, 2048), (2048, 5504), (50264, 2048)):
+            a = torch.randn(m, k, device="cuda").bfloat16()
+            b = torch.randn(n, k, device="cuda").bfloat16()
+            out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+            t = timeit(lambda: native.gemm(a, b, "nt", out=out))
+            t2 = timeit(lambda: torch.matmul(a, b.t(), out=out))
+            print(json.dumps({"op": "gemm-decode", "m": m, "n": n, "k": k, "us": round(t * 1e3, 1),
+                              "weight_gbs": round(n * k * 2 / t / 1e6, 1), "cublas_us": round(t2 * 1e3, 1)}), flush=True)
+    native.check_status()
+
+
 def main(argv=None):
     argv = argv if argv is not None else sys.argv[1:]
     mode = argv[0] if argv else "gemm"
+    if mode == "decode":
+        return bench_decode(argv[1:])
     {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "gemm-small": gemm_small, "gemm-pair-small": gemm_pair_small, "attention-trace": attention_trace,
      "attention-small": attention_small}[mode]()
 

@@ -96,8 +96,6 @@ def _declare(lib):
         "b200_flash_bwd_rope": [P, P, P, P, P, P, I, I, I, I, F, P, I, P, P],
         "b200_gemm_bf16_pair_rope": [P, P, P, I, I, I, L, L, L, P, I, I, I, I, P, P],
         "b200_gemm_bf16_pair_swiglu": [P, P, P, P, I, I, I, L, L, L, L, P, P, ctypes.c_ulonglong, I, I, P, P],
-        "b200_paged_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P],
-        "b200_kv_append": [P, P, P, P, L, I, P],
         "b200_sample": [P, L, L, I, F, I, P, P, P, P],
     }
     for name, args in {**sigs, **optional}.items():

@@ -16,9 +16,9 @@ def _lib():
     lib = native.load()
     if not _declared:
         P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-        lib.b200_paged_decode.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P]
+        lib.b200_paged_decode.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
         lib.b200_paged_decode.restype = I
-        lib.b200_kv_append.argtypes = [P, P, P, P, L, I, P]
+        lib.b200_kv_append.argtypes = [P, P, P, P, L, I, L, P, P]
         lib.b200_kv_append.restype = I
         _declared = True
     return lib
@@ -33,8 +33,11 @@ def kv_append(k_cache, v_cache, qkv, slot_mapping):
     d = qkv.shape[1] // 3
     native._req(qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and k_cache.is_contiguous(), "bad kv_append inputs")
     native._req(slot_mapping.dtype == torch.int64 and slot_mapping.numel() == qkv.shape[0], "bad slot mapping")
+    native._req(k_cache.shape == v_cache.shape and k_cache.shape[-1] == d, "cache shape does not match qkv")
+    num_slots = k_cache.shape[0] * k_cache.shape[1]
     native._check(lib.b200_kv_append(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(),
-                                     qkv.shape[0], d, native._stream()), "kv_append")
+                                     qkv.shape[0], d, num_slots, native.status_word(qkv.device).data_ptr(),
+                                     native._stream()), "kv_append")
 
 
 def choose_splits(rows: int, heads: int, max_context: int, sms: int = 148) -> int:
@@ -49,7 +52,8 @@ def paged_decode_attention(qkv, k_cache, v_cache, block_tables, context_lens, n_
 
     qkv: (R, 3d) packed (only the query third is read) or (R, d); caches: (num_pages, page_size, d);
     block_tables: (R, max_pages) int32; context_lens: (R,) int32, number of cached tokens to attend to.
-    Returns (R, d).
+    Returns (R, d).  The values inside the tables are checked on the device: a length beyond ``max_pages * page`` or
+    a page id beyond the cache is skipped and recorded in the status word (``native.check_status`` raises).
     """
     r, width = qkv.shape
     d = k_cache.shape[-1]
@@ -59,6 +63,10 @@ def paged_decode_attention(qkv, k_cache, v_cache, block_tables, context_lens, n_
     lib = _lib()
     native._req(qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1, "qkv must be bf16 with unit inner stride")
     native._req(block_tables.dtype == torch.int32 and context_lens.dtype == torch.int32, "tables must be int32")
+    native._req(block_tables.dim() == 2 and block_tables.is_contiguous() and block_tables.shape[0] >= r
+                and context_lens.is_contiguous() and context_lens.numel() >= r, "one table row and one length per request")
+    native._req(k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape == v_cache.shape and
+                width in (d, 3 * d) and dh * n_heads == d, "cache / query shapes do not match")
     page = k_cache.shape[1]
     max_pages = block_tables.shape[1]
     if splits <= 0:
@@ -71,5 +79,6 @@ def paged_decode_attention(qkv, k_cache, v_cache, block_tables, context_lens, n_
     native._check(lib.b200_paged_decode(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                                         context_lens.data_ptr(), out.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(),
                                         r, qkv.stride(0), n_heads, dh, page, max_pages, splits, 1.0 / math.sqrt(dh),
-                                        native._stream()), "paged_decode")
+                                        k_cache.shape[0], native.status_word(qkv.device).data_ptr(), native._stream()),
+                  "paged_decode")
     return out

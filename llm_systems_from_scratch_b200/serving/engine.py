@@ -63,6 +63,7 @@ class ServingEngine:
             self._host_rt = host_runtime if host_runtime.available() else None
         except Exception:
             self._host_rt = None
+        self._temperature, self._top_k = 0.0, None
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "prefill_steps": 0}
 
     # ------------------------------------------------------------------ model pieces
@@ -85,7 +86,25 @@ class ServingEngine:
         return buf
 
     def _greedy(self, logits_buf):
-        return ops.argmax_rows(logits_buf, self.cfg.vocab)
+        """Next token per row: argmax, or a draw from softmax(logits / temperature) over the top-k logits when
+        ``set_sampling`` asked for one (one kernel on the GPU: filter, softmax and inverse-CDF draw, no sort)."""
+        if self._temperature == 0:
+            return ops.argmax_rows(logits_buf, self.cfg.vocab)
+        rows = logits_buf.shape[0]
+        if logits_buf.is_cuda and logits_buf.dtype == torch.bfloat16:
+            u = torch.rand(rows, device=logits_buf.device)
+            return ops.sample_topk(logits_buf, u, self._temperature, self._top_k, self.cfg.vocab)
+        last = logits_buf[:, :self.cfg.vocab].float() / self._temperature
+        if self._top_k:
+            kth = torch.topk(last, min(self._top_k, last.shape[-1])).values[:, -1:]
+            last = last.masked_fill(last < kth, float("-inf"))
+        return torch.multinomial(torch.softmax(last, dim=-1), 1).reshape(-1)
+
+    def set_sampling(self, temperature: float = 0.0, top_k: int | None = None):
+        """temperature 0 = greedy.  Decode graphs captured under another setting are dropped."""
+        if (temperature, top_k) != (self._temperature, self._top_k):
+            self._temperature, self._top_k = float(temperature), top_k
+            self._graphs.clear()
 
     # ------------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -250,8 +269,12 @@ class ServingEngine:
                 if realtime and nxt is not None and nxt > now:
                     time.sleep(min(nxt - now, 0.05))
                     continue
-            if self.step(now) == 0 and not self.sched.running and self.sched.waiting and not realtime:
-                raise RuntimeError("request does not fit in the KV cache")
+            produced = self.step(now)
+            if produced == 0 and not self.sched.running and self.sched.waiting:
+                head = self.sched.waiting[0]
+                if not realtime or head.arrival <= now:
+                    # nothing runs, so every page is free, and the oldest arrived request still was not admitted
+                    raise RuntimeError(f"request {head.rid} does not fit in the KV cache")
         if self.cuda:
             torch.cuda.synchronize()
         wall = time.perf_counter() - self._t0
@@ -272,8 +295,11 @@ class ServingEngine:
                 "ttft_p50_s": ttft.pct(50), "ttft_p99_s": ttft.pct(99), "latency_p50_s": lat.pct(50),
                 "kv_pages": self.cache.num_pages, "kv_occupancy_end": self.cache.occupancy()}
 
-    def generate(self, prompts: list[list[int]], max_new_tokens: int, eos_token_id: int | None = None) -> list[list[int]]:
-        """Offline batched greedy generation through the continuous-batching loop."""
+    def generate(self, prompts: list[list[int]], max_new_tokens: int, eos_token_id: int | None = None,
+                 temperature: float = 0.0, top_k: int | None = None) -> list[list[int]]:
+        """Offline batched generation through the continuous-batching loop (greedy unless a temperature is given).
+        An end-of-sequence token ends a request and is part of its output."""
+        self.set_sampling(temperature, top_k)
         reqs = [Request(i, list(p), max_new_tokens, 0.0, eos_token_id) for i, p in enumerate(prompts)]
         self.run(reqs, realtime=False)
         return [r.output for r in reqs]

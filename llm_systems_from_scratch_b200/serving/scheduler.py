@@ -68,6 +68,10 @@ class Scheduler:
         if len(req.prompt) + req.max_new_tokens > self.max_context:
             raise ValueError(f"request {req.rid} needs {len(req.prompt) + req.max_new_tokens} positions, "
                              f"limit is {self.max_context}")
+        total = getattr(self.alloc, "num_pages", None)
+        if total is not None and self._pages_needed(req) > total:
+            # it could never be admitted: refuse it here instead of letting the engine wait for pages forever
+            raise ValueError(f"request {req.rid} needs {self._pages_needed(req)} KV pages, the cache has {total}")
         self.waiting.append(req)
 
     def _pages_needed(self, req: Request) -> int:

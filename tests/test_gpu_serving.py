@@ -35,6 +35,38 @@ def test_kv_append_writes_only_selected_slots():
     assert int((kf.abs().sum(-1) > 0).sum()) == 3
 
 
+def test_paged_kernels_report_bad_tables_instead_of_reading_them():
+    """A page id beyond the cache, a length beyond the table and a slot beyond the cache are skipped and recorded in
+    the status word; good rows of the same launch are unaffected and the context stays usable."""
+    from llm_systems_from_scratch_b200.ops import native, serving_ops, torch_impl
+    heads, dh, page, n_pages, r = 4, 128, 16, 32, 3
+    d = heads * dh
+    g = torch.Generator(device="cuda").manual_seed(0)
+    kc = torch.randn(n_pages, page, d, device="cuda", generator=g).bfloat16()
+    vc = torch.randn(n_pages, page, d, device="cuda", generator=g).bfloat16()
+    qkv = torch.randn(r, 3 * d, device="cuda", generator=g).bfloat16()
+    tables = torch.stack([torch.randperm(n_pages, device="cuda", generator=g)[:4] for _ in range(r)]).int()
+    good_lens = torch.tensor([10, 33, 64], dtype=torch.int32, device="cuda")
+    ref = torch_impl.paged_decode_attention(qkv[:, :d].float(), kc.float(), vc.float(), tables.cpu(), good_lens.cpu(), heads)
+    native.status_word().zero_()
+    for bad_tables, bad_lens in ((tables.clone().index_put_((torch.tensor([1]), torch.tensor([0])), torch.tensor(n_pages + 7, dtype=torch.int32, device="cuda")), good_lens),
+                                 (tables, torch.tensor([10, 33, 4 * page + 1], dtype=torch.int32, device="cuda"))):
+        out = serving_ops.paged_decode_attention(qkv, kc, vc, bad_tables, bad_lens, heads, 2)
+        torch.cuda.synchronize()
+        with pytest.raises(native.KernelError):
+            native.check_status()
+        assert (out[0].float() - ref[0]).abs().max().item() < 2e-2       # the untouched row is still right
+        assert torch.isfinite(out.float()).all()
+    before = kc.clone()
+    serving_ops.kv_append(kc, vc, qkv, torch.tensor([3, n_pages * page, -1], device="cuda"))
+    torch.cuda.synchronize()
+    with pytest.raises(native.KernelError):
+        native.check_status()
+    changed = (kc.view(-1, d) != before.view(-1, d)).any(-1).nonzero().flatten().tolist()
+    assert changed == [3]
+    native.check_status()                                                 # cleared; nothing pending
+
+
 @pytest.mark.parametrize("graphs", [False, True])
 def test_engine_matches_full_recompute_on_gpu(graphs):
     from llm_systems_from_scratch_b200.models.transformer import TransformerLM

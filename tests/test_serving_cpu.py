@@ -111,3 +111,28 @@ def test_host_runtime_matches_python_paths():
     assert hr.slots(pages, 16, 14, 20) == [pages[t // 16] * 16 + t % 16 for t in range(14, 34)]
     table = hr.block_table([[1, 2, 3], [4], []], 4, pad=-1)
     assert table.tolist() == [[1, 2, 3, -1], [4, -1, -1, -1], [-1, -1, -1, -1]]
+
+
+def test_generate_runs_through_the_paged_kv_engine():
+    """``TransformerLM.generate`` on the fused engine (prefill + cached decode steps) returns the tokens of the
+    reference-style loop that re-runs the whole context for every token; the stop token is not returned."""
+    from llm_systems_from_scratch_b200.models.transformer import TransformerLM
+    torch.manual_seed(0)
+    cfg = dict(vocab_size=211, context_length=64, d_model=64, num_layers=2, num_heads=4, d_ff=136, rope_theta=10000.0)
+    fused = TransformerLM(**cfg, use_custom_triton=True).eval()
+    eager = TransformerLM(**cfg, use_custom_triton=False).eval()
+    eager.load_state_dict(fused.canonical_state_dict())
+    prompt = torch.randint(0, 211, (9,), generator=torch.Generator().manual_seed(3))
+    want = eager.generate(prompt, 12, temperature=0)            # eager modules: the re-forward loop
+    got = fused.generate(prompt, 12, temperature=0)             # fused engine: paged KV cache
+    assert got.shape == (1, 12) and torch.equal(got, want)
+    stop = int(want[0, 5])
+    cut = fused.generate(prompt, 12, temperature=0, eos_token_id=stop)
+    first = want[0].tolist().index(stop)
+    assert cut[0].tolist() == want[0, :first].tolist()
+    torch.manual_seed(1)
+    sampled = fused.generate(prompt, 12, temperature=0.8, top_k=5)
+    assert sampled.shape == (1, 12) and int(sampled.max()) < 211
+    # beyond the context window the sliding re-forward loop still serves the call
+    long = fused.generate(prompt, 64, temperature=0)
+    assert long.shape == (1, 64)
