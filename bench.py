@@ -18,6 +18,17 @@ Two numbers are measured, both on the device with CUDA events and reduced as the
 
 ``--impl reference`` runs the unmodified reference implementation (installed under baseline/_ref)
 through its own public classes on the same config and prints the same JSON line.
+
+Serving (the second half of the headline metric: continuous-batching decode tokens/s and time to first
+token of the 1.3B model under a Poisson trace, one replica per GPU):
+
+    python bench.py --workload serve [--gpus N] [--serving-requests 1024]
+
+prints a line of its own (``serving_decode_tok_per_s``).  The default training run appends a short
+version of the same measurement (``--serving-requests`` requests, 0 switches it off) under the key
+``serving`` of its JSON line, so that one command reports both halves.  The reference has no serving
+engine; its arm replays the head of the same trace through its ``TransformerLM`` with a per-request greedy
+loop that re-runs the whole context for every token (what its ``generate`` does) for a bounded time.
 """
 from __future__ import annotations
 
@@ -45,6 +56,11 @@ CONFIGS = {
 }
 
 LR, WEIGHT_DECAY, MAX_GRAD_NORM = 3e-4, 0.1, 1.0
+
+# continuous-batching serving of the 1.3B model: Poisson arrivals per GPU, 16-token KV pages, greedy decoding
+SERVE = dict(model="TransformerLM-1.3B", vocab_size=50257, context_length=2560, d_model=2048, num_layers=24,
+             num_heads=16, d_ff=5504, rope_theta=10000.0, page_size=16, max_batch=256, rate=20.0,
+             prompt_len=(128, 2048), output_len=(64, 512))
 
 
 class ClockSampler:
@@ -114,6 +130,12 @@ def parse_args():
     ap.add_argument("--fused-optimizer", choices=["auto", "on", "off"], default="auto",
                     help="FSDP on 2+ GPUs: run AdamW inside each unit's reduce-scatter (clip coefficient from the previous "
                          "step's norm); auto = on.  off = reduce-scatter, exact global-norm clip, then one AdamW launch")
+    ap.add_argument("--workload", choices=["train", "serve"], default="train")
+    ap.add_argument("--serving-requests", type=int, default=None,
+                    help="requests of the Poisson trace per GPU (serve: default 1024; train: a short serving run of "
+                         "this many requests is appended to the line, default 160, 0 = none)")
+    ap.add_argument("--serving-time-limit", type=float, default=20.0,
+                    help="seconds after which the reference's per-request loop stops")
     ap.add_argument("--seed", type=int, default=0)
     return ap.parse_args()
 
@@ -267,6 +289,87 @@ def run_native(args, cfg, rank, local_rank, world):
                            "AdamW fp32 state, one launch, exact global-norm clip 1.0"))
 
 
+def run_serving(args, rank, local_rank, world, n_requests):
+    """One serving replica on this rank's GPU: the Poisson trace in real time (decode tokens/s, TTFT), then the
+    first requests again with arrival times ignored (throughput).  Prompts start as host token lists and every
+    sampled token is read back to the host, so the numbers are end to end by construction."""
+    import torch
+    sys.path.insert(0, ROOT)
+    from llm_systems_from_scratch_b200.serving import ServingEngine, poisson_trace
+    dev = torch.device("cuda", local_rank)
+    keys = ("vocab_size", "context_length", "d_model", "num_layers", "num_heads", "d_ff", "rope_theta")
+    trace = poisson_trace(n_requests, SERVE["rate"], SERVE["prompt_len"], SERVE["output_len"], SERVE["vocab_size"],
+                          seed=args.seed + rank)
+    if args.impl == "reference":
+        ref_dir = os.path.join(ROOT, "baseline", "_ref")
+        if not os.path.isdir(os.path.join(ref_dir, "llm_core")):
+            return {"unavailable": "reference is not installed under baseline/_ref"}
+        sys.path.insert(0, ref_dir)
+        from llm_core.model import TransformerLM as RefLM
+        from serve import naive_loop
+        torch.manual_seed(args.seed)
+        model = RefLM(**{k: SERVE[k] for k in keys}, use_flash_attn=True).to(dev).eval()
+        res = naive_loop(model, trace, str(dev), args.serving_time_limit)
+        del model
+        torch.cuda.empty_cache()
+        return {"decode_tok_per_s": res["decode_tok_per_s"], "ttft_p50_ms": res["ttft_p50_s"] * 1e3, "ttft_p99_ms": None,
+                "requests": res["requests"], "output_tokens": res["output_tokens"], "wall_s": res["wall_s"],
+                "offline_tok_per_s": None, "engine": "none: per-request greedy loop over the reference TransformerLM, whole "
+                "context re-run per token, stopped after --serving-time-limit seconds", "launches": None}
+    from llm_systems_from_scratch_b200.models.transformer import TransformerLM
+    from llm_systems_from_scratch_b200.ops import native
+    torch.manual_seed(args.seed)
+    with torch.device(dev):
+        model = TransformerLM(**{k: SERVE[k] for k in keys}, use_flash_attn=True, use_custom_triton=True)
+    model.eval()
+    eng = ServingEngine(model, page_size=SERVE["page_size"], max_batch=SERVE["max_batch"],
+                        max_context=SERVE["context_length"])
+    native.reset_launch_count()
+    res = eng.run(trace, realtime=True)
+    native.check_status()
+    launches = native.launch_count()
+    off_trace = poisson_trace(min(n_requests, 512), SERVE["rate"], SERVE["prompt_len"], SERVE["output_len"],
+                              SERVE["vocab_size"], seed=args.seed + 1000 + rank)
+    off = eng.run(off_trace, realtime=False)
+    native.check_status()
+    out = {"decode_tok_per_s": res["decode_tok_per_s"], "ttft_p50_ms": res["ttft_p50_s"] * 1e3,
+           "ttft_p99_ms": res["ttft_p99_s"] * 1e3, "requests": res["requests"], "output_tokens": res["output_tokens"],
+           "wall_s": res["wall_s"], "offline_tok_per_s": off["decode_tok_per_s"], "offline_requests": off["requests"],
+           "decode_steps": res["decode_steps"], "prefill_tokens": res["prefill_tokens"], "kv_pages": res["kv_pages"],
+           "engine": f"continuous batching, paged KV ({SERVE['page_size']}-token pages), max batch {SERVE['max_batch']}, "
+                     "CUDA-graphed decode steps", "launches": launches}
+    del eng, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def gather_serving(rec, world):
+    """Whole-job serving record: tokens/s add up over the replicas, TTFT is the median / worst of the replicas'."""
+    if world == 1 or rec is None:
+        return rec
+    import torch.distributed as dist
+    allr = [None] * world
+    dist.all_gather_object(allr, rec)
+    if any("unavailable" in r for r in allr):
+        return next(r for r in allr if "unavailable" in r)
+    wall = max(r["wall_s"] for r in allr)
+    out = dict(allr[0])
+    out.update(decode_tok_per_s=sum(r["output_tokens"] for r in allr) / wall, wall_s=wall,
+               requests=sum(r["requests"] for r in allr), output_tokens=sum(r["output_tokens"] for r in allr),
+               ttft_p50_ms=statistics.median(r["ttft_p50_ms"] for r in allr),
+               ttft_p99_ms=None if allr[0]["ttft_p99_ms"] is None else max(r["ttft_p99_ms"] for r in allr),
+               offline_tok_per_s=None if allr[0]["offline_tok_per_s"] is None else sum(r["offline_tok_per_s"] for r in allr),
+               per_replica_tok_per_s=[round(r["decode_tok_per_s"], 1) for r in allr])
+    return out
+
+
+def serving_config():
+    return {"model": SERVE["model"], "arrival": f"Poisson {SERVE['rate']} requests/s per GPU", "prompt_len": list(SERVE["prompt_len"]),
+            "output_len": list(SERVE["output_len"]), "page_size": SERVE["page_size"], "decoding": "greedy",
+            "replicas": "one data-parallel replica per GPU", "vocab": SERVE["vocab_size"], "d_model": SERVE["d_model"],
+            "layers": SERVE["num_layers"], "heads": SERVE["num_heads"], "d_ff": SERVE["d_ff"]}
+
+
 def run_reference(args, cfg, rank, local_rank, world):
     """The reference's own classes on its stock fastest path: bf16 autocast, SDPA, Triton kernels, its FSDP."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
@@ -354,6 +457,35 @@ def main():
             return 0
         raise
     rank, local_rank, world = init_dist(args)
+    if args.workload == "serve":
+        n_req = args.serving_requests if args.serving_requests is not None else 1024
+        clocks = ClockSampler(local_rank) if rank == 0 else None
+        if clocks:
+            clocks.start()
+        rec = gather_serving(run_serving(args, rank, local_rank, world, n_req), world)
+        clk = clocks.stop() if clocks else None
+        if rank == 0:
+            if "unavailable" in rec:
+                print(json.dumps({"impl": args.impl, "workload": "serve", "unavailable": rec["unavailable"]}))
+            else:
+                r1 = lambda v: None if v is None else round(v, 1)
+                print(json.dumps({
+                    "metric": "serving_decode_tok_per_s", "value": r1(rec["decode_tok_per_s"]), "unit": "tokens/s",
+                    "n_gpus": world, "steps": rec["requests"], "warmup": 0, "higher_is_better": True, "scaling": "weak",
+                    "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
+                    "ttft_p50_ms": r1(rec["ttft_p50_ms"]), "ttft_p99_ms": r1(rec["ttft_p99_ms"]),
+                    "offline_tok_per_s": r1(rec["offline_tok_per_s"]), "output_tokens": rec["output_tokens"],
+                    "wall_s": round(rec["wall_s"], 2), "config": serving_config(), "engine": rec["engine"], "clocks": clk,
+                    "e2e": {"value": r1(rec["decode_tok_per_s"]), "unit": "tokens/s",
+                            "note": "prompts are host token lists copied to the device per prefill; every sampled token is "
+                                    "read back to the host each decode step"},
+                    "gpu_launches": rec["launches"],
+                    "timing": "wall clock around the trace with a device synchronisation on both sides (arrival-driven "
+                              "workload); max over replicas"}))
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        return 0
     if args.impl == "reference":
         try:
             res, why = run_reference(args, cfg, rank, local_rank, world)
@@ -365,6 +497,17 @@ def main():
             return 0
     else:
         res = run_native(args, cfg, rank, local_rank, world)
+    # second half of the headline metric, short form: a serving replica per GPU after the training model is gone
+    n_serv = 160 if args.serving_requests is None else args.serving_requests
+    serving = None
+    if n_serv > 0 and args.config == "fsdp_1p3b":
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            serving = gather_serving(run_serving(args, rank, local_rank, world, n_serv), world)
+        except torch.cuda.OutOfMemoryError as e:
+            serving = gather_serving({"unavailable": f"out of device memory: {str(e)[:100]}"}, world)
     if rank == 0:
         ms_step = res["ms"] / args.steps
         value = res["tokens_per_step"] / (ms_step / 1e3)
@@ -384,6 +527,12 @@ def main():
             "gpu_launches": res["launches"],
             "final_loss": round(res["loss"], 4), "peak_mem_gb": round(res["mem_gb"], 2),
         }
+        if serving is not None:
+            if "unavailable" not in serving:
+                serving = {k: (round(v, 1) if isinstance(v, float) else v) for k, v in serving.items()}
+                serving["metric"] = "serving_decode_tok_per_s"
+                serving["config"] = serving_config()
+            line["serving"] = serving
         print(json.dumps(line))
     if world > 1 or args.impl == "reference":
         import torch.distributed as dist

@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import base64
 import json
+import mmap
 import multiprocessing
 import os
 import re
@@ -31,39 +32,29 @@ _PRE = regex.compile(PRE_TOKENIZE_REGEX)
 
 
 def find_chunk_boundaries(file: BinaryIO, desired_num_chunks: int, split_special_token: bytes) -> list[int]:
-    """Byte offsets that cut ``file`` into up to ``desired_num_chunks`` pieces, each cut placed at the
-    next occurrence of ``split_special_token`` so that no document is split."""
-    assert isinstance(split_special_token, bytes), "Must represent special token as a bytestring"
-    file.seek(0, os.SEEK_END)
-    size = file.tell()
-    step = size // desired_num_chunks
-    cuts = [i * step for i in range(desired_num_chunks + 1)]
-    cuts[-1] = size
-    probe = 4096
-    for i in range(1, len(cuts) - 1):
-        pos = cuts[i]
-        file.seek(pos)
-        while True:
-            buf = file.read(probe)
-            if not buf:
-                cuts[i] = size
-                break
-            hit = buf.find(split_special_token)
-            if hit >= 0:
-                cuts[i] = pos + hit
-                break
-            pos += probe
-    return sorted(set(cuts))
+    """Byte offsets that cut ``file`` into at most ``desired_num_chunks`` pieces without splitting a document: the
+    file is mapped into memory and every interior cut is moved forward to the next occurrence of
+    ``split_special_token`` with one ``find`` (to the end of the file when there is none).  Same contract as the
+    reference helper (tokenizer/BPETokenizer.py:14-49): sorted, de-duplicated, first 0 and last the file size."""
+    if not isinstance(split_special_token, bytes):
+        raise TypeError("Must represent special token as a bytestring")
+    size = os.fstat(file.fileno()).st_size
+    if size == 0:
+        return [0]
+    with mmap.mmap(file.fileno(), 0, access=mmap.ACCESS_READ) as view:
+        interior = (view.find(split_special_token, k * (size // desired_num_chunks)) for k in range(1, desired_num_chunks))
+        cuts = {0, size} | {size if hit < 0 else hit for hit in interior}
+    return sorted(cuts)
 
 
 def get_chunk(input_path: str, desired_num_chunks: int) -> list[str]:
-    out = []
+    """The pieces of ``input_path`` between the boundaries of ``find_chunk_boundaries``, decoded as UTF-8."""
     with open(input_path, "rb") as f:
         cuts = find_chunk_boundaries(f, desired_num_chunks, b"<|endoftext|>")
-        for a, b in zip(cuts[:-1], cuts[1:]):
-            f.seek(a)
-            out.append(f.read(b - a).decode("utf-8", errors="ignore"))
-    return out
+        if len(cuts) < 2:
+            return []
+        with mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ) as view:
+            return [view[a:b].decode("utf-8", errors="ignore") for a, b in zip(cuts, cuts[1:])]
 
 
 @dataclass
