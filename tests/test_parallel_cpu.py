@@ -180,3 +180,27 @@ def test_flag_protocol_model_checker():
         except ProtocolViolation:
             found += 1
     assert found > 0
+
+
+def test_allreduce_and_weight_gather_protocols():
+    """The two other flag protocols under random interleavings: the two-shot in-place all-reduce (a chunk is read only
+    while it holds local gradients, consumed only when reduced) and the FSDP weight shards (gathers of step s read
+    version s - 1 and never overlap an update; gather slots are not refilled while in use).  Each checker must also
+    find the race when the wait that prevents it is taken out."""
+    from llm_systems_from_scratch_b200.parallel.protocol_check import (ProtocolViolation, check_allreduce_protocol,
+                                                                     check_weight_gather_protocol)
+    for seed in range(150):
+        check_allreduce_protocol(world=2 + seed % 4, buckets=1 + seed % 3, steps=3, seed=seed)
+        check_weight_gather_protocol(world=2 + seed % 4, units=1 + seed % 4, steps=3, seed=seed,
+                                     fused_update=bool(seed % 2))
+    found_ar = found_w = 0
+    for seed in range(100):
+        try:
+            check_allreduce_protocol(world=4, buckets=1, steps=3, seed=seed, wait_for_pushes=False)
+        except ProtocolViolation:
+            found_ar += 1
+        try:
+            check_weight_gather_protocol(world=4, units=2, steps=3, seed=seed, await_weights=False)
+        except ProtocolViolation:
+            found_w += 1
+    assert found_ar > 0 and found_w > 0
