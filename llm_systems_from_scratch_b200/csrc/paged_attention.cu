@@ -6,19 +6,34 @@
 // the pages listed in its row of `block_tables`.
 //
 // Decode attention is bandwidth bound (every cached K and V byte is read once per step), so the kernel is
-// organised around fully coalesced 16-byte loads: 16 lanes cover the 256 bytes of one token's head
-// (dh = 128; 8 lanes for dh = 64), each warp streams two (four) tokens per iteration, scores are reduced
-// with shuffles, and the softmax is kept online.  The context of one (request, head) is split over
-// gridDim.y CTAs (flash-decoding); partial (max, sum, output) triples go to a scratch buffer and a
-// second kernel merges them.
+// organised around reading whole token rows: one CTA serves one request (all its heads) over one split of the
+// context, 16 lanes cover the 256 bytes of one head (dh = 128; 8 lanes for dh = 64), scores are reduced with
+// shuffles, the softmax is kept online in registers and eight tokens' rows are in flight per thread.  The context
+// of a request is split over gridDim.y CTAs (flash-decoding); partial (max, sum, output) triples go to a scratch
+// buffer and a second kernel merges them.
 #include "ptx.cuh"
 
 namespace b200 {
 
-constexpr int PD_THREADS = 128;
+constexpr int PD_UNROLL = 8;     // tokens whose K / V rows are in flight together, per CTA
 
+// 16-byte load of cache data that is read exactly once per step: do not keep it in L1.
+__device__ __forceinline__ uint4 ld_stream(const __nv_bfloat16* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// One CTA = one request x one split of its context; its threads cover ALL heads: thread i owns the 8 head-columns
+// [8 i, 8 i + 8) of the token row, so the CTA reads every cached token as one contiguous row of H * DH elements (and
+// the 16 tokens of a page as one contiguous 16-row block), which is the access pattern DRAM serves at full speed.
+// A head's score is reduced over its DH / 8 neighbouring lanes with shuffles; each thread keeps the online-softmax
+// state (max, sum) of its head and its 8 output columns for the whole split, so nothing is combined inside the CTA.
+// The K and V rows of PD_UNROLL tokens are requested before the first score is computed.
 template <int DH>
-__global__ void __launch_bounds__(PD_THREADS)
+__global__ void __launch_bounds__(512)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q,        // (R, 3d) packed qkv or (R, d): row stride q_ld
                     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                     const int* __restrict__ block_tables, const int* __restrict__ context_lens,
@@ -26,10 +41,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,        // (R, 3d) packe
                     float* __restrict__ part_ml,                 // (R, H, splits, 2)
                     int q_ld, int heads, int page_size, int max_pages, int splits, float scale_log2, int num_pages,
                     uint32_t* __restrict__ status) {
-  constexpr int LPT = DH / 8;            // lanes per token (16-byte loads)
-  constexpr int TPW = 32 / LPT;          // tokens per warp iteration
-  const int r = blockIdx.x / heads, h = blockIdx.x % heads;
-  const int split = blockIdx.y;
+  constexpr int LPT = DH / 8;            // lanes per head (16-byte loads)
+  const int r = blockIdx.x, split = blockIdx.y;
+  const int d = heads * DH;
+  const int col = threadIdx.x * 8;       // first of this thread's 8 columns of the token row
+  const bool active = col < d;           // the block is rounded up to whole warps
+  const int h = active ? col / DH : 0;
+  const int li = (threadIdx.x % LPT);
   // The tables come from the host scheduler; a length beyond the table or a page id beyond the cache is reported
   // through the status word and skipped, never dereferenced.
   int ctx = context_lens[r];
@@ -37,80 +55,99 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,        // (R, 3d) packe
     if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0u, ERR_BAD_ARG | (1u << 8));
     ctx = ctx < 0 ? 0 : max_pages * page_size;
   }
-  const int d = heads * DH;
-  const int per = (ctx + splits - 1) / splits;
+  // splits start on multiples of PD_UNROLL tokens so that a chunk of PD_UNROLL tokens never straddles a page whose
+  // size is a multiple of PD_UNROLL: one table lookup (and one integer division) per chunk instead of one per token
+  const int per = ((ctx + splits - 1) / splits + PD_UNROLL - 1) / PD_UNROLL * PD_UNROLL;
   const int t0 = split * per;
   const int t1 = min(ctx, t0 + per);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int sub = lane / LPT;            // which token of the warp's group
-  const int li = lane % LPT;             // which 8-element slice of the head
 
-  float qv[8];
-  {
-    const uint4 u = *reinterpret_cast<const uint4*>(q + (size_t)r * q_ld + h * DH + li * 8);
+  float qv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (active) {
+    const uint4 u = *reinterpret_cast<const uint4*>(q + (size_t)r * q_ld + col);
     const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), e = unpack_bf16x2(u.w);
     qv[0] = a.x; qv[1] = a.y; qv[2] = b.x; qv[3] = b.y; qv[4] = c.x; qv[5] = c.y; qv[6] = e.x; qv[7] = e.y;
   }
   float m = -INFINITY, l = 0.f;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   const int* table = block_tables + (size_t)r * max_pages;
-  // The loop bound is uniform across the warp so that the shuffles below are executed by all 32 lanes;
-  // a token group whose index runs past the end of the split only skips its loads and its update.
-  for (int tb = t0 + warp * TPW; tb < t1; tb += (PD_THREADS / 32) * TPW) {
-    const int t = tb + sub;
-    uint4 ku = make_uint4(0, 0, 0, 0), vu = make_uint4(0, 0, 0, 0);
-    bool valid = t < t1;
-    if (valid) {
-      const int page = table[t / page_size];
-      if ((unsigned)page >= (unsigned)num_pages) {
-        if (status != nullptr) atomicCAS(status, 0u, ERR_BAD_ARG | (2u << 8));
-        valid = false;
-      } else {
-        const size_t row = ((size_t)page * page_size + (t % page_size)) * d + h * DH + li * 8;
-        ku = *reinterpret_cast<const uint4*>(k_cache + row);
-        vu = *reinterpret_cast<const uint4*>(v_cache + row);
+  for (int tb = t0; tb < t1; tb += PD_UNROLL) {
+    uint4 ku[PD_UNROLL], vu[PD_UNROLL];
+    bool valid[PD_UNROLL];
+    const int pg = tb / page_size, off = tb - pg * page_size;
+    if (off + PD_UNROLL <= page_size) {
+      // the whole chunk lies in one page: consecutive rows of the cache
+      const int page = table[pg];
+      const bool page_ok = (unsigned)page < (unsigned)num_pages;
+      if (!page_ok && threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0u, ERR_BAD_ARG | (2u << 8));
+      const size_t row0 = ((size_t)(page_ok ? page : 0) * page_size + off) * d + col;
+#pragma unroll
+      for (int u = 0; u < PD_UNROLL; ++u) {
+        valid[u] = page_ok && tb + u < t1;
+        ku[u] = make_uint4(0, 0, 0, 0);
+        vu[u] = make_uint4(0, 0, 0, 0);
+        if (valid[u] && active) {
+          ku[u] = ld_stream(k_cache + row0 + (size_t)u * d);
+          vu[u] = ld_stream(v_cache + row0 + (size_t)u * d);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < PD_UNROLL; ++u) {
+        const int t = tb + u;
+        valid[u] = t < t1;
+        ku[u] = make_uint4(0, 0, 0, 0);
+        vu[u] = make_uint4(0, 0, 0, 0);
+        if (valid[u]) {
+          const int page = table[t / page_size];
+          if ((unsigned)page >= (unsigned)num_pages) {
+            if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0u, ERR_BAD_ARG | (2u << 8));
+            valid[u] = false;
+          } else if (active) {
+            const size_t row = ((size_t)page * page_size + (t % page_size)) * d + col;
+            ku[u] = ld_stream(k_cache + row);
+            vu[u] = ld_stream(v_cache + row);
+          }
+        }
       }
     }
-    const float2 k0 = unpack_bf16x2(ku.x), k1 = unpack_bf16x2(ku.y), k2 = unpack_bf16x2(ku.z), k3 = unpack_bf16x2(ku.w);
-    float s = qv[0] * k0.x + qv[1] * k0.y + qv[2] * k1.x + qv[3] * k1.y + qv[4] * k2.x + qv[5] * k2.y + qv[6] * k3.x +
-              qv[7] * k3.y;
+    // scores of the whole chunk first (independent of one another), then ONE running-max update for the chunk:
+    // the serial chain of the online softmax is per chunk, not per token
+    float sc[PD_UNROLL];
+    float mc = m;
 #pragma unroll
-    for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (valid) {
-      s *= scale_log2;
-      const float mn = fmaxf(m, s);
-      const float corr = exp2f(m - mn);   // 0 when m == -inf
-      const float p = exp2f(s - mn);
-      l = l * corr + p;
-      const float2 v0 = unpack_bf16x2(vu.x), v1 = unpack_bf16x2(vu.y), v2 = unpack_bf16x2(vu.z), v3 = unpack_bf16x2(vu.w);
-      acc[0] = acc[0] * corr + p * v0.x; acc[1] = acc[1] * corr + p * v0.y;
-      acc[2] = acc[2] * corr + p * v1.x; acc[3] = acc[3] * corr + p * v1.y;
-      acc[4] = acc[4] * corr + p * v2.x; acc[5] = acc[5] * corr + p * v2.y;
-      acc[6] = acc[6] * corr + p * v3.x; acc[7] = acc[7] * corr + p * v3.y;
-      m = mn;
+    for (int u = 0; u < PD_UNROLL; ++u) {
+      const float2 k0 = unpack_bf16x2(ku[u].x), k1 = unpack_bf16x2(ku[u].y), k2 = unpack_bf16x2(ku[u].z),
+                   k3 = unpack_bf16x2(ku[u].w);
+      float s = qv[0] * k0.x + qv[1] * k0.y + qv[2] * k1.x + qv[3] * k1.y + qv[4] * k2.x + qv[5] * k2.y +
+                qv[6] * k3.x + qv[7] * k3.y;
+#pragma unroll
+      for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      sc[u] = valid[u] ? s * scale_log2 : -INFINITY;
+      mc = fmaxf(mc, sc[u]);
+    }
+    if (mc > -INFINITY) {
+      const float corr = exp2f(m - mc);       // 0 when m == -inf
+      l *= corr;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= corr;
+#pragma unroll
+      for (int u = 0; u < PD_UNROLL; ++u) {
+        const float p = exp2f(sc[u] - mc);    // 0 for tokens beyond the split or on a bad page
+        l += p;
+        const float2 v0 = unpack_bf16x2(vu[u].x), v1 = unpack_bf16x2(vu[u].y), v2 = unpack_bf16x2(vu[u].z),
+                     v3 = unpack_bf16x2(vu[u].w);
+        acc[0] += p * v0.x; acc[1] += p * v0.y; acc[2] += p * v1.x; acc[3] += p * v1.y;
+        acc[4] += p * v2.x; acc[5] += p * v2.y; acc[6] += p * v3.x; acc[7] += p * v3.y;
+      }
+      m = mc;
     }
   }
-  // ---- combine the (PD_THREADS / LPT) token groups of the CTA through shared memory
-  constexpr int GROUPS = PD_THREADS / LPT;
-  __shared__ float sm_m[GROUPS], sm_l[GROUPS];
-  __shared__ float sm_o[GROUPS][DH];
-  const int grp = threadIdx.x / LPT;
-  if (li == 0) { sm_m[grp] = m; sm_l[grp] = l; }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) sm_o[grp][li * 8 + i] = acc[i];
-  __syncthreads();
-  if (threadIdx.x < DH) {
-    float gm = -INFINITY;
-    for (int g = 0; g < GROUPS; ++g) gm = fmaxf(gm, sm_m[g]);
-    float gl = 0.f, go = 0.f;
-    for (int g = 0; g < GROUPS; ++g) {
-      const float w = (sm_m[g] == -INFINITY) ? 0.f : exp2f(sm_m[g] - gm);
-      gl += sm_l[g] * w;
-      go += sm_o[g][threadIdx.x] * w;
-    }
+  if (active) {
     const size_t idx = ((size_t)r * heads + h) * splits + split;
-    part_o[idx * DH + threadIdx.x] = go;
-    if (threadIdx.x == 0) { part_ml[idx * 2] = gm; part_ml[idx * 2 + 1] = gl; }
+    float4* o = reinterpret_cast<float4*>(part_o + idx * DH + li * 8);
+    o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if (li == 0) { part_ml[idx * 2] = m; part_ml[idx * 2 + 1] = l; }
   }
 }
 
@@ -168,19 +205,21 @@ extern "C" int b200_paged_decode(const void* q, const void* k_cache, const void*
     return -10;
   if (rows <= 0) return 0;
   if (splits < 1) splits = 1;
-  const dim3 grid(rows * heads, splits);
+  const int threads = (heads * (dh / 8) + 31) / 32 * 32;      // one thread per 8 columns of the token row, whole warps
+  if (threads > 512) return -12;     // heads * dh <= 4096
+  const dim3 grid(rows, splits);
   const float sl2 = scale * 1.4426950408889634f;
   if (dh == 128) {
-    paged_decode_kernel<128><<<grid, PD_THREADS, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
-                                                          (const __nv_bfloat16*)v_cache, block_tables, context_lens,
-                                                          part_o, part_ml, q_ld, heads, page_size, max_pages, splits, sl2,
-                                                          num_pages, status);
+    paged_decode_kernel<128><<<grid, threads, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
+                                                       (const __nv_bfloat16*)v_cache, block_tables, context_lens, part_o,
+                                                       part_ml, q_ld, heads, page_size, max_pages, splits, sl2, num_pages,
+                                                       status);
     paged_decode_merge_kernel<128><<<rows * heads, 128, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, heads, splits);
   } else {
-    paged_decode_kernel<64><<<grid, PD_THREADS, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
-                                                         (const __nv_bfloat16*)v_cache, block_tables, context_lens,
-                                                         part_o, part_ml, q_ld, heads, page_size, max_pages, splits, sl2,
-                                                          num_pages, status);
+    paged_decode_kernel<64><<<grid, threads, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
+                                                      (const __nv_bfloat16*)v_cache, block_tables, context_lens, part_o,
+                                                      part_ml, q_ld, heads, page_size, max_pages, splits, sl2, num_pages,
+                                                      status);
     paged_decode_merge_kernel<64><<<rows * heads, 64, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, heads, splits);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

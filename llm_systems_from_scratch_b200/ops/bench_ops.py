@@ -219,7 +219,7 @@ def bench_decode(argv=()):
     weight_bytes = 2 * (cfg["num_layers"] * (4 * 2048 * 2048 + 3 * 2048 * 5504) + 50257 * 2048)
     g = torch.Generator().manual_seed(1)
     for batch in (32, 64, 128, 256):
-        reqs = [Request(i, torch.randint(0, 50257, (ctx,), generator=g).tolist(), 8) for i in range(batch)]
+        reqs = [Request(i, torch.randint(0, 50257, (ctx,), generator=g).tolist(), 400) for i in range(batch)]
         for r in reqs:
             eng.sched.add(r)
         eng._realtime, eng._virtual = False, float("inf")
@@ -251,7 +251,7 @@ def bench_decode(argv=()):
                           "paged_attention_layer_ms": round(att_ms, 4),
                           "paged_attention_gbs": round(kv_bytes / cfg["num_layers"] / att_ms / 1e6, 1)}), flush=True)
         for r in running:
-            r.output.extend([0] * 8)
+            r.output.extend([0] * 400)
         eng.sched.retire(0.0)
     for m in (32, 64, 128, 256):
         for n, k in ((6144, 2048), (2048, 2048), (11008, 2048), (2048, 5504), (50264, 2048)):

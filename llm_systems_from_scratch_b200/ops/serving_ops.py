@@ -41,9 +41,10 @@ def kv_append(k_cache, v_cache, qkv, slot_mapping):
 
 
 def choose_splits(rows: int, heads: int, max_context: int, sms: int = 148) -> int:
-    """Enough CTAs to fill the GPU, at least ~256 tokens per split."""
-    want = max(1, (2 * sms + rows * heads - 1) // max(1, rows * heads))
-    return max(1, min(want, max(1, max_context // 256), 32))
+    """The decode kernel runs one CTA per (request, split): enough splits for about four CTAs per SM, at least ~128
+    tokens per split."""
+    want = max(1, (4 * sms + rows - 1) // max(1, rows))
+    return max(1, min(want, max(1, max_context // 128), 32))
 
 
 def paged_decode_attention(qkv, k_cache, v_cache, block_tables, context_lens, n_heads: int, splits: int = 0,
