@@ -110,12 +110,16 @@ class ServingEngine:
     @torch.no_grad()
     def prefill(self, reqs: list[Request]) -> torch.Tensor:
         """Run the prompts of ``reqs`` (pages already reserved); returns their first generated tokens."""
+        ps = self.page_size
         lens = [len(r.prompt) for r in reqs]
-        tokens = torch.tensor([t for r in reqs for t in r.prompt], dtype=torch.int64)
-        positions = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens])
-        slots = torch.tensor([s for r in reqs for s in self.cache.slots(r.pages, 0, len(r.prompt))], dtype=torch.int64)
-        cu = torch.zeros(len(reqs) + 1, dtype=torch.int32)
-        cu[1:] = torch.tensor(lens).cumsum(0)
+        # packed inputs built with numpy (one C loop per request instead of one Python iteration per token)
+        tok_np = np.concatenate([np.asarray(r.prompt, dtype=np.int64) for r in reqs])
+        pos_np = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+        slot_np = np.concatenate([np.asarray(r.pages, dtype=np.int64)[np.arange(n) // ps] * ps + np.arange(n) % ps
+                                  for r, n in zip(reqs, lens)])
+        cu_np = np.zeros(len(reqs) + 1, dtype=np.int32)
+        cu_np[1:] = np.cumsum(lens)
+        tokens, positions, slots, cu = (torch.from_numpy(a) for a in (tok_np, pos_np, slot_np, cu_np))
         last = (cu[1:] - 1).long()
         if self.cuda:
             tokens, positions, slots, cu_d, last = (t.pin_memory().to(self.device, non_blocking=True)
@@ -227,27 +231,169 @@ class ServingEngine:
         return new
 
     # ---------------------------------------------------------------------- main loop
-    def step(self, now: float) -> int:
-        """One engine iteration at time ``now``: admit + prefill, then one decode step.  Returns the
-        number of tokens produced."""
+    # Requests keep one row of the batch arrays for their whole life; the token each row feeds next stays on the
+    # device (the decode graph copies its output there), so a decode step can be launched before the previous step's
+    # tokens have reached the host.  The host reads them one step behind: while step k + 1 runs on the GPU it appends
+    # step k's tokens, retires finished requests and prepares step k + 2.
+    def _rows_init(self):
+        n = self._bucket(self.max_batch)
+        dev = self.device
+        self._row_req: list[Request | None] = [None] * n
+        self._row_pos = np.full(n, -1, dtype=np.int64)        # position of the token the row feeds next; -1 = idle
+        self._row_tab = np.zeros((n, self.max_pages_per_req), dtype=np.int64)
+        self._free_rows = list(range(n - 1, -1, -1))
+        self._d = {"tokens": torch.zeros(n, dtype=torch.int64, device=dev),
+                   "positions": torch.zeros(n, dtype=torch.int32, device=dev),
+                   "slots": torch.full((n,), -1, dtype=torch.int64, device=dev),
+                   "ctx": torch.ones(n, dtype=torch.int32, device=dev),
+                   "tables": torch.zeros((n, self.max_pages_per_req), dtype=torch.int32, device=dev)}
+        mk = lambda shape, dt: torch.zeros(shape, dtype=dt, pin_memory=self.cuda)
+        # two sets of pinned staging used in turn: a set is refilled only after the step before last has completed
+        self._stage = [{"positions": mk(n, torch.int32), "slots": mk(n, torch.int64), "ctx": mk(n, torch.int32),
+                        "out": mk(n, torch.int64)} for _ in range(2)]
+        self._stage_np = [{k: v.numpy() for k, v in st.items()} for st in self._stage]
+        self._tab_host = mk((n, self.max_pages_per_req), torch.int32)
+        self._tab_dirty = False
+        self._parity = 0
+        self._pending: list[tuple] = []
+        self._row_graphs: dict[int, dict] = {}
+
+    def _row_graph(self, bucket: int) -> dict:
+        g = self._row_graphs.get(bucket)
+        if g is not None:
+            return g
+        d = self._d
+        splits = serving_ops.choose_splits(bucket, self.cfg.n_heads, self.max_context)
+
+        def run():
+            out = self._decode_body(d["tokens"][:bucket], d["positions"][:bucket], d["slots"][:bucket],
+                                    d["tables"][:bucket], d["ctx"][:bucket], splits)
+            d["tokens"][:bucket].copy_(out)          # the next step of every row starts from this token
+        g = {"run": run}
+        if self.use_graphs:
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            keep = d["tokens"][:bucket].clone()
+            with torch.cuda.stream(side):            # warm-up outside capture: first-launch set-up happens here
+                run()
+            torch.cuda.current_stream().wait_stream(side)
+            d["tokens"][:bucket].copy_(keep)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                run()
+            d["tokens"][:bucket].copy_(keep)         # capture does not execute, but keep the contract obvious
+            g["graph"] = graph
+        self._row_graphs[bucket] = g
+        return g
+
+    def _admit_rows(self, reqs: list[Request], first: torch.Tensor):
+        rows = [self._free_rows.pop() for _ in reqs]
+        for row, r in zip(rows, reqs):
+            self._row_req[row] = r
+            r.row = row
+            r.issued = 1                                     # the prefill produced the first token
+            self._row_pos[row] = len(r.prompt)
+            self._row_tab[row, :] = 0
+            self._row_tab[row, :len(r.pages)] = r.pages
+            if r.issued >= r.max_new_tokens:
+                self._row_pos[row] = -1                      # nothing left to decode
+        self._tab_host.numpy()[rows] = self._row_tab[rows]
+        self._tab_dirty = True
+        idx = torch.tensor(rows, dtype=torch.int64)
+        if self.cuda:
+            idx = idx.pin_memory().to(self.device, non_blocking=True)
+        self._d["tokens"].index_copy_(0, idx, first.to(torch.int64))
+        self._read_back("prefill", first, list(zip(range(len(reqs)), reqs)))
+
+    def _read_back(self, kind: str, dev_tokens: torch.Tensor, who: list):
+        """Queue a device-to-host read of ``dev_tokens``; ``who`` lists (index into it, request)."""
+        if self.cuda:
+            host = torch.empty(dev_tokens.shape, dtype=torch.int64, pin_memory=True) if kind == "prefill" else \
+                self._stage[self._parity]["out"][:dev_tokens.shape[0]]
+            host.copy_(dev_tokens, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        else:
+            host, ev = dev_tokens.clone(), None
+        self._pending.append((kind, ev, host, who))
+
+    def _launch_decode(self) -> int:
+        active = np.nonzero(self._row_pos >= 0)[0]
+        if active.size == 0:
+            return 0
+        bucket = self._bucket(int(active[-1]) + 1)
+        ps = self.page_size
+        st = self._stage_np[self._parity]
+        pos = self._row_pos[:bucket]
+        live = pos >= 0
+        p = np.where(live, pos, 0)
+        st["positions"][:bucket] = p
+        st["slots"][:bucket] = np.where(live, self._row_tab[np.arange(bucket), p // ps] * ps + p % ps, -1)
+        st["ctx"][:bucket] = np.where(live, p + 1, 1)
+        d, host = self._d, self._stage[self._parity]
+        for name in ("positions", "slots", "ctx"):
+            d[name][:bucket].copy_(host[name][:bucket], non_blocking=True)
+        if self._tab_dirty:
+            d["tables"].copy_(self._tab_host, non_blocking=True)
+            self._tab_dirty = False
+        g = self._row_graph(bucket)
+        if self.use_graphs:
+            g["graph"].replay()
+        else:
+            g["run"]()
+        who = [(int(row), self._row_req[row]) for row in active]
+        self._read_back("decode", d["tokens"][:bucket], who)
+        self._parity ^= 1
+        # bookkeeping that needs no token values: positions advance, rows whose last token is now in flight go idle
+        self._row_pos[active] += 1
+        for row, r in who:
+            r.issued += 1
+            if r.issued >= r.max_new_tokens:
+                self._row_pos[row] = -1
+        self.stats["decode_tokens"] += len(who)
+        self.stats["decode_steps"] += 1
+        return len(who)
+
+    def _finish(self, keep_last: int = 0) -> int:
+        """Consume queued read-backs, oldest first, leaving the ``keep_last`` most recent ones in flight."""
         produced = 0
+        while len(self._pending) > keep_last:
+            kind, ev, host, who = self._pending.pop(0)
+            if ev is not None:
+                ev.synchronize()
+            vals = host.numpy() if host.device.type == "cpu" else host.cpu().numpy()
+            t = self._clock()
+            for i, r in who:
+                if r.t_done is not None:
+                    continue                                  # ended by its stop token a step earlier
+                r.output.append(int(vals[i]))
+                produced += 1
+                if kind == "prefill":
+                    r.t_first = t
+                if r.finished:
+                    r.t_done = t
+                    row = r.row
+                    self._row_pos[row] = -1
+                    self._row_req[row] = None
+                    self._free_rows.append(row)
+                    self.sched.finish(r)
+        return produced
+
+    def step(self, now: float) -> int:
+        """One engine iteration at time ``now``: admit + prefill, launch one decode step, then collect the tokens
+        of the step before.  Returns the number of tokens that reached the host."""
+        if not hasattr(self, "_row_req"):
+            self._rows_init()
         admitted = self.sched.admit(now)
         if admitted:
-            first = self.prefill(admitted).tolist()
-            t = self._clock()
-            for r, tok in zip(admitted, first):
-                r.output.append(int(tok))
-                r.t_first = t
+            first = self.prefill(admitted)
             self.sched.start(admitted)
-            produced += len(admitted)
-            self.sched.retire(t)
-        if self.sched.running:
-            batch = list(self.sched.running)
-            for r, tok in zip(batch, self.decode(batch)):
-                r.output.append(int(tok))
-            produced += len(batch)
-            self.sched.retire(self._clock())
-        return produced
+            self._admit_rows(admitted, first)
+        launched = self._launch_decode()
+        # on the GPU the newest read-back stays in flight while the host goes on; when nothing was launched (every
+        # row's last token is already in flight) or without streams, everything is collected now
+        return self._finish(keep_last=1 if (self.cuda and launched) else 0)
 
     def _clock(self) -> float:
         return time.perf_counter() - self._t0 if self._realtime else self._virtual
@@ -262,15 +408,17 @@ class ServingEngine:
         if self.cuda:
             torch.cuda.synchronize()
         self._t0 = time.perf_counter()
-        while not self.sched.idle:
+        if not hasattr(self, "_row_req"):
+            self._rows_init()
+        while not self.sched.idle or self._pending:
             now = self._clock()
-            if not self.sched.running:
+            if not self.sched.running and not self._pending:
                 nxt = self.sched.next_arrival()
                 if realtime and nxt is not None and nxt > now:
                     time.sleep(min(nxt - now, 0.05))
                     continue
             produced = self.step(now)
-            if produced == 0 and not self.sched.running and self.sched.waiting:
+            if produced == 0 and not self.sched.running and not self._pending and self.sched.waiting:
                 head = self.sched.waiting[0]
                 if not realtime or head.arrival <= now:
                     # nothing runs, so every page is free, and the oldest arrived request still was not admitted

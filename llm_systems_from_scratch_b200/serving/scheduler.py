@@ -27,6 +27,8 @@ class Request:
     output: list[int] = field(default_factory=list)
     t_first: float | None = None
     t_done: float | None = None
+    row: int = -1            # row of the engine's batch arrays while running
+    issued: int = 0          # tokens produced on the device so far (the host may not have read the last one yet)
 
     @property
     def context_len(self) -> int:
@@ -107,6 +109,12 @@ class Scheduler:
                 self.alloc.give(r.pages)
                 r.pages = []
         return done
+
+    def finish(self, req: Request):
+        """``req`` has produced its last token: return its pages and drop it from the running set."""
+        self.running.remove(req)
+        self.alloc.give(req.pages)
+        req.pages = []
 
     @property
     def idle(self) -> bool:
