@@ -856,10 +856,18 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
                                         cudaStream_t st) {
   if (d > B200_NOALLOC_MAX_D) return B200_ERR_NOALLOC_TOO_LARGE;
   if (d <= 0 || d % 8 || rows < 0) return -10;
-  if (!ALIGNED16(dy) || !ALIGNED16(x) || !ALIGNED16(w) || !ALIGNED16(dx) || !ALIGNED16(dres)) return -10;
-  if (rows == 0) return 0;
+  if (dw == nullptr || (reinterpret_cast<uintptr_t>(dw) & 3)) return -10;
+  if (rows > 0 && (dy == nullptr || x == nullptr || w == nullptr || rstd == nullptr || dx == nullptr)) return -10;
+  if (!ALIGNED16(dy) || !ALIGNED16(x) || !ALIGNED16(w) || !ALIGNED16(dx) || !ALIGNED16(dres) ||
+      (reinterpret_cast<uintptr_t>(rstd) & 3))
+    return -10;
   float* scratch = noalloc_scratch_for_current_device();
   if (scratch == nullptr) return B200_ERR_NOALLOC_SETUP;
+  if (rows == 0) {
+    // no rows: the weight gradient of this call is zero (dw is cleared, or left as it is when accumulating)
+    rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 256, 0, st>>>(scratch, dw, 0, d, accumulate_dw);
+    CHECK_LAUNCH();
+  }
   const int parts = rows < B200_NOALLOC_MAX_PARTS ? rows : B200_NOALLOC_MAX_PARTS;
   // Every partial row [0, parts) x [0, d) is written by the first kernel before the second reads it,
   // so nothing in the shared array has to be cleared between calls.

@@ -33,7 +33,8 @@ extern "C" {
 
 // dx = [dres +] d(RMSNorm)/dx ; dw (=|+=) d(RMSNorm)/dw.  All pointers are device pointers:
 // dy, x, dres (may be null), dx: bf16 (rows, d);  w: bf16 (d);  rstd: fp32 (rows);  dw: fp32 (d).
-// Returns 0 on success, -10 for misaligned / unsupported arguments, B200_ERR_NOALLOC_TOO_LARGE when
+// With rows == 0 the call still defines dw (zero, or unchanged when accumulating).
+// Returns 0 on success, -10 for null / misaligned / unsupported arguments, B200_ERR_NOALLOC_TOO_LARGE when
 // d exceeds B200_NOALLOC_MAX_D, B200_ERR_NOALLOC_SETUP when the scratch address cannot be resolved.
 int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                              void* dx, float* dw, int rows, int d, int accumulate_dw, cudaStream_t stream);

@@ -36,16 +36,19 @@ def _case(rows, d, seed):
 
 
 def test_noalloc_entry_matches_allocating_entry_twice_in_a_row():
-    from llm_systems_from_scratch_b200.ops import native
+    from llm_systems_from_scratch_b200.ops import native, torch_impl
     lib = _lib()
     stream = torch.cuda.current_stream().cuda_stream
-    # two different problems back to back: the second call finds the first call's partials in the array
-    for rows, d, seed in [(1000, 2048, 0), (333, 768, 1)]:
+    # different problems back to back: every later call finds an earlier call's partials in the array.  The shapes
+    # cover one to four column groups per thread, the widest row the entry accepts, and fewer rows than blocks.
+    for rows, d, seed in [(1000, 2048, 0), (333, 768, 1), (5, 8192, 2), (200, 4104, 3)]:
         x, w, dy, dres = _case(rows, d, seed)
         _, rstd = native.rmsnorm_fwd(x, w, 1e-5)
         ref_dx, ref_dw = native.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
         dx = torch.empty_like(x)
         dw = torch.empty(d, dtype=torch.float32, device="cuda")
+        # PyTorch's allocator must stay untouched by the call (a raw cudaMalloc inside the library would not show
+        # here; that the entry point makes none is a property of its source, which calls no allocating routine)
         before = torch.cuda.memory_allocated()
         rc = lib.b200_rmsnorm_bwd_noalloc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr(),
                                           dx.data_ptr(), dw.data_ptr(), rows, d, 0, stream)
@@ -55,6 +58,11 @@ def test_noalloc_entry_matches_allocating_entry_twice_in_a_row():
         assert (dx.float() - ref_dx.float()).abs().max().item() <= 3e-2
         err = (dw - ref_dw).abs()
         assert bool((err <= 1e-2 * math.sqrt(rows) + 1e-2 * ref_dw.abs()).all()), err.max().item()
+        # and against the fp32 PyTorch statement of the same op (the oracle of the other kernel tests)
+        o_dx, o_dw = torch_impl.rmsnorm_bwd(dy.float(), x.float(), w.float(), rstd)
+        assert (dx.float() - (o_dx + dres.float())).abs().max().item() <= 6e-2
+        err = (dw - o_dw).abs()
+        assert bool((err <= 2e-2 * math.sqrt(rows) + 2e-2 * o_dw.abs()).all()), err.max().item()
         # accumulate mode adds onto what dw already holds
         rc = lib.b200_rmsnorm_bwd_noalloc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), None,
                                           dx.data_ptr(), dw.data_ptr(), rows, d, 1, stream)
@@ -78,3 +86,25 @@ def test_noalloc_entry_rejects_widths_beyond_its_maximum():
     assert rc == -12                      # refused: nothing was launched, outputs untouched
     torch.cuda.synchronize()
     assert bool((dw == 7.0).all())
+
+
+def test_noalloc_entry_with_no_rows_and_with_null_outputs():
+    lib = _lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    d = 512
+    w = torch.ones(d, device="cuda", dtype=torch.bfloat16)
+    dw = torch.full((d,), 7.0, device="cuda")
+    # no rows, accumulate: dw is left as it is; no rows, overwrite: dw becomes the (zero) gradient
+    assert lib.b200_rmsnorm_bwd_noalloc(None, None, w.data_ptr(), None, None, None, dw.data_ptr(), 0, d, 1, stream) == 0
+    torch.cuda.synchronize()
+    assert bool((dw == 7.0).all())
+    assert lib.b200_rmsnorm_bwd_noalloc(None, None, w.data_ptr(), None, None, None, dw.data_ptr(), 0, d, 0, stream) == 0
+    torch.cuda.synchronize()
+    assert bool((dw == 0.0).all())
+    # a missing output or a missing rstd is refused before anything is launched
+    x = torch.zeros(4, d, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.ones(4, device="cuda")
+    assert lib.b200_rmsnorm_bwd_noalloc(x.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), None, x.data_ptr(),
+                                        None, 4, d, 0, stream) == -10
+    assert lib.b200_rmsnorm_bwd_noalloc(x.data_ptr(), x.data_ptr(), w.data_ptr(), None, None, x.data_ptr(),
+                                        dw.data_ptr(), 4, d, 0, stream) == -10
