@@ -324,6 +324,8 @@ def run_serving(args, rank, local_rank, world, n_requests):
     model.eval()
     eng = ServingEngine(model, page_size=SERVE["page_size"], max_batch=SERVE["max_batch"],
                         max_context=SERVE["context_length"])
+    eng.warmup()                                   # decode graphs of every batch bucket are captured before the trace
+    eng.generate([trace[0].prompt[:256]], 4)       # one short request end to end: first-launch set-up of the prefill path
     native.reset_launch_count()
     res = eng.run(trace, realtime=True)
     native.check_status()

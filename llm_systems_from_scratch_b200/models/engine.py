@@ -16,6 +16,7 @@ the packed QKV activation, so no head transposes exist anywhere.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import NamedTuple
 
@@ -404,7 +405,8 @@ class NativeEngine:
         self.cfg = cfg
         self.provider = provider
         self.rope_cache = rope_cache
-        self.loss_chunk_rows = 4096
+        # rows of logits that exist at a time in the fused head + loss (B200_LOSS_CHUNK_ROWS overrides)
+        self.loss_chunk_rows = int(os.environ.get("B200_LOSS_CHUNK_ROWS", "4096"))
 
     def _anchor(self):
         return self.provider.arena.anchor

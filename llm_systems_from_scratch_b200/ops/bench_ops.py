@@ -8,6 +8,7 @@
     python -m llm_systems_from_scratch_b200.ops.bench_ops attention-small # one small attention fwd+bwd (for ncu)
     python -m llm_systems_from_scratch_b200.ops.bench_ops attention-trace # in-kernel timeline of one CTA per kernel
     python -m llm_systems_from_scratch_b200.ops.bench_ops decode [ctx]    # serving decode step vs its memory roofline
+    python -m llm_systems_from_scratch_b200.ops.bench_ops paged-decode-small  # paged decode attention alone (for ncu)
 
 Each line of output is one JSON record.  The "-small" modes exist so that a profiler capture ends by
 itself in seconds: inputs are larger than L2 but only a few hundred MB.
@@ -275,11 +276,35 @@ def bench_decode(argv=()):
     native.check_status()
 
 
+def paged_decode_small():
+    """Three launches of the paged decode attention on a cache larger than L2 (batch 64, 1024 cached tokens per
+    request, 16 heads of 128: 268 MB of K and 268 MB of V are read per launch); small enough for a profiler."""
+    from . import serving_ops
+    heads, dh, page, batch, ctx = 16, 128, 16, 64, 1024
+    d = heads * dh
+    n_pages = batch * ctx // page
+    kc = torch.randn(n_pages, page, d, device="cuda").bfloat16()
+    vc = torch.randn(n_pages, page, d, device="cuda").bfloat16()
+    qkv = torch.randn(batch, 3 * d, device="cuda").bfloat16()
+    tables = torch.randperm(n_pages, device="cuda").int().view(batch, ctx // page).contiguous()
+    lens = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
+    splits = serving_ops.choose_splits(batch, heads, ctx)
+    for _ in range(3):
+        serving_ops.paged_decode_attention(qkv, kc, vc, tables, lens, heads, splits)
+    torch.cuda.synchronize()
+    native.check_status()
+    t = timeit(lambda: serving_ops.paged_decode_attention(qkv, kc, vc, tables, lens, heads, splits))
+    print(json.dumps({"op": "paged-decode-small", "ms": round(t, 4), "gb_per_s": round(2 * kc.numel() * 2 / t / 1e6, 1),
+                      "splits": splits, "ok": True}))
+
+
 def main(argv=None):
     argv = argv if argv is not None else sys.argv[1:]
     mode = argv[0] if argv else "gemm"
     if mode == "decode":
         return bench_decode(argv[1:])
+    if mode == "paged-decode-small":
+        return paged_decode_small()
     {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "gemm-small": gemm_small, "gemm-pair-small": gemm_pair_small, "attention-trace": attention_trace,
      "attention-small": attention_small}[mode]()
 

@@ -287,6 +287,18 @@ class ServingEngine:
         self._row_graphs[bucket] = g
         return g
 
+    def warmup(self):
+        """Capture the decode graph of every batch bucket up to ``max_batch`` now, so that no request of a trace pays
+        for a capture (a few tenths of a second each) with its time to first token."""
+        if not hasattr(self, "_row_req"):
+            self._rows_init()
+        if self.use_graphs:
+            top = self._bucket(self.max_batch)
+            for b in self.BUCKETS:
+                if b <= top:
+                    self._row_graph(b)
+            torch.cuda.synchronize()
+
     def _admit_rows(self, reqs: list[Request], first: torch.Tensor):
         rows = [self._free_rows.pop() for _ in reqs]
         for row, r in zip(rows, reqs):

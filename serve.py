@@ -93,6 +93,7 @@ def main(argv=None):
         model.eval()
         eng = ServingEngine(model, page_size=s["page_size"], max_batch=s["max_batch"], max_context=s["max_context"],
                             use_cuda_graphs=not args.no_graphs)
+        eng.warmup()
         res = eng.run(trace, realtime=not args.offline)
     if world > 1:
         import torch.distributed as dist
