@@ -41,6 +41,7 @@ struct GemmParams {
   ReduceTask reduce;
   const uint32_t* wait_counter;  // optional: do not touch operand B before *wait_counter >= wait_value
   uint32_t wait_value;
+  unsigned long long wait_limit_ns;   // how long the producer warp polls wait_counter before it gives up
   // Optional rotary embedding fused into the epilogue of the QKV projection: output columns [0, 2*rope_d)
   // (the Q and K thirds) are rotated pair-wise by the angle of position (row % rope_seq); the table is
   // (2, rope_ctx, rope_dh/2) fp32 (cos, then sin).  Null = off.

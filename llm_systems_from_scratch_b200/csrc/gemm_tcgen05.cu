@@ -343,7 +343,7 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   p.gather.dst = nullptr; p.gather.done = nullptr; p.gather.shard_vec = 0; p.gather.world = 0; p.gather.rank = 0;
   p.reduce.n = 0;
   p.tma_store = 0;
-  p.wait_counter = nullptr; p.wait_value = 0;
+  p.wait_counter = nullptr; p.wait_value = 0; p.wait_limit_ns = 0;
   p.rope_cs = nullptr; p.rope_seq = p.rope_d = p.rope_dh = p.rope_ctx = 0;
   p.swiglu_f = 0; p.H = nullptr; p.ldh = 0;
 

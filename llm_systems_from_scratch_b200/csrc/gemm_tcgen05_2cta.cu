@@ -165,7 +165,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         // operand B is being gathered by another kernel: wait (bounded) until every slice has landed
         const uint64_t t0 = globaltimer_ns();
         while ((int32_t)(ld_acquire_gpu(p.wait_counter) - p.wait_value) < 0) {
-          if (globaltimer_ns() - t0 > B200_WAIT_LIMIT_NS) {
+          if (globaltimer_ns() - t0 > p.wait_limit_ns) {
             report(p, abort_word, ERR_WAIT_FLAG);
             ok = false;
             break;
@@ -599,6 +599,14 @@ static int g_pair_tma_store = []() {
   const char* e = getenv("B200_GEMM_TMA_STORE");
   return (e == nullptr || e[0] != '0') ? 1 : 0;
 }();
+// How long a GEMM launched with a wait counter (its B operand is still being written by another kernel) polls
+// before it records ERR_WAIT_FLAG and unwinds.  Returns the previous limit.
+static unsigned long long g_counter_wait_limit_ns = B200_WAIT_LIMIT_NS;
+extern "C" unsigned long long b200_gemm_set_wait_limit_ns(unsigned long long ns) {
+  const unsigned long long old = g_counter_wait_limit_ns;
+  g_counter_wait_limit_ns = ns;
+  return old;
+}
 extern "C" int b200_gemm_set_tma_store(int on) {
   const int old = g_pair_tma_store;
   g_pair_tma_store = on ? 1 : 0;
@@ -636,7 +644,7 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
   else { p.gather.dst = nullptr; p.gather.done = nullptr; p.gather.shard_vec = 0; p.gather.world = 0; p.gather.rank = 0; }
   if (reduce != nullptr) p.reduce = *reduce;
   else p.reduce.n = 0;
-  p.wait_counter = wait_counter; p.wait_value = wait_value;
+  p.wait_counter = wait_counter; p.wait_value = wait_value; p.wait_limit_ns = g_counter_wait_limit_ns;
   p.rope_cs = rope_cs; p.rope_seq = rope_seq; p.rope_d = rope_d; p.rope_dh = rope_dh; p.rope_ctx = rope_ctx;
   p.swiglu_f = swiglu_f; p.H = H; p.ldh = ldh;
   // TMA-store epilogue: needs a 16-byte aligned output whose row pitch is a multiple of 16 bytes.  A TMA store

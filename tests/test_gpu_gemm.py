@@ -217,3 +217,41 @@ def test_gemm_swiglu_backward_epilogue(m, f, k):
     s = torch.sigmoid(g)
     ref = torch.cat([dh * u * (s + g * s * (1 - s)), dh * g * s], dim=1)
     assert (out.float() - ref).abs().max().item() < 4e-2 * max(1.0, ref.abs().max().item()) / 4
+
+
+def test_gemm_wait_counter_is_bounded_and_reports():
+    """A GEMM whose B operand is announced through a device counter (another kernel is still writing it): with the
+    counter never bumped and a 1 ms limit the kernel gives up, records the wait in the status word, frees its tensor
+    memory and returns; the context stays usable and the same launch with the counter set computes the product."""
+    import ctypes
+    from llm_systems_from_scratch_b200.ops import native
+    lib = native.load()
+    P, I, L, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint
+    lib.b200_gemm_set_wait_limit_ns.argtypes = [ctypes.c_ulonglong]
+    lib.b200_gemm_set_wait_limit_ns.restype = ctypes.c_ulonglong
+    m, n, k = 512, 512, 256
+    a, b = _make("nt", m, n, k, "cuda")
+    out = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = native.status_word()
+    status.zero_()
+
+    def launch():
+        rc = lib.b200_gemm_bf16_pair_gather(a.data_ptr(), b.data_ptr(), out.data_ptr(), None, m, n, k, k, k, n, 0, 0, 0, 0,
+                                            None, None, 0, 0, 0, None, None, counter.data_ptr(), 1, status.data_ptr(),
+                                            torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+
+    old = lib.b200_gemm_set_wait_limit_ns(1_000_000)
+    try:
+        launch()
+        with pytest.raises(native.KernelError):
+            native.check_status()
+        assert float(out.float().abs().sum()) == 0.0          # it gave up before producing anything
+        counter.fill_(1)
+        launch()
+        native.check_status()
+        _check(out, _ref(a, b, "nt"), k)
+    finally:
+        lib.b200_gemm_set_wait_limit_ns(old)

@@ -31,7 +31,7 @@ def test_logits_loss_and_grads_close_to_fp32():
     loss = native.loss(x, y)
     loss.backward()
     nat.check_status()
-    assert abs(loss.item() - ref.item()) < 2e-2
+    assert abs(loss.item() - ref.item()) < 2e-3
     ge = dict(eager.named_parameters())
     for k, p in native.named_parameters():
         g = p.grad
@@ -41,8 +41,13 @@ def test_logits_loss_and_grads_close_to_fp32():
             gref = ge[k.replace("w_down", "down_proj")].grad
         else:
             gref = ge[k].grad
+        # Error budget from the arithmetic: activations and gradients are rounded to bf16 (unit round-off 2^-8) at
+        # every kernel boundary and the roundings of a path add up roughly in quadrature.  The head tensors sit two
+        # roundings from the loss, everything below them behind a dozen or more: 2 and 4 units of 2^-8 (observed
+        # 1.0 - 1.4 and 2.0 - 3.0 units).
         rel = (g - gref).norm() / (gref.norm() + 1e-12)
-        assert rel.item() < 0.06, (k, rel.item())
+        units = 2 if k in ("lm_head.weight", "final_norm.weight") else 4
+        assert rel.item() < units * 2.0 ** -8, (k, rel.item())
 
 
 def test_training_reduces_loss_and_fsdp_single_gpu_matches_plain():
