@@ -130,6 +130,8 @@ def parse_args():
     ap.add_argument("--fused-optimizer", choices=["auto", "on", "off"], default="auto",
                     help="FSDP on 2+ GPUs: run AdamW inside each unit's reduce-scatter (clip coefficient from the previous "
                          "step's norm); auto = on.  off = reduce-scatter, exact global-norm clip, then one AdamW launch")
+    ap.add_argument("--activation-checkpointing", choices=["config", "on", "off"], default="config",
+                    help="per-block activation checkpointing: as the config names it (on for fsdp_7b), or forced")
     ap.add_argument("--workload", choices=["train", "serve"], default="train")
     ap.add_argument("--serving-requests", type=int, default=None,
                     help="requests of the Poisson trace per GPU (serve: default 1024; train: a short serving run of "
@@ -218,7 +220,9 @@ def run_native(args, cfg, rank, local_rank, world):
     mkeys = ("vocab_size", "context_length", "d_model", "num_layers", "num_heads", "d_ff", "rope_theta")
     with torch.device(dev):
         model = TransformerLM(**{k: cfg[k] for k in mkeys}, use_flash_attn=True, use_custom_triton=True)
-    model.activation_checkpointing = bool(cfg.get("activation_checkpointing", False))
+    ac = bool(cfg.get("activation_checkpointing", False)) if args.activation_checkpointing == "config" else \
+        args.activation_checkpointing == "on"
+    model.activation_checkpointing = ac
     wrapped = FSDP(model, comm=args.comm) if args.parallel == "fsdp" else DDP(model, comm=args.comm)
     opt = FusedAdamW(wrapped.parameters(), lr=LR, weight_decay=WEIGHT_DECAY)
     fused = (args.parallel == "fsdp" and world > 1 and args.fused_optimizer != "off"
@@ -284,6 +288,7 @@ def run_native(args, cfg, rank, local_rank, world):
                 launches=launches_timed, loss=loss_a, h2d=sampler.bytes_per_batch(), d2h=4,
                 mem_gb=torch.cuda.max_memory_allocated() / 2 ** 30,
                 parallelism=f"{args.parallel}{world}", comm=type(wrapped.comm).__name__, comm_launches=comm_launches,
+                activation_checkpointing=ac,
                 optimizer=("AdamW fp32 sharded state, update fused into each unit's reduce-scatter, global-norm clip 1.0 "
                            "with the previous step's norm" if fused else
                            "AdamW fp32 state, one launch, exact global-norm clip 1.0"))
@@ -440,7 +445,7 @@ def run_reference(args, cfg, rank, local_rank, world):
     os.unlink(tmp.name)
     return dict(ms=ms, ms_e2e=ms_e2e, wall=wall, clocks=clocks, tokens_per_step=b * s * world, launches=None,
                 loss=loss_a, h2d=2 * b * s * 8, d2h=4, mem_gb=torch.cuda.max_memory_allocated() / 2 ** 30,
-                parallelism=f"{args.parallel}{world}", comm="NCCL", comm_launches=None,
+                parallelism=f"{args.parallel}{world}", comm="NCCL", comm_launches=None, activation_checkpointing=False,
                 optimizer="reference FusedAdamW (Triton), clip 1.0 by each rank's local shard norm (the reference's "
                           "clip_gradient over its FSDP shards)" if args.parallel == "fsdp" and world > 1 else
                           "reference FusedAdamW (Triton), global-norm clip 1.0"), None
@@ -522,7 +527,8 @@ def main():
                        "parallelism": res["parallelism"], "micro_batch_per_gpu": cfg["micro_batch"],
                        "vocab": cfg["vocab_size"], "d_model": cfg["d_model"], "layers": cfg["num_layers"],
                        "heads": cfg["num_heads"], "d_ff": cfg["d_ff"], "l2_policy": l2_policy(cfg)},
-            "optimizer": res["optimizer"], "comm": res["comm"], "comm_launches_per_step": res["comm_launches"],
+            "optimizer": res["optimizer"], "comm": res["comm"], "comm_launches_timed_region": res["comm_launches"],
+            "activation_checkpointing": res["activation_checkpointing"],
             "clocks": res["clocks"],
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(res["ms_e2e"] / args.steps, 3),
                     "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"]},
