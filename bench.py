@@ -129,7 +129,11 @@ def parse_args():
     ap.add_argument("--comm", choices=["auto", "torch", "peer"], default="auto")
     ap.add_argument("--fused-optimizer", choices=["auto", "on", "off"], default="auto",
                     help="FSDP on 2+ GPUs: run AdamW inside each unit's reduce-scatter (clip coefficient from the previous "
-                         "step's norm); auto = on.  off = reduce-scatter, exact global-norm clip, then one AdamW launch")
+                         "step's norm); auto = on from 4 GPUs.  off = reduce-scatter, exact global-norm clip, then one "
+                         "AdamW launch")
+    ap.add_argument("--nvls", action="store_true",
+                    help="gradient staging bound to an NVLink multicast object: the reduce-scatters use multimem.ld_reduce "
+                         "(the switch adds the copies) instead of peer loads")
     ap.add_argument("--activation-checkpointing", choices=["config", "on", "off"], default="config",
                     help="per-block activation checkpointing: as the config names it (on for fsdp_7b), or forced")
     ap.add_argument("--workload", choices=["train", "serve"], default="train")
@@ -216,6 +220,8 @@ def run_native(args, cfg, rank, local_rank, world):
     from llm_systems_from_scratch_b200.parallel import DDP, FSDP
 
     dev = torch.device("cuda", local_rank)
+    if args.nvls:
+        os.environ["B200_NVLS"] = "1"
     torch.manual_seed(args.seed)
     mkeys = ("vocab_size", "context_length", "d_model", "num_layers", "num_heads", "d_ff", "rope_theta")
     with torch.device(dev):
@@ -225,8 +231,10 @@ def run_native(args, cfg, rank, local_rank, world):
     model.activation_checkpointing = ac
     wrapped = FSDP(model, comm=args.comm) if args.parallel == "fsdp" else DDP(model, comm=args.comm)
     opt = FusedAdamW(wrapped.parameters(), lr=LR, weight_decay=WEIGHT_DECAY)
-    fused = (args.parallel == "fsdp" and world > 1 and args.fused_optimizer != "off"
-             and wrapped.attach_optimizer(opt, MAX_GRAD_NORM))
+    # auto: from four ranks on.  On two ranks a rank's shard is half the model and the AdamW pass that the copy warps
+    # of a GEMM then carry (658 MB of optimizer state per unit) outlasts the GEMM; there the one-launch AdamW is faster.
+    want_fused = args.fused_optimizer == "on" or (args.fused_optimizer == "auto" and world >= 4)
+    fused = args.parallel == "fsdp" and world > 1 and want_fused and wrapped.attach_optimizer(opt, MAX_GRAD_NORM)
     arena = wrapped.shard_arena if args.parallel == "fsdp" else model.engine().provider.arena
     b, s = cfg["micro_batch"], cfg["context_length"]
     tokens = synthetic_tokens(cfg["vocab_size"], 1 << 24, args.seed + 1)
@@ -287,7 +295,9 @@ def run_native(args, cfg, rank, local_rank, world):
     return dict(ms=ms, ms_e2e=ms_e2e, wall=wall, clocks=clocks, tokens_per_step=tokens_per_step,
                 launches=launches_timed, loss=loss_a, h2d=sampler.bytes_per_batch(), d2h=4,
                 mem_gb=torch.cuda.max_memory_allocated() / 2 ** 30,
-                parallelism=f"{args.parallel}{world}", comm=type(wrapped.comm).__name__, comm_launches=comm_launches,
+                parallelism=f"{args.parallel}{world}",
+                comm=type(wrapped.comm).__name__ + (" + NVLS reduce-scatter" if getattr(wrapped.comm, "nvls", False) else ""),
+                comm_launches=comm_launches,
                 activation_checkpointing=ac,
                 optimizer=("AdamW fp32 sharded state, update fused into each unit's reduce-scatter, global-norm clip 1.0 "
                            "with the previous step's norm" if fused else

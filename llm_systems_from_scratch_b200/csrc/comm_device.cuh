@@ -22,6 +22,17 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
   return v;
 }
+// Sum over all GPUs bound to the multicast object of the 16 bytes (8 bf16) at `mc_addr`, added up in fp32 inside the
+// switch and returned as 8 bf16.  `mc_addr` must be a multicast address; it is only ever used by this instruction.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const uint4* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+
 // Barrier among `nthreads` threads of a CTA (a multiple of 32) on hardware barrier `id` (1..15; 0 is __syncthreads).
 __device__ __forceinline__ void group_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
@@ -43,6 +54,10 @@ struct AdamArgs {
 // Handshake: `ready` row - rank r's staging is complete; `done` row - rank r no longer reads anybody's staging.
 struct ReduceTask {
   PeerPtrs staging;
+  // Optional NVLS path: the multicast address of this rank's slice of the staging (an NVLink multicast object bound
+  // to every rank's staging buffer).  When set, one `multimem.ld_reduce` per 16 bytes lets the NVSwitch read the
+  // eight copies and return their sum, instead of eight peer loads per thread.  Null = plain peer loads.
+  const uint4* mc_slice;
   PeerPtrs flag_bases;
   unsigned long long ready_row, done_row;   // element offsets of the two flag rows (world words each)
   float* grad_out;
@@ -60,6 +75,7 @@ struct ReduceTask {
 // Host description of a reduce-scatter (mirrors ReduceTask; filled by the Python side through ctypes).
 struct B200ReduceDesc {
   unsigned long long staging[16];
+  unsigned long long mc_staging;       // multicast address of the staging buffer (same offset as staging[]), 0 = none
   unsigned long long flag_bases[16];
   unsigned long long ready_row, done_row;
   float* grad_out;
@@ -126,25 +142,10 @@ __device__ __forceinline__ void reduce_scatter_body(const ReduceTask& t, int tid
     const size_t stride = (size_t)nparts * nthreads;
     constexpr int NW = WORLD > 0 ? WORLD : 1;
     const int world = WORLD > 0 ? WORLD : t.world;
-    // One 16-byte piece of this rank's slice: sum the `world` copies in rank order (bitwise reproducible), scale,
-    // then store the gradient or run the AdamW update.
-    auto consume = [&](size_t i, const uint4 (&in)[NW]) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int p = 0; p < NW; ++p) {
-        const uint4 u = in[p];
-        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
-        acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
-      }
-      if (WORLD == 0) {      // world sizes without a specialisation: one peer at a time
-        for (int p = 1; p < world; ++p) {
-          const uint4 u = reinterpret_cast<const uint4*>(t.staging.p[p])[(size_t)t.rank * n_vec + i];
-          const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-          acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
-          acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
-        }
-      }
+    // One 16-byte piece of this rank's slice: the `world` copies are summed in rank order (bitwise reproducible) by
+    // `consume`, or by the switch on the NVLS path; `apply` scales and stores the gradient or runs the AdamW update.
+    // `acc` holds the sum over ranks of 8 consecutive gradient elements: scale, then store or update.
+    auto apply = [&](size_t i, float (&acc)[8]) {
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] *= inv;
       if (MODE == 0) {
@@ -183,11 +184,40 @@ __device__ __forceinline__ void reduce_scatter_body(const ReduceTask& t, int tid
         }
       }
     };
+    auto add8 = [](float (&acc)[8], const uint4& u) {
+      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+      acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    };
+    auto consume = [&](size_t i, const uint4 (&in)[NW]) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int p = 0; p < NW; ++p) add8(acc, in[p]);
+      if (WORLD == 0)        // world sizes without a specialisation: one peer at a time
+        for (int p = 1; p < world; ++p) add8(acc, reinterpret_cast<const uint4*>(t.staging.p[p])[(size_t)t.rank * n_vec + i]);
+      apply(i, acc);
+    };
     // every peer's copy of U consecutive strides is requested before the first one is consumed: WORLD x U 16-byte
     // loads in flight per thread keep all NVLink ports busy and cover the round trip
     size_t i = (size_t)part * nthreads + tid;
     const size_t base = (size_t)t.rank * n_vec;
-    if (U > 1) {
+    if (t.mc_slice != nullptr) {
+      // NVLS: the switch adds the copies (fp32 accumulation, bf16 result); 4 reduced pieces in flight per thread
+      constexpr int UM = 4;
+      auto from_sum = [&](size_t idx, const uint4& sum) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        add8(acc, sum);
+        apply(idx, acc);
+      };
+      for (; i + (UM - 1) * stride < n_vec; i += UM * stride) {
+        uint4 sum[UM];
+#pragma unroll
+        for (int u = 0; u < UM; ++u) sum[u] = multimem_ld_reduce_bf16x8(t.mc_slice + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < UM; ++u) from_sum(i + u * stride, sum[u]);
+      }
+      for (; i < n_vec; i += stride) from_sum(i, multimem_ld_reduce_bf16x8(t.mc_slice + i));
+    } else if (U > 1) {
       for (; i + (U - 1) * stride < n_vec; i += U * stride) {
         uint4 in[U][NW];
 #pragma unroll

@@ -239,6 +239,11 @@ int b200_make_reduce_task(const B200ReduceDesc* d, uint32_t* status, bool carrie
   if (d->mode == 1 && (d->master == nullptr || d->m == nullptr || d->v == nullptr)) return -11;
   ReduceTask t;
   t.staging = make_ptrs(d->staging, d->world);
+  // the multicast address covers the same buffer; this rank's slice starts rank * n elements in
+  t.mc_slice = d->mc_staging
+                   ? reinterpret_cast<const uint4*>(d->mc_staging + (unsigned long long)d->rank * d->n * 2ull)
+                   : nullptr;
+  if (d->mc_staging & 15) return -10;
   t.flag_bases = make_ptrs(d->flag_bases, d->world);
   t.ready_row = d->ready_row; t.done_row = d->done_row;
   t.grad_out = d->grad_out; t.sumsq = d->sumsq;

@@ -84,7 +84,12 @@ def main():
     padded = -(-args.numel // quantum) * quantum
     n = padded // ws
     hbm = _hbm_gbs()
-    out = []
+
+    class _Out(list):
+        def append(self, rec):          # rank 0 prints every record as soon as it exists
+            super().append(rec)
+            print(json.dumps(rec), flush=True)
+    out = _Out()
 
     # ---- link bandwidth as this box delivers it: every rank pulls 256 MiB from its right-hand neighbour
     probe_n = 256 << 20
@@ -181,6 +186,19 @@ def main():
     t_n = _time(nccl_then_adamw)
     report("peer_reduce_scatter + AdamW (one kernel)", t, (ws - 1) * n * 2, n * 2 + n * 26, t_n)
 
+    # ---- the same two kernels with the staging bound to an NVLink multicast object (NVLS): one multimem.ld_reduce per
+    # 16 bytes, the switch adds the copies.  Link bytes per GPU are the same (every GPU still sends 7/8 of its staging
+    # into the switch), so the roofline does not move; the SMs issue an eighth of the loads.
+    comm.nvls = os.environ.get("B200_NVLS", "1") == "1"
+    stage_mc = comm.alloc_multicast(padded, torch.bfloat16)
+    if comm.nvls:
+        stage_mc.copy_(stage)
+        comm.barrier()
+        t = _time(lambda: comm.reduce_scatter_mean(grad, stage_mc, key="bench_mc", sumsq=ss))
+        report("NVLS reduce-scatter + scale + sumsq (multimem.ld_reduce)", t, (ws - 1) * n * 2, n * 2 + n * 4, float("nan"))
+        t = _time(lambda: comm.reduce_scatter_adamw(stage_mc, "bench_mc", p, m, v, mirror, 1e-4, 0.9, 0.95, 1e-8, 0.1, 5))
+        report("NVLS reduce-scatter + AdamW (one kernel)", t, (ws - 1) * n * 2, n * 2 + n * 26, float("nan"))
+
     # ---- the same two reduce-scatters carried by the GEMM that follows a block's backward in FSDP (the dgrad of the
     # gate|up projection, 16384 x 2048 x 11008): one kernel, the copy warps reduce while the MMA warps compute.
     # Roofline: the slower of the GEMM at the measured cuBLAS burst peak and the reduce-scatter's NVLink time.
@@ -221,9 +239,6 @@ def main():
     report("peer_allreduce two-shot (25 MiB fp32 bucket)", t, (ws - 1) * chunk, (ws + 1) * chunk + nb * 4, t_n)
     torch.cuda.synchronize()
     native.check_status()
-    if rank == 0:
-        for rec in out:
-            print(json.dumps(rec))
     dist.destroy_process_group()
 
 

@@ -314,7 +314,7 @@ class FSDP(nn.Module):
         return self.lmhead_unit
 
     def _comm_buffer(self, numel: int) -> torch.Tensor:
-        alloc = getattr(self.comm, "alloc", None)
+        alloc = getattr(self.comm, "alloc_multicast", None) or getattr(self.comm, "alloc", None)
         if alloc is not None:
             return alloc(numel, self.compute_dtype)
         return torch.zeros(numel, dtype=self.compute_dtype, device=self.device)   # the padding behind a unit stays zero

@@ -33,7 +33,8 @@ class _CudaArray:
 
 class ReduceDesc(ctypes.Structure):
     """Mirror of ``B200ReduceDesc`` (csrc/comm_device.cuh): one reduce-scatter of a unit's gradient staging."""
-    _fields_ = [("staging", _ULL * 16), ("flag_bases", _ULL * 16), ("ready_row", _ULL), ("done_row", _ULL),
+    _fields_ = [("staging", _ULL * 16), ("mc_staging", _ULL), ("flag_bases", _ULL * 16), ("ready_row", _ULL),
+                ("done_row", _ULL),
                 ("grad_out", ctypes.c_void_p), ("sumsq", ctypes.c_void_p), ("master", ctypes.c_void_p),
                 ("m", ctypes.c_void_p), ("v", ctypes.c_void_p), ("mirror", ctypes.c_void_p),
                 ("gscale", ctypes.c_void_p), ("lr", ctypes.c_float), ("b1", ctypes.c_float), ("b2", ctypes.c_float),
@@ -88,7 +89,7 @@ class PeerComm(Communicator):
     COUNTER_SLOTS = 256     # CTA counters handed out in turn; a slot is reused only 256 collective launches later
     WAIT_LIMIT_NS = 5_000_000_000   # a peer that is 5 s late is reported, never waited for indefinitely
 
-    def __init__(self, group=None, wait_limit_s: float | None = None):
+    def __init__(self, group=None, wait_limit_s: float | None = None, nvls: bool | None = None):
         if not torch.cuda.is_available():
             raise RuntimeError("PeerComm needs CUDA")
         self.group = group
@@ -101,6 +102,7 @@ class PeerComm(Communicator):
         _declare(self.lib)
         self.fallback = TorchDistComm(group)
         self.limit_ns = int((wait_limit_s * 1e9) if wait_limit_s else self.WAIT_LIMIT_NS)
+        self.nvls = os.environ.get("B200_NVLS", "0") == "1" if nvls is None else bool(nvls)
         self._allocs: list[dict] = []      # {"base", "nbytes", "peers": [ptr per rank]}
         self._epochs: dict[int, int] = {}
         self._next_row = 2          # row 0: barrier, row 1: "weights published"
@@ -142,6 +144,31 @@ class PeerComm(Communicator):
         self._allocs.append({"base": base, "nbytes": nbytes, "peers": peers})
         raw = torch.as_tensor(_CudaArray(base, nbytes), device=self.device)
         return raw.view(dtype)[:numel]
+
+    def alloc_multicast(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """Collective: like ``alloc``, but the buffer is also bound to an NVLink multicast object (NVLS), so that a
+        reduce-scatter can let the NVSwitch add the ranks' copies (``multimem.ld_reduce``) instead of loading every
+        peer's copy.  The memory comes from ``torch.distributed._symmetric_memory`` (plumbing: it creates the
+        multicast object and exchanges the handles).  Falls back to ``alloc`` when NVLS is off (``B200_NVLS=1`` turns
+        it on) or the fabric has no multicast support.  Keep NVLS off in runs where a rank may leave."""
+        if not self.nvls:
+            return self.alloc(numel, dtype)
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(numel, dtype=dtype, device=self.device)
+        t.zero_()
+        handle = symm_mem.rendezvous(t, self.group if self.group is not None else dist.group.WORLD)
+        mc = int(handle.multicast_ptr or 0)
+        ok = torch.tensor([1 if mc else 0], device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            self.nvls = False
+            return self.alloc(numel, dtype)
+        nbytes = numel * t.element_size()
+        self._allocs.append({"base": t.data_ptr(), "nbytes": nbytes, "peers": [int(p) for p in handle.buffer_ptrs],
+                             "mc": mc, "keep": (t, handle)})
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)        # every rank's buffer is zeroed before anybody reduces over it
+        return t
 
     def _find(self, t: torch.Tensor):
         p = t.data_ptr()
@@ -260,6 +287,9 @@ class PeerComm(Communicator):
         for r in range(self.world_size):
             d.staging[r] = a["peers"][r] + off
             d.flag_bases[r] = self._flag_peers[r]
+        d.mc_staging = a["mc"] + off if a.get("mc") else 0        # NVLS: the switch adds the copies
+        if d.mc_staging:
+            self._count("reduce_scatter_nvls")
         d.ready_row, d.done_row = ready * self.world_size, done * self.world_size
         d.grad_out, d.sumsq = ptr(grad_out), ptr(sumsq)
         d.master, d.m, d.v, d.mirror = ptr(ad.get("master")), ptr(ad.get("m")), ptr(ad.get("v")), ptr(ad.get("mirror"))
@@ -293,8 +323,8 @@ class PeerComm(Communicator):
         self._launch_reduce(self._adamw_desc(full, key, master, m, v, mirror, lr, beta1, beta2, eps, weight_decay, step,
                                              grad_scale, grad_out, sumsq))
 
-    def _adamw_desc(self, full, key, master, m, v, mirror, lr, beta1, beta2, eps, weight_decay, step, grad_scale,
-                    grad_out, sumsq) -> ReduceDesc:
+    def _adamw_desc(self, full, key, master, m, v, mirror, lr, beta1, beta2, eps, weight_decay, step, grad_scale=None,
+                    grad_out=None, sumsq=None) -> ReduceDesc:
         alpha_t = lr * math.sqrt(1 - beta2 ** step) / (1 - beta1 ** step)
         return self._reduce_desc(full, key, 1, grad_out, sumsq,
                                  dict(master=master, m=m, v=v, mirror=mirror, gscale=grad_scale, lr=lr, b1=beta1,

@@ -27,7 +27,7 @@ def _init(rank, world, port):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")      # no rank leaves in these tests; NCCL is plumbing only
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
 
@@ -165,6 +165,71 @@ def _collectives(rank, world, port):
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_peer_collectives_match_nccl(world):
     _spawn(_collectives, world)
+
+
+def _collectives_nvls(rank, world, port):
+    """Reduce-scatter through an NVLink multicast object: the switch adds the ranks' copies (multimem.ld_reduce)."""
+    import torch.distributed as dist
+    _init(rank, world, port)
+    try:
+        from llm_systems_from_scratch_b200.ops import native, torch_impl
+        from llm_systems_from_scratch_b200.parallel.peer import PeerComm
+        comm = PeerComm(nvls=True)
+        n = 64 * 1024 + 64
+        g = torch.Generator(device="cuda").manual_seed(200 + rank)
+        stage = comm.alloc_multicast(world * n, torch.bfloat16)
+        if not comm.nvls:
+            if rank == 0:
+                print("NVLS multicast is not available on this fabric: nothing to test")
+            return
+        a = torch.randn(2048, 512, device="cuda", generator=g).bfloat16()
+        w = torch.randn(1024, 512, device="cuda", generator=g).bfloat16()
+        want_c = native.gemm(a, w, "nt", pair=True)
+        for it in range(4):
+            comm.wait_readers(stage, "t")
+            stage.copy_(torch.randn(world * n, device="cuda", generator=g))
+            tmp = stage.float()
+            dist.all_reduce(tmp)
+            want = tmp[rank * n:(rank + 1) * n] / world
+            out = torch.zeros(n, dtype=torch.float32, device="cuda")
+            ss = torch.zeros((), device="cuda")
+            if it % 2 == 0:                         # a kernel of its own
+                comm.reduce_scatter_mean(out, stage, key="t", sumsq=ss)
+            else:                                   # carried by a GEMM
+                task = comm.reduce_task(stage, "t", out_shard=out, sumsq=ss)
+                c = native.gemm(a, w, "nt", pair=True, reduce=task)
+                assert task.done and torch.equal(c, want_c)
+            # the switch returns the sum as bf16 (fp32 accumulation inside): up to one ulp of bf16 on the sum
+            assert torch.allclose(out, want, rtol=2.0 ** -7, atol=1e-6), (out - want).abs().max()
+            assert abs(ss.item() - want.pow(2).sum().item()) < 2e-2 * want.pow(2).sum().item()
+        comm.wait_readers(stage, "t")
+        stage.copy_(torch.randn(world * n, device="cuda", generator=g))
+        tmp = stage.float()
+        dist.all_reduce(tmp)
+        gref = tmp[rank * n:(rank + 1) * n] / world
+        p0 = torch.randn(n, device="cuda", generator=g)
+        m0 = 0.1 * torch.randn(n, device="cuda", generator=g)
+        v0 = 0.1 * torch.rand(n, device="cuda", generator=g)
+        pr, mr, vr = p0.clone(), m0.clone(), v0.clone()
+        torch_impl.adamw_step(pr, gref, mr, vr, None, 1e-3, 0.9, 0.95, 1e-8, 0.1, 3)
+        p, m, v = p0.clone(), m0.clone(), v0.clone()
+        mirror = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        comm.reduce_scatter_adamw(stage, "t", p, m, v, mirror, 1e-3, 0.9, 0.95, 1e-8, 0.1, 3)
+        # the gradient carries up to one bf16 ulp of error: (1 - beta1) of it reaches m, twice its relative size v
+        assert torch.allclose(m, mr, rtol=0, atol=0.1 * 2.0 ** -7 * gref.abs().max().item() + 1e-6)
+        assert torch.allclose(v, vr, rtol=2.0 ** -5, atol=1e-6)
+        assert (p - pr).abs().max().item() < 2e-4
+        assert torch.equal(mirror, p.bfloat16())
+        assert comm.launches.get("reduce_scatter_nvls", 0) == 5
+        torch.cuda.synchronize()
+        native.check_status()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_nvls_reduce_scatter_matches_nccl(world):
+    _spawn(_collectives_nvls, world)
 
 
 CFG = dict(vocab_size=1003, context_length=128, d_model=256, num_layers=3, num_heads=4, d_ff=768, rope_theta=10000.0)
