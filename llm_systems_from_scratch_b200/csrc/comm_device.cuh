@@ -145,7 +145,22 @@ __device__ __forceinline__ void reduce_scatter_body(const ReduceTask& t, int tid
     // One 16-byte piece of this rank's slice: the `world` copies are summed in rank order (bitwise reproducible) by
     // `consume`, or by the switch on the NVLS path; `apply` scales and stores the gradient or runs the AdamW update.
     // `acc` holds the sum over ranks of 8 consecutive gradient elements: scale, then store or update.
-    auto apply = [&](size_t i, float (&acc)[8]) {
+    struct AdamState {
+      float pw[8], mw[8], vw[8];
+    };
+    // The optimizer state of a piece is requested together with the peers' copies of the gradient, not after they
+    // have arrived: the two latencies overlap instead of adding up.
+    auto load_state = [&](size_t i, AdamState& st) {
+      if (MODE == 1) {
+        const float4* pm = reinterpret_cast<const float4*>(t.adam.master) + 2 * i;
+        const float4* mm = reinterpret_cast<const float4*>(t.adam.m) + 2 * i;
+        const float4* vv = reinterpret_cast<const float4*>(t.adam.v) + 2 * i;
+        *reinterpret_cast<float4*>(st.pw) = pm[0]; *reinterpret_cast<float4*>(st.pw + 4) = pm[1];
+        *reinterpret_cast<float4*>(st.mw) = mm[0]; *reinterpret_cast<float4*>(st.mw + 4) = mm[1];
+        *reinterpret_cast<float4*>(st.vw) = vv[0]; *reinterpret_cast<float4*>(st.vw + 4) = vv[1];
+      }
+    };
+    auto apply = [&](size_t i, float (&acc)[8], AdamState& st) {
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] *= inv;
       if (MODE == 0) {
@@ -158,10 +173,7 @@ __device__ __forceinline__ void reduce_scatter_body(const ReduceTask& t, int tid
         float4* pm = reinterpret_cast<float4*>(t.adam.master) + 2 * i;
         float4* mm = reinterpret_cast<float4*>(t.adam.m) + 2 * i;
         float4* vv = reinterpret_cast<float4*>(t.adam.v) + 2 * i;
-        float pw[8], mw[8], vw[8];
-        *reinterpret_cast<float4*>(pw) = pm[0]; *reinterpret_cast<float4*>(pw + 4) = pm[1];
-        *reinterpret_cast<float4*>(mw) = mm[0]; *reinterpret_cast<float4*>(mw + 4) = mm[1];
-        *reinterpret_cast<float4*>(vw) = vv[0]; *reinterpret_cast<float4*>(vw + 4) = vv[1];
+        float (&pw)[8] = st.pw, (&mw)[8] = st.mw, (&vw)[8] = st.vw;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const float g = acc[k] * gs;
@@ -189,50 +201,66 @@ __device__ __forceinline__ void reduce_scatter_body(const ReduceTask& t, int tid
       acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
       acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
     };
-    auto consume = [&](size_t i, const uint4 (&in)[NW]) {
+    auto consume = [&](size_t i, const uint4 (&in)[NW], AdamState& st) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int p = 0; p < NW; ++p) add8(acc, in[p]);
       if (WORLD == 0)        // world sizes without a specialisation: one peer at a time
         for (int p = 1; p < world; ++p) add8(acc, reinterpret_cast<const uint4*>(t.staging.p[p])[(size_t)t.rank * n_vec + i]);
-      apply(i, acc);
+      apply(i, acc, st);
     };
+    // strides in flight per thread: U for the plain reduction; with the AdamW state travelling along (24 more floats
+    // per stride) two, or four at two ranks
+    constexpr int UA = MODE == 1 ? (U > 2 ? (WORLD == 2 ? 4 : 2) : U) : U;
     // every peer's copy of U consecutive strides is requested before the first one is consumed: WORLD x U 16-byte
     // loads in flight per thread keep all NVLink ports busy and cover the round trip
     size_t i = (size_t)part * nthreads + tid;
     const size_t base = (size_t)t.rank * n_vec;
     if (t.mc_slice != nullptr) {
       // NVLS: the switch adds the copies (fp32 accumulation, bf16 result); 4 reduced pieces in flight per thread
-      constexpr int UM = 4;
-      auto from_sum = [&](size_t idx, const uint4& sum) {
+      constexpr int UM = MODE == 1 ? 2 : 4;
+      auto from_sum = [&](size_t idx, const uint4& sum, AdamState& st) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         add8(acc, sum);
-        apply(idx, acc);
+        apply(idx, acc, st);
       };
       for (; i + (UM - 1) * stride < n_vec; i += UM * stride) {
         uint4 sum[UM];
+        AdamState st[UM];
 #pragma unroll
         for (int u = 0; u < UM; ++u) sum[u] = multimem_ld_reduce_bf16x8(t.mc_slice + i + u * stride);
 #pragma unroll
-        for (int u = 0; u < UM; ++u) from_sum(i + u * stride, sum[u]);
-      }
-      for (; i < n_vec; i += stride) from_sum(i, multimem_ld_reduce_bf16x8(t.mc_slice + i));
-    } else if (U > 1) {
-      for (; i + (U - 1) * stride < n_vec; i += U * stride) {
-        uint4 in[U][NW];
+        for (int u = 0; u < UM; ++u) load_state(i + u * stride, st[u]);
 #pragma unroll
-        for (int u = 0; u < U; ++u)
+        for (int u = 0; u < UM; ++u) from_sum(i + u * stride, sum[u], st[u]);
+      }
+      for (; i < n_vec; i += stride) {
+        AdamState st;
+        const uint4 sum = multimem_ld_reduce_bf16x8(t.mc_slice + i);
+        load_state(i, st);
+        from_sum(i, sum, st);
+      }
+    } else if (UA > 1) {
+      for (; i + (UA - 1) * stride < n_vec; i += UA * stride) {
+        uint4 in[UA][NW];
+        AdamState st[UA];
+#pragma unroll
+        for (int u = 0; u < UA; ++u)
 #pragma unroll
           for (int p = 0; p < NW; ++p) in[u][p] = reinterpret_cast<const uint4*>(t.staging.p[p])[base + i + u * stride];
 #pragma unroll
-        for (int u = 0; u < U; ++u) consume(i + u * stride, in[u]);
+        for (int u = 0; u < UA; ++u) load_state(i + u * stride, st[u]);
+#pragma unroll
+        for (int u = 0; u < UA; ++u) consume(i + u * stride, in[u], st[u]);
       }
     }
     for (; i < n_vec; i += stride) {
       uint4 in[NW];
+      AdamState st;
 #pragma unroll
       for (int p = 0; p < NW; ++p) in[p] = reinterpret_cast<const uint4*>(t.staging.p[p])[base + i];
-      consume(i, in);
+      load_state(i, st);
+      consume(i, in, st);
     }
   } else if (tid == 0 && t.status != nullptr) {
     atomicCAS(t.status, 0u, ERR_WAIT_FLAG | (1u << 8));

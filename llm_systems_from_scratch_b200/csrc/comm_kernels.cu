@@ -94,8 +94,10 @@ __global__ void peer_allgather_kernel(PeerPtrs src, uint4* __restrict__ dst, siz
 constexpr int RS_MAX_CTAS = 1024;
 __device__ float g_rs_sumsq_partials[2][RS_MAX_CTAS];
 
+// The AdamW variant keeps the optimizer state of two strides in registers next to the peers' copies: 256 threads
+// per CTA (and twice the CTAs) give it the registers for that without spilling.
 template <int MODE>
-__global__ void __launch_bounds__(512) peer_reduce_scatter_kernel(const ReduceTask t) {
+__global__ void __launch_bounds__(MODE == 1 ? 256 : 512) peer_reduce_scatter_kernel(const ReduceTask t) {
   __shared__ ReduceSmem sm;
   reduce_scatter_any<MODE>(t, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x, 1, &sm);
 }
@@ -264,7 +266,7 @@ extern "C" int b200_peer_reduce_scatter_desc(const B200ReduceDesc* d, uint32_t* 
   if (rc) return rc;
   const int grid = ctas > 0 ? (ctas > RS_MAX_CTAS ? RS_MAX_CTAS : ctas) : 96;
   if (d->mode == 0) peer_reduce_scatter_kernel<0><<<grid, 512, 0, st>>>(t);
-  else peer_reduce_scatter_kernel<1><<<grid, 512, 0, st>>>(t);
+  else peer_reduce_scatter_kernel<1><<<(2 * grid > RS_MAX_CTAS ? RS_MAX_CTAS : 2 * grid), 256, 0, st>>>(t);
   COMM_CHECK();
 }
 
