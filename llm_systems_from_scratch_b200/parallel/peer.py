@@ -87,7 +87,10 @@ class PeerComm(Communicator):
     FLAG_ROWS = 1024        # rows of `world` uint32 flags: two per logical buffer (a DDP bucket, an FSDP staging slot)
     ROW_BARRIER = 0
     COUNTER_SLOTS = 256     # CTA counters handed out in turn; a slot is reused only 256 collective launches later
-    WAIT_LIMIT_NS = 5_000_000_000   # a peer that is 5 s late is reported, never waited for indefinitely
+    # A peer that is this late is reported, never waited for indefinitely.  Thirty seconds by default
+    # (B200_PEER_WAIT_LIMIT_S): longer than any skew a healthy job produces (first-step set-up, a rank that writes a
+    # checkpoint is followed by a host barrier), shorter than the host heartbeat's 60 s.
+    WAIT_LIMIT_NS = int(float(os.environ.get("B200_PEER_WAIT_LIMIT_S", "30")) * 1e9)
 
     def __init__(self, group=None, wait_limit_s: float | None = None, nvls: bool | None = None):
         if not torch.cuda.is_available():
