@@ -187,7 +187,7 @@ USE_PAIR = os.environ.get("B200_GEMM_PAIR", "1") == "1"
 # single-CTA kernel to the CTA-pair kernel as well (it handles any shape; small ones just fill fewer SMs).
 FORCE_PAIR = os.environ.get("B200_GEMM_FORCE_PAIR", "0") == "1"
 # Decode-size problems (at most 256 rows, K-major operands, bf16 output) run on the swap-AB cluster split-K kernel.
-USE_SMALLM = os.environ.get("B200_GEMM_SMALLM", "1") == "1"
+USE_SMALLM = os.environ.get("B200_GEMM_SMALLM", "0") == "1"     # off until measured on the target
 SMALLM_MAX_M = 256
 
 

@@ -283,6 +283,5 @@ def test_gemm_small_m_cluster_split_k(m, n, k):
         assert (o.float() - outs[0].float()).abs().max().item() <= 2e-2 * k ** 0.5
     again = native.gemm_smallm(a, b, split=8)
     assert torch.equal(again, outs[4])                      # the same launch twice: bitwise equal
-    routed = native.gemm(a, b, "nt")                        # the default route for these shapes
-    if n >= 128 and k >= 128:
-        assert torch.equal(routed, outs[0])
+    if native.USE_SMALLM and n >= 128 and k >= 128:
+        assert torch.equal(native.gemm(a, b, "nt"), outs[0])     # the route ops.gemm takes for these shapes
