@@ -118,7 +118,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     const __nv_bfloat16* dyr = dy + (size_t)row * d;
     const __nv_bfloat16* xr = x + (size_t)row * d;
     const float r = rstd[row];
-    float g[RMS_BWD_MAXC][8], xv[RMS_BWD_MAXC][8];
+    float g[RMS_BWD_MAXC][8], xv[RMS_BWD_MAXC][8], ev[RMS_BWD_MAXC][8];
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < RMS_BWD_MAXC; ++j) {
@@ -127,6 +127,9 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         float dyv[8];
         load8(dyr + c, dyv);
         load8(xr + c, xv[j]);
+        // the residual-branch gradient is requested with the other two rows, not after the block-wide reduction:
+        // its memory latency then overlaps theirs instead of following the reduction
+        if (dres != nullptr) load8(dres + (size_t)row * d + c, ev[j]);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           dwacc[j][i] += dyv[i] * xv[j][i] * r;
@@ -146,10 +149,8 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = r * g[j][i] - coef * xv[j][i];
         if (dres != nullptr) {  // gradient arriving through the residual branch
-          float e[8];
-          load8(dres + (size_t)row * d + c, e);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] += e[i];
+          for (int i = 0; i < 8; ++i) o[i] += ev[j][i];
         }
         store8(dxr + c, o);
       }
