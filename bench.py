@@ -522,9 +522,10 @@ def main():
         gc.collect()
         torch.cuda.empty_cache()
         try:
-            serving = gather_serving(run_serving(args, rank, local_rank, world, n_serv), world)
-        except torch.cuda.OutOfMemoryError as e:
-            serving = gather_serving({"unavailable": f"out of device memory: {str(e)[:100]}"}, world)
+            rec = run_serving(args, rank, local_rank, world, n_serv)
+        except Exception as e:      # the training numbers above stand whatever happens to the serving record
+            rec = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
+        serving = gather_serving(rec, world)
     if rank == 0:
         ms_step = res["ms"] / args.steps
         value = res["tokens_per_step"] / (ms_step / 1e3)
