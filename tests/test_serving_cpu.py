@@ -136,3 +136,24 @@ def test_generate_runs_through_the_paged_kv_engine():
     # beyond the context window the sliding re-forward loop still serves the call
     long = fused.generate(prompt, 64, temperature=0)
     assert long.shape == (1, 64)
+
+
+def test_realtime_trace_and_requests_that_can_never_fit():
+    """A small Poisson trace against the wall clock: every request is served, time to first token and latency are
+    measured from its arrival, tokens equal the offline run.  A request that needs more pages than the cache holds is
+    refused when it is submitted; one that fits the cache but not beside nothing at all is reported, not waited for."""
+    torch.manual_seed(0)
+    model = TransformerLM(**CFG).eval()
+    trace = poisson_trace(12, 200.0, (4, 20), (3, 6), CFG["vocab_size"], seed=3)
+    eng = ServingEngine(model, page_size=4, max_batch=4, max_context=64)
+    res = eng.run(trace, realtime=True)
+    assert res["requests"] == 12 and res["output_tokens"] == sum(r.max_new_tokens for r in trace)
+    assert res["ttft_p50_s"] >= 0 and res["latency_p50_s"] >= res["ttft_p50_s"]
+    assert all(r.t_first is not None and r.t_done >= r.t_first >= r.arrival for r in trace)
+    again = poisson_trace(12, 200.0, (4, 20), (3, 6), CFG["vocab_size"], seed=3)
+    eng2 = ServingEngine(model, page_size=4, max_batch=4, max_context=64)
+    eng2.run(again, realtime=False)
+    assert [r.output for r in again] == [r.output for r in trace]
+    small = ServingEngine(model, num_pages=3, page_size=4, max_batch=2, max_context=64)
+    with pytest.raises(ValueError):
+        small.sched.add(Request(0, [1] * 10, 8, 0.0))          # 18 positions = 5 pages > 3
