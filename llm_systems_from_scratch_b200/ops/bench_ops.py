@@ -270,12 +270,9 @@ def bench_decode(argv=()):
             b = torch.randn(n, k, device="cuda").bfloat16()
             out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
             t = timeit(lambda: native.gemm(a, b, "nt", out=out))
-            native.USE_SMALLM = False
-            t_old = timeit(lambda: native.gemm(a, b, "nt", out=out))      # the 128-row-tile kernel on the same shape
-            native.USE_SMALLM = True
             t2 = timeit(lambda: torch.matmul(a, b.t(), out=out))
             print(json.dumps({"op": "gemm-decode", "m": m, "n": n, "k": k, "us": round(t * 1e3, 1),
-                              "weight_gbs": round(n * k * 2 / t / 1e6, 1), "single_cta_tile_kernel_us": round(t_old * 1e3, 1),
+                              "weight_gbs": round(n * k * 2 / t / 1e6, 1),
                               "cublas_us": round(t2 * 1e3, 1)}), flush=True)
     native.check_status()
 

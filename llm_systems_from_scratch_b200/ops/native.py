@@ -66,7 +66,6 @@ def _declare(lib):
     sigs = {
         "b200_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, P, P],
         "b200_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P],
-        "b200_gemm_smallm": [P, P, P, P, I, I, I, L, L, L, L, I, P, P],
         "b200_gemm_bf16_pair_gather": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P, ctypes.c_ulonglong, I, I, P, P,
                                        P, ctypes.c_uint, P, P],
         "b200_rmsnorm_fwd": [P, P, P, P, I, I, F, P],
@@ -186,9 +185,6 @@ USE_PAIR = os.environ.get("B200_GEMM_PAIR", "1") == "1"
 # Tests of the GEMM-carried collectives run tiny models: this switch sends every GEMM whose default would be the
 # single-CTA kernel to the CTA-pair kernel as well (it handles any shape; small ones just fill fewer SMs).
 FORCE_PAIR = os.environ.get("B200_GEMM_FORCE_PAIR", "0") == "1"
-# Decode-size problems (at most 256 rows, K-major operands, bf16 output) run on the swap-AB cluster split-K kernel.
-USE_SMALLM = os.environ.get("B200_GEMM_SMALLM", "0") == "1"     # off until measured on the target
-SMALLM_MAX_M = 256
 
 
 def _pair_pays(m: int, n: int, sms: int = 148) -> bool:
@@ -235,33 +231,6 @@ def _gemm_pair_tasks(lib, a, b, out, r, m, n, k, lda, ldb, ldc, ldr, a_mn, b_mn,
             ctypes.byref(gdesc) if gdesc is not None else None, ctypes.byref(rdesc) if rdesc is not None else None,
             _ptr(status_word(a.device)), _stream())
     _check(rc, "b200_gemm_bf16_pair_tasks")
-
-
-def gemm_smallm(a, b, out=None, residual=None, split: int = 0):
-    """C = a @ b.T (+ residual) for at most 256 rows of ``a`` on the swap-AB cluster split-K kernel; ``split`` forces
-    the number of K splits (1, 2, 4, 8; 0 = chosen from the shape)."""
-    lib = load()
-    _req(a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "gemm inputs must be bf16")
-    _rowmajor(a, "a")
-    _rowmajor(b, "b")
-    m, k = a.shape
-    n, kb = b.shape
-    _req(k == kb and m <= SMALLM_MAX_M, "bad shapes for the small-M kernel")
-    _req(a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0,
-         "operands must be 16-byte aligned with leading dimensions that are multiples of 8")
-    if out is None:
-        out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
-    _rowmajor(out, "out")
-    _req(out.dtype == torch.bfloat16 and tuple(out.shape) == (m, n), "out must be bf16 (M, N)")
-    ldr = 0
-    if residual is not None:
-        _rowmajor(residual, "residual")
-        _req(residual.dtype == torch.bfloat16 and tuple(residual.shape) == (m, n), "residual must be bf16 (M, N)")
-        ldr = residual.stride(0)
-    rc = lib.b200_gemm_smallm(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, a.stride(0), b.stride(0),
-                              out.stride(0), ldr, split, _ptr(status_word(a.device)), _stream())
-    _check(rc, "b200_gemm_smallm")
-    return out
 
 
 def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, bn_hint=0, max_ctas=0,
@@ -316,16 +285,6 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
         _rowmajor(residual, "residual")
         _req(residual.dtype == torch.bfloat16 and tuple(residual.shape) == (m, n), "residual must be bf16 (M,N)")
         ldr = residual.stride(0)
-    if (USE_SMALLM and layout == "nt" and m <= SMALLM_MAX_M and out.dtype == torch.bfloat16 and not pair
-            and bn_hint == 0 and max_ctas == 0 and not FORCE_PAIR and n >= 128 and k >= 128):
-        if gather is not None and not gather.done:
-            gather.run()
-        if reduce is not None and not reduce.done:
-            reduce.run()
-        rc = lib.b200_gemm_smallm(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb, out.stride(0), ldr, 0,
-                                  _ptr(status_word(a.device)), _stream())
-        _check(rc, "b200_gemm_smallm")
-        return out
     if pair is None:
         pair = USE_PAIR and bn_hint == 0 and max_ctas == 0 and (
             FORCE_PAIR or (m >= PAIR_MIN_M and n >= 256 and _pair_pays(m, n)))

@@ -255,33 +255,3 @@ def test_gemm_wait_counter_is_bounded_and_reports():
         _check(out, _ref(a, b, "nt"), k)
     finally:
         lib.b200_gemm_set_wait_limit_ns(old)
-
-
-@pytest.mark.parametrize("m", [1, 7, 32, 100, 128, 200, 256])
-@pytest.mark.parametrize("n,k", [(2048, 2048), (6144, 2048), (2048, 5504), (1001, 520), (11008, 2048), (136, 136)])
-def test_gemm_small_m_cluster_split_k(m, n, k):
-    """Decode-size GEMM (swap-AB, K split over a thread-block cluster, partials added through distributed shared
-    memory) against the fp32 product, for every split factor the shape allows; the result does not depend on it."""
-    from llm_systems_from_scratch_b200.ops import native
-    a, b = _make("nt", m, n, k, "cuda")
-    ld = -(-n // 8) * 8
-    res = torch.randn(m, n, device="cuda").bfloat16()
-    ref = _ref(a, b, "nt")
-    outs = []
-    for split in (0, 1, 2, 4, 8):
-        buf = torch.full((m, ld + 8), 7.0, device="cuda", dtype=torch.bfloat16)
-        native.gemm_smallm(a, b, out=buf[:, :n], split=split)
-        native.check_status()
-        _check(buf[:, :n], ref, k)
-        assert (buf[:, n:] == 7.0).all()
-        outs.append(buf[:, :n].clone())
-        r = native.gemm_smallm(a, b, residual=res, split=split)
-        native.check_status()
-        _check(r, ref + res.float(), k)
-    # fp32 partial sums are added in a fixed order, but a different split factor is a different order
-    for o in outs[1:]:
-        assert (o.float() - outs[0].float()).abs().max().item() <= 2e-2 * k ** 0.5
-    again = native.gemm_smallm(a, b, split=8)
-    assert torch.equal(again, outs[4])                      # the same launch twice: bitwise equal
-    if native.USE_SMALLM and n >= 128 and k >= 128:
-        assert torch.equal(native.gemm(a, b, "nt"), outs[0])     # the route ops.gemm takes for these shapes
