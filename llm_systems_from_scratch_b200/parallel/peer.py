@@ -91,6 +91,8 @@ class PeerComm(Communicator):
     # (B200_PEER_WAIT_LIMIT_S): longer than any skew a healthy job produces (first-step set-up, a rank that writes a
     # checkpoint is followed by a host barrier), shorter than the host heartbeat's 60 s.
     WAIT_LIMIT_NS = int(float(os.environ.get("B200_PEER_WAIT_LIMIT_S", "30")) * 1e9)
+    GUARD_BYTES = 4096      # canary band before and after every peer-addressable buffer (a multiple of 256)
+    GUARD_PATTERN = 0xA5
 
     def __init__(self, group=None, wait_limit_s: float | None = None, nvls: bool | None = None):
         if not torch.cuda.is_available():
@@ -125,12 +127,19 @@ class PeerComm(Communicator):
         ``alloc`` in the same order with the same sizes."""
         nbytes = -(-numel * torch.empty((), dtype=dtype).element_size() // 256) * 256
         out = _ULL(0)
-        rc = self.lib.b200_ipc_alloc(nbytes, ctypes.byref(out))
+        # A guard band on either side of the payload, filled with a pattern that no kernel writes: a peer (or a local
+        # kernel) that runs over the end of a staging buffer or a flag row changes it, and ``check_guards`` says so.
+        rc = self.lib.b200_ipc_alloc(nbytes + 2 * self.GUARD_BYTES, ctypes.byref(out))
         if rc != 0:
             raise RuntimeError(f"peer buffer allocation of {nbytes} bytes failed ({rc})")
-        base = out.value
+        block = out.value
+        bands = torch.as_tensor(_CudaArray(block, nbytes + 2 * self.GUARD_BYTES), device=self.device)
+        bands[:self.GUARD_BYTES] = self.GUARD_PATTERN
+        bands[self.GUARD_BYTES + nbytes:] = self.GUARD_PATTERN
+        torch.cuda.synchronize()
+        base = block + self.GUARD_BYTES
         handle = ctypes.create_string_buffer(64)
-        if self.lib.b200_ipc_get_handle(base, handle) != 0:
+        if self.lib.b200_ipc_get_handle(block, handle) != 0:
             raise RuntimeError("cudaIpcGetMemHandle failed")
         gathered = [None] * self.world_size
         dist.all_gather_object(gathered, bytes(handle.raw), group=self.group)
@@ -143,8 +152,8 @@ class PeerComm(Communicator):
             rc = self.lib.b200_ipc_open(h, ctypes.byref(p))
             if rc != 0:
                 raise RuntimeError(f"cudaIpcOpenMemHandle for rank {r} failed ({rc})")
-            peers.append(p.value)
-        self._allocs.append({"base": base, "nbytes": nbytes, "peers": peers})
+            peers.append(p.value + self.GUARD_BYTES)
+        self._allocs.append({"base": base, "nbytes": nbytes, "peers": peers, "guards": bands})
         raw = torch.as_tensor(_CudaArray(base, nbytes), device=self.device)
         return raw.view(dtype)[:numel]
 
@@ -172,6 +181,24 @@ class PeerComm(Communicator):
         torch.cuda.synchronize()
         dist.barrier(group=self.group)        # every rank's buffer is zeroed before anybody reduces over it
         return t
+
+    def check_guards(self) -> None:
+        """Raise if any guard band around this rank's peer-addressable buffers was written (one small device
+        comparison per buffer and one host read; call it where the host synchronises anyway)."""
+        bad = []
+        for i, a in enumerate(self._allocs):
+            g = a.get("guards")
+            if g is None:
+                continue
+            n = a["nbytes"]
+            bad.append(((g[:self.GUARD_BYTES] != self.GUARD_PATTERN).sum()
+                        + (g[self.GUARD_BYTES + n:] != self.GUARD_PATTERN).sum()).reshape(1))
+        if bad:
+            counts = torch.cat(bad).tolist()
+            hit = [(i, c) for i, c in enumerate(counts) if c]
+            if hit:
+                raise RuntimeError(f"rank {self.rank}: guard bytes around peer buffers were overwritten "
+                                   f"(buffer index, bytes): {hit}")
 
     def _find(self, t: torch.Tensor):
         p = t.data_ptr()

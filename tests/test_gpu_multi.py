@@ -158,6 +158,15 @@ def _collectives(rank, world, port):
             assert torch.equal(t, want)
         torch.cuda.synchronize()
         native.check_status()
+        comm.check_guards()        # nothing wrote outside a peer-addressable buffer
+        # the check itself: a byte written just past a buffer is reported
+        probe = comm.alloc(256, torch.uint8)
+        band = comm._find(probe)["guards"]
+        band[comm.GUARD_BYTES + 256] = 0
+        with pytest.raises(RuntimeError, match="guard bytes"):
+            comm.check_guards()
+        band[comm.GUARD_BYTES + 256] = comm.GUARD_PATTERN
+        comm.check_guards()
     finally:
         dist.destroy_process_group()
 
@@ -269,6 +278,8 @@ def _train(rank, world, port, mode, comm_kind, fused, out):
             losses.append(t.item() / world)
         torch.cuda.synchronize()
         native.check_status()
+        if hasattr(wrapped.comm, "check_guards"):
+            wrapped.comm.check_guards()
         state = wrapped.full_state_dict() if mode == "fsdp" else None      # collective
         carried = getattr(wrapped.comm, "launches", {})
         if rank == 0:

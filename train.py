@@ -248,6 +248,9 @@ def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None 
             rejoin()
             if on_gpu:
                 native_ops.check_status()
+                guards = getattr(getattr(model, "comm", None), "check_guards", None)
+                if guards is not None:
+                    guards()        # canary bands around the peer-addressable buffers are intact
 
         if wandb_run is not None and step % gpu_log_interval == 0 and torch.cuda.is_available():
             rec = {"allocated_memory": int(torch.cuda.memory_allocated() / 1024 ** 2),
