@@ -210,6 +210,10 @@ def timed_region(step_fn, steps, warmup, world, sampler_gpu):
     return ms, wall, (clocks.stop() if clocks else None)
 
 
+class PeerPathGaveUp(RuntimeError):
+    """Raised on every rank together: the peer-memory collectives reported an error during the first step."""
+
+
 def run_native(args, cfg, rank, local_rank, world):
     import torch
     sys.path.insert(0, ROOT)
@@ -263,6 +267,23 @@ def run_native(args, cfg, rank, local_rank, world):
         it["i"] += 1
         last["loss"] = train_step(x, y)
 
+    if world > 1 and args.comm == "auto":
+        # One untimed step, then all ranks agree on whether any of them saw a device wait run out (a peer that never
+        # signalled) or an exception: either every rank goes on, or every rank raises and main() repeats the run
+        # on the library collectives and says so in its line.
+        import torch.distributed as dist
+        bad = torch.zeros(1, dtype=torch.int32, device=dev)
+        why = ""
+        try:
+            step_resident()
+            torch.cuda.synchronize()
+            native.check_status()
+        except Exception as e:      # noqa: BLE001 - whatever it was, the ranks must leave this step together
+            bad.fill_(1)
+            why = f"{type(e).__name__}: {str(e)[:120]}"
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()):
+            raise PeerPathGaveUp(why or "another rank reported an error")
     native.reset_launch_count()
     comm_counts = getattr(wrapped.comm, "launches", None)
     if comm_counts is not None:
@@ -513,7 +534,15 @@ def main():
                 print(json.dumps({"impl": "reference", "unavailable": why}))
             return 0
     else:
-        res = run_native(args, cfg, rank, local_rank, world)
+        try:
+            res = run_native(args, cfg, rank, local_rank, world)
+        except PeerPathGaveUp as e:
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+            args.comm, args.fused_optimizer = "torch", "off"
+            res = run_native(args, cfg, rank, local_rank, world)
+            res["comm"] += f" (the peer-memory collectives gave up in the first step and the run was repeated: {e})"
     # second half of the headline metric, short form: a serving replica per GPU after the training model is gone
     n_serv = 160 if args.serving_requests is None else args.serving_requests
     serving = None

@@ -108,14 +108,19 @@ __device__ __forceinline__ void signal_row(const PeerPtrs& flag_bases, unsigned 
   }
 }
 
-// Thread `tid` < world polls flags[tid] until it reaches `epoch` (wrap-safe) or the limit runs out.
+// Thread `tid` < world polls flags[tid] until it reaches `epoch` (wrap-safe) or the limit runs out.  Once the device
+// status word is set (some wait of this step has already given up) later waits give up at once: the step is lost
+// anyway, and a rank whose peer is gone then unwinds in one limit instead of one limit per collective.
 __device__ __forceinline__ bool poll_flag(const uint32_t* flags, int world, uint32_t epoch, unsigned long long limit_ns,
-                                          int tid) {
+                                          int tid, const uint32_t* status = nullptr) {
   if (tid >= world) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while ((int32_t)(ld_acquire_sys(flags + tid) - epoch) < 0) {
-    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
+    if ((++spins & 0xff) == 1) {
+      if (status != nullptr && *reinterpret_cast<const volatile uint32_t*>(status) != 0) return false;
+      if (globaltimer_ns() - t0 > limit_ns) return false;
+    }
     __nanosleep(64);
   }
   return true;
@@ -131,7 +136,7 @@ __device__ __forceinline__ void reduce_scatter_body(const ReduceTask& t, int tid
   if (tid == 0) sm->flag = 0;
   group_sync(bar_id, nthreads);
   const uint32_t* ready = reinterpret_cast<const uint32_t*>(t.flag_bases.p[t.rank]) + t.ready_row;
-  if (!poll_flag(ready, t.world, t.epoch, t.limit_ns, tid)) sm->flag = 1;
+  if (!poll_flag(ready, t.world, t.epoch, t.limit_ns, tid, t.status)) sm->flag = 1;
   group_sync(bar_id, nthreads);
   const bool ok = sm->flag == 0;
   float ss = 0.f;

@@ -23,8 +23,9 @@
 namespace b200 {
 
 // Block-wide forms of the flag helpers (all threads of the CTA call them).
-__device__ __forceinline__ bool wait_flags(const uint32_t* flags, int world, uint32_t epoch, uint64_t limit_ns) {
-  const bool ok = poll_flag(flags, world, epoch, limit_ns, threadIdx.x);
+__device__ __forceinline__ bool wait_flags(const uint32_t* flags, int world, uint32_t epoch, uint64_t limit_ns,
+                                           const uint32_t* status = nullptr) {
+  const bool ok = poll_flag(flags, world, epoch, limit_ns, threadIdx.x, status);
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 __device__ __forceinline__ void signal_peers(const PeerPtrs& flag_bases, size_t row_offset, int world, int rank,
@@ -36,7 +37,7 @@ __global__ void peer_barrier_kernel(PeerPtrs flag_bases, size_t row_offset, int 
                                     uint64_t limit_ns, uint32_t* status) {
   signal_peers(flag_bases, row_offset, world, rank, epoch);
   const uint32_t* mine = reinterpret_cast<const uint32_t*>(flag_bases.p[rank]) + row_offset;
-  if (!wait_flags(mine, world, epoch, limit_ns) && threadIdx.x == 0 && status) atomicCAS(status, 0u, ERR_WAIT_FLAG);
+  if (!wait_flags(mine, world, epoch, limit_ns, status) && threadIdx.x == 0 && status) atomicCAS(status, 0u, ERR_WAIT_FLAG);
 }
 
 // dst[p * n_vec + i] = src_p[i] for every peer p (16-byte vectors); the local shard is copied too.
@@ -109,7 +110,7 @@ __global__ void peer_signal_kernel(PeerPtrs flag_bases, size_t row_offset, int w
 
 // Wait for a row of flags (used before a staging buffer is overwritten).
 __global__ void peer_wait_kernel(const uint32_t* flags, int world, uint32_t epoch, uint64_t limit_ns, uint32_t* status) {
-  if (!wait_flags(flags, world, epoch, limit_ns) && threadIdx.x == 0 && status)
+  if (!wait_flags(flags, world, epoch, limit_ns, status) && threadIdx.x == 0 && status)
     atomicCAS(status, 0u, ERR_WAIT_FLAG | (2u << 8));
 }
 
@@ -121,7 +122,7 @@ peer_allreduce_kernel(PeerPtrs bufs, PeerPtrs flag_bases, size_t ready_row, size
   const uint32_t* ready = reinterpret_cast<const uint32_t*>(flag_bases.p[rank]) + ready_row;
   // A CTA whose wait ran out reports, skips the data and still takes part in the CTA count below, so that the
   // counter is back at zero for the next launch.
-  const bool ok = wait_flags(ready, world, epoch, limit_ns);
+  const bool ok = wait_flags(ready, world, epoch, limit_ns, status);
   if (!ok && threadIdx.x == 0 && status) atomicCAS(status, 0u, ERR_WAIT_FLAG | (3u << 8));
   const size_t n_vec = ok ? n / 4 : 0;
   const size_t chunk = (n_vec + world - 1) / world;
@@ -155,7 +156,7 @@ peer_allreduce_kernel(PeerPtrs bufs, PeerPtrs flag_bases, size_t ready_row, size
     if (threadIdx.x == 0) *counter = 0;
     signal_peers(flag_bases, done_row, world, rank, epoch);   // my chunk has been pushed everywhere
     const uint32_t* done = reinterpret_cast<const uint32_t*>(flag_bases.p[rank]) + done_row;
-    if (!wait_flags(done, world, epoch, limit_ns) && threadIdx.x == 0 && status)
+    if (!wait_flags(done, world, epoch, limit_ns, status) && threadIdx.x == 0 && status)
       atomicCAS(status, 0u, ERR_WAIT_FLAG | (4u << 8));
   }
 }

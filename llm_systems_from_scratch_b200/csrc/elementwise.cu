@@ -88,6 +88,67 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
   }
 }
 
+// Persistent variant for d = NC * 256: a warp walks rows warp, warp + n_warps, ... with the whole row in
+// registers (read once) and the next row's loads issued before the current row is reduced, so a warp always has
+// a row in flight; the grid is a few blocks per SM instead of one short-lived block per eight rows.
+__device__ __forceinline__ uint4 ld_stream16(const __nv_bfloat16* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+template <int NC>
+__global__ void __launch_bounds__(256, 2) rmsnorm_fwd_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               __nv_bfloat16* __restrict__ y,
+                                                               float* __restrict__ rstd, int rows, float eps) {
+  constexpr int D = NC * 256;
+  const int lane = threadIdx.x & 31;
+  const int n_warps = gridDim.x * (blockDim.x >> 5);
+  int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  uint4 cur[NC], nxt[NC];
+  if (row < rows) {
+#pragma unroll
+    for (int j = 0; j < NC; ++j) cur[j] = ld_stream16(x + (size_t)row * D + j * 256 + lane * 8);
+  }
+  for (; row < rows; row += n_warps) {
+    const int nrow = row + n_warps;
+    if (nrow < rows) {
+#pragma unroll
+      for (int j = 0; j < NC; ++j) nxt[j] = ld_stream16(x + (size_t)nrow * D + j * 256 + lane * 8);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      float f[8];
+      unpack8(cur[j], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)D + eps);
+    if (lane == 0 && rstd != nullptr) rstd[row] = r;
+    __nv_bfloat16* yr = y + (size_t)row * D;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      float f[8], g[8];
+      unpack8(cur[j], f);
+      load8(w + j * 256 + lane * 8, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * r * g[i];
+      store8(yr + j * 256 + lane * 8, f);
+    }
+#pragma unroll
+    for (int j = 0; j < NC; ++j) cur[j] = nxt[j];
+  }
+}
+
 // ------------------------------------------------------------------------ RMSNorm bwd
 // dx = [dres +] rstd * (dy*w) - rstd^3/d * sum(dy*w*x) * x ;  dw += dy * x * rstd.
 // Each block walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a thread owns up to MAXC groups of
@@ -114,22 +175,42 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
     if (c < d) load8(w + c, wreg[j]);
   }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const __nv_bfloat16* dyr = dy + (size_t)row * d;
-    const __nv_bfloat16* xr = x + (size_t)row * d;
-    const float r = rstd[row];
-    float g[RMS_BWD_MAXC][8], xv[RMS_BWD_MAXC][8], ev[RMS_BWD_MAXC][8];
+  // The next row's dy, x and residual gradient are requested before the current row's block-wide reduction, so
+  // the memory system always has a row per block in flight.
+  uint4 cdy[RMS_BWD_MAXC], cx[RMS_BWD_MAXC], ce[RMS_BWD_MAXC];
+  uint4 ndy[RMS_BWD_MAXC], nx[RMS_BWD_MAXC], ne[RMS_BWD_MAXC];
+  auto request = [&](int row, uint4 (&qdy)[RMS_BWD_MAXC], uint4 (&qx)[RMS_BWD_MAXC], uint4 (&qe)[RMS_BWD_MAXC]) {
+#pragma unroll
+    for (int j = 0; j < RMS_BWD_MAXC; ++j) {
+      const int c = (j * RMS_BWD_THREADS + threadIdx.x) * 8;
+      if (c < d) {
+        qdy[j] = ld_stream16(dy + (size_t)row * d + c);
+        qx[j] = ld_stream16(x + (size_t)row * d + c);
+        if (dres != nullptr) qe[j] = ld_stream16(dres + (size_t)row * d + c);
+      }
+    }
+  };
+  int row = blockIdx.x;
+  float r = 0.f, rn = 0.f;
+  if (row < rows) {
+    request(row, cdy, cx, ce);
+    r = rstd[row];
+  }
+  for (; row < rows; row += gridDim.x) {
+    const int nrow = row + gridDim.x;
+    if (nrow < rows) {
+      request(nrow, ndy, nx, ne);
+      rn = rstd[nrow];
+    }
+    float g[RMS_BWD_MAXC][8], xv[RMS_BWD_MAXC][8];
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < RMS_BWD_MAXC; ++j) {
       const int c = (j * RMS_BWD_THREADS + threadIdx.x) * 8;
       if (c < d) {
         float dyv[8];
-        load8(dyr + c, dyv);
-        load8(xr + c, xv[j]);
-        // the residual-branch gradient is requested with the other two rows, not after the block-wide reduction:
-        // its memory latency then overlaps theirs instead of following the reduction
-        if (dres != nullptr) load8(dres + (size_t)row * d + c, ev[j]);
+        unpack8(cdy[j], dyv);
+        unpack8(cx[j], xv[j]);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           dwacc[j][i] += dyv[i] * xv[j][i] * r;
@@ -149,12 +230,21 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = r * g[j][i] - coef * xv[j][i];
         if (dres != nullptr) {  // gradient arriving through the residual branch
+          float ev[8];
+          unpack8(ce[j], ev);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] += ev[j][i];
+          for (int i = 0; i < 8; ++i) o[i] += ev[i];
         }
         store8(dxr + c, o);
       }
     }
+#pragma unroll
+    for (int j = 0; j < RMS_BWD_MAXC; ++j) {
+      cdy[j] = ndy[j];
+      cx[j] = nx[j];
+      ce[j] = ne[j];
+    }
+    r = rn;
   }
   float* part = dw_partial + (size_t)blockIdx.x * d;
 #pragma unroll
@@ -620,10 +710,30 @@ using namespace b200;
 #define CHECK_LAUNCH() return (cudaGetLastError() == cudaSuccess) ? 0 : -4
 #define ALIGNED16(p) ((reinterpret_cast<uintptr_t>(p) & 15) == 0)
 
+static int g_rmsnorm_fwd_rows = 1;
+// 0 = always the one-block-per-eight-rows kernel (kept for A/B timing and as the general-width path)
+extern "C" void b200_rmsnorm_set_fwd_rows(int on) { g_rmsnorm_fwd_rows = on; }
+
 extern "C" int b200_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d, float eps,
                                 cudaStream_t st) {
   if (d % 8 || !ALIGNED16(x) || !ALIGNED16(w) || !ALIGNED16(y)) return -10;
   if (rows == 0) return 0;
+  // widths that are a multiple of 256 up to 2048 with enough rows to fill the GPU: the row-pipelined kernel
+  const int nc = d / 256;
+  if (g_rmsnorm_fwd_rows && d % 256 == 0 && nc <= 8 && rows >= 148 * 8 * 2 * 2) {
+    const int grid = 148 * 2;      // two resident blocks per SM at the widest instance (128 registers)
+#define RMS_FWD_ROWS(NC)                                                                                  \
+  case NC:                                                                                                \
+    rmsnorm_fwd_rows_kernel<NC><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,   \
+                                                      (__nv_bfloat16*)y, rstd, rows, eps);                \
+    break
+    switch (nc) {
+      RMS_FWD_ROWS(1); RMS_FWD_ROWS(2); RMS_FWD_ROWS(3); RMS_FWD_ROWS(4);
+      RMS_FWD_ROWS(5); RMS_FWD_ROWS(6); RMS_FWD_ROWS(7); RMS_FWD_ROWS(8);
+    }
+#undef RMS_FWD_ROWS
+    CHECK_LAUNCH();
+  }
   rmsnorm_fwd_kernel<<<(rows + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
                                                      (__nv_bfloat16*)y, rstd, rows, d, eps);
   CHECK_LAUNCH();

@@ -24,8 +24,13 @@ from . import attention, native
 
 
 def timeit(fn, iters: int = 10, warm: int = 3, flush: bool = True) -> float:
-    """Median milliseconds of ``fn`` over ``iters`` runs; L2 is overwritten between runs."""
+    """Median milliseconds of ``fn`` over ``iters`` runs; L2 is replaced between runs.
+
+    The flush writes a 256 MB buffer and then reads another one: after the write alone L2 is full of *dirty* lines,
+    and the timed kernel would pay for their write-back (up to 126 MB of DRAM writes, about 20 us) on top of its own
+    traffic - a cost that belongs to the flush, not to the kernel.  After the read pass L2 holds clean, unrelated lines."""
     scrub = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    clean = torch.zeros(64 << 20, dtype=torch.float32, device="cuda") if flush else None
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
@@ -33,6 +38,7 @@ def timeit(fn, iters: int = 10, warm: int = 3, flush: bool = True) -> float:
     for _ in range(iters):
         if scrub is not None:
             scrub.zero_()
+            clean.sum()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
@@ -107,6 +113,7 @@ def bench_elementwise():
     x = torch.randn(rows, d, device="cuda").bfloat16()
     w = torch.ones(d, device="cuda").bfloat16()
     dy = torch.randn_like(x)
+    dres = torch.randn_like(x)
     gu = torch.randn(rows, 2 * f, device="cuda").bfloat16()
     dh = torch.randn(rows, f, device="cuda").bfloat16()
     _, rstd = native.rmsnorm_fwd(x, w, 1e-5)
@@ -114,8 +121,17 @@ def bench_elementwise():
     p, g, m, v = (torch.randn(n, device="cuda") for _ in range(4))
     v.abs_()
     mirror = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    lib = native.load(required=True)
+
+    def fwd_per_block():       # the general-width kernel (one block per eight rows), for comparison
+        lib.b200_rmsnorm_set_fwd_rows(0)
+        native.rmsnorm_fwd(x, w, 1e-5)
+        lib.b200_rmsnorm_set_fwd_rows(1)
+
     cases = [("rmsnorm_fwd", lambda: native.rmsnorm_fwd(x, w, 1e-5), 2 * x.numel() * 2),
-             ("rmsnorm_bwd", lambda: native.rmsnorm_bwd(dy, x, w, rstd, dres=dy), 4 * x.numel() * 2),
+             ("rmsnorm_fwd_general_width_kernel", fwd_per_block, 2 * x.numel() * 2),
+             ("rmsnorm_bwd", lambda: native.rmsnorm_bwd(dy, x, w, rstd, dres=dres), 4 * x.numel() * 2),
+             ("rmsnorm_bwd_no_residual", lambda: native.rmsnorm_bwd(dy, x, w, rstd), 3 * x.numel() * 2),
              ("silu_mul_fwd", lambda: native.silu_mul_fwd(gu), 3 * rows * f * 2),
              ("silu_mul_bwd", lambda: native.silu_mul_bwd(dh, gu), 5 * rows * f * 2),
              ("adamw", lambda: native.adamw_step(p, g, m, v, mirror, 1e-3, 0.9, 0.95, 1e-8, 0.1, 3), n * 30)]

@@ -69,6 +69,7 @@ def _declare(lib):
         "b200_gemm_bf16_pair_gather": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P, ctypes.c_ulonglong, I, I, P, P,
                                        P, ctypes.c_uint, P, P],
         "b200_rmsnorm_fwd": [P, P, P, P, I, I, F, P],
+        "b200_rmsnorm_set_fwd_rows": [I],
         "b200_rmsnorm_bwd_parts": [I],
         "b200_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
         "b200_silu_mul_fwd": [P, P, L, I, P],

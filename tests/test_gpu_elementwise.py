@@ -14,7 +14,10 @@ def _close(a, b, atol, rtol=2e-2):
     assert bool((err <= lim).all()), f"max err {err.max().item()} (limit {atol}+{rtol}*|ref|)"
 
 
-@pytest.mark.parametrize("rows,d", [(64, 512), (1000, 2048), (33, 768), (257, 4096), (16, 1344)])
+@pytest.mark.parametrize("rows,d", [(64, 512), (1000, 2048), (33, 768), (257, 4096), (16, 1344),
+                                    # enough rows for the row-pipelined forward (widths 256 * 1..8) and several
+                                    # rows per block in the backward
+                                    (4800, 2048), (5003, 768), (6001, 1280), (4737, 256), (5000, 1344)])
 def test_rmsnorm_fwd_bwd(rows, d):
     from llm_systems_from_scratch_b200.ops import native, torch_impl
     x = torch.randn(rows, d, device="cuda").bfloat16()
@@ -31,6 +34,9 @@ def test_rmsnorm_fwd_bwd(rows, d):
     dw2 = dw.clone()
     native.rmsnorm_bwd(dy, x, w, rstd, dw_out=dw2, accumulate=True)
     _close(dw2, 2 * dwr, 2e-2 * math.sqrt(rows), 1e-2)
+    dres = torch.randn(rows, d, device="cuda").bfloat16()
+    dx3, _ = native.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
+    _close(dx3, dxr + dres.float(), 4e-2)
 
 
 @pytest.mark.parametrize("rows,f", [(128, 1344), (1000, 5504), (7, 8)])
