@@ -258,22 +258,33 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 }
 
 // dw[c] (=|+=) sum_p partial[p][c], fixed summation order => bitwise reproducible.
-// A block of 256 threads owns 32 columns: thread (g, x) sums partial rows g, g+8, ... of column x, then the
-// 8 row groups are combined in a fixed order through shared memory.
-__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nparts, int d,
-                                         int accumulate) {
-  __shared__ float sm[8][32];
+// A block of 1024 threads owns 32 columns: thread (g, x) sums partial rows g, g+32, ... of column x (four
+// independent loads in flight at a time), then the 32 row groups are combined in a fixed order through shared
+// memory.  With 592 partial rows a thread adds 18 or 19 of them, so the kernel takes a few microseconds.
+constexpr int RMS_DW_GROUPS = 32;
+__global__ void __launch_bounds__(32 * RMS_DW_GROUPS)
+rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nparts, int d, int accumulate) {
+  __shared__ float sm[RMS_DW_GROUPS][33];
   const int x = threadIdx.x & 31, g = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + x;
   float s = 0.f;
-  if (c < d)
-    for (int p = g; p < nparts; p += 8) s += partial[(size_t)p * d + c];
+  if (c < d) {
+    int p = g;
+    for (; p + 3 * RMS_DW_GROUPS < nparts; p += 4 * RMS_DW_GROUPS) {
+      const float a0 = partial[(size_t)p * d + c];
+      const float a1 = partial[(size_t)(p + RMS_DW_GROUPS) * d + c];
+      const float a2 = partial[(size_t)(p + 2 * RMS_DW_GROUPS) * d + c];
+      const float a3 = partial[(size_t)(p + 3 * RMS_DW_GROUPS) * d + c];
+      s += a0; s += a1; s += a2; s += a3;
+    }
+    for (; p < nparts; p += RMS_DW_GROUPS) s += partial[(size_t)p * d + c];
+  }
   sm[g][x] = s;
   __syncthreads();
   if (g == 0 && c < d) {
     float t = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) t += sm[k][x];
+    for (int k = 0; k < RMS_DW_GROUPS; ++k) t += sm[k][x];
     dw[c] = accumulate ? dw[c] + t : t;
   }
 }
@@ -762,7 +773,7 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
   else if (d <= 4096) RMS_BWD_LAUNCH(2);
   else RMS_BWD_LAUNCH(4);
 #undef RMS_BWD_LAUNCH
-  rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 256, 0, st>>>(dw_partial, dw, parts, d, accumulate_dw);
+  rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 32 * RMS_DW_GROUPS, 0, st>>>(dw_partial, dw, parts, d, accumulate_dw);
   CHECK_LAUNCH();
 }
 
@@ -976,7 +987,7 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   if (scratch == nullptr) return B200_ERR_NOALLOC_SETUP;
   if (rows == 0) {
     // no rows: the weight gradient of this call is zero (dw is cleared, or left as it is when accumulating)
-    rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 256, 0, st>>>(scratch, dw, 0, d, accumulate_dw);
+    rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 32 * RMS_DW_GROUPS, 0, st>>>(scratch, dw, 0, d, accumulate_dw);
     CHECK_LAUNCH();
   }
   const int parts = rows < B200_NOALLOC_MAX_PARTS ? rows : B200_NOALLOC_MAX_PARTS;
@@ -985,6 +996,6 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   rmsnorm_bwd_kernel<RMS_BWD_MAXC_LIMIT><<<parts, RMS_BWD_THREADS, 0, st>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
       (__nv_bfloat16*)dx, scratch, rows, d);
-  rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 256, 0, st>>>(scratch, dw, parts, d, accumulate_dw);
+  rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 32 * RMS_DW_GROUPS, 0, st>>>(scratch, dw, parts, d, accumulate_dw);
   CHECK_LAUNCH();
 }

@@ -62,6 +62,12 @@ struct GemmParams {
   int tma_store;       // CTA-pair kernel: the epilogue stages tiles in shared memory and writes them with TMA stores
   int num_m_tiles, num_n_tiles, group_m;
   uint32_t* status;
+  // Split-K (single-CTA kernel, small M): `splits` CTAs share an output tile, each contracts a slice of K and leaves
+  // an fp32 partial tile in `ws`; the epilogue warp that arrives last at the counter of its 32 rows adds their partials in
+  // split order (so the result does not depend on which CTA that is) and runs the epilogue.  splits <= 1 = off.
+  int splits;
+  float* ws;                  // splits * tiles partial tiles of BM x BN floats
+  uint32_t* tile_counters;    // four per tile (one per 32-row quarter), zero between launches (the last warp resets its own)
 };
 
 __device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& m_blk, int& n_blk) {

@@ -72,6 +72,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
+  // work unit = (tile, K slice); consecutive units are the slices of one tile, so they run at the same time on
+  // neighbouring CTAs
+  const int splits = p.splits > 1 ? p.splits : 1;
+  const int num_units = num_tiles * splits;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -79,11 +83,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int tile = unit / splits, split = unit - tile * splits;
+        const int kb_lo = split * num_kb / splits, kb_hi = (split + 1) * num_kb / splits;
         int m_blk, n_blk;
         tile_coords(tile, p, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word)) {
             report(p, abort_word, ERR_WAIT_EMPTY);
             ok = false;
@@ -121,7 +127,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t acc_phase[2] = {0, 0};
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++local) {
+        const int split = unit % splits;
+        const int kb_lo = split * num_kb / splits, kb_hi = (split + 1) * num_kb / splits;
         const int acc = local & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1, abort_word)) {
           report(p, abort_word, ERR_WAIT_TMEM_EMPTY);
@@ -131,7 +139,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         acc_phase[acc] ^= 1;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_word)) {
             report(p, abort_word, ERR_WAIT_FULL);
             ok = false;
@@ -146,7 +154,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                                          : make_smem_desc(a_base + k * (UMMA_K * 2), 16, 1024);
             const uint64_t b_desc = B_MN ? make_smem_desc(b_base + k * (UMMA_K * 128), 8192, 1024)
                                          : make_smem_desc(b_base + k * (UMMA_K * 2), 16, 1024);
-            umma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // smem stage is free once these MMAs have read it
           if (++stage == STAGES) {
@@ -163,7 +171,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint32_t acc_phase[2] = {0, 0};
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++local) {
+      const int tile = unit / splits, split = unit - tile * splits;
       int m_blk, n_blk;
       tile_coords(tile, p, m_blk, n_blk);
       const int acc = local & 1;
@@ -174,19 +183,77 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       }
       acc_phase[acc] ^= 1;
       tc_fence_after();
-      const int row = m_blk * BM + quarter * 32 + lane;
+      const int row_in_tile = quarter * 32 + lane;
+      const int row = m_blk * BM + row_in_tile;
       const int n0 = n_blk * BN;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      if (splits == 1) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (n0 + c * 32 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          epilogue_store(p, row, n0 + c * 32, r);
+        }
+        tc_fence_before();
+        mbar_arrive(&tmem_empty[acc]);
+        continue;
+      }
+      // Split-K.  The partial tile goes to the workspace as (BN / 4) x BM float4: piece j of every row is contiguous
+      // over the rows, so a warp's store (and the matching load of the reduction) is one 512-byte run.
+      float4* part = reinterpret_cast<float4*>(p.ws) + (size_t)unit * (BM * BN / 4);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         if (n0 + c * 32 >= p.N) break;
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        epilogue_store(p, row, n0 + c * 32, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          __stcg(part + (size_t)(c * 8 + j) * BM + row_in_tile,
+                 make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                             __uint_as_float(r[4 * j + 3])));
       }
       tc_fence_before();
-      mbar_arrive(&tmem_empty[acc]);
+      mbar_arrive(&tmem_empty[acc]);        // the accumulator is free: the next unit's MMAs may start
+      // Rows [32 * quarter, 32 * quarter + 32) of the tile are written by this warp in every one of the `splits`
+      // CTAs, so they have a counter of their own: the warp that arrives last adds the partials of its 32 rows.
+      // No CTA-wide barrier is involved.
+      __threadfence();                      // this lane's partial is visible before the warp is counted
+      __syncwarp();
+      uint32_t seen = 0;
+      if (lane == 0) {
+        __threadfence();
+        seen = atomicAdd(&p.tile_counters[tile * 4 + quarter], 1u);
+        if (seen == (uint32_t)splits - 1) p.tile_counters[tile * 4 + quarter] = 0;    // clean for the next launch
+      }
+      seen = __shfl_sync(0xffffffffu, seen, 0);
+      if (seen == (uint32_t)splits - 1) {
+        __threadfence();
+        const float4* first = reinterpret_cast<const float4*>(p.ws) + (size_t)tile * splits * (BM * BN / 4);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (n0 + c * 32 >= p.N) break;
+          float sum[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[j] = 0.f;
+          for (int sp = 0; sp < splits; ++sp) {      // fixed order: independent of which CTA does the adding
+            const float4* src = first + (size_t)sp * (BM * BN / 4) + (size_t)(c * 8) * BM + row_in_tile;
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + (size_t)j * BM);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              sum[4 * j] += v[j].x; sum[4 * j + 1] += v[j].y; sum[4 * j + 2] += v[j].z; sum[4 * j + 3] += v[j].w;
+            }
+          }
+          uint32_t r[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[j]);
+          epilogue_store(p, row, n0 + c * 32, r);
+        }
+      }
     }
   }
 
@@ -279,10 +346,10 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   p.num_m_tiles = (p.M + BM - 1) / BM;
   p.num_n_tiles = (p.N + BN - 1) / BN;
   p.group_m = 16;
-  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int units = p.num_m_tiles * p.num_n_tiles * (p.splits > 1 ? p.splits : 1);
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (tiles < grid) grid = tiles;
+  if (units < grid) grid = units;
   kern<<<grid, 192, S::TOTAL, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -298,9 +365,10 @@ using namespace b200;
 // Requirements (checked): base pointers 16-byte aligned; lda, ldb multiples of 8 elements.
 // Returns 0 on success, negative on argument / launch errors.  `status` (device uint32, may be null)
 // receives a non-zero code if a bounded wait inside the kernel gave up.
-extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
-                              long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int b_mn,
-                              int epi, int bn_hint, int max_ctas, uint32_t* status, cudaStream_t stream) {
+static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda,
+                          long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int epi, int bn_hint,
+                          int max_ctas, int splits, float* ws, uint32_t* tile_counters, uint32_t* status,
+                          cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -10;
@@ -346,6 +414,7 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   p.wait_counter = nullptr; p.wait_value = 0; p.wait_limit_ns = 0;
   p.rope_cs = nullptr; p.rope_seq = p.rope_d = p.rope_dh = p.rope_ctx = 0;
   p.swiglu_f = 0; p.H = nullptr; p.ldh = 0;
+  p.splits = splits > 1 ? splits : 1; p.ws = ws; p.tile_counters = tile_counters;
 
 #define DISPATCH(BN_)                                                                    \
   if (a_mn && b_mn) return launch_gemm<BN_, true, true>(tmA, tmB, p, max_ctas, stream);   \
@@ -357,4 +426,67 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   if (bn == 32) return launch_gemm<32, false, false>(tmA, tmB, p, max_ctas, stream);
   DISPATCH(128)
 #undef DISPATCH
+}
+
+extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                              long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int b_mn,
+                              int epi, int bn_hint, int max_ctas, uint32_t* status, cudaStream_t stream) {
+  return gemm_bf16_impl(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn, b_mn, epi, bn_hint, max_ctas, 1, nullptr,
+                        nullptr, status, stream);
+}
+
+// Tile width and number of K slices for a GEMM with at most two rows of tiles (decode: M <= 256, weights streamed
+// once).  A plain launch would use N / BN CTAs, each reading all of A and a BN-row slab of B over the whole of K; with
+// `splits` slices there are splits times as many CTAs, each reading a slice of both.  The estimate counts, per wave of
+// CTAs, the 128-byte operand rows a CTA loads, a fixed cost per CTA and the partial tiles the last CTA adds up.
+extern "C" void b200_gemm_splitk_plan(int M, int N, int K, int* bn_out, int* splits_out) {
+  const int sms = num_sms();
+  const int mt = (M + BM - 1) / BM;
+  const int num_kb = (K + BK - 1) / BK;
+  long long best = -1;
+  *bn_out = 0;
+  *splits_out = 1;
+  const int cand[3] = {256, 128, 64};
+  for (int ci = 0; ci < 3; ++ci) {
+    const int bn = cand[ci];
+    const int tiles = mt * ((N + bn - 1) / bn);
+    int s = sms / tiles;
+    if (s > 8) s = 8;
+    if (s > num_kb / 4) s = num_kb / 4;
+    if (s < 1) s = 1;
+    const int units = tiles * s;
+    const long long waves = (units + sms - 1) / sms;
+    const long long kb_per = (num_kb + s - 1) / s;
+    const long long cost = waves * (kb_per * (BM + bn) + 2048 + (s > 1 ? 2LL * s * bn : 0));
+    if (best < 0 || cost < best) {
+      best = cost;
+      *bn_out = bn;
+      *splits_out = s;
+    }
+  }
+}
+
+// Workspace a split-K launch needs: floats of partial tiles and tile counters (one CTA per unit, at most one wave
+// by construction of the plan, so 148 units of 128 x 256 floats bound it).
+extern "C" long long b200_gemm_splitk_ws_floats(void) { return (long long)num_sms() * BM * 256; }
+extern "C" int b200_gemm_splitk_counters(void) { return 4 * num_sms() * 4; }
+
+// b200_gemm_bf16 for K-major operands and M <= 256 with K split over CTAs (see b200_gemm_splitk_plan).  `ws` and
+// `tile_counters` are scratch of the sizes above; the counters must be zero on entry and are zero again on exit.
+// One launch at a time may use a given workspace (launches on one stream are ordered; other streams need their own).
+extern "C" int b200_gemm_bf16_splitk(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                                     long long lda, long long ldb, long long ldc, long long ldr, int epi, float* ws,
+                                     long long ws_floats, uint32_t* tile_counters, int n_counters, uint32_t* status,
+                                     cudaStream_t stream) {
+  int bn = 0, splits = 1;
+  b200_gemm_splitk_plan(M, N, K, &bn, &splits);
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  if (splits > 1 && (ws == nullptr || tile_counters == nullptr || (reinterpret_cast<uintptr_t>(ws) & 15) ||
+                     tiles * splits * BM * bn > ws_floats || tiles * 4 > n_counters))
+    return -12;
+  if (epi != EPI_BF16 && epi != EPI_F32 && epi != EPI_BF16_RES && epi != EPI_F32_ACC) return -11;
+  if (splits <= 1)
+    return gemm_bf16_impl(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, 0, 0, epi, 0, 0, 1, nullptr, nullptr, status, stream);
+  return gemm_bf16_impl(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, 0, 0, epi, bn, 0, splits, ws, tile_counters, status,
+                        stream);
 }

@@ -68,6 +68,9 @@ def _declare(lib):
         "b200_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P],
         "b200_gemm_bf16_pair_gather": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P, ctypes.c_ulonglong, I, I, P, P,
                                        P, ctypes.c_uint, P, P],
+        "b200_gemm_bf16_splitk": [P, P, P, P, I, I, I, L, L, L, L, I, P, L, P, I, P, P],
+        "b200_gemm_splitk_plan": [I, I, I, P, P],
+        "b200_gemm_splitk_counters": [],
         "b200_rmsnorm_fwd": [P, P, P, P, I, I, F, P],
         "b200_rmsnorm_set_fwd_rows": [I],
         "b200_rmsnorm_bwd_parts": [I],
@@ -136,6 +139,8 @@ def check_status(device=None):
     v = int(w[0].item())
     if v != 0:
         w.zero_()
+        for _, counters in _SPLITK_SCRATCH.values():     # a kernel that gave up may have left its tile counters mid-count
+            counters.zero_()
         raise KernelError(f"kernel reported error code {v & 0xff} from CTA {v >> 8}")
 
 
@@ -313,10 +318,52 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
                                      ldr, a_mn, b_mn, epi, _ptr(status_word(a.device)), _stream())
         _check(rc, "b200_gemm_bf16_pair")
         return out
+    if USE_SPLITK and layout == "nt" and m <= SPLITK_MAX_M and bn_hint == 0 and max_ctas == 0:
+        scratch = _splitk_scratch(a.device)
+        if scratch is not None:
+            ws, counters = scratch
+            rc = lib.b200_gemm_bf16_splitk(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb, out.stride(0),
+                                           ldr, epi, _ptr(ws), ws.numel(), _ptr(counters), counters.numel(),
+                                           _ptr(status_word(a.device)), _stream())
+            _check(rc, "b200_gemm_bf16_splitk")
+            return out
     rc = lib.b200_gemm_bf16(_ptr(a), _ptr(b), _ptr(out), _ptr(residual), m, n, k, lda, ldb, out.stride(0), ldr,
                             a_mn, b_mn, epi, bn_hint, max_ctas, _ptr(status_word(a.device)), _stream())
     _check(rc, "b200_gemm_bf16")
     return out
+
+
+# Split-K for GEMMs with at most two rows of tiles (decode).  One scratch (partial tiles, tile counters) per device,
+# kept for the life of the process because captured CUDA graphs hold its address.  Launches that use it must be
+# ordered with respect to each other: this package issues its GEMMs of a device on one stream at a time (the serving
+# engine replays its graphs on the stream that also runs the prefills), so they are; a caller that runs small-M
+# GEMMs on two streams at once must switch split-K off (B200_SPLITK=0).  The scratch is created outside CUDA-graph
+# capture only (memory allocated during a capture belongs to that graph's pool): a capture that comes first falls
+# back to the plain kernel.
+USE_SPLITK = os.environ.get("B200_SPLITK", "0") != "0"
+SPLITK_MAX_M = 256
+_SPLITK_SCRATCH: dict = {}
+
+
+def _splitk_scratch(device):
+    key = torch.device(device).index
+    got = _SPLITK_SCRATCH.get(key)
+    if got is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        lib = load()
+        lib.b200_gemm_splitk_ws_floats.restype = c_ll
+        ws = torch.empty(int(lib.b200_gemm_splitk_ws_floats()), dtype=torch.float32, device=device)
+        counters = torch.zeros(int(lib.b200_gemm_splitk_counters()), dtype=torch.int32, device=device)
+        got = _SPLITK_SCRATCH[key] = (ws, counters)
+    return got
+
+
+def splitk_plan(m: int, n: int, k: int) -> tuple[int, int]:
+    """(tile width, K slices) the split-K launcher picks for an (m, n, k) problem; slices == 1 means the plain kernel."""
+    bn, s = c_int(0), c_int(1)
+    load().b200_gemm_splitk_plan(m, n, k, ctypes.byref(bn), ctypes.byref(s))
+    return bn.value, s.value
 
 
 def gemm_qkv_rope(x, wqkv, cos_sin, seq: int, n_heads: int):

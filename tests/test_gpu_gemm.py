@@ -255,3 +255,45 @@ def test_gemm_wait_counter_is_bounded_and_reports():
         _check(out, _ref(a, b, "nt"), k)
     finally:
         lib.b200_gemm_set_wait_limit_ns(old)
+
+
+@pytest.mark.parametrize("shape", [(128, 2048, 2048), (64, 6144, 2048), (128, 11008, 2048), (128, 2048, 5504),
+                                   (256, 2048, 2048), (200, 1000, 320), (1, 2048, 2048), (130, 6152, 2112),
+                                   (128, 50264, 2048)])
+def test_gemm_split_k_small_m(shape, monkeypatch):
+    """Decode-sized GEMMs with K split over CTAs: same result as the fp32 matmul for every epilogue, bitwise the
+    same from run to run (the partial tiles are added in slice order whichever CTA arrives last), counters left at
+    zero, and the plain kernel's answer within rounding."""
+    from llm_systems_from_scratch_b200.ops import native
+    m, n, k = shape
+    a, b = _make("nt", m, n, k, "cuda")
+    ref = _ref(a, b, "nt")
+    monkeypatch.setattr(native, "USE_SPLITK", False)
+    plain = native.gemm(a, b, "nt")
+    monkeypatch.setattr(native, "USE_SPLITK", True)
+    bn, splits = native.splitk_plan(m, n, k)
+    assert bn in (64, 128, 256) and 1 <= splits <= 8
+    if (m, n, k) in ((128, 2048, 2048), (64, 6144, 2048), (128, 2048, 5504)):
+        assert splits > 1          # the shapes this exists for really are split
+    out = native.gemm(a, b, "nt")
+    _check(out, ref, k)
+    assert (out.float() - plain.float()).abs().max().item() <= 2e-2 * (k ** 0.5)
+    for _ in range(3):
+        assert torch.equal(native.gemm(a, b, "nt"), out)
+    res = torch.randn(m, n, device="cuda").bfloat16()
+    _check(native.gemm(a, b, "nt", residual=res), ref + res.float(), k)
+    out32 = native.gemm(a, b, "nt", out_dtype=torch.float32)
+    _check(out32, ref, k)
+    acc = out32.clone()
+    native.gemm(a, b, "nt", out=acc, accumulate=True)
+    _check(acc, 2 * ref, k)
+    # a strided output view (a column block of a wider buffer), as the serving engine's fused projections use
+    wide = torch.zeros(m, n + 64, device="cuda", dtype=torch.bfloat16)
+    view = wide[:, 32:32 + n] if n % 8 == 0 else wide[:, :n]
+    native.gemm(a, b, "nt", out=view)
+    _check(view, ref, k)
+    assert float(wide[:, n + 32:].abs().sum()) == 0.0 or n % 8 != 0
+    torch.cuda.synchronize()
+    native.check_status()
+    _, counters = native._splitk_scratch(a.device)
+    assert int(counters.abs().sum().item()) == 0
