@@ -238,14 +238,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           float sum[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) sum[j] = 0.f;
-          for (int sp = 0; sp < splits; ++sp) {      // fixed order: independent of which CTA does the adding
-            const float4* src = first + (size_t)sp * (BM * BN / 4) + (size_t)(c * 8) * BM + row_in_tile;
-            float4 v[8];
+          // added in slice order whichever CTA does the adding; four slices' loads are in flight at a time
+          for (int sp0 = 0; sp0 < splits; sp0 += 4) {
+            float4 v[4][8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + (size_t)j * BM);
+            for (int u = 0; u < 4; ++u) {
+              if (sp0 + u < splits) {
+                const float4* src = first + (size_t)(sp0 + u) * (BM * BN / 4) + (size_t)(c * 8) * BM + row_in_tile;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              sum[4 * j] += v[j].x; sum[4 * j + 1] += v[j].y; sum[4 * j + 2] += v[j].z; sum[4 * j + 3] += v[j].w;
+                for (int j = 0; j < 8; ++j) v[u][j] = __ldcg(src + (size_t)j * BM);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (sp0 + u < splits) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  sum[4 * j] += v[u][j].x; sum[4 * j + 1] += v[u][j].y;
+                  sum[4 * j + 2] += v[u][j].z; sum[4 * j + 3] += v[u][j].w;
+                }
+              }
             }
           }
           uint32_t r[32];
@@ -380,10 +392,22 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* R, 
   const bool small_ok = !a_mn && !b_mn;   // narrow tiles exist for the K-major (decode) layout only
   if (small_ok && (bn == 32 || bn == 64)) {
     // explicit request
-  } else if (small_ok && bn != 128 && bn != 256 && M <= BM) {
-    // one row of tiles: weight streaming is the bound, so use enough CTAs to pull from all of HBM
+  } else if (small_ok && bn != 128 && bn != 256 && M <= 2 * BM) {
+    // One or two rows of tiles (decode): every CTA streams its B rows once and all of A's rows over the whole of K,
+    // so a CTA's time goes with BM + bn and the launch's with the number of waves.  Narrow tiles spread the weights
+    // over more SMs but re-read A more often; a tile count just above the SM count costs a whole second wave.
     const int sms = num_sms();
-    bn = (N / 128 >= sms) ? 128 : ((N / 64 >= sms * 2 / 3) ? 64 : 32);
+    const int mt = (M + BM - 1) / BM;
+    long long best = -1;
+    const int cand[4] = {32, 64, 128, 256};
+    for (int ci = 0; ci < 4; ++ci) {
+      const long long tiles = (long long)mt * ((N + cand[ci] - 1) / cand[ci]);
+      const long long cost = ((tiles + sms - 1) / sms) * (BM + cand[ci]);
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn = cand[ci];
+      }
+    }
   } else if (bn != 128 && bn != 256) {
     const long long mt = (M + BM - 1) / BM;
     const long long sms = num_sms();

@@ -87,6 +87,55 @@ def bench_gemm():
                           "cublas_tflops": round(flops / t2 / 1e9, 1)}), flush=True)
 
 
+def bench_gemm_decode():
+    """The GEMMs of one decode step of the 1.3B model (QKV, output, gate|up, down projections of 24 layers; lm_head)
+    at batch 64 / 128 / 256: the plain single-CTA kernel, the same kernel with K split over CTAs where the launcher
+    would split, and torch.matmul (cuBLAS), against the time the weights alone need at the measured copy bandwidth.
+
+    CUDA events resolve about 2 us here, so a single 10 - 20 us kernel cannot be timed on its own: each figure is a
+    CUDA graph of 24 launches of the shape, every launch with its own weight matrix (24 layers; 0.2 - 1.1 GB per
+    shape, larger than L2), divided by 24."""
+    shapes = [("qkv", 6144, 2048, 24), ("out", 2048, 2048, 24), ("gate_up", 11008, 2048, 24), ("down", 2048, 5504, 24),
+              ("lm_head", 50264, 2048, 4)]
+    weights = {name: [torch.randn(n, k, device="cuda").bfloat16() for _ in range(reps)] for name, n, k, reps in shapes}
+
+    def graph_us(fn, ws):
+        for w in ws[:2]:
+            fn(w)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for w in ws:
+                fn(w)
+        return timeit(g.replay, iters=10, warm=2) * 1e3 / len(ws)
+
+    for m in (64, 128, 256):
+        tot = {"plain": 0.0, "splitk": 0.0, "cublas": 0.0}
+        for name, n, k, reps in shapes:
+            a = torch.randn(m, k, device="cuda").bfloat16()
+            out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+            prev = native.USE_SPLITK
+            native.USE_SPLITK = False
+            t_plain = graph_us(lambda w: native.gemm(a, w, "nt", out=out), weights[name])
+            native.USE_SPLITK = True
+            native.SPLITK_MIN_K = 0
+            t_split = graph_us(lambda w: native.gemm(a, w, "nt", out=out), weights[name])
+            native.USE_SPLITK = prev
+            native.SPLITK_MIN_K = native.SPLITK_MIN_K_DEFAULT
+            t_lib = graph_us(lambda w: torch.matmul(a, w.t(), out=out), weights[name])
+            native.check_status()
+            bn, splits = native.splitk_plan(m, n, k)
+            w_us = n * k * 2 / 6541.8e3
+            per_step = 1 if name == "lm_head" else 24
+            for key, t in (("plain", t_plain), ("splitk", t_split), ("cublas", t_lib)):
+                tot[key] += per_step * t / 1e3
+            print(json.dumps({"op": "gemm-decode", "name": name, "m": m, "n": n, "k": k, "split_tile_n": bn,
+                              "k_slices": splits, "plain_us": round(t_plain, 2), "splitk_us": round(t_split, 2),
+                              "cublas_us": round(t_lib, 2), "weights_at_copy_bw_us": round(w_us, 2)}), flush=True)
+        print(json.dumps({"op": "gemm-decode-step", "m": m, "layers": 24,
+                          **{k + "_ms": round(v, 3) for k, v in tot.items()}}), flush=True)
+
+
 def bench_attention():
     for b, s, h, dh in [(8, 2048, 16, 128), (16, 1024, 12, 64), (2, 4096, 32, 128)]:
         qkv = torch.randn(b * s, 3 * h * dh, device="cuda").bfloat16()
@@ -315,14 +364,51 @@ def paged_decode_small():
                       "splits": splits, "ok": True}))
 
 
+def decode_launches(argv=()):
+    """One decode step of the 1.3B serving model at a given batch and context with every kernel launched on its own
+    (no CUDA graph), bracketed by cudaProfilerStart / Stop: under ``ncu --profile-from-start off`` the capture is
+    exactly the launches of that step."""
+    from ..models.transformer import TransformerLM
+    from ..serving import Request, ServingEngine
+    batch = int(argv[0]) if argv else 128
+    ctx = int(argv[1]) if len(argv) > 1 else 1200
+    cfg = dict(vocab_size=50257, context_length=2048, d_model=2048, num_layers=24, num_heads=16, d_ff=5504, rope_theta=10000.0)
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = TransformerLM(**cfg, use_flash_attn=True, use_custom_triton=True)
+    model.eval()
+    g = torch.Generator().manual_seed(1)
+    eng = ServingEngine(model, num_pages=batch * (-(-(ctx + 64) // 16)) + 8, page_size=16, max_batch=batch,
+                        max_context=2048, use_cuda_graphs=False)
+    for i in range(batch):
+        eng.sched.add(Request(i, torch.randint(0, 50257, (ctx,), generator=g).tolist(), 64))
+    eng._realtime, eng._virtual = False, float("inf")
+    while eng.sched.waiting:
+        eng.step(float("inf"))
+    running = list(eng.sched.running)
+    for _ in range(2):
+        eng.decode(running)
+    torch.cuda.synchronize()
+    native.reset_launch_count()
+    torch.cuda.profiler.start()
+    eng.decode(running)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    native.check_status()
+    print(json.dumps({"op": "decode-launches", "batch": batch, "context": ctx, "own_launches": native.launch_count(),
+                      "split_k": native.USE_SPLITK}))
+
+
 def main(argv=None):
     argv = argv if argv is not None else sys.argv[1:]
     mode = argv[0] if argv else "gemm"
     if mode == "decode":
         return bench_decode(argv[1:])
+    if mode == "decode-launches":
+        return decode_launches(argv[1:])
     if mode == "paged-decode-small":
         return paged_decode_small()
-    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "gemm-small": gemm_small, "gemm-pair-small": gemm_pair_small, "attention-trace": attention_trace,
+    {"gemm": bench_gemm, "gemm-decode": bench_gemm_decode, "attention": bench_attention, "elementwise": bench_elementwise, "gemm-small": gemm_small, "gemm-pair-small": gemm_pair_small, "attention-trace": attention_trace,
      "attention-small": attention_small}[mode]()
 
 

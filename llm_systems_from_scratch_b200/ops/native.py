@@ -318,7 +318,7 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
                                      ldr, a_mn, b_mn, epi, _ptr(status_word(a.device)), _stream())
         _check(rc, "b200_gemm_bf16_pair")
         return out
-    if USE_SPLITK and layout == "nt" and m <= SPLITK_MAX_M and bn_hint == 0 and max_ctas == 0:
+    if USE_SPLITK and layout == "nt" and m <= SPLITK_MAX_M and k >= SPLITK_MIN_K and bn_hint == 0 and max_ctas == 0:
         scratch = _splitk_scratch(a.device)
         if scratch is not None:
             ws, counters = scratch
@@ -340,8 +340,10 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
 # GEMMs on two streams at once must switch split-K off (B200_SPLITK=0).  The scratch is created outside CUDA-graph
 # capture only (memory allocated during a capture belongs to that graph's pool): a capture that comes first falls
 # back to the plain kernel.
-USE_SPLITK = os.environ.get("B200_SPLITK", "0") != "0"
+USE_SPLITK = os.environ.get("B200_SPLITK", "1") != "0"
 SPLITK_MAX_M = 256
+SPLITK_MIN_K_DEFAULT = 4096      # measured: splitting pays for the long contractions (the down projection) only
+SPLITK_MIN_K = SPLITK_MIN_K_DEFAULT
 _SPLITK_SCRATCH: dict = {}
 
 

@@ -30,7 +30,8 @@ def _make(layout, m, n, k, dev):
 
 def _check(out, ref, k):
     err = (out.float() - ref).abs().max().item()
-    tol = 2e-2 * (k ** 0.5) if out.dtype == torch.bfloat16 else 1e-3 * (k ** 0.5)
+    # accumulation error grows with sqrt(k); a bf16 result adds half an ulp of the largest value on top
+    tol = 2e-2 * (k ** 0.5) + ref.abs().max().item() * 2.0 ** -8 if out.dtype == torch.bfloat16 else 1e-3 * (k ** 0.5)
     assert err <= tol, f"max abs err {err} > {tol}"
 
 
@@ -271,13 +272,15 @@ def test_gemm_split_k_small_m(shape, monkeypatch):
     monkeypatch.setattr(native, "USE_SPLITK", False)
     plain = native.gemm(a, b, "nt")
     monkeypatch.setattr(native, "USE_SPLITK", True)
+    monkeypatch.setattr(native, "SPLITK_MIN_K", 0)
     bn, splits = native.splitk_plan(m, n, k)
     assert bn in (64, 128, 256) and 1 <= splits <= 8
     if (m, n, k) in ((128, 2048, 2048), (64, 6144, 2048), (128, 2048, 5504)):
         assert splits > 1          # the shapes this exists for really are split
     out = native.gemm(a, b, "nt")
     _check(out, ref, k)
-    assert (out.float() - plain.float()).abs().max().item() <= 2e-2 * (k ** 0.5)
+    # two bf16 roundings of sums taken in different orders: up to one ulp of the largest value apart
+    assert (out.float() - plain.float()).abs().max().item() <= 2e-2 * (k ** 0.5) + ref.abs().max().item() * 2.0 ** -7
     for _ in range(3):
         assert torch.equal(native.gemm(a, b, "nt"), out)
     res = torch.randn(m, n, device="cuda").bfloat16()
