@@ -63,6 +63,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
                                                           const __nv_bfloat16* __restrict__ w,
                                                           __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
                                                           int rows, int d, float eps) {
+  pdl_sync();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -108,6 +109,7 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_fwd_rows_kernel(const __nv_bfl
                                                                const __nv_bfloat16* __restrict__ w,
                                                                __nv_bfloat16* __restrict__ y,
                                                                float* __restrict__ rstd, int rows, float eps) {
+  pdl_sync();
   constexpr int D = NC * 256;
   const int lane = threadIdx.x & 31;
   const int n_warps = gridDim.x * (blockDim.x >> 5);
@@ -257,6 +259,89 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// Variant for d = NC * 256 and enough rows to fill the GPU: one warp per row, no block-wide barrier inside the row
+// loop.  A lane owns 8 * NC columns; a row's dy, x and residual gradient (3 * NC 16-byte loads per lane) are all
+// requested before the first is used, and with eight independent warps per SM a row's latency is covered by the
+// other warps.  The weight-gradient partial of a lane's columns stays in registers over all rows of the warp; at the
+// end the eight warps of a block add theirs in warp order through shared memory, so a launch leaves gridDim.x
+// partial rows (148 instead of 592) for rmsnorm_dw_reduce_kernel.
+template <int NC>
+__global__ void __launch_bounds__(256, 1)
+rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                        float* __restrict__ dw_partial, int rows) {
+  constexpr int D = NC * 256;
+  __shared__ float dw_s[D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = gridDim.x * 8;
+  // the weight row (4 KB at most) is re-read from L1 where it is used: keeping it in registers as well would spill
+  const __nv_bfloat16* wl = w + lane * 8;
+  float dwacc[NC][8];
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+  }
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += n_warps) {
+    const size_t base = (size_t)row * D + lane * 8;
+    uint4 qdy[NC], qx[NC], qe[NC];
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      qdy[j] = ld_stream16(dy + base + j * 256);
+      qx[j] = ld_stream16(x + base + j * 256);
+      if (dres != nullptr) qe[j] = ld_stream16(dres + base + j * 256);
+    }
+    const float r = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      float dyv[8], xv[8], wv[8];
+      unpack8(qdy[j], dyv);
+      unpack8(qx[j], xv);
+      load8(wl + j * 256, wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        dwacc[j][i] += dyv[i] * xv[i] * r;
+        dot += dyv[i] * wv[i] * xv[i];
+      }
+    }
+    dot = warp_sum(dot);
+    const float coef = r * r * r * dot / (float)D;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      float dyv[8], xv[8], wv[8], o[8];
+      unpack8(qdy[j], dyv);
+      unpack8(qx[j], xv);
+      load8(wl + j * 256, wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = r * (dyv[i] * wv[i]) - coef * xv[i];
+      if (dres != nullptr) {
+        float ev[8];
+        unpack8(qe[j], ev);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += ev[i];
+      }
+      store8(dx + base + j * 256, o);
+    }
+  }
+  // block partial: warps add in warp order (fixed), one barrier per warp
+  for (int wi = 0; wi < 8; ++wi) {
+    if (warp == wi) {
+#pragma unroll
+      for (int j = 0; j < NC; ++j) {
+        float* dst = dw_s + j * 256 + lane * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dst[i] = (wi == 0) ? dwacc[j][i] : dst[i] + dwacc[j][i];
+      }
+    }
+    __syncthreads();
+  }
+  float* part = dw_partial + (size_t)blockIdx.x * D;
+  for (int c = threadIdx.x * 4; c < D; c += 256 * 4)
+    *reinterpret_cast<float4*>(part + c) = *reinterpret_cast<const float4*>(dw_s + c);
+}
+
 // dw[c] (=|+=) sum_p partial[p][c], fixed summation order => bitwise reproducible.
 // A block of 1024 threads owns 32 columns: thread (g, x) sums partial rows g, g+32, ... of column x (four
 // independent loads in flight at a time), then the 32 row groups are combined in a fixed order through shared
@@ -293,6 +378,7 @@ rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ 
 // gu is (rows, 2F): gate columns [0,F), up columns [F,2F).
 __global__ void silu_mul_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h,
                                     long long rows, int F) {
+  pdl_sync();
   const long long groups = rows * (F / 8);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < groups;
        i += (long long)gridDim.x * blockDim.x) {
@@ -336,6 +422,7 @@ __global__ void silu_mul_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const 
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cos_sin,
                             const int* __restrict__ positions, long long rows, int seq, int d, int dh, int ctx,
                             float sign) {
+  pdl_sync();
   const int gpr = 2 * d / 8;  // groups of 8 elements per row over the Q and K parts
   const long long groups = rows * gpr;
   const float* cosb = cos_sin;
@@ -366,6 +453,7 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __rest
 // ------------------------------------------------------------------------ Embedding
 __global__ void embedding_fwd_kernel(const long long* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
                                      __nv_bfloat16* __restrict__ out, long long rows, int d, int vocab) {
+  pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -532,6 +620,7 @@ __global__ void sum_rows_kernel(const float* __restrict__ v, long long n, float*
 // argmax over the first `vocab` columns of each row of bf16 logits; ties -> lowest index.
 __global__ void argmax_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int vocab,
                               long long* __restrict__ out) {
+  pdl_sync();
   __shared__ float sv[32];
   __shared__ int si[32];
   const __nv_bfloat16* lr = logits + (long long)blockIdx.x * ld;
@@ -721,7 +810,20 @@ using namespace b200;
 #define CHECK_LAUNCH() return (cudaGetLastError() == cudaSuccess) ? 0 : -4
 #define ALIGNED16(p) ((reinterpret_cast<uintptr_t>(p) & 15) == 0)
 
+namespace b200 {
+int g_pdl_enabled = 0;
+}
+// 1 = kernels of the decode path (norm, GEMM, rotary embedding, KV append, paged attention, SiLU, embedding, argmax)
+// are launched as programmatic dependents of the kernel before them; returns the previous setting.
+extern "C" int b200_set_pdl(int on) {
+  const int old = b200::g_pdl_enabled;
+  b200::g_pdl_enabled = on ? 1 : 0;
+  return old;
+}
+
 static int g_rmsnorm_fwd_rows = 1;
+static int g_rmsnorm_bwd_rows = 1;
+extern "C" void b200_rmsnorm_set_bwd_rows(int on) { g_rmsnorm_bwd_rows = on; }
 // 0 = always the one-block-per-eight-rows kernel (kept for A/B timing and as the general-width path)
 extern "C" void b200_rmsnorm_set_fwd_rows(int on) { g_rmsnorm_fwd_rows = on; }
 
@@ -735,8 +837,8 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* w, void* y, float* rs
     const int grid = 148 * 2;      // two resident blocks per SM at the widest instance (128 registers)
 #define RMS_FWD_ROWS(NC)                                                                                  \
   case NC:                                                                                                \
-    rmsnorm_fwd_rows_kernel<NC><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,   \
-                                                      (__nv_bfloat16*)y, rstd, rows, eps);                \
+    launch_dep(rmsnorm_fwd_rows_kernel<NC>, grid, 256, 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, \
+               (__nv_bfloat16*)y, rstd, rows, eps);                                                       \
     break
     switch (nc) {
       RMS_FWD_ROWS(1); RMS_FWD_ROWS(2); RMS_FWD_ROWS(3); RMS_FWD_ROWS(4);
@@ -745,8 +847,8 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* w, void* y, float* rs
 #undef RMS_FWD_ROWS
     CHECK_LAUNCH();
   }
-  rmsnorm_fwd_kernel<<<(rows + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                                     (__nv_bfloat16*)y, rstd, rows, d, eps);
+  launch_dep(rmsnorm_fwd_kernel, (rows + 7) / 8, 256, 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+             (__nv_bfloat16*)y, rstd, rows, d, eps);
   CHECK_LAUNCH();
 }
 
@@ -763,6 +865,24 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
       !ALIGNED16(dres))
     return -10;
   if (rows == 0) return 0;
+  const int nc = d / 256;
+  if (g_rmsnorm_bwd_rows && d % 256 == 0 && nc <= 8 && rows >= 148 * 8) {
+    const int parts = 148;        // <= b200_rmsnorm_bwd_parts(rows) partial rows of the scratch are used
+#define RMS_BWD_ROWS(NC)                                                                                     \
+  case NC:                                                                                                   \
+    rmsnorm_bwd_rows_kernel<NC><<<parts, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,    \
+                                                       (const __nv_bfloat16*)w, rstd,                        \
+                                                       (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx,       \
+                                                       dw_partial, rows);                                    \
+    break
+    switch (nc) {
+      RMS_BWD_ROWS(1); RMS_BWD_ROWS(2); RMS_BWD_ROWS(3); RMS_BWD_ROWS(4);
+      RMS_BWD_ROWS(5); RMS_BWD_ROWS(6); RMS_BWD_ROWS(7); RMS_BWD_ROWS(8);
+    }
+#undef RMS_BWD_ROWS
+    rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 32 * RMS_DW_GROUPS, 0, st>>>(dw_partial, dw, parts, d, accumulate_dw);
+    CHECK_LAUNCH();
+  }
   const int parts = b200_rmsnorm_bwd_parts(rows);
 #define RMS_BWD_LAUNCH(C)                                                                                   \
   rmsnorm_bwd_kernel<C><<<parts, RMS_BWD_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, \
@@ -780,7 +900,8 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
 extern "C" int b200_silu_mul_fwd(const void* gu, void* h, long long rows, int F, cudaStream_t st) {
   if (F % 8 || !ALIGNED16(gu) || !ALIGNED16(h)) return -10;
   if (rows == 0) return 0;
-  silu_mul_fwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)h, rows, F);
+  launch_dep(silu_mul_fwd_kernel, grid_for(rows * (F / 8), 256), 256, 0, st, (const __nv_bfloat16*)gu, (__nv_bfloat16*)h,
+             rows, F);
   CHECK_LAUNCH();
 }
 
@@ -797,8 +918,8 @@ extern "C" int b200_rope(void* qkv, const float* cos_sin, const int* positions, 
   if (dh % 8 || d % dh || !ALIGNED16(qkv) || !ALIGNED16(cos_sin) || seq <= 0) return -10;
   if (positions == nullptr && seq > ctx) return -11;
   if (rows == 0) return 0;
-  rope_kernel<<<grid_for(rows * (2 * d / 8), 256), 256, 0, st>>>((__nv_bfloat16*)qkv, cos_sin, positions, rows, seq, d,
-                                                                 dh, ctx, inverse ? -1.f : 1.f);
+  launch_dep(rope_kernel, grid_for(rows * (2 * d / 8), 256), 256, 0, st, (__nv_bfloat16*)qkv, cos_sin, positions, rows,
+             seq, d, dh, ctx, inverse ? -1.f : 1.f);
   CHECK_LAUNCH();
 }
 
@@ -806,8 +927,8 @@ extern "C" int b200_embedding_fwd(const long long* tokens, const void* table, vo
                                   int vocab, cudaStream_t st) {
   if (d % 8 || !ALIGNED16(table) || !ALIGNED16(out)) return -10;
   if (rows == 0) return 0;
-  embedding_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(tokens, (const __nv_bfloat16*)table,
-                                                                   (__nv_bfloat16*)out, rows, d, vocab);
+  launch_dep(embedding_fwd_kernel, (unsigned)((rows + 7) / 8), 256, 0, st, tokens, (const __nv_bfloat16*)table,
+             (__nv_bfloat16*)out, rows, d, vocab);
   CHECK_LAUNCH();
 }
 
@@ -879,7 +1000,7 @@ extern "C" int b200_xent(void* logits, const long long* targets, float* loss, fl
 
 extern "C" int b200_argmax(const void* logits, long long rows, long long ld, int vocab, long long* out, cudaStream_t st) {
   if (rows == 0) return 0;
-  argmax_kernel<<<(unsigned)rows, 256, 0, st>>>((const __nv_bfloat16*)logits, ld, vocab, out);
+  launch_dep(argmax_kernel, (unsigned)rows, 256, 0, st, (const __nv_bfloat16*)logits, ld, vocab, out);
   CHECK_LAUNCH();
 }
 

@@ -65,6 +65,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     tmem_alloc(tmem_holder, TMEM_COLS);
     tmem_relinquish();
   }
+  // Everything above touches only shared and tensor memory, so as a programmatic dependent it overlaps the tail of
+  // the kernel before this one; from here on global memory is read and written.
+  pdl_sync();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -172,7 +175,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     int local = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++local) {
-      const int tile = unit / splits, split = unit - tile * splits;
+      const int tile = unit / splits;
       int m_blk, n_blk;
       tile_coords(tile, p, m_blk, n_blk);
       const int acc = local & 1;
@@ -362,7 +365,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (units < grid) grid = units;
-  kern<<<grid, 192, S::TOTAL, stream>>>(tmA, tmB, p);
+  if (launch_dep(kern, grid, 192, S::TOTAL, stream, tmA, tmB, p) != cudaSuccess) return -4;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -41,6 +41,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,        // (R, 3d) packe
                     float* __restrict__ part_ml,                 // (R, H, splits, 2)
                     int q_ld, int heads, int page_size, int max_pages, int splits, float scale_log2, int num_pages,
                     uint32_t* __restrict__ status) {
+  pdl_sync();
   constexpr int LPT = DH / 8;            // lanes per head (16-byte loads)
   const int r = blockIdx.x, split = blockIdx.y;
   const int d = heads * DH;
@@ -154,6 +155,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,        // (R, 3d) packe
 template <int DH>
 __global__ void paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                           __nv_bfloat16* __restrict__ out, int heads, int splits) {
+  pdl_sync();
   const int r = blockIdx.x / heads, h = blockIdx.x % heads;
   const size_t base = ((size_t)r * heads + h) * splits;
   float gm = -INFINITY;
@@ -172,6 +174,7 @@ __global__ void paged_decode_merge_kernel(const float* __restrict__ part_o, cons
 __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ k_cache,
                                  __nv_bfloat16* __restrict__ v_cache, const long long* __restrict__ slots, long long rows,
                                  int d, long long num_slots, uint32_t* __restrict__ status) {
+  pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -210,17 +213,17 @@ extern "C" int b200_paged_decode(const void* q, const void* k_cache, const void*
   const dim3 grid(rows, splits);
   const float sl2 = scale * 1.4426950408889634f;
   if (dh == 128) {
-    paged_decode_kernel<128><<<grid, threads, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
-                                                       (const __nv_bfloat16*)v_cache, block_tables, context_lens, part_o,
-                                                       part_ml, q_ld, heads, page_size, max_pages, splits, sl2, num_pages,
-                                                       status);
-    paged_decode_merge_kernel<128><<<rows * heads, 128, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, heads, splits);
+    launch_dep(paged_decode_kernel<128>, grid, threads, 0, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
+               (const __nv_bfloat16*)v_cache, block_tables, context_lens, part_o, part_ml, q_ld, heads, page_size,
+               max_pages, splits, sl2, num_pages, status);
+    launch_dep(paged_decode_merge_kernel<128>, rows * heads, 128, 0, st, part_o, part_ml, (__nv_bfloat16*)out, heads,
+               splits);
   } else {
-    paged_decode_kernel<64><<<grid, threads, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
-                                                      (const __nv_bfloat16*)v_cache, block_tables, context_lens, part_o,
-                                                      part_ml, q_ld, heads, page_size, max_pages, splits, sl2, num_pages,
-                                                      status);
-    paged_decode_merge_kernel<64><<<rows * heads, 64, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, heads, splits);
+    launch_dep(paged_decode_kernel<64>, grid, threads, 0, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
+               (const __nv_bfloat16*)v_cache, block_tables, context_lens, part_o, part_ml, q_ld, heads, page_size,
+               max_pages, splits, sl2, num_pages, status);
+    launch_dep(paged_decode_merge_kernel<64>, rows * heads, 64, 0, st, part_o, part_ml, (__nv_bfloat16*)out, heads,
+               splits);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -231,7 +234,7 @@ extern "C" int b200_kv_append(const void* qkv, void* k_cache, void* v_cache, con
       (reinterpret_cast<uintptr_t>(v_cache) & 15))
     return -10;
   if (rows <= 0) return 0;
-  kv_append_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)k_cache,
-                                                               (__nv_bfloat16*)v_cache, slots, rows, d, num_slots, status);
+  launch_dep(kv_append_kernel, (unsigned)((rows + 7) / 8), 256, 0, st, (const __nv_bfloat16*)qkv,
+             (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slots, rows, d, num_slots, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -298,4 +298,34 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   return __bfloat1622float2(v);
 }
 
+
+// Programmatic dependent launch.  A kernel launched through launch_dep() may be placed on the SMs while the kernel
+// before it on the stream is still running: its CTAs do their set-up (barriers, tensor memory, index arithmetic) and
+// then block in pdl_sync() until that kernel has completed and its writes are visible.  pdl_sync() must come before
+// the first access to global memory of any kind (a write may alias something the previous kernel still reads).  It
+// then lets the kernel after this one start the same way.  In a kernel launched the ordinary way both instructions
+// do nothing.
+__device__ __forceinline__ void pdl_sync() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+extern int g_pdl_enabled;   // host switch (b200_set_pdl); defined in elementwise.cu
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = g_pdl_enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 }  // namespace b200

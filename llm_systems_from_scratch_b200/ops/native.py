@@ -51,6 +51,8 @@ def load(required: bool = True):
     lib = ctypes.CDLL(str(_LIB_PATH))
     _declare(lib)
     _LIB = lib
+    if os.environ.get("B200_PDL", "1") != "0":
+        lib.b200_set_pdl(1)
     return lib
 
 
@@ -73,6 +75,8 @@ def _declare(lib):
         "b200_gemm_splitk_counters": [],
         "b200_rmsnorm_fwd": [P, P, P, P, I, I, F, P],
         "b200_rmsnorm_set_fwd_rows": [I],
+        "b200_rmsnorm_set_bwd_rows": [I],
+        "b200_set_pdl": [I],
         "b200_rmsnorm_bwd_parts": [I],
         "b200_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
         "b200_silu_mul_fwd": [P, P, L, I, P],
@@ -110,6 +114,13 @@ def _declare(lib):
             continue
         fn.argtypes = args
         fn.restype = I
+
+
+def set_pdl(on: bool) -> bool:
+    """Launch the kernels of the decode path as programmatic dependents of the kernel before them (their set-up then
+    overlaps that kernel's tail; each waits for it to complete before touching global memory).  Returns the previous
+    setting."""
+    return bool(load().b200_set_pdl(1 if on else 0))
 
 
 def has(symbol: str) -> bool:

@@ -93,3 +93,31 @@ def test_engine_matches_full_recompute_on_gpu(graphs):
             ids = torch.cat((ids, torch.tensor([[tok]], device="cuda")), dim=1)
     assert total > 20 and agree == total, (agree, total)
     assert eng.cache.allocator.free == eng.cache.num_pages
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_engine_with_programmatic_dependent_launch_gives_the_same_tokens(graphs):
+    """The decode-path kernels launched as programmatic dependents (each starts while the kernel before it drains and
+    waits for it before touching global memory) must produce exactly the tokens of ordinary launches, eagerly and in
+    captured graphs, and leave the status word clean."""
+    from llm_systems_from_scratch_b200.models.transformer import TransformerLM
+    from llm_systems_from_scratch_b200.ops import native
+    from llm_systems_from_scratch_b200.serving import ServingEngine
+    torch.manual_seed(0)
+    cfg = dict(vocab_size=503, context_length=256, d_model=256, num_layers=3, num_heads=4, d_ff=688, rope_theta=10000.0)
+    model = TransformerLM(**cfg, use_custom_triton=True).cuda().eval()
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 503, (n,), generator=g).tolist() for n in (7, 120, 40, 64, 19, 90)]
+    outs = {}
+    prev = native.set_pdl(False)
+    try:
+        for pdl in (False, True):
+            native.set_pdl(pdl)
+            eng = ServingEngine(model, page_size=16, max_batch=4, max_context=256, use_cuda_graphs=graphs)
+            outs[pdl] = eng.generate(prompts, 24)
+            torch.cuda.synchronize()
+            native.check_status()
+            assert eng.cache.allocator.free == eng.cache.num_pages
+    finally:
+        native.set_pdl(prev)
+    assert outs[True] == outs[False]
