@@ -191,6 +191,53 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfl
   }
 }
 
+// Rotary embedding of the Q and K thirds of qkv (in place, interleaved pairs, angle of positions[row]) and the append
+// of the rotated K row and the V row to their cache slot, in one pass over the row: what rope_kernel followed by
+// kv_append_kernel do, with one launch and one read of K less.  slot < 0: rotate only.
+__global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cos_sin,
+                                      const int* __restrict__ positions, __nv_bfloat16* __restrict__ k_cache,
+                                      __nv_bfloat16* __restrict__ v_cache, const long long* __restrict__ slots,
+                                      long long rows, int d, int dh, int ctx, long long num_slots,
+                                      uint32_t* __restrict__ status) {
+  pdl_sync();
+  const int gpr = 3 * d / 8;             // groups of 8 elements per row
+  const long long groups = rows * gpr;
+  const float* cosb = cos_sin;
+  const float* sinb = cos_sin + (size_t)ctx * (dh / 2);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < groups;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / gpr;
+    const int c = (int)(i - row * gpr) * 8;            // column within [0, 3d)
+    long long slot = slots[row];
+    if (slot >= num_slots) {                           // beyond the cache: report, do not write
+      if (c == 0 && status != nullptr) atomicCAS(status, 0u, ERR_BAD_ARG | (3u << 8));
+      slot = -1;
+    }
+    __nv_bfloat16* p = qkv + row * 3 * d + c;
+    uint4 raw = *reinterpret_cast<const uint4*>(p);
+    if (c < 2 * d) {
+      const int pos = positions[row];
+      const int e = c % dh;                            // element offset inside the head (multiple of 8)
+      const float4 cs = *reinterpret_cast<const float4*>(cosb + (size_t)pos * (dh / 2) + e / 2);
+      const float4 sn = *reinterpret_cast<const float4*>(sinb + (size_t)pos * (dh / 2) + e / 2);
+      const float cc[4] = {cs.x, cs.y, cs.z, cs.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+      const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 v = unpack_bf16x2(in[k]);
+        o[k] = pack_bf16x2(cc[k] * v.x - ss[k] * v.y, ss[k] * v.x + cc[k] * v.y);
+      }
+      raw = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4*>(p) = raw;
+    }
+    if (slot >= 0 && c >= d) {
+      __nv_bfloat16* dst = (c < 2 * d) ? k_cache + (size_t)slot * d + (c - d) : v_cache + (size_t)slot * d + (c - 2 * d);
+      *reinterpret_cast<uint4*>(dst) = raw;
+    }
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -236,5 +283,22 @@ extern "C" int b200_kv_append(const void* qkv, void* k_cache, void* v_cache, con
   if (rows <= 0) return 0;
   launch_dep(kv_append_kernel, (unsigned)((rows + 7) / 8), 256, 0, st, (const __nv_bfloat16*)qkv,
              (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slots, rows, d, num_slots, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Rotary embedding of Q and K in place plus the append of K and V to their cache slots, one launch.
+extern "C" int b200_rope_kv_append(void* qkv, const float* cos_sin, const int* positions, void* k_cache, void* v_cache,
+                                   const long long* slots, long long rows, int d, int dh, int ctx, long long num_slots,
+                                   uint32_t* status, cudaStream_t st) {
+  if (dh % 8 || d % dh || positions == nullptr || slots == nullptr ||
+      ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+        reinterpret_cast<uintptr_t>(cos_sin)) & 15))
+    return -10;
+  if (rows <= 0) return 0;
+  const long long groups = rows * (3 * d / 8);
+  long long blocks = (groups + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  launch_dep(rope_kv_append_kernel, (unsigned)blocks, 256, 0, st, (__nv_bfloat16*)qkv, cos_sin, positions,
+             (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slots, rows, d, dh, ctx, num_slots, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -20,6 +20,8 @@ def _lib():
         lib.b200_paged_decode.restype = I
         lib.b200_kv_append.argtypes = [P, P, P, P, L, I, L, P, P]
         lib.b200_kv_append.restype = I
+        lib.b200_rope_kv_append.argtypes = [P, P, P, P, P, P, L, I, I, I, L, P, P]
+        lib.b200_rope_kv_append.restype = I
         _declared = True
     return lib
 
@@ -38,6 +40,31 @@ def kv_append(k_cache, v_cache, qkv, slot_mapping):
     native._check(lib.b200_kv_append(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(),
                                      qkv.shape[0], d, num_slots, native.status_word(qkv.device).data_ptr(),
                                      native._stream()), "kv_append")
+
+
+def rope_kv_append(qkv, cos_sin, positions, k_cache, v_cache, slot_mapping, n_heads: int):
+    """Rotate the Q and K thirds of qkv (R, 3d) in place by the angle of ``positions`` and write the rotated K row and
+    the V row into cache slot ``slot_mapping`` (-1: rotate only).  One kernel on the GPU; the two separate ops elsewhere."""
+    if not qkv.is_cuda:
+        from . import rope_ as _rope
+        _rope(qkv, cos_sin, positions, n_heads, False, None)
+        return kv_append(k_cache, v_cache, qkv, slot_mapping)
+    lib = _lib()
+    d = qkv.shape[1] // 3
+    dh = d // n_heads
+    native._req(qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous(),
+                "bad rope_kv_append inputs")
+    native._req(slot_mapping.dtype == torch.int64 and slot_mapping.numel() == qkv.shape[0], "bad slot mapping")
+    native._req(positions.dtype == torch.int32 and positions.numel() == qkv.shape[0] and positions.is_contiguous(),
+                "positions must be int32 (R,)")
+    native._req(k_cache.shape == v_cache.shape and k_cache.shape[-1] == d, "cache shape does not match qkv")
+    native._req(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[0] == 2
+                and cos_sin.shape[2] == dh // 2 and dh % 8 == 0, "bad rope cache")
+    num_slots = k_cache.shape[0] * k_cache.shape[1]
+    native._check(lib.b200_rope_kv_append(qkv.data_ptr(), cos_sin.data_ptr(), positions.data_ptr(), k_cache.data_ptr(),
+                                          v_cache.data_ptr(), slot_mapping.data_ptr(), qkv.shape[0], d, dh,
+                                          cos_sin.shape[1], num_slots, native.status_word(qkv.device).data_ptr(),
+                                          native._stream()), "rope_kv_append")
 
 
 def choose_splits(rows: int, heads: int, max_context: int, sms: int = 148) -> int:

@@ -71,8 +71,8 @@ class ServingEngine:
         cfg = self.cfg
         h, _ = ops.rmsnorm_fwd(x, w.n1, cfg.eps)
         qkv = ops.gemm(h, w.wqkv, "nt")
-        ops.rope_(qkv, self.rope, positions, cfg.n_heads, False, None)
-        serving_ops.kv_append(self.cache.k[li], self.cache.v[li], qkv, slots)
+        # rotary embedding of Q and K in place and the append of K, V to the paged cache: one kernel on the GPU
+        serving_ops.rope_kv_append(qkv, self.rope, positions, self.cache.k[li], self.cache.v[li], slots, cfg.n_heads)
         o = attend(qkv, li)
         x = ops.gemm(o, w.wo, "nt", residual=x)
         h, _ = ops.rmsnorm_fwd(x, w.n2, cfg.eps)

@@ -121,3 +121,40 @@ def test_engine_with_programmatic_dependent_launch_gives_the_same_tokens(graphs)
     finally:
         native.set_pdl(prev)
     assert outs[True] == outs[False]
+
+
+@pytest.mark.parametrize("heads,dh", [(4, 128), (6, 64), (16, 128)])
+def test_rope_kv_append_equals_the_two_separate_kernels(heads, dh):
+    from llm_systems_from_scratch_b200.models.transformer import RotaryEmbedding
+    from llm_systems_from_scratch_b200.ops import native, serving_ops
+    d, page, n_pages, r = heads * dh, 16, 12, 37
+    g = torch.Generator(device="cuda").manual_seed(3)
+    cache = RotaryEmbedding._build_cache(300, dh, 10000.0).cuda().contiguous()
+    qkv = torch.randn(r, 3 * d, device="cuda", generator=g).bfloat16()
+    pos = torch.randint(0, 300, (r,), device="cuda", generator=g).int()
+    slots = torch.randperm(n_pages * page, device="cuda", generator=g)[:r].long()
+    slots[3] = -1
+    slots[11] = -1
+    a_qkv, b_qkv = qkv.clone(), qkv.clone()
+    ka, va = (torch.zeros(n_pages, page, d, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    kb, vb = torch.zeros_like(ka), torch.zeros_like(va)
+    native.rope_(a_qkv, cache, pos, heads)
+    serving_ops.kv_append(ka, va, a_qkv, slots)
+    serving_ops.rope_kv_append(b_qkv, cache, pos, kb, vb, slots, heads)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.equal(a_qkv, b_qkv) and torch.equal(ka, kb) and torch.equal(va, vb)
+    # a slot beyond the cache is reported and not written; the row is still rotated
+    bad = slots.clone()
+    bad[5] = n_pages * page + 9
+    c_qkv, kc, vc = qkv.clone(), torch.zeros_like(ka), torch.zeros_like(va)
+    serving_ops.rope_kv_append(c_qkv, cache, pos, kc, vc, bad, heads)
+    torch.cuda.synchronize()
+    with pytest.raises(native.KernelError):
+        native.check_status()
+    assert torch.equal(c_qkv, a_qkv)
+    keep = torch.ones(r, dtype=torch.bool, device="cuda")
+    keep[5] = False
+    keep &= slots >= 0
+    assert torch.equal(kc.view(-1, d)[slots[keep]], ka.view(-1, d)[slots[keep]])
+    assert float(kc.view(-1, d)[slots[5]].abs().sum()) == 0.0
