@@ -20,6 +20,9 @@ enum GemmEpilogue : int {
   // Flag or-ed into the epilogue code by the caller (CTA-pair kernel): output columns from N up to the next 16-byte
   // boundary lie inside the row pitch and may be overwritten with zeros.
   EPI_PAD_WRITABLE = 0x100,
+  // Flag or-ed into the epilogue code by the caller (single-CTA kernel): operand B is not written by the kernel
+  // before this one on the stream (inference weights), so its first tiles may be requested before that kernel ends.
+  EPI_B_STABLE = 0x200,
 };
 
 // Optional all-gather carried by a GEMM launch: while the MMA warps work, two copy warps per CTA pull
@@ -65,6 +68,9 @@ struct GemmParams {
   // Split-K (single-CTA kernel, small M): `splits` CTAs share an output tile, each contracts a slice of K and leaves
   // an fp32 partial tile in `ws`; the epilogue warp that arrives last at the counter of its 32 rows adds their partials in
   // split order (so the result does not depend on which CTA that is) and runs the epilogue.  splits <= 1 = off.
+  // B (the weights) does not depend on the kernel before this one: as a programmatic dependent the kernel requests
+  // its first B tiles before it waits for that kernel, so the weights' DRAM latency overlaps the predecessor's tail.
+  int b_early;
   int splits;
   float* ws;                  // splits * tiles partial tiles of BM x BN floats
   uint32_t* tile_counters;    // four per tile (one per 32-row quarter), zero between launches (the last warp resets its own)

@@ -60,6 +60,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     fence_barrier_init();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
+    if (!B_MN && p.b_early) {
+      // first work unit of this CTA: the B tiles of its first STAGES k-blocks are requested now; the producer below
+      // adds the A tiles to the same barriers after the wait for the previous kernel
+      const int sp = p.splits > 1 ? p.splits : 1;
+      const int nkb = (p.K + BK - 1) / BK;
+      const int unit = blockIdx.x;
+      if (unit < p.num_m_tiles * p.num_n_tiles * sp) {
+        const int tile = unit / sp, split = unit - tile * sp;
+        const int kb_lo = split * nkb / sp, kb_hi = (split + 1) * nkb / sp;
+        int m_blk, n_blk;
+        tile_coords(tile, p, m_blk, n_blk);
+        for (int i = 0; i < STAGES && kb_lo + i < kb_hi; ++i) {
+          mbar_expect_tx(&full_bar[i], S::A_BYTES + S::B_BYTES);
+          tma_load_2d(smem_b + i * S::B_BYTES, &tmB, &full_bar[i], (kb_lo + i) * BK, n_blk * BN);
+        }
+      }
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_holder, TMEM_COLS);
@@ -86,19 +103,22 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int early = (!B_MN && p.b_early) ? STAGES : 0;   // k-blocks whose B tile and byte count were posted in the prologue
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
         const int tile = unit / splits, split = unit - tile * splits;
         const int kb_lo = split * num_kb / splits, kb_hi = (split + 1) * num_kb / splits;
         int m_blk, n_blk;
         tile_coords(tile, p, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN;
+        if (unit != (int)blockIdx.x) early = 0;
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          const bool posted = kb - kb_lo < early;
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word)) {
             report(p, abort_word, ERR_WAIT_EMPTY);
             ok = false;
             break;
           }
-          mbar_expect_tx(&full_bar[stage], S::A_BYTES + S::B_BYTES);
+          if (!posted) mbar_expect_tx(&full_bar[stage], S::A_BYTES + S::B_BYTES);
           uint8_t* a_dst = smem_a + stage * S::A_BYTES;
           uint8_t* b_dst = smem_b + stage * S::B_BYTES;
           const int k0 = kb * BK;
@@ -111,7 +131,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[stage], n0 + j * 64, k0);
-          } else {
+          } else if (!posted) {
             tma_load_2d(b_dst, &tmB, &full_bar[stage], k0, n0);
           }
           if (++stage == STAGES) {
@@ -387,6 +407,8 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* R, 
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return -10;
+  const int b_early = (epi & EPI_B_STABLE) ? 1 : 0;
+  epi &= ~EPI_B_STABLE;
   if (epi == EPI_BF16_RES && R == nullptr) return -11;
   if (epi == EPI_SWIGLU_BWD &&
       (R == nullptr || (N & 7) || (ldr & 7) || (ldc & 7) || ((reinterpret_cast<uintptr_t>(R) | reinterpret_cast<uintptr_t>(C)) & 15)))
@@ -442,6 +464,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* R, 
   p.rope_cs = nullptr; p.rope_seq = p.rope_d = p.rope_dh = p.rope_ctx = 0;
   p.swiglu_f = 0; p.H = nullptr; p.ldh = 0;
   p.splits = splits > 1 ? splits : 1; p.ws = ws; p.tile_counters = tile_counters;
+  p.b_early = b_early;
 
 #define DISPATCH(BN_)                                                                    \
   if (a_mn && b_mn) return launch_gemm<BN_, true, true>(tmA, tmB, p, max_ctas, stream);   \
@@ -511,7 +534,8 @@ extern "C" int b200_gemm_bf16_splitk(const void* A, const void* B, void* C, cons
   if (splits > 1 && (ws == nullptr || tile_counters == nullptr || (reinterpret_cast<uintptr_t>(ws) & 15) ||
                      tiles * splits * BM * bn > ws_floats || tiles * 4 > n_counters))
     return -12;
-  if (epi != EPI_BF16 && epi != EPI_F32 && epi != EPI_BF16_RES && epi != EPI_F32_ACC) return -11;
+  const int base_epi = epi & ~EPI_B_STABLE;
+  if (base_epi != EPI_BF16 && base_epi != EPI_F32 && base_epi != EPI_BF16_RES && base_epi != EPI_F32_ACC) return -11;
   if (splits <= 1)
     return gemm_bf16_impl(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, 0, 0, epi, 0, 0, 1, nullptr, nullptr, status, stream);
   return gemm_bf16_impl(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, 0, 0, epi, bn, 0, splits, ws, tile_counters, status,

@@ -644,7 +644,7 @@ static int gemm_pair_impl(const void* A, const void* B, void* C, const void* R, 
   else { p.gather.dst = nullptr; p.gather.done = nullptr; p.gather.shard_vec = 0; p.gather.world = 0; p.gather.rank = 0; }
   if (reduce != nullptr) p.reduce = *reduce;
   else p.reduce.n = 0;
-  p.splits = 1; p.ws = nullptr; p.tile_counters = nullptr;
+  p.splits = 1; p.ws = nullptr; p.tile_counters = nullptr; p.b_early = 0;
   p.wait_counter = wait_counter; p.wait_value = wait_value; p.wait_limit_ns = g_counter_wait_limit_ns;
   p.rope_cs = rope_cs; p.rope_seq = rope_seq; p.rope_d = rope_d; p.rope_dh = rope_dh; p.rope_ctx = rope_ctx;
   p.swiglu_f = swiglu_f; p.H = H; p.ldh = ldh;

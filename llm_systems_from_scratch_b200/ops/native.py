@@ -189,6 +189,7 @@ def _rowmajor(t: torch.Tensor, name: str):
 # ----------------------------------------------------------------------------- GEMM
 EPI_BF16, EPI_F32, EPI_BF16_RES, EPI_F32_ACC, EPI_SWIGLU_BWD = 0, 1, 2, 3, 4
 EPI_PAD_WRITABLE = 0x100
+EPI_B_STABLE = 0x200
 
 
 # Problems at least this large (rows of the output) run on CTA pairs (cta_group::2, 256 x 256 tiles).
@@ -251,13 +252,16 @@ def _gemm_pair_tasks(lib, a, b, out, r, m, n, k, lda, ldb, ldc, ldr, a_mn, b_mn,
 
 
 def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, bn_hint=0, max_ctas=0,
-         pair=None, gather=None, pad_writable=False, reduce=None):
+         pair=None, gather=None, pad_writable=False, reduce=None, b_stable=False):
     """bf16 tensor-core GEMM (tcgen05).  layout 'nt' | 'nn' | 'tn' as in ``torch_impl.gemm``.
 
     ``pair`` forces (True) or forbids (False) the CTA-pair kernel; by default large problems use it.
     ``gather`` / ``reduce``: a pending all-gather / reduce-scatter (``parallel.comm.GatherTask`` /
     ``ReduceScatterTask``) that the CTA-pair kernel carries on its copy warps; a launch that cannot carry them
     performs them first as collectives of their own.
+    ``b_stable``: ``b`` is not written by the kernel launched before this one on the stream (inference weights); the
+    single-CTA kernel then requests its first weight tiles before it waits for that kernel (programmatic dependent
+    launch), so the weights' DRAM latency overlaps the predecessor's tail.
     ``pad_writable``: ``out`` is a column slice of a wider buffer and the columns from N up to the next 16-byte
     boundary (inside the row pitch) may be overwritten with zeros; this lets a row count that is not a multiple of
     16 bytes (a vocabulary of 50,257) use the TMA-store epilogue."""
@@ -329,6 +333,8 @@ def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=
                                      ldr, a_mn, b_mn, epi, _ptr(status_word(a.device)), _stream())
         _check(rc, "b200_gemm_bf16_pair")
         return out
+    if b_stable and layout == "nt":
+        epi |= EPI_B_STABLE
     if USE_SPLITK and layout == "nt" and m <= SPLITK_MAX_M and k >= SPLITK_MIN_K and bn_hint == 0 and max_ctas == 0:
         scratch = _splitk_scratch(a.device)
         if scratch is not None:

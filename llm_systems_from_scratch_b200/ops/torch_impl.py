@@ -20,10 +20,10 @@ def _f(x: torch.Tensor) -> torch.Tensor:
 
 # ----------------------------------------------------------------------------- GEMM
 def gemm(a, b, layout: str, out=None, out_dtype=None, residual=None, accumulate=False, gather=None,
-         pad_writable=False, reduce=None):
+         pad_writable=False, reduce=None, b_stable=False):
     """layout 'nt': a(M,K) b(N,K) -> a@b.T ; 'nn': a(M,K) b(K,N) ; 'tn': a(K,M) b(K,N) -> a.T@b.
     ``gather`` (a pending all-gather that the CUDA kernel would carry) is simply performed first;
-    ``pad_writable`` is a permission for the CUDA kernel and changes nothing here."""
+    ``pad_writable`` and ``b_stable`` are permissions for the CUDA kernel and change nothing here."""
     if gather is not None:
         gather.run()
     if reduce is not None:

@@ -70,19 +70,19 @@ class ServingEngine:
     def _block(self, x, w, li: int, positions, slots, attend):
         cfg = self.cfg
         h, _ = ops.rmsnorm_fwd(x, w.n1, cfg.eps)
-        qkv = ops.gemm(h, w.wqkv, "nt")
+        qkv = ops.gemm(h, w.wqkv, "nt", b_stable=True)
         # rotary embedding of Q and K in place and the append of K, V to the paged cache: one kernel on the GPU
         serving_ops.rope_kv_append(qkv, self.rope, positions, self.cache.k[li], self.cache.v[li], slots, cfg.n_heads)
         o = attend(qkv, li)
-        x = ops.gemm(o, w.wo, "nt", residual=x)
+        x = ops.gemm(o, w.wo, "nt", residual=x, b_stable=True)
         h, _ = ops.rmsnorm_fwd(x, w.n2, cfg.eps)
-        gu = ops.gemm(h, w.wgu, "nt")
-        return ops.gemm(ops.silu_mul_fwd(gu), w.wdown, "nt", residual=x)
+        gu = ops.gemm(h, w.wgu, "nt", b_stable=True)
+        return ops.gemm(ops.silu_mul_fwd(gu), w.wdown, "nt", residual=x, b_stable=True)
 
     def _logits(self, x):
         h, _ = ops.rmsnorm_fwd(x, self.head.norm, self.cfg.eps)
         buf = torch.empty((x.shape[0], self.cfg.vocab_padded), dtype=x.dtype, device=x.device)
-        ops.gemm(h, self.head.lm, "nt", out=buf[:, :self.cfg.vocab])
+        ops.gemm(h, self.head.lm, "nt", out=buf[:, :self.cfg.vocab], b_stable=True)
         return buf
 
     def _greedy(self, logits_buf):

@@ -300,3 +300,27 @@ def test_gemm_split_k_small_m(shape, monkeypatch):
     native.check_status()
     _, counters = native._splitk_scratch(a.device)
     assert int(counters.abs().sum().item()) == 0
+
+
+@pytest.mark.parametrize("shape,max_ctas", [((128, 2048, 2048), 0), ((64, 6144, 2048), 0), ((256, 2048, 5504), 0),
+                                            ((1000, 1336, 520), 5), ((130, 520, 136), 1), ((128, 50264, 2048), 0)])
+@pytest.mark.parametrize("pdl", [False, True])
+def test_gemm_early_weight_tiles_give_the_same_result(shape, max_ctas, pdl):
+    """``b_stable`` lets the kernel request its first weight tiles before it waits for the kernel ahead of it; the
+    result must be bitwise that of the ordinary order, also when a CTA walks several tiles and when K is split."""
+    from llm_systems_from_scratch_b200.ops import native
+    m, n, k = shape
+    a, b = _make("nt", m, n, k, "cuda")
+    res = torch.randn(m, n, device="cuda").bfloat16()
+    prev = native.set_pdl(pdl)
+    try:
+        want = native.gemm(a, b, "nt", residual=res, max_ctas=max_ctas, pair=False)
+        for _ in range(3):
+            a2 = a.clone()      # a fresh producer kernel right before the GEMM: the wait has something to wait for
+            got = native.gemm(a2, b, "nt", residual=res, max_ctas=max_ctas, pair=False, b_stable=True)
+            assert torch.equal(got, want)
+        torch.cuda.synchronize()
+        native.check_status()
+    finally:
+        native.set_pdl(prev)
+    _check(want, _ref(a, b, "nt") + res.float(), k)
