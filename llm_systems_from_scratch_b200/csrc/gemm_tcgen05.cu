@@ -362,8 +362,11 @@ static int g_num_sms = 0;
 static int num_sms() {
   if (g_num_sms == 0) {
     int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_num_sms <= 0) {
+      cudaGetLastError();
+      return 148;      // no device visible (planning helpers called on a CPU-only machine): a B200's count
+    }
   }
   return g_num_sms;
 }

@@ -1,4 +1,5 @@
 """CPU unit tests: functional ops, schedule, optimizer order, loader, tokenizer, checkpoints, watchdog."""
+import ctypes
 import json
 import math
 import os
@@ -231,3 +232,22 @@ def test_sample_topk_statement():
     assert freq[~keep].sum().item() == 0
     assert (freq - p).abs().max().item() < 0.015
     assert torch.equal(ops.sample_topk(logits, torch.tensor([0.3]), 1.0, 1), torch.tensor([4]))
+
+
+def test_split_k_plan_for_decode_shapes():
+    """The launcher's choice of tile width and K slices is host arithmetic: long contractions at decode sizes are
+    split, a problem with more tiles than SMs is not, and every plan fits the scratch the Python side allocates."""
+    from llm_systems_from_scratch_b200.ops import native
+    if native.load(required=False) is None:
+        pytest.skip("kernel library not built")
+    lib = native.load()
+    lib.b200_gemm_splitk_ws_floats.restype = ctypes.c_longlong
+    ws_floats, counters = lib.b200_gemm_splitk_ws_floats(), lib.b200_gemm_splitk_counters()
+    for m in (1, 64, 128, 256):
+        for n, k in ((6144, 2048), (2048, 2048), (11008, 2048), (2048, 5504), (50264, 2048), (1000, 320)):
+            bn, s = native.splitk_plan(m, n, k)
+            assert bn in (64, 128, 256) and 1 <= s <= 8
+            tiles = -(-m // 128) * -(-n // bn)
+            assert s == 1 or (tiles * s * 128 * bn <= ws_floats and tiles * 4 <= counters and s <= (k + 63) // 64)
+    assert native.splitk_plan(128, 2048, 5504)[1] > 1
+    assert native.splitk_plan(128, 50264, 2048)[1] == 1
