@@ -822,8 +822,14 @@ extern "C" int b200_set_pdl(int on) {
 }
 
 static int g_rmsnorm_fwd_rows = 1;
+// 0: the general-width kernel (a block per row); 1: one warp per row where the width allows it
 static int g_rmsnorm_bwd_rows = 1;
-extern "C" void b200_rmsnorm_set_bwd_rows(int on) { g_rmsnorm_bwd_rows = on; }
+extern "C" int b200_rmsnorm_set_bwd_rows(int variant) {
+  const int old = g_rmsnorm_bwd_rows;
+  g_rmsnorm_bwd_rows = variant;
+  return old;
+}
+
 // 0 = always the one-block-per-eight-rows kernel (kept for A/B timing and as the general-width path)
 extern "C" void b200_rmsnorm_set_fwd_rows(int on) { g_rmsnorm_fwd_rows = on; }
 

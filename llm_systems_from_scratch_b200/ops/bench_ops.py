@@ -177,15 +177,17 @@ def bench_elementwise():
         native.rmsnorm_fwd(x, w, 1e-5)
         lib.b200_rmsnorm_set_fwd_rows(1)
 
-    def bwd_per_block():       # the general-width backward (a block per row, block-wide reduction), for comparison
-        lib.b200_rmsnorm_set_bwd_rows(0)
-        native.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
-        lib.b200_rmsnorm_set_bwd_rows(1)
+    def bwd_variant(v):        # 0: a block per row, block-wide reduction; 1: a warp per row
+        def run():
+            old = lib.b200_rmsnorm_set_bwd_rows(v)
+            native.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
+            lib.b200_rmsnorm_set_bwd_rows(old)
+        return run
 
     cases = [("rmsnorm_fwd", lambda: native.rmsnorm_fwd(x, w, 1e-5), 2 * x.numel() * 2),
              ("rmsnorm_fwd_general_width_kernel", fwd_per_block, 2 * x.numel() * 2),
              ("rmsnorm_bwd", lambda: native.rmsnorm_bwd(dy, x, w, rstd, dres=dres), 4 * x.numel() * 2),
-             ("rmsnorm_bwd_general_width_kernel", bwd_per_block, 4 * x.numel() * 2),
+             ("rmsnorm_bwd_general_width_kernel", bwd_variant(0), 4 * x.numel() * 2),
              ("rmsnorm_bwd_no_residual", lambda: native.rmsnorm_bwd(dy, x, w, rstd), 3 * x.numel() * 2),
              ("silu_mul_fwd", lambda: native.silu_mul_fwd(gu), 3 * rows * f * 2),
              ("silu_mul_bwd", lambda: native.silu_mul_bwd(dh, gu), 5 * rows * f * 2),

@@ -201,3 +201,40 @@ def test_sample_topk_kernel():
     assert (freq - p).abs().max().item() < 0.015
     assert freq[~keep].sum().item() == 0
     native.check_status()
+
+
+@pytest.mark.parametrize("rows,d", [(4800, 2048), (5003, 768), (1184, 256), (6001, 1280), (16384, 2048)])
+def test_rmsnorm_bwd_variants_agree(rows, d):
+    """Both backward kernels (a block per row with a block-wide reduction; a warp per row) against the fp32 statement,
+    with and without the residual gradient; each is bitwise reproducible from run to run."""
+    from llm_systems_from_scratch_b200.ops import native, torch_impl
+    lib = native.load(required=True)
+    g = torch.Generator(device="cuda").manual_seed(rows + d)
+    x = torch.randn(rows, d, device="cuda", generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(d, device="cuda", generator=g)).bfloat16()
+    dy = torch.randn(rows, d, device="cuda", generator=g).bfloat16()
+    dres = torch.randn(rows, d, device="cuda", generator=g).bfloat16()
+    _, rstd = native.rmsnorm_fwd(x, w, 1e-5)
+    dxr, dwr = torch_impl.rmsnorm_bwd(dy.float(), x.float(), w.float(), rstd)
+    got = {}
+    old = lib.b200_rmsnorm_set_bwd_rows(0)
+    try:
+        for v in (0, 1):
+            lib.b200_rmsnorm_set_bwd_rows(v)
+            dx, dw = native.rmsnorm_bwd(dy, x, w, rstd)
+            dx2, dw2 = native.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
+            torch.cuda.synchronize()
+            native.check_status()
+            _close(dx, dxr, 3e-2)
+            _close(dx2, dxr + dres.float(), 4e-2)
+            _close(dw, dwr, 1e-2 * math.sqrt(rows), 1e-2)
+            assert torch.equal(dw, dw2)
+            got[v] = (dx, dx2, dw)
+    finally:
+        lib.b200_rmsnorm_set_bwd_rows(old)
+    lib.b200_rmsnorm_set_bwd_rows(1)
+    try:
+        again = native.rmsnorm_bwd(dy, x, w, rstd)
+    finally:
+        lib.b200_rmsnorm_set_bwd_rows(old)
+    assert torch.equal(again[0], got[1][0]) and torch.equal(again[1], got[1][2])
