@@ -275,6 +275,8 @@ def run_native(args, cfg, rank, local_rank, world):
         bad = torch.zeros(1, dtype=torch.int32, device=dev)
         why = ""
         try:
+            if os.environ.get("B200_BENCH_INJECT_FIRST_STEP_ERROR") == str(rank):
+                raise RuntimeError("injected on the host to exercise the fallback")     # test hook, off by default
             step_resident()
             torch.cuda.synchronize()
             native.check_status()
