@@ -536,15 +536,18 @@ def main():
                 print(json.dumps({"impl": "reference", "unavailable": why}))
             return 0
     else:
+        gave_up = None
         try:
             res = run_native(args, cfg, rank, local_rank, world)
         except PeerPathGaveUp as e:
+            gave_up = str(e)        # leave the handler first: the traceback keeps the first model alive
+        if gave_up is not None:
             import gc
             gc.collect()
             torch.cuda.empty_cache()
             args.comm, args.fused_optimizer = "torch", "off"
             res = run_native(args, cfg, rank, local_rank, world)
-            res["comm"] += f" (the peer-memory collectives gave up in the first step and the run was repeated: {e})"
+            res["comm"] += f" (the peer-memory collectives gave up in the first step and the run was repeated: {gave_up})"
     # second half of the headline metric, short form: a serving replica per GPU after the training model is gone
     n_serv = 160 if args.serving_requests is None else args.serving_requests
     serving = None
