@@ -40,9 +40,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,        // (R, 3d) packe
                     float* __restrict__ part_o,                  // (R, H, splits, DH)
                     float* __restrict__ part_ml,                 // (R, H, splits, 2)
                     int q_ld, int heads, int page_size, int max_pages, int splits, float scale_log2, int num_pages,
-                    uint32_t* __restrict__ status,
-                    __nv_bfloat16* __restrict__ out,             // (R, H * DH); used when merge_counters is given
-                    uint32_t* __restrict__ merge_counters) {     // one per request, zero between launches; null = off
+                    uint32_t* __restrict__ status) {
   pdl_sync();
   constexpr int LPT = DH / 8;            // lanes per head (16-byte loads)
   const int r = blockIdx.x, split = blockIdx.y;
@@ -145,54 +143,12 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,        // (R, 3d) packe
       m = mc;
     }
   }
-  if (merge_counters != nullptr && splits == 1) {      // nothing to merge: normalise and store
-    if (active) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      *reinterpret_cast<uint4*>(out + ((size_t)r * heads + h) * DH + li * 8) =
-          make_uint4(pack_bf16x2(acc[0] * inv, acc[1] * inv), pack_bf16x2(acc[2] * inv, acc[3] * inv),
-                     pack_bf16x2(acc[4] * inv, acc[5] * inv), pack_bf16x2(acc[6] * inv, acc[7] * inv));
-    }
-    return;
-  }
   if (active) {
     const size_t idx = ((size_t)r * heads + h) * splits + split;
     float4* o = reinterpret_cast<float4*>(part_o + idx * DH + li * 8);
     o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     if (li == 0) { part_ml[idx * 2] = m; part_ml[idx * 2 + 1] = l; }
-  }
-  if (merge_counters == nullptr) return;      // the merge is a kernel of its own
-  // The CTA that finishes last among the `splits` CTAs of this request merges their partial results (in split order,
-  // so the result does not depend on which one that is): no second launch, no waiting.
-  __shared__ uint32_t is_last;
-  __threadfence();                 // this thread's partials are visible before the CTA is counted
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const uint32_t seen = atomicAdd(&merge_counters[r], 1u);
-    is_last = (seen == (uint32_t)splits - 1) ? 1u : 0u;
-    if (is_last) merge_counters[r] = 0;      // clean for the next launch
-  }
-  __syncthreads();
-  if (is_last && active) {
-    __threadfence();
-    const size_t base = ((size_t)r * heads + h) * splits;
-    float gm = -INFINITY;
-    for (int s = 0; s < splits; ++s) gm = fmaxf(gm, __ldcg(part_ml + (base + s) * 2));
-    float gl = 0.f, go[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < splits; ++s) {
-      const float ms = __ldcg(part_ml + (base + s) * 2);
-      const float wgt = (ms == -INFINITY) ? 0.f : exp2f(ms - gm);
-      gl += __ldcg(part_ml + (base + s) * 2 + 1) * wgt;
-      const float4 a = __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * DH + li * 8));
-      const float4 b = __ldcg(reinterpret_cast<const float4*>(part_o + (base + s) * DH + li * 8) + 1);
-      go[0] += a.x * wgt; go[1] += a.y * wgt; go[2] += a.z * wgt; go[3] += a.w * wgt;
-      go[4] += b.x * wgt; go[5] += b.y * wgt; go[6] += b.z * wgt; go[7] += b.w * wgt;
-    }
-    const float inv = gl > 0.f ? 1.f / gl : 0.f;
-    *reinterpret_cast<uint4*>(out + ((size_t)r * heads + h) * DH + li * 8) =
-        make_uint4(pack_bf16x2(go[0] * inv, go[1] * inv), pack_bf16x2(go[2] * inv, go[3] * inv),
-                   pack_bf16x2(go[4] * inv, go[5] * inv), pack_bf16x2(go[6] * inv, go[7] * inv));
   }
 }
 
@@ -288,12 +244,10 @@ using namespace b200;
 
 // q: rows of stride q_ld elements whose first d entries are the queries (pass the packed qkv buffer with
 // q_ld = 3d).  part_o: R*H*splits*dh floats, part_ml: R*H*splits*2 floats (caller-provided scratch).
-// merge_counters: `rows` zero-initialised words (zero again on return) - the last CTA of a request then merges the
-// splits itself; null = a second kernel does the merge.
 extern "C" int b200_paged_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
                                  const int* context_lens, void* out, float* part_o, float* part_ml, int rows, int q_ld,
                                  int heads, int dh, int page_size, int max_pages, int splits, float scale,
-                                 int num_pages, uint32_t* status, uint32_t* merge_counters, cudaStream_t st) {
+                                 int num_pages, uint32_t* status, cudaStream_t st) {
   if (dh != 64 && dh != 128) return -10;
   if (page_size <= 0 || max_pages <= 0 || num_pages <= 0) return -11;
   if (q_ld % 8 || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
@@ -308,17 +262,15 @@ extern "C" int b200_paged_decode(const void* q, const void* k_cache, const void*
   if (dh == 128) {
     launch_dep(paged_decode_kernel<128>, grid, threads, 0, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
                (const __nv_bfloat16*)v_cache, block_tables, context_lens, part_o, part_ml, q_ld, heads, page_size,
-               max_pages, splits, sl2, num_pages, status, (__nv_bfloat16*)out, merge_counters);
-    if (merge_counters == nullptr)
-      launch_dep(paged_decode_merge_kernel<128>, rows * heads, 128, 0, st, part_o, part_ml, (__nv_bfloat16*)out, heads,
-                 splits);
+               max_pages, splits, sl2, num_pages, status);
+    launch_dep(paged_decode_merge_kernel<128>, rows * heads, 128, 0, st, part_o, part_ml, (__nv_bfloat16*)out, heads,
+               splits);
   } else {
     launch_dep(paged_decode_kernel<64>, grid, threads, 0, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
                (const __nv_bfloat16*)v_cache, block_tables, context_lens, part_o, part_ml, q_ld, heads, page_size,
-               max_pages, splits, sl2, num_pages, status, (__nv_bfloat16*)out, merge_counters);
-    if (merge_counters == nullptr)
-      launch_dep(paged_decode_merge_kernel<64>, rows * heads, 64, 0, st, part_o, part_ml, (__nv_bfloat16*)out, heads,
-                 splits);
+               max_pages, splits, sl2, num_pages, status);
+    launch_dep(paged_decode_merge_kernel<64>, rows * heads, 64, 0, st, part_o, part_ml, (__nv_bfloat16*)out, heads,
+               splits);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -16,7 +16,7 @@ def _lib():
     lib = native.load()
     if not _declared:
         P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-        lib.b200_paged_decode.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, P]
+        lib.b200_paged_decode.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
         lib.b200_paged_decode.restype = I
         lib.b200_kv_append.argtypes = [P, P, P, P, L, I, L, P, P]
         lib.b200_kv_append.restype = I
@@ -104,32 +104,9 @@ def paged_decode_attention(qkv, k_cache, v_cache, block_tables, context_lens, n_
         scratch = torch.empty(r * n_heads * splits * (dh + 2), dtype=torch.float32, device=qkv.device)
     part_o = scratch[:r * n_heads * splits * dh]
     part_ml = scratch[r * n_heads * splits * dh:]
-    counters = _merge_counters(qkv.device, r) if FOLD_MERGE else None
     native._check(lib.b200_paged_decode(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                                         context_lens.data_ptr(), out.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(),
                                         r, qkv.stride(0), n_heads, dh, page, max_pages, splits, 1.0 / math.sqrt(dh),
-                                        k_cache.shape[0], native.status_word(qkv.device).data_ptr(),
-                                        0 if counters is None else counters.data_ptr(), native._stream()),
+                                        k_cache.shape[0], native.status_word(qkv.device).data_ptr(), native._stream()),
                   "paged_decode")
     return out
-
-
-# The last CTA of a request merges its context splits inside the attention kernel (one launch less per layer).  It
-# needs one zero-initialised counter per request, kept per device for the life of the process (captured graphs hold
-# the address) and created outside CUDA-graph capture only; launches that use it must be ordered (one stream at a
-# time, as everywhere in this package).  Without counters the merge is a second kernel.
-FOLD_MERGE = True
-_MERGE_MAX_ROWS = 4096
-_MERGE_COUNTERS: dict = {}
-
-
-def _merge_counters(device, rows: int):
-    if rows > _MERGE_MAX_ROWS:
-        return None
-    key = torch.device(device).index
-    got = _MERGE_COUNTERS.get(key)
-    if got is None:
-        if torch.cuda.is_current_stream_capturing():
-            return None
-        got = _MERGE_COUNTERS[key] = torch.zeros(_MERGE_MAX_ROWS, dtype=torch.int32, device=device)
-    return got
