@@ -168,7 +168,8 @@ class ServingEngine:
               "slots": torch.full((bucket,), -1, dtype=torch.int64, device=dev),
               "tables": torch.zeros((bucket, self.max_pages_per_req), dtype=torch.int32, device=dev),
               "ctx": torch.ones(bucket, dtype=torch.int32, device=dev)}
-        st["splits"] = serving_ops.choose_splits(bucket, self.cfg.n_heads, self.max_context)
+        st["splits"] = serving_ops.choose_splits(bucket, self.cfg.n_heads, self.max_context,
+                                                  head_dim=self.cfg.d_model // self.cfg.n_heads)
         run = lambda: self._decode_body(st["tokens"], st["positions"], st["slots"], st["tables"], st["ctx"], st["splits"])
         if self.use_graphs:
             side = torch.cuda.Stream(device=dev)
@@ -263,7 +264,8 @@ class ServingEngine:
         if g is not None:
             return g
         d = self._d
-        splits = serving_ops.choose_splits(bucket, self.cfg.n_heads, self.max_context)
+        splits = serving_ops.choose_splits(bucket, self.cfg.n_heads, self.max_context,
+                                           head_dim=self.cfg.d_model // self.cfg.n_heads)
 
         def run():
             out = self._decode_body(d["tokens"][:bucket], d["positions"][:bucket], d["slots"][:bucket],
