@@ -372,6 +372,32 @@ def paged_decode_small():
                       "splits": splits, "ok": True}))
 
 
+def paged_splits_sweep(argv=()):
+    """Paged decode attention of one layer of the 1.3B model (16 heads of 128) at context 1200 for every number of
+    context splits from 1 to 32, per batch size: achieved GB/s of K and V, and the number `choose_splits` picks."""
+    from . import serving_ops
+    heads, dh, page = 16, 128, 16
+    d = heads * dh
+    ctx = int(argv[0]) if argv else 1200
+    for batch in (32, 64, 128, 256):
+        pages_per = -(-(ctx + 16) // page)
+        n_pages = batch * pages_per + 8
+        kc = torch.randn(n_pages, page, d, device="cuda").bfloat16()
+        vc = torch.randn(n_pages, page, d, device="cuda").bfloat16()
+        qkv = torch.randn(batch, 3 * d, device="cuda").bfloat16()
+        tables = torch.zeros(batch, 128, dtype=torch.int32, device="cuda")
+        tables[:, :pages_per] = torch.randperm(n_pages, device="cuda")[:batch * pages_per].int().view(batch, pages_per)
+        lens = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
+        res = {}
+        for s in range(1, 33):
+            t = timeit(lambda: serving_ops.paged_decode_attention(qkv, kc, vc, tables, lens, heads, s), iters=10, warm=2)
+            res[s] = round(batch * ctx * 2 * d * 2 / t / 1e6)
+        native.check_status()
+        print(json.dumps({"op": "paged-splits", "batch": batch, "context": ctx,
+                          "chosen": serving_ops.choose_splits(batch, heads, 2048, head_dim=dh), "gbs_by_splits": res}),
+              flush=True)
+
+
 def decode_launches(argv=()):
     """One decode step of the 1.3B serving model at a given batch and context with every kernel launched on its own
     (no CUDA graph), bracketed by cudaProfilerStart / Stop: under ``ncu --profile-from-start off`` the capture is
@@ -414,6 +440,8 @@ def main(argv=None):
         return bench_decode(argv[1:])
     if mode == "decode-launches":
         return decode_launches(argv[1:])
+    if mode == "paged-splits":
+        return paged_splits_sweep(argv[1:])
     if mode == "paged-decode-small":
         return paged_decode_small()
     {"gemm": bench_gemm, "gemm-decode": bench_gemm_decode, "attention": bench_attention, "elementwise": bench_elementwise, "gemm-small": gemm_small, "gemm-pair-small": gemm_pair_small, "attention-trace": attention_trace,
