@@ -270,13 +270,13 @@ def run_native(args, cfg, rank, local_rank, world):
     if world > 1 and args.comm == "auto":
         # One untimed step, then all ranks agree on whether any of them saw a device wait run out (a peer that never
         # signalled) or an exception: either every rank goes on, or every rank raises and main() repeats the run
-        # on the library collectives and says so in its line.
+        # on the library collectives and says so in its line.  This covers failures that every rank lives through
+        # (a status word set by a bounded wait, an error all ranks raise); a rank that leaves the step early also
+        # leaves the step's host collectives unmatched, and that ends in the process group's timeout as before.
         import torch.distributed as dist
         bad = torch.zeros(1, dtype=torch.int32, device=dev)
         why = ""
         try:
-            if os.environ.get("B200_BENCH_INJECT_FIRST_STEP_ERROR") == str(rank):
-                raise RuntimeError("injected on the host to exercise the fallback")     # test hook, off by default
             step_resident()
             torch.cuda.synchronize()
             native.check_status()
