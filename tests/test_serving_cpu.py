@@ -157,3 +157,20 @@ def test_realtime_trace_and_requests_that_can_never_fit():
     small = ServingEngine(model, num_pages=3, page_size=4, max_batch=2, max_context=64)
     with pytest.raises(ValueError):
         small.sched.add(Request(0, [1] * 10, 8, 0.0))          # 18 positions = 5 pages > 3
+
+
+def test_context_splits_fill_the_waves_of_the_attention_launch():
+    """``choose_splits`` is host arithmetic: for the 2048-wide model two CTAs fit on an SM (296 per wave on 148 SMs);
+    the chosen split count never leaves less than 256 tokens per split at full context, and no other admissible count
+    fills its last wave better."""
+    from llm_systems_from_scratch_b200.ops.serving_ops import choose_splits
+    resident = 148 * 2
+    fill = lambda ctas: ctas / (-(-ctas // resident) * resident)
+    for rows in (1, 3, 16, 32, 48, 64, 96, 128, 160, 192, 224, 256, 300):
+        s = choose_splits(rows, 16, 2048)
+        assert 1 <= s <= 8
+        assert all(fill(rows * s) >= fill(rows * other) - 1e-9 for other in range(1, 9))
+    assert choose_splits(128, 16, 2048) == 8          # 1024 CTAs = 3.46 waves of 296: 0.865 full, like 2, 4 and 6; ties go up
+    assert choose_splits(48, 16, 2048) == 6           # 288 of 296
+    assert choose_splits(5, 4, 256, head_dim=128) == 1    # a short context is not split
+    assert choose_splits(64, 12, 1024, head_dim=64) <= 4
