@@ -78,3 +78,21 @@ def test_profile_flag_writes_chrome_trace(tmp_path, monkeypatch):
     train.train_worker(0, 1, [], cfg, False, False, False, True)
     trace = tmp_path / "ckpt" / "trace_rank0.json"
     assert trace.exists() and trace.stat().st_size > 1000
+
+
+def test_bench_reference_arm_without_a_gpu_says_so_and_exits_zero():
+    """``bench.py --impl reference`` must never fail the caller: without a CUDA device it prints its one-line
+    ``unavailable`` record and exits 0; the default arm needs a GPU and says so by raising."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    ref = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference"], capture_output=True,
+                         text=True, env=env, timeout=300)
+    assert ref.returncode == 0, ref.stderr[-400:]
+    rec = json.loads(ref.stdout.strip().splitlines()[-1])
+    assert rec["impl"] == "reference" and "unavailable" in rec
+    own = subprocess.run([sys.executable, os.path.join(root, "bench.py")], capture_output=True, text=True, env=env,
+                         timeout=300)
+    assert own.returncode != 0 and "no CUDA device" in own.stderr
