@@ -173,6 +173,8 @@ def test_flag_protocol_model_checker():
     from llm_systems_from_scratch_b200.parallel.protocol_check import ProtocolViolation, check_reduce_scatter_protocol
     for seed in range(200):
         check_reduce_scatter_protocol(world=2 + seed % 4, units=1 + seed % 3, steps=3, seed=seed)
+    for seed in range(30):      # the world size of the flagship configuration
+        check_reduce_scatter_protocol(world=8, units=1 + seed % 3, steps=3, seed=1000 + seed)
     found = 0
     for seed in range(200):
         try:
@@ -193,6 +195,9 @@ def test_allreduce_and_weight_gather_protocols():
         check_allreduce_protocol(world=2 + seed % 4, buckets=1 + seed % 3, steps=3, seed=seed)
         check_weight_gather_protocol(world=2 + seed % 4, units=1 + seed % 4, steps=3, seed=seed,
                                      fused_update=bool(seed % 2))
+    for seed in range(20):
+        check_allreduce_protocol(world=8, buckets=1 + seed % 3, steps=3, seed=2000 + seed)
+        check_weight_gather_protocol(world=8, units=1 + seed % 4, steps=3, seed=2000 + seed, fused_update=bool(seed % 2))
     found_ar = found_w = 0
     for seed in range(100):
         try:
