@@ -36,6 +36,7 @@ class Heartbeat:
         self._thread: threading.Thread | None = None
         self._count = 0
         self._paused = False
+        self._seen: set[int] = set()      # peers whose heartbeat key has been read at least once
         self.beat()
 
     def beat(self):
@@ -75,8 +76,17 @@ class Heartbeat:
         for r in range(self.world_size):
             if r == self.rank:
                 continue
+            key = f"hb/{r}"
             try:
-                raw = self.store.get(f"hb/{r}").decode()
+                # A peer seen before whose key is gone (dropped from the store) is reported at once: `get` on a torch
+                # store would wait for the key up to the store's own timeout, `check` answers immediately.  A peer
+                # not seen yet is still starting up; for it the wait inside `get` is the start-up rendezvous.
+                probe = getattr(self.store, "check", None)
+                if r in self._seen and probe is not None and not probe([key]):
+                    dead.append(r)
+                    continue
+                raw = self.store.get(key).decode()
+                self._seen.add(r)
             except Exception:
                 dead.append(r)
                 continue

@@ -5,6 +5,8 @@ import os
 import socket
 import time
 
+import pytest
+
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -74,3 +76,29 @@ def test_heartbeat_done_rank_is_not_a_failure(tmp_path):
     now[0] += 100.0
     a.check()
     assert a.silent_ranks() == []
+
+
+def test_heartbeat_late_rank_and_dropped_key_on_a_real_store():
+    """Two more failures made on the host, against a real TCPStore: a rank whose heartbeat stalls is reported while it
+    is silent and no longer once it beats again (a late rank is not a dead one); a rank whose key has been dropped
+    from the store is reported at once - the check must not sit in the store's own wait for a missing key."""
+    from llm_systems_from_scratch_b200.utils.watchdog import Heartbeat, RankFailure
+    store = dist.TCPStore("127.0.0.1", _free_port(), 1, True)
+    now = [1000.0]
+    a = Heartbeat(store, 0, 3, interval=10, timeout=2.0, clock=lambda: now[0])
+    b = Heartbeat(store, 1, 3, interval=10, timeout=2.0, clock=lambda: now[0])
+    c = Heartbeat(store, 2, 3, interval=10, timeout=2.0, clock=lambda: now[0])
+    a.check()
+    now[0] += 5.0           # b and c stall (nobody beats); a beats
+    a.beat()
+    with pytest.raises(RankFailure) as err:
+        a.check()
+    assert sorted(err.value.dead) == [1, 2]
+    b.beat()                # b was only late
+    c.beat()
+    a.check()
+    store.delete_key("hb/2")
+    t0 = time.time()
+    with pytest.raises(RankFailure) as err:
+        a.check()
+    assert err.value.dead == [2] and time.time() - t0 < 5.0
