@@ -184,9 +184,14 @@ def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None 
     # optional torch.profiler trace of a few steps (B200_PROFILE_STEPS=N, set by --profile N): Chrome trace per rank
     profile_steps = int(os.environ.get("B200_PROFILE_STEPS", "0"))
     profiler = None
+    inject = os.environ.get("B200_INJECT_FAIL_STEP")      # host-made failure for the restart tests: "<step>[:<rank>]"
     for step in range(start_step, max_steps):
         if heartbeat is not None:
             heartbeat.check()          # between steps: nothing of this rank is in flight
+        if inject and resume is None:
+            at, _, who = inject.partition(":")
+            if step == int(at) and rank == int(who or 0):
+                raise RuntimeError(f"rank {rank}: failure injected on the host before step {step}")
         if watchdog.expired:
             raise RuntimeError(f"step {step - 1} exceeded training.step_timeout_s; restart from the last checkpoint")
         watchdog.arm()
@@ -294,6 +299,9 @@ def main():
     ap.add_argument("--profile", type=int, default=0, metavar="N",
                     help="torch.profiler Chrome trace of N steps (after 3 warm-up steps) into the checkpoint directory")
     ap.add_argument("--nvtx", action="store_true", help="NVTX ranges per block, phase and collective")
+    ap.add_argument("--max-restarts", type=int, default=0, metavar="N",
+                    help="after a failed run (a worker that died, a rank failure, a kernel status error) start again "
+                         "from the newest periodic checkpoint, at most N times")
     args = ap.parse_args()
     if args.profile:
         os.environ["B200_PROFILE_STEPS"] = str(args.profile)   # inherited by spawned ranks
@@ -305,12 +313,44 @@ def main():
         raise ValueError("--parallel fsdp and --compile are not compatible: FSDP always runs the fused engine")
     if args.eager and ("fsdp" in args.parallel or args.custom_triton):
         raise ValueError("--eager excludes --custom-triton and --parallel fsdp (FSDP always runs the fused engine)")
-    common = (args.config, args.amp, args.compile, args.flash_attn, args.custom_triton, args.resume, None, args.eager)
     if args.parallel:
         mp.set_start_method("spawn", force=True)
-        mp.spawn(train_worker, args=(args.world_size, args.parallel, *common), nprocs=args.world_size, join=True)
-    else:
-        train_worker(0, 1, [], *common)
+    resume, restarts = args.resume, 0
+    while True:
+        common = (args.config, args.amp, args.compile, args.flash_attn, args.custom_triton, resume, None, args.eager)
+        try:
+            if args.parallel:
+                mp.spawn(train_worker, args=(args.world_size, args.parallel, *common), nprocs=args.world_size,
+                         join=True)
+            else:
+                train_worker(0, 1, [], *common)
+            return
+        except KeyboardInterrupt:
+            raise
+        except Exception as e:      # noqa: BLE001 - a worker died (mp.spawn re-raises it), a rank failure, a kernel error
+            if restarts >= args.max_restarts:
+                raise
+            restarts += 1
+            newest = latest_checkpoint(load_config(args.config)["training"]["checkpoint_dir"])
+            resume = newest or resume
+            print(f"[launcher] run failed ({type(e).__name__}: {str(e).strip().splitlines()[-1][:160] if str(e).strip() else ''}); "
+                  f"restart {restarts}/{args.max_restarts} from {resume or 'the beginning'}", flush=True)
+
+
+def latest_checkpoint(checkpoint_dir: str) -> str | None:
+    """The newest periodic checkpoint of a run: ``sharded_<step>`` directories (FSDP, any world size can load them) or
+    ``ckpt_<step>.pt`` files; None if there is none yet."""
+    best, best_step = None, -1
+    if not os.path.isdir(checkpoint_dir):
+        return None
+    for name in os.listdir(checkpoint_dir):
+        stem = name[:-3] if name.endswith(".pt") else name
+        kind, _, num = stem.rpartition("_")
+        if kind in ("sharded", "ckpt") and num.isdigit() and int(num) > best_step:
+            if kind == "sharded" and not os.path.isdir(os.path.join(checkpoint_dir, name)):
+                continue
+            best, best_step = os.path.join(checkpoint_dir, name), int(num)
+    return best
 
 
 if __name__ == "__main__":
