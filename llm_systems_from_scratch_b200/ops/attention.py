@@ -3,6 +3,10 @@
 qkv is (batch*seq, 3*H*dh) row-major (Q | K | V, heads inside each third); o is (batch*seq, H*dh).
 Head sizes 64 and 128 run on the tensor-core kernels; other multiples of 8 up to 128 are zero-padded
 to the next supported size around the call (the scale keeps the true head size).
+
+Replaces the reference's attention call (llm-core/llm_core/model.py:381-385: ``scaled_dot_product_attention`` with
+``is_causal=True`` on (B, H, S, dh) views, or the explicit softmax(QK^T / sqrt(dh)) V of model.py:34-52 without
+``--flash-attn``) and the library backward autograd derives for it.
 """
 from __future__ import annotations
 

@@ -1,4 +1,7 @@
-"""Decode-time ops: paged-KV attention and KV-cache append (CUDA kernels, PyTorch statement on CPU)."""
+"""Decode-time ops: paged-KV attention and KV-cache append (CUDA kernels, PyTorch statement on CPU).
+
+The reference decodes by running the whole context through the model again for every token
+(llm-core/llm_core/model.py:187-236, no KV cache); these ops are what a cached decode step needs instead."""
 from __future__ import annotations
 
 import ctypes

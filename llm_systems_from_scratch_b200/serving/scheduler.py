@@ -6,6 +6,9 @@ cache can hold the request's whole lifetime (prompt + maximum output, reserved u
 running request is never pre-empted), and (2) hands all running requests to one decode step.
 Finished requests return their pages immediately, so a request that arrives mid-flight joins the
 batch at the next iteration instead of waiting for the batch to drain.
+
+The reference has no serving loop: its ``generate`` (llm-core/llm_core/model.py:187-236) handles one prompt at a
+time and ``generate.py`` is a REPL around it.
 """
 from __future__ import annotations
 
