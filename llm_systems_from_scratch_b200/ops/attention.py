@@ -5,7 +5,7 @@ Head sizes 64 and 128 run on the tensor-core kernels; other multiples of 8 up to
 to the next supported size around the call (the scale keeps the true head size).
 
 Replaces the reference's attention call (llm-core/llm_core/model.py:381-385: ``scaled_dot_product_attention`` with
-``is_causal=True`` on (B, H, S, dh) views, or the explicit softmax(QK^T / sqrt(dh)) V of model.py:34-52 without
+``is_causal=True`` on (B, H, S, dh) views, or the explicit softmax(QK^T / sqrt(dh)) V of model.py:308-325 without
 ``--flash-attn``) and the library backward autograd derives for it.
 """
 from __future__ import annotations

@@ -6,8 +6,8 @@ faulting), allocates outputs with PyTorch's caching allocator, and launches on t
 current CUDA stream.  On a machine with a GPU a missing library is an error, never a
 silent fallback.
 
-The kernels stand where the reference has its Triton kernels (llm-systems/llm_systems/kernels/triton_rms_norm.py:30-149,
-triton_swiglu.py:36-133, triton_cross_entropy.py:22-131, triton_adamw.py:134-191) and the library calls behind
+The kernels stand where the reference has its Triton kernels (llm-systems/llm_systems/kernels/triton_rms_norm.py:30-153,
+triton_swiglu.py:27-91, triton_cross_entropy.py:22-145, triton_adamw.py:134-191) and the library calls behind
 ``Linear`` and attention (llm-core/llm_core/model.py:31-32, 381-385).
 """
 from __future__ import annotations

@@ -13,7 +13,7 @@ What these replace in the reference: ``dist.all_gather`` of the unit shards
 (llm-systems/llm_systems/parallelism/fsdp_zero3.py:131-134), ``dist.reduce_scatter`` + divide + clone followed by the
 Triton AdamW (fsdp_zero3.py:172-231, llm-systems/llm_systems/kernels/triton_adamw.py:134-191), the flatten / divide /
 ``dist.all_reduce`` / unflatten of a DDP bucket (llm-systems/llm_systems/parallelism/ddp.py:20-24) and the parameter
-broadcast at construction (ddp.py:46-48).
+broadcast at construction (ddp.py:57-58).
 """
 from __future__ import annotations
 
