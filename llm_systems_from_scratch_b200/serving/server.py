@@ -1,0 +1,195 @@
+"""Online serving: the continuous-batching engine on a thread of its own, fed by a thread-safe queue, and an HTTP
+front end for it.
+
+``EngineServer`` owns the engine loop.  Callers (any thread, any asyncio loop) ``submit`` token ids and get a
+``concurrent.futures.Future`` that resolves with a ``Completion`` (the generated ids, time to first token, total
+latency).  The loop is the one ``ServingEngine.run`` uses for a recorded trace - admit, prefill, one decode step,
+collect - except that arrivals come from the queue as they happen: a request that arrives while others are decoding
+joins the batch at the next iteration.  The engine itself is only ever touched by the loop thread.
+
+``build_app`` wraps a server in a small FastAPI application (``POST /generate``, ``GET /health``, ``GET /stats``);
+``serve.py --http PORT`` runs it under uvicorn.  The reference has no serving loop (its ``generate`` handles one
+prompt at a time, llm-core/llm_core/model.py:187-236, behind the REPL of generate.py).
+"""
+from __future__ import annotations
+
+import itertools
+import queue
+import threading
+import time
+from concurrent.futures import Future
+from dataclasses import dataclass
+
+from .scheduler import Request
+
+try:        # the HTTP front end is optional; the engine server itself needs none of this
+    from pydantic import BaseModel
+
+    class GenerateRequest(BaseModel):
+        prompt: str | None = None
+        prompt_ids: list[int] | None = None
+        max_new_tokens: int | None = None
+        eos_token_id: int | None = None
+except ImportError:      # pragma: no cover
+    GenerateRequest = None
+
+
+@dataclass
+class Completion:
+    request_id: int
+    output_ids: list[int]
+    ttft_s: float | None        # arrival -> first token on the host
+    latency_s: float | None     # arrival -> last token on the host
+
+
+class EngineServer:
+    def __init__(self, engine, idle_wait_s: float = 0.002):
+        self.engine = engine
+        self.idle_wait_s = idle_wait_s
+        self._inbox: queue.Queue = queue.Queue()
+        self._ids = itertools.count()
+        self._live: dict[int, tuple[Request, Future]] = {}
+        self._stop = threading.Event()
+        self._error: BaseException | None = None
+        self._thread: threading.Thread | None = None
+        self.completed = 0
+
+    # ------------------------------------------------------------------ client side (any thread)
+    def submit(self, prompt_ids: list[int], max_new_tokens: int, eos_token_id: int | None = None) -> Future:
+        """Queue one request; the future resolves with a ``Completion`` or raises what the engine raised for it
+        (a prompt longer than the context, a request that can never fit in the KV cache)."""
+        if self._error is not None:
+            raise RuntimeError("the engine loop has stopped") from self._error
+        if not prompt_ids or max_new_tokens < 1:
+            raise ValueError("a request needs at least one prompt token and one token to generate")
+        fut: Future = Future()
+        self._inbox.put((list(map(int, prompt_ids)), int(max_new_tokens), eos_token_id, fut))
+        return fut
+
+    def generate(self, prompt_ids: list[int], max_new_tokens: int, eos_token_id: int | None = None,
+                 timeout: float | None = None) -> Completion:
+        return self.submit(prompt_ids, max_new_tokens, eos_token_id).result(timeout)
+
+    def stats(self) -> dict:
+        eng = self.engine
+        return {"running": len(eng.sched.running), "waiting": len(eng.sched.waiting) + self._inbox.qsize(),
+                "completed": self.completed, "kv_pages": eng.cache.num_pages, "kv_occupancy": eng.cache.occupancy(),
+                "prefill_tokens": eng.stats["prefill_tokens"], "decode_steps": eng.stats["decode_steps"],
+                "alive": self._thread is not None and self._thread.is_alive() and self._error is None}
+
+    # ------------------------------------------------------------------ loop thread
+    def start(self, warmup: bool = True):
+        if self._thread is None:
+            eng = self.engine
+            eng._realtime, eng._virtual = True, float("inf")
+            eng._t0 = time.perf_counter()
+            if warmup:
+                eng.warmup()             # decode graphs are captured before the first request, not during it
+            elif not hasattr(eng, "_row_req"):
+                eng._rows_init()
+            self._thread = threading.Thread(target=self._loop, daemon=True, name="engine-loop")
+            self._thread.start()
+        return self
+
+    def stop(self, timeout: float = 10.0):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout)
+        for _, fut in list(self._live.values()):
+            if not fut.done():
+                fut.set_exception(RuntimeError("server stopped before the request finished"))
+        self._live.clear()
+
+    def _take(self, block_s: float):
+        """Move queued submissions into the scheduler; blocks up to ``block_s`` when there is nothing else to do."""
+        eng = self.engine
+        try:
+            item = self._inbox.get(timeout=block_s) if block_s > 0 else self._inbox.get_nowait()
+        except queue.Empty:
+            return
+        while True:
+            prompt, max_new, eos, fut = item
+            req = Request(next(self._ids), prompt, max_new, arrival=eng._clock(), eos_token_id=eos)
+            try:
+                eng.sched.add(req)           # validates against the context length and the cache capacity
+                self._live[req.rid] = (req, fut)
+            except Exception as e:           # noqa: BLE001 - the caller gets the scheduler's verdict
+                fut.set_exception(e)
+            try:
+                item = self._inbox.get_nowait()
+            except queue.Empty:
+                return
+
+    def _loop(self):
+        eng = self.engine
+        try:
+            if eng.cuda:                     # the current device is per thread and starts at 0 in a new one
+                import torch
+                torch.cuda.set_device(eng.device)
+            while not self._stop.is_set():
+                busy = bool(eng.sched.running or eng.sched.waiting or eng._pending)
+                self._take(0.0 if busy else self.idle_wait_s)
+                if not (eng.sched.running or eng.sched.waiting or eng._pending):
+                    continue
+                eng.step(eng._clock())
+                for rid in [rid for rid, (r, _) in self._live.items() if r.t_done is not None]:
+                    r, fut = self._live.pop(rid)
+                    self.completed += 1
+                    fut.set_result(Completion(rid, list(r.output),
+                                              None if r.t_first is None else r.t_first - r.arrival,
+                                              r.t_done - r.arrival))
+        except BaseException as e:           # noqa: BLE001 - surfaces in every pending and future request
+            self._error = e
+            for _, fut in list(self._live.values()):
+                if not fut.done():
+                    fut.set_exception(e)
+            self._live.clear()
+
+
+def build_app(server: EngineServer, tokenizer=None, default_max_new_tokens: int = 128):
+    """FastAPI application around a started ``EngineServer``.
+
+    ``POST /generate`` takes ``{"prompt_ids": [...]}`` or, with a tokenizer, ``{"prompt": "text"}``, plus optional
+    ``max_new_tokens`` and ``eos_token_id``; it answers with the generated ids (and text), the time to first token
+    and the latency in milliseconds.  Requests are served concurrently by the one engine loop."""
+    import asyncio
+
+    from fastapi import FastAPI, HTTPException
+
+    app = FastAPI(title="B200 LLM serving")
+
+    @app.get("/health")
+    def health():
+        s = server.stats()
+        if not s["alive"]:
+            raise HTTPException(status_code=503, detail="engine loop is not running")
+        return {"status": "ok"}
+
+    @app.get("/stats")
+    def stats():
+        return server.stats()
+
+    @app.post("/generate")
+    async def generate(body: GenerateRequest):
+        if body.prompt_ids is not None:
+            ids = body.prompt_ids
+        elif body.prompt is not None and tokenizer is not None:
+            ids = tokenizer.encode(body.prompt)
+        else:
+            raise HTTPException(status_code=422, detail="give prompt_ids, or prompt when the server has a tokenizer")
+        try:
+            fut = server.submit(ids, body.max_new_tokens or default_max_new_tokens, body.eos_token_id)
+            done = await asyncio.wrap_future(fut)
+        except (ValueError, RuntimeError) as e:
+            raise HTTPException(status_code=400, detail=str(e))
+        out = {"request_id": done.request_id, "output_ids": done.output_ids,
+               "ttft_ms": None if done.ttft_s is None else round(done.ttft_s * 1e3, 3),
+               "latency_ms": None if done.latency_s is None else round(done.latency_s * 1e3, 3)}
+        if tokenizer is not None:
+            try:
+                out["text"] = tokenizer.decode(done.output_ids)
+            except (KeyError, IndexError):      # the model's vocabulary is larger than the tokenizer's
+                out["text"] = None
+        return out
+
+    return app

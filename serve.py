@@ -3,6 +3,7 @@
 
     python serve.py --config configures/serve_1p3b.yaml [--num-requests N] [--rate R] [--offline]
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 serve.py ...   (one replica per GPU)
+    python serve.py --config configures/serve_1p3b.yaml --checkpoint ckpt_final.pt --http 8000   (online: POST /generate)
 
 Weights are random-init unless ``--checkpoint`` points at a checkpoint written by train.py.  Each replica
 serves its own trace (seed + rank); rank 0 prints one JSON line with the aggregate decode tokens/s and
@@ -50,6 +51,22 @@ def naive_loop(model, requests, device, limit_s: float):
             "ttft_p50_s": ttft[len(ttft) // 2] if ttft else float("nan"), "truncated_after_s": limit_s}
 
 
+def serve_http(engine, args):
+    """Run the engine loop on its own thread and an HTTP front end (uvicorn) in this one until interrupted."""
+    import uvicorn
+    from llm_systems_from_scratch_b200.serving.server import EngineServer, build_app
+    tokenizer = None
+    if args.vocab and args.merges:
+        from llm_systems_from_scratch_b200.tokenizer.bpe import Tokenizer
+        tokenizer = Tokenizer.from_files(args.vocab, args.merges, special_tokens=["<|endoftext|>"])
+    server = EngineServer(engine).start()
+    try:
+        uvicorn.run(build_app(server, tokenizer), host=args.host, port=args.http, log_level="info")
+    finally:
+        server.stop()
+    return 0
+
+
 def main(argv=None):
     from llm_systems_from_scratch_b200.models.transformer import TransformerLM
     from llm_systems_from_scratch_b200.serving import ServingEngine, poisson_trace
@@ -63,6 +80,11 @@ def main(argv=None):
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--time-limit", type=float, default=120.0, help="seconds after which the reference loop stops")
+    ap.add_argument("--http", type=int, default=None, metavar="PORT",
+                    help="serve POST /generate, GET /health and GET /stats on this port instead of replaying a trace")
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--vocab", default=None, help="tokenizer vocabulary (with --merges: text prompts over HTTP)")
+    ap.add_argument("--merges", default=None)
     args = ap.parse_args(argv)
     cfg = validate(load_config(args.config), require_dataset=False)
     m, s = cfg["model"], cfg["serving"]
@@ -93,6 +115,8 @@ def main(argv=None):
         model.eval()
         eng = ServingEngine(model, page_size=s["page_size"], max_batch=s["max_batch"], max_context=s["max_context"],
                             use_cuda_graphs=not args.no_graphs)
+        if args.http is not None:
+            return serve_http(eng, args)
         eng.warmup()
         res = eng.run(trace, realtime=not args.offline)
     if world > 1:

@@ -174,3 +174,85 @@ def test_context_splits_fill_the_waves_of_the_attention_launch():
     assert choose_splits(48, 16, 2048) == 6           # 288 of 296
     assert choose_splits(5, 4, 256, head_dim=128) == 1    # a short context is not split
     assert choose_splits(64, 12, 1024, head_dim=64) <= 4
+
+
+def test_online_server_serves_concurrent_requests_with_the_tokens_of_the_greedy_loop():
+    """``EngineServer``: requests submitted from several threads while others are decoding get exactly the tokens of
+    the per-request greedy recompute loop; a request that can never fit is refused to its caller only; every page is
+    back in the pool afterwards."""
+    import threading
+    from llm_systems_from_scratch_b200.serving.server import EngineServer
+    torch.manual_seed(0)
+    model = TransformerLM(**CFG).eval()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 101, (n,), generator=g).tolist() for n in (5, 17, 9, 30, 3, 12, 21)]
+    want = [_greedy_reference(model, p, 7) for p in prompts]
+    eng = ServingEngine(model, page_size=4, max_batch=3, max_context=64)
+    server = EngineServer(eng).start()
+    try:
+        got = [None] * len(prompts)
+
+        def client(i):
+            got[i] = server.generate(prompts[i], 7, timeout=120)
+
+        threads = [threading.Thread(target=client, args=(i,)) for i in range(len(prompts))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(180)
+        assert [c.output_ids for c in got] == want
+        assert all(c.ttft_s is not None and 0 <= c.ttft_s <= c.latency_s for c in got)
+        with pytest.raises(Exception):
+            server.generate(list(range(60)), 30, timeout=30)         # 90 tokens do not fit a context of 64
+        assert server.generate(prompts[0], 7, timeout=60).output_ids == want[0]     # the loop is still serving
+        s = server.stats()
+        assert s["alive"] and s["completed"] == len(prompts) + 1 and s["running"] == 0
+    finally:
+        server.stop()
+    assert eng.cache.allocator.free == eng.cache.num_pages
+
+
+def test_http_front_end():
+    from fastapi.testclient import TestClient
+    from llm_systems_from_scratch_b200.serving.server import EngineServer, build_app
+    torch.manual_seed(0)
+    model = TransformerLM(**CFG).eval()
+    eng = ServingEngine(model, page_size=4, max_batch=4, max_context=64)
+    server = EngineServer(eng).start()
+    try:
+        client = TestClient(build_app(server, default_max_new_tokens=5))
+        assert client.get("/health").json() == {"status": "ok"}
+        prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+        r = client.post("/generate", json={"prompt_ids": prompt, "max_new_tokens": 6})
+        assert r.status_code == 200
+        body = r.json()
+        assert body["output_ids"] == _greedy_reference(model, prompt, 6) and body["latency_ms"] >= body["ttft_ms"] >= 0
+        assert len(client.post("/generate", json={"prompt_ids": prompt}).json()["output_ids"]) == 5
+        assert client.post("/generate", json={"prompt": "text without a tokenizer"}).status_code == 422
+        assert client.post("/generate", json={"prompt_ids": list(range(60)), "max_new_tokens": 30}).status_code == 400
+        stats = client.get("/stats").json()
+        assert stats["completed"] == 2 and stats["kv_pages"] == eng.cache.num_pages
+    finally:
+        server.stop()
+
+
+def test_http_front_end_with_text_prompts():
+    """With a tokenizer the app takes text and answers with text; the ids are those of the greedy loop on the encoded
+    prompt."""
+    import os
+    from fastapi.testclient import TestClient
+    from llm_systems_from_scratch_b200.serving.server import EngineServer, build_app
+    from llm_systems_from_scratch_b200.tokenizer.bpe import Tokenizer
+    data = os.path.join(os.path.dirname(__file__), "data")
+    tok = Tokenizer.from_files(os.path.join(data, "vocab.json"), os.path.join(data, "merges.json"),
+                               special_tokens=["<|endoftext|>"])
+    torch.manual_seed(0)
+    model = TransformerLM(**dict(CFG, vocab_size=len(tok.id_to_bytes))).eval()
+    server = EngineServer(ServingEngine(model, page_size=4, max_batch=4, max_context=64)).start()
+    try:
+        client = TestClient(build_app(server, tok, default_max_new_tokens=6))
+        body = client.post("/generate", json={"prompt": "the cat"}).json()
+        assert body["output_ids"] == _greedy_reference(model, tok.encode("the cat"), 6)
+        assert body["text"] == tok.decode(body["output_ids"])
+    finally:
+        server.stop()
