@@ -30,6 +30,7 @@ try:        # the HTTP front end is optional; the engine server itself needs non
         prompt_ids: list[int] | None = None
         max_new_tokens: int | None = None
         eos_token_id: int | None = None
+        stream: bool = False
 except ImportError:      # pragma: no cover
     GenerateRequest = None
 
@@ -49,21 +50,27 @@ class EngineServer:
         self._inbox: queue.Queue = queue.Queue()
         self._ids = itertools.count()
         self._live: dict[int, tuple[Request, Future]] = {}
+        self._streams: dict[int, list] = {}        # request id -> [callback, tokens already delivered]
+        self.ttft_s: list[float] = []              # of completed requests (bounded: the newest 4096)
+        self.latency_s: list[float] = []
+        self.output_tokens = 0
         self._stop = threading.Event()
         self._error: BaseException | None = None
         self._thread: threading.Thread | None = None
         self.completed = 0
 
     # ------------------------------------------------------------------ client side (any thread)
-    def submit(self, prompt_ids: list[int], max_new_tokens: int, eos_token_id: int | None = None) -> Future:
+    def submit(self, prompt_ids: list[int], max_new_tokens: int, eos_token_id: int | None = None,
+               on_tokens=None) -> Future:
         """Queue one request; the future resolves with a ``Completion`` or raises what the engine raised for it
-        (a prompt longer than the context, a request that can never fit in the KV cache)."""
+        (a prompt longer than the context, a request that can never fit in the KV cache).  ``on_tokens(ids)`` is called
+        on the loop thread with every batch of new token ids as they reach the host (streaming); keep it short."""
         if self._error is not None:
             raise RuntimeError("the engine loop has stopped") from self._error
         if not prompt_ids or max_new_tokens < 1:
             raise ValueError("a request needs at least one prompt token and one token to generate")
         fut: Future = Future()
-        self._inbox.put((list(map(int, prompt_ids)), int(max_new_tokens), eos_token_id, fut))
+        self._inbox.put((list(map(int, prompt_ids)), int(max_new_tokens), eos_token_id, fut, on_tokens))
         return fut
 
     def generate(self, prompt_ids: list[int], max_new_tokens: int, eos_token_id: int | None = None,
@@ -73,7 +80,8 @@ class EngineServer:
     def stats(self) -> dict:
         eng = self.engine
         return {"running": len(eng.sched.running), "waiting": len(eng.sched.waiting) + self._inbox.qsize(),
-                "completed": self.completed, "kv_pages": eng.cache.num_pages, "kv_occupancy": eng.cache.occupancy(),
+                "completed": self.completed, "output_tokens": self.output_tokens,
+                "kv_pages": eng.cache.num_pages, "kv_occupancy": eng.cache.occupancy(),
                 "prefill_tokens": eng.stats["prefill_tokens"], "decode_steps": eng.stats["decode_steps"],
                 "alive": self._thread is not None and self._thread.is_alive() and self._error is None}
 
@@ -108,11 +116,13 @@ class EngineServer:
         except queue.Empty:
             return
         while True:
-            prompt, max_new, eos, fut = item
+            prompt, max_new, eos, fut, on_tokens = item
             req = Request(next(self._ids), prompt, max_new, arrival=eng._clock(), eos_token_id=eos)
             try:
                 eng.sched.add(req)           # validates against the context length and the cache capacity
                 self._live[req.rid] = (req, fut)
+                if on_tokens is not None:
+                    self._streams[req.rid] = [on_tokens, 0]
             except Exception as e:           # noqa: BLE001 - the caller gets the scheduler's verdict
                 fut.set_exception(e)
             try:
@@ -132,29 +142,48 @@ class EngineServer:
                 if not (eng.sched.running or eng.sched.waiting or eng._pending):
                     continue
                 eng.step(eng._clock())
+                for rid, st in list(self._streams.items()):          # streaming: hand over what is new
+                    r = self._live[rid][0]
+                    if len(r.output) > st[1]:
+                        new, st[1] = r.output[st[1]:], len(r.output)
+                        try:
+                            st[0](list(new))
+                        except Exception:        # noqa: BLE001 - a client's callback must not stop the loop
+                            self._streams.pop(rid, None)
                 for rid in [rid for rid, (r, _) in self._live.items() if r.t_done is not None]:
                     r, fut = self._live.pop(rid)
+                    self._streams.pop(rid, None)
                     self.completed += 1
-                    fut.set_result(Completion(rid, list(r.output),
-                                              None if r.t_first is None else r.t_first - r.arrival,
-                                              r.t_done - r.arrival))
+                    self.output_tokens += len(r.output)
+                    ttft = None if r.t_first is None else r.t_first - r.arrival
+                    if ttft is not None:
+                        self.ttft_s.append(ttft)
+                    self.latency_s.append(r.t_done - r.arrival)
+                    del self.ttft_s[:-4096], self.latency_s[:-4096]
+                    fut.set_result(Completion(rid, list(r.output), ttft, r.t_done - r.arrival))
         except BaseException as e:           # noqa: BLE001 - surfaces in every pending and future request
             self._error = e
             for _, fut in list(self._live.values()):
                 if not fut.done():
                     fut.set_exception(e)
             self._live.clear()
+            self._streams.clear()
 
 
 def build_app(server: EngineServer, tokenizer=None, default_max_new_tokens: int = 128):
     """FastAPI application around a started ``EngineServer``.
 
     ``POST /generate`` takes ``{"prompt_ids": [...]}`` or, with a tokenizer, ``{"prompt": "text"}``, plus optional
-    ``max_new_tokens`` and ``eos_token_id``; it answers with the generated ids (and text), the time to first token
-    and the latency in milliseconds.  Requests are served concurrently by the one engine loop."""
+    ``max_new_tokens``, ``eos_token_id`` and ``stream``; it answers with the generated ids (and text), the time to
+    first token and the latency in milliseconds - or, with ``"stream": true``, with server-sent events, one
+    ``data: {"output_ids": [...]}`` per batch of new tokens and a final event that carries the timings.
+    ``GET /metrics`` is a Prometheus text exposition of the server's counters.  Requests are served concurrently by
+    the one engine loop."""
     import asyncio
+    import json
 
     from fastapi import FastAPI, HTTPException
+    from fastapi.responses import PlainTextResponse, StreamingResponse
 
     app = FastAPI(title="B200 LLM serving")
 
@@ -169,6 +198,25 @@ def build_app(server: EngineServer, tokenizer=None, default_max_new_tokens: int 
     def stats():
         return server.stats()
 
+    @app.get("/metrics")
+    def metrics():
+        s = server.stats()
+        pct = lambda xs, q: sorted(xs)[min(len(xs) - 1, int(q * len(xs)))] if xs else float("nan")
+        lines = ["# TYPE llm_requests_completed_total counter", f"llm_requests_completed_total {s['completed']}",
+                 "# TYPE llm_output_tokens_total counter", f"llm_output_tokens_total {s['output_tokens']}",
+                 "# TYPE llm_prefill_tokens_total counter", f"llm_prefill_tokens_total {s['prefill_tokens']}",
+                 "# TYPE llm_decode_steps_total counter", f"llm_decode_steps_total {s['decode_steps']}",
+                 "# TYPE llm_requests_running gauge", f"llm_requests_running {s['running']}",
+                 "# TYPE llm_requests_waiting gauge", f"llm_requests_waiting {s['waiting']}",
+                 "# TYPE llm_kv_cache_occupancy gauge", f"llm_kv_cache_occupancy {s['kv_occupancy']}",
+                 "# TYPE llm_ttft_seconds summary",
+                 f'llm_ttft_seconds{{quantile="0.5"}} {pct(server.ttft_s, 0.5)}',
+                 f'llm_ttft_seconds{{quantile="0.99"}} {pct(server.ttft_s, 0.99)}',
+                 "# TYPE llm_request_latency_seconds summary",
+                 f'llm_request_latency_seconds{{quantile="0.5"}} {pct(server.latency_s, 0.5)}',
+                 f'llm_request_latency_seconds{{quantile="0.99"}} {pct(server.latency_s, 0.99)}']
+        return PlainTextResponse("\n".join(lines) + "\n")
+
     @app.post("/generate")
     async def generate(body: GenerateRequest):
         if body.prompt_ids is not None:
@@ -177,8 +225,39 @@ def build_app(server: EngineServer, tokenizer=None, default_max_new_tokens: int 
             ids = tokenizer.encode(body.prompt)
         else:
             raise HTTPException(status_code=422, detail="give prompt_ids, or prompt when the server has a tokenizer")
+        n_new = body.max_new_tokens or default_max_new_tokens
+        if body.stream:
+            loop = asyncio.get_running_loop()
+            chunks: asyncio.Queue = asyncio.Queue()
+            try:
+                fut = server.submit(ids, n_new, body.eos_token_id,
+                                    on_tokens=lambda new: loop.call_soon_threadsafe(chunks.put_nowait, new))
+            except (ValueError, RuntimeError) as e:
+                raise HTTPException(status_code=400, detail=str(e))
+            done_fut = asyncio.wrap_future(fut)
+
+            async def events():
+                while True:
+                    getter = asyncio.ensure_future(chunks.get())
+                    finished, _ = await asyncio.wait({getter, done_fut}, return_when=asyncio.FIRST_COMPLETED)
+                    if getter in finished:
+                        yield "data: " + json.dumps({"output_ids": getter.result()}) + "\n\n"
+                        continue
+                    getter.cancel()
+                    while not chunks.empty():      # what arrived together with the completion
+                        yield "data: " + json.dumps({"output_ids": chunks.get_nowait()}) + "\n\n"
+                    if done_fut.exception() is not None:
+                        yield "data: " + json.dumps({"error": str(done_fut.exception())}) + "\n\n"
+                    else:
+                        d = done_fut.result()
+                        yield "data: " + json.dumps({"done": True, "request_id": d.request_id,
+                                                     "ttft_ms": None if d.ttft_s is None else round(d.ttft_s * 1e3, 3),
+                                                     "latency_ms": round(d.latency_s * 1e3, 3)}) + "\n\n"
+                    return
+
+            return StreamingResponse(events(), media_type="text/event-stream")
         try:
-            fut = server.submit(ids, body.max_new_tokens or default_max_new_tokens, body.eos_token_id)
+            fut = server.submit(ids, n_new, body.eos_token_id)
             done = await asyncio.wrap_future(fut)
         except (ValueError, RuntimeError) as e:
             raise HTTPException(status_code=400, detail=str(e))

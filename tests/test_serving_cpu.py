@@ -236,6 +236,38 @@ def test_http_front_end():
         server.stop()
 
 
+def test_http_streaming_and_metrics():
+    """``"stream": true`` answers with server-sent events whose token batches concatenate to the greedy loop's output
+    and end with the timings; ``/metrics`` exposes the counters in the Prometheus text format."""
+    import json
+    from fastapi.testclient import TestClient
+    from llm_systems_from_scratch_b200.serving.server import EngineServer, build_app
+    torch.manual_seed(0)
+    model = TransformerLM(**CFG).eval()
+    eng = ServingEngine(model, page_size=4, max_batch=4, max_context=64)
+    server = EngineServer(eng).start()
+    try:
+        client = TestClient(build_app(server))
+        prompt = [7, 3, 9, 1, 12, 40]
+        want = _greedy_reference(model, prompt, 9)
+        with client.stream("POST", "/generate", json={"prompt_ids": prompt, "max_new_tokens": 9, "stream": True}) as r:
+            assert r.status_code == 200 and r.headers["content-type"].startswith("text/event-stream")
+            events = [json.loads(line[len("data: "):]) for line in r.iter_lines() if line.startswith("data: ")]
+        assert events[-1].get("done") is True and events[-1]["latency_ms"] >= events[-1]["ttft_ms"] >= 0
+        assert sum((e["output_ids"] for e in events[:-1]), []) == want
+        assert len(events) > 2                                  # tokens arrived in more than one batch
+        # callbacks straight on the server object
+        seen = []
+        done = server.submit(prompt, 5, on_tokens=seen.extend).result(60)
+        assert seen == done.output_ids == want[:5]
+        text = client.get("/metrics").text
+        assert "llm_requests_completed_total 2" in text and f"llm_output_tokens_total {9 + 5}" in text
+        assert 'llm_ttft_seconds{quantile="0.5"}' in text and "llm_kv_cache_occupancy 0" in text
+    finally:
+        server.stop()
+    assert eng.cache.allocator.free == eng.cache.num_pages
+
+
 def test_http_front_end_with_text_prompts():
     """With a tokenizer the app takes text and answers with text; the ids are those of the greedy loop on the encoded
     prompt."""
