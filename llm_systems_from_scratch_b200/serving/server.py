@@ -43,10 +43,15 @@ class Completion:
     latency_s: float | None     # arrival -> last token on the host
 
 
+class QueueFull(RuntimeError):
+    """More requests are waiting than the server was told to hold; the caller should retry later."""
+
+
 class EngineServer:
-    def __init__(self, engine, idle_wait_s: float = 0.002):
+    def __init__(self, engine, idle_wait_s: float = 0.002, max_waiting: int | None = None):
         self.engine = engine
         self.idle_wait_s = idle_wait_s
+        self.max_waiting = max_waiting       # back-pressure: submissions beyond this many waiting requests are refused
         self._inbox: queue.Queue = queue.Queue()
         self._ids = itertools.count()
         self._live: dict[int, tuple[Request, Future]] = {}
@@ -69,6 +74,8 @@ class EngineServer:
             raise RuntimeError("the engine loop has stopped") from self._error
         if not prompt_ids or max_new_tokens < 1:
             raise ValueError("a request needs at least one prompt token and one token to generate")
+        if self.max_waiting is not None and len(self.engine.sched.waiting) + self._inbox.qsize() >= self.max_waiting:
+            raise QueueFull(f"{self.max_waiting} requests are already waiting")
         fut: Future = Future()
         self._inbox.put((list(map(int, prompt_ids)), int(max_new_tokens), eos_token_id, fut, on_tokens))
         return fut
@@ -232,6 +239,8 @@ def build_app(server: EngineServer, tokenizer=None, default_max_new_tokens: int 
             try:
                 fut = server.submit(ids, n_new, body.eos_token_id,
                                     on_tokens=lambda new: loop.call_soon_threadsafe(chunks.put_nowait, new))
+            except QueueFull as e:
+                raise HTTPException(status_code=503, detail=str(e), headers={"Retry-After": "1"})
             except (ValueError, RuntimeError) as e:
                 raise HTTPException(status_code=400, detail=str(e))
             done_fut = asyncio.wrap_future(fut)
@@ -259,6 +268,8 @@ def build_app(server: EngineServer, tokenizer=None, default_max_new_tokens: int 
         try:
             fut = server.submit(ids, n_new, body.eos_token_id)
             done = await asyncio.wrap_future(fut)
+        except QueueFull as e:
+            raise HTTPException(status_code=503, detail=str(e), headers={"Retry-After": "1"})
         except (ValueError, RuntimeError) as e:
             raise HTTPException(status_code=400, detail=str(e))
         out = {"request_id": done.request_id, "output_ids": done.output_ids,

@@ -236,6 +236,24 @@ def test_http_front_end():
         server.stop()
 
 
+def test_server_back_pressure():
+    """With ``max_waiting`` the server refuses what it cannot hold instead of queueing without bound (HTTP 503)."""
+    from fastapi.testclient import TestClient
+    from llm_systems_from_scratch_b200.serving.server import EngineServer, QueueFull, build_app
+    torch.manual_seed(0)
+    model = TransformerLM(**CFG).eval()
+    server = EngineServer(ServingEngine(model, page_size=4, max_batch=2, max_context=64), max_waiting=0).start()
+    try:
+        with pytest.raises(QueueFull):
+            server.submit([1, 2, 3], 4)
+        r = TestClient(build_app(server)).post("/generate", json={"prompt_ids": [1, 2, 3], "max_new_tokens": 4})
+        assert r.status_code == 503 and r.headers["retry-after"] == "1"
+        server.max_waiting = 8
+        assert len(server.generate([1, 2, 3], 4, timeout=60).output_ids) == 4
+    finally:
+        server.stop()
+
+
 def test_http_streaming_and_metrics():
     """``"stream": true`` answers with server-sent events whose token batches concatenate to the greedy loop's output
     and end with the timings; ``/metrics`` exposes the counters in the Prometheus text format."""
