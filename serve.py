@@ -59,7 +59,7 @@ def serve_http(engine, args):
     if args.vocab and args.merges:
         from llm_systems_from_scratch_b200.tokenizer.bpe import Tokenizer
         tokenizer = Tokenizer.from_files(args.vocab, args.merges, special_tokens=["<|endoftext|>"])
-    server = EngineServer(engine).start()
+    server = EngineServer(engine, max_waiting=args.max_waiting).start()
     try:
         uvicorn.run(build_app(server, tokenizer), host=args.host, port=args.http, log_level="info")
     finally:
@@ -83,6 +83,8 @@ def main(argv=None):
     ap.add_argument("--http", type=int, default=None, metavar="PORT",
                     help="serve POST /generate, GET /health and GET /stats on this port instead of replaying a trace")
     ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--max-waiting", type=int, default=None,
+                    help="with --http: refuse (503) submissions while this many requests are already waiting")
     ap.add_argument("--vocab", default=None, help="tokenizer vocabulary (with --merges: text prompts over HTTP)")
     ap.add_argument("--merges", default=None)
     args = ap.parse_args(argv)
