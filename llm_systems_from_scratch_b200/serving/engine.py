@@ -394,6 +394,27 @@ class ServingEngine:
                     self.sched.finish(r)
         return produced
 
+    def cancel(self, req: Request) -> bool:
+        """Stop ``req`` now: a waiting request leaves the queue, a running one gives its row and its KV pages back and
+        keeps the tokens that have reached the host.  Like a stop token, it may have one decode step in flight; that
+        step's token is dropped when it is read, and its KV write lands (in stream order) before anything a later owner
+        of the pages writes.  Returns False if the request had already finished."""
+        if req.t_done is not None:
+            return False
+        if req in self.sched.waiting:
+            self.sched.waiting.remove(req)
+            req.t_done = self._clock()
+            return True
+        if req.row < 0 or self._row_req[req.row] is not req:
+            return False
+        row = req.row
+        req.t_done = self._clock()
+        self._row_pos[row] = -1
+        self._row_req[row] = None
+        self._free_rows.append(row)
+        self.sched.finish(req)
+        return True
+
     def step(self, now: float) -> int:
         """One engine iteration at time ``now``: admit + prefill, launch one decode step, then collect the tokens
         of the step before.  Returns the number of tokens that reached the host."""

@@ -41,6 +41,7 @@ class Completion:
     output_ids: list[int]
     ttft_s: float | None        # arrival -> first token on the host
     latency_s: float | None     # arrival -> last token on the host
+    cancelled: bool = False     # stopped by ``cancel`` before it had all its tokens
 
 
 class QueueFull(RuntimeError):
@@ -54,8 +55,10 @@ class EngineServer:
         self.max_waiting = max_waiting       # back-pressure: submissions beyond this many waiting requests are refused
         self._inbox: queue.Queue = queue.Queue()
         self._ids = itertools.count()
+        self._id_lock = threading.Lock()
         self._live: dict[int, tuple[Request, Future]] = {}
         self._streams: dict[int, list] = {}        # request id -> [callback, tokens already delivered]
+        self._cancelled: set[int] = set()
         self.ttft_s: list[float] = []              # of completed requests (bounded: the newest 4096)
         self.latency_s: list[float] = []
         self.output_tokens = 0
@@ -77,8 +80,17 @@ class EngineServer:
         if self.max_waiting is not None and len(self.engine.sched.waiting) + self._inbox.qsize() >= self.max_waiting:
             raise QueueFull(f"{self.max_waiting} requests are already waiting")
         fut: Future = Future()
-        self._inbox.put((list(map(int, prompt_ids)), int(max_new_tokens), eos_token_id, fut, on_tokens))
+        with self._id_lock:
+            fut.request_id = next(self._ids)         # what ``cancel`` takes
+        self._inbox.put(("add", fut.request_id, list(map(int, prompt_ids)), int(max_new_tokens), eos_token_id, fut,
+                         on_tokens))
         return fut
+
+    def cancel(self, request_id: int) -> None:
+        """Ask the loop to stop a request (a client that went away): its future resolves with what it has so far and
+        ``cancelled=True``; its row and KV pages are free for the next request at once.  Unknown or finished ids are
+        ignored."""
+        self._inbox.put(("cancel", request_id))
 
     def generate(self, prompt_ids: list[int], max_new_tokens: int, eos_token_id: int | None = None,
                  timeout: float | None = None) -> Completion:
@@ -123,15 +135,20 @@ class EngineServer:
         except queue.Empty:
             return
         while True:
-            prompt, max_new, eos, fut, on_tokens = item
-            req = Request(next(self._ids), prompt, max_new, arrival=eng._clock(), eos_token_id=eos)
-            try:
-                eng.sched.add(req)           # validates against the context length and the cache capacity
-                self._live[req.rid] = (req, fut)
-                if on_tokens is not None:
-                    self._streams[req.rid] = [on_tokens, 0]
-            except Exception as e:           # noqa: BLE001 - the caller gets the scheduler's verdict
-                fut.set_exception(e)
+            if item[0] == "cancel":
+                live = self._live.get(item[1])
+                if live is not None and eng.cancel(live[0]):
+                    self._cancelled.add(item[1])
+            else:
+                _, rid, prompt, max_new, eos, fut, on_tokens = item
+                req = Request(rid, prompt, max_new, arrival=eng._clock(), eos_token_id=eos)
+                try:
+                    eng.sched.add(req)       # validates against the context length and the cache capacity
+                    self._live[req.rid] = (req, fut)
+                    if on_tokens is not None:
+                        self._streams[req.rid] = [on_tokens, 0]
+                except Exception as e:       # noqa: BLE001 - the caller gets the scheduler's verdict
+                    fut.set_exception(e)
             try:
                 item = self._inbox.get_nowait()
             except queue.Empty:
@@ -146,9 +163,10 @@ class EngineServer:
             while not self._stop.is_set():
                 busy = bool(eng.sched.running or eng.sched.waiting or eng._pending)
                 self._take(0.0 if busy else self.idle_wait_s)
-                if not (eng.sched.running or eng.sched.waiting or eng._pending):
+                if eng.sched.running or eng.sched.waiting or eng._pending:
+                    eng.step(eng._clock())
+                elif not self._cancelled:
                     continue
-                eng.step(eng._clock())
                 for rid, st in list(self._streams.items()):          # streaming: hand over what is new
                     r = self._live[rid][0]
                     if len(r.output) > st[1]:
@@ -167,7 +185,9 @@ class EngineServer:
                         self.ttft_s.append(ttft)
                     self.latency_s.append(r.t_done - r.arrival)
                     del self.ttft_s[:-4096], self.latency_s[:-4096]
-                    fut.set_result(Completion(rid, list(r.output), ttft, r.t_done - r.arrival))
+                    was_cancelled = rid in self._cancelled
+                    self._cancelled.discard(rid)
+                    fut.set_result(Completion(rid, list(r.output), ttft, r.t_done - r.arrival, was_cancelled))
         except BaseException as e:           # noqa: BLE001 - surfaces in every pending and future request
             self._error = e
             for _, fut in list(self._live.values()):
@@ -246,6 +266,14 @@ def build_app(server: EngineServer, tokenizer=None, default_max_new_tokens: int 
             done_fut = asyncio.wrap_future(fut)
 
             async def events():
+                try:
+                    async for chunk in _events():
+                        yield chunk
+                finally:
+                    if not done_fut.done():          # the client went away: free the request's row and pages now
+                        server.cancel(fut.request_id)
+
+            async def _events():
                 while True:
                     getter = asyncio.ensure_future(chunks.get())
                     finished, _ = await asyncio.wait({getter, done_fut}, return_when=asyncio.FIRST_COMPLETED)

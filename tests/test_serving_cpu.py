@@ -236,6 +236,42 @@ def test_http_front_end():
         server.stop()
 
 
+def test_server_cancellation_frees_the_row_and_the_pages():
+    """A cancelled request (a client that went away) resolves with what it has and ``cancelled=True``, whether it was
+    still waiting or already decoding; its KV pages are back in the pool and the requests around it still get exactly
+    the tokens of the greedy loop."""
+    import time
+    from llm_systems_from_scratch_b200.serving.server import EngineServer
+    torch.manual_seed(0)
+    model = TransformerLM(**CFG).eval()
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 101, (n,), generator=g).tolist() for n in (6, 11, 8)]
+    want = [_greedy_reference(model, p, 20) for p in prompts]
+    eng = ServingEngine(model, page_size=4, max_batch=2, max_context=64)
+    server = EngineServer(eng).start()
+    try:
+        seen = []
+        futs = [server.submit(prompts[0], 20),
+                server.submit(prompts[1], 40, on_tokens=seen.extend),      # the one to cancel while it decodes
+                server.submit(prompts[2], 20)]                             # waits: the batch holds two
+        late = server.submit(prompts[0], 30)                               # cancelled while still waiting
+        server.cancel(late.request_id)
+        while len(seen) < 3:                                               # let the victim produce a few tokens
+            time.sleep(0.001)
+        server.cancel(futs[1].request_id)
+        done = [f.result(120) for f in futs]
+        gone = late.result(120)
+        assert gone.cancelled and gone.output_ids == [] and gone.ttft_s is None
+        assert done[1].cancelled and 3 <= len(done[1].output_ids) < 40
+        assert done[1].output_ids == _greedy_reference(model, prompts[1], len(done[1].output_ids))
+        assert not done[0].cancelled and done[0].output_ids == want[0] and done[2].output_ids == want[2]
+        server.cancel(futs[0].request_id)                                  # finished already: ignored
+        assert server.generate(prompts[1], 20, timeout=60).output_ids == want[1]
+    finally:
+        server.stop()
+    assert eng.cache.allocator.free == eng.cache.num_pages
+
+
 def test_server_back_pressure():
     """With ``max_waiting`` the server refuses what it cannot hold instead of queueing without bound (HTTP 503)."""
     from fastapi.testclient import TestClient
