@@ -134,3 +134,22 @@ def test_latest_checkpoint_picks_the_highest_step(tmp_path):
     (d / "sharded_final").mkdir()
     (d / "sharded_30").write_text("not a directory")
     assert train.latest_checkpoint(str(d)).endswith("sharded_20")
+
+
+def test_train_under_an_external_launcher(tmp_path):
+    """``python -m torch.distributed.run ... train.py --parallel fsdp``: every process is one rank (rank, world size
+    and rendezvous from the environment) instead of train.py spawning the ranks itself."""
+    import socket
+    import subprocess
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    cfg = _config(tmp_path, max_steps=5)
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    run = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "train.py"),
+                          "--config", cfg, "--parallel", "fsdp"], capture_output=True, text=True, env=env, timeout=600)
+    assert run.returncode == 0, run.stderr[-800:]
+    assert "[Rank 0] Step 4:" in run.stdout and "[Rank 1] Step 4:" in run.stdout
+    assert (tmp_path / "ckpt" / "sharded_final").is_dir()

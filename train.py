@@ -95,7 +95,7 @@ def train_worker(rank: int = 0, world_size: int = 1, parallel: list[str] | None 
         backend = backend or ("nccl" if use_cuda else "gloo")
         dist.init_process_group(backend, rank=rank, world_size=world_size)
         if use_cuda:
-            local_rank = rank % torch.cuda.device_count()
+            local_rank = int(os.environ.get("LOCAL_RANK", rank % torch.cuda.device_count()))
             torch.cuda.set_device(local_rank)
             device = f"cuda:{local_rank}"
         else:
@@ -313,6 +313,12 @@ def main():
         raise ValueError("--parallel fsdp and --compile are not compatible: FSDP always runs the fused engine")
     if args.eager and ("fsdp" in args.parallel or args.custom_triton):
         raise ValueError("--eager excludes --custom-triton and --parallel fsdp (FSDP always runs the fused engine)")
+    if args.parallel and "RANK" in os.environ and "WORLD_SIZE" in os.environ:
+        # started by an external launcher (python -m torch.distributed.run ... train.py --parallel ...): this process
+        # is one rank; rendezvous, rank and world size come from the environment and --world-size is ignored
+        train_worker(int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), args.parallel, args.config, args.amp,
+                     args.compile, args.flash_attn, args.custom_triton, args.resume, None, args.eager)
+        return
     if args.parallel:
         mp.set_start_method("spawn", force=True)
     resume, restarts = args.resume, 0
