@@ -59,6 +59,7 @@ def serve_http(engine, args):
     if args.vocab and args.merges:
         from llm_systems_from_scratch_b200.tokenizer.bpe import Tokenizer
         tokenizer = Tokenizer.from_files(args.vocab, args.merges, special_tokens=["<|endoftext|>"])
+    engine.set_sampling(args.temperature, args.top_k)       # one setting per server: the decode graphs are captured with it
     server = EngineServer(engine, max_waiting=args.max_waiting).start()
     try:
         uvicorn.run(build_app(server, tokenizer), host=args.host, port=args.http, log_level="info")
@@ -85,6 +86,8 @@ def main(argv=None):
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--max-waiting", type=int, default=None,
                     help="with --http: refuse (503) submissions while this many requests are already waiting")
+    ap.add_argument("--temperature", type=float, default=0.0, help="with --http: 0 = greedy, else sample on the device")
+    ap.add_argument("--top-k", type=int, default=None, help="with --http and a temperature: keep the k best logits")
     ap.add_argument("--vocab", default=None, help="tokenizer vocabulary (with --merges: text prompts over HTTP)")
     ap.add_argument("--merges", default=None)
     args = ap.parse_args(argv)
